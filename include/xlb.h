@@ -1,0 +1,260 @@
+/*
+ * xlb.h — C ABI of the B200-native semi-naive Datalog fixpoint data plane.
+ *
+ * Every entry point is what a foreign-function binding for the reference's
+ * relational operator surface would bind.  The reference has no FFI seam of its
+ * own (its executor calls inherent methods of `CudaKernelProvider`), so each
+ * declaration cites the reference method or type whose contract it keeps, by
+ * path inside the reference project.
+ *
+ * Conventions
+ *   - every function returns an xlb_status and never aborts or traps;
+ *   - out-parameters are written only on XLB_OK;
+ *   - operators never mutate their inputs and return fresh relations
+ *     (the reference's convention: crates/xlog-cuda/src/provider/relational.rs);
+ *   - a relation handed back to the caller is caller-owned (xlb_rel_free);
+ *     xlb_store_put transfers ownership to the context's store;
+ *   - a context may be used from one thread at a time
+ *     (crates/xlog-runtime/src/relation.rs:20-23 states the same for the reference);
+ *   - all device work of a call has completed when the call returns;
+ *   - there is no CPU fallback: without a CUDA device xlb_ctx_create fails.
+ *
+ * Relations are device-resident, column-major, with 32-bit or 64-bit unsigned
+ * columns (crates/xlog-cuda/src/memory.rs:1429-1433,1758-1774).
+ */
+#ifndef XLB_H
+#define XLB_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define XLB_MAX_ARITY 8u
+#define XLB_MAX_KEYS 2u
+#define XLB_UNIQUE_ID_BYTES 128u
+
+typedef struct xlb_ctx xlb_ctx;
+typedef struct xlb_rel xlb_rel;
+
+/* Error classes of the reference's XlogError (crates/xlog-core/src/error.rs:8-100). */
+typedef enum xlb_status {
+    XLB_OK = 0,
+    XLB_ERR_INVALID = 1,            /* bad argument / malformed plan   (XlogError::Execution)         */
+    XLB_ERR_TYPE = 2,               /* schema or key type mismatch     (XlogError::Kernel)            */
+    XLB_ERR_RESOURCE_EXHAUSTED = 3, /* device memory budget refused    (XlogError::ResourceExhausted) */
+    XLB_ERR_CAPACITY = 4,           /* an output exceeded its capacity (device overflow flag)         */
+    XLB_ERR_ITER_LIMIT = 5,         /* recursive SCC iteration limit   (executor/recursive.rs:947-954)*/
+    XLB_ERR_CUDA = 6,
+    XLB_ERR_NCCL = 7,
+    XLB_ERR_TIMEOUT = 8,            /* a bounded device-side wait ran out */
+    XLB_ERR_UNSUPPORTED = 9,        /* valid request outside the built scope */
+    XLB_ERR_NOT_FOUND = 10          /* store lookup miss */
+} xlb_status;
+
+/* Column types: the reference's kernel type codes (crates/xlog-core/src/types.rs:33-62).
+ * Built here: U32, U64 and SYMBOL (an interned u32 id, ordered as u32). */
+typedef enum xlb_type {
+    XLB_U32 = 0,
+    XLB_U64 = 1,
+    XLB_I32 = 2,
+    XLB_I64 = 3,
+    XLB_F32 = 4,
+    XLB_F64 = 5,
+    XLB_BOOL = 6,
+    XLB_SYMBOL = 7
+} xlb_type;
+
+/* Schema: arity + column types (names are ignored by every operator, as in the
+ * reference's type-compatibility check, relational.rs:859-971). */
+typedef struct xlb_schema {
+    uint32_t arity;
+    uint8_t types[XLB_MAX_ARITY];
+} xlb_schema;
+
+/* RuntimeConfig subset (crates/xlog-core/src/config.rs:57-200). */
+typedef struct xlb_config {
+    int32_t device;               /* CUDA device ordinal; -1 = current device                     */
+    uint64_t memory_budget_bytes; /* 0 = 90 % of the device's free memory (MemoryBudget)          */
+    uint64_t max_iterations;      /* 0 = 1,000,000, the reference default (config.rs:164)         */
+    uint64_t join_chunk_tuples;   /* upper bound on join candidates materialised at once; 0 = auto */
+    uint32_t flags;               /* XLB_FLAG_*                                                    */
+} xlb_config;
+
+#define XLB_FLAG_PROFILE 1u        /* time every phase with CUDA events (RuntimeConfig.profile)     */
+#define XLB_FLAG_UNFUSED_SETOPS 2u /* use separate difference and union passes instead of the fused one */
+
+/* ---- context ------------------------------------------------------------------------------ */
+
+/* Replaces provider construction: CudaKernelProvider::with_runtime +
+ * GpuMemoryManager::with_runtime (crates/xlog-cli/src/main.rs:1151-1186). */
+xlb_status xlb_ctx_create(const xlb_config* cfg, xlb_ctx** out);
+void xlb_ctx_destroy(xlb_ctx* ctx);
+
+/* Message of the last failing call on this context (XlogError's Display text). */
+const char* xlb_last_error(const xlb_ctx* ctx);
+
+/* GpuMemoryManager::allocated_bytes / peak_bytes (crates/xlog-cuda/src/memory.rs:1096-1126). */
+xlb_status xlb_memory_stats(const xlb_ctx* ctx, uint64_t* allocated_bytes, uint64_t* peak_bytes);
+
+/* ---- relations ---------------------------------------------------------------------------- */
+
+/* create_buffer_from_slices (crates/xlog-cuda/src/provider/io.rs:75): one host array per
+ * column, `rows` elements each, of the width the schema gives.  Host -> device copy. */
+xlb_status xlb_rel_from_host(xlb_ctx* ctx, const xlb_schema* schema, const void* const* cols,
+                             uint64_t rows, xlb_rel** out);
+/* create_empty_buffer(schema). */
+xlb_status xlb_rel_empty(xlb_ctx* ctx, const xlb_schema* schema, xlb_rel** out);
+/* device_row_count (crates/xlog-cuda/src/provider/mod.rs:2823): the logical row count. */
+xlb_status xlb_rel_rows(const xlb_rel* rel, uint64_t* rows);
+xlb_status xlb_rel_schema(const xlb_rel* rel, xlb_schema* schema);
+/* canonical_full_row_set_certified (memory.rs:1771-1773): sorted by all columns and unique. */
+xlb_status xlb_rel_is_canonical(const xlb_rel* rel, int* canonical);
+/* download_column::<T> for every column (crates/xlog-cuda/src/provider/transfer.rs:22).
+ * Copies min(rows, cap_rows) rows into the host arrays and reports the logical row count. */
+xlb_status xlb_rel_to_host(xlb_ctx* ctx, const xlb_rel* rel, void* const* cols, uint64_t cap_rows,
+                           uint64_t* rows);
+/* clone_buffer (relational.rs:6113). */
+xlb_status xlb_rel_clone(xlb_ctx* ctx, const xlb_rel* rel, xlb_rel** out);
+void xlb_rel_free(xlb_rel* rel);
+
+/* ---- relational operators ----------------------------------------------------------------- */
+
+/* JoinType (crates/xlog-ir/src/rir.rs). Built here: INNER, SEMI, ANTI. */
+typedef enum xlb_join_type { XLB_JOIN_INNER = 0, XLB_JOIN_SEMI = 1, XLB_JOIN_ANTI = 2 } xlb_join_type;
+
+/* hash_join_v2 (relational.rs:2926): equi-join on up to XLB_MAX_KEYS key columns.
+ * INNER: output columns = all left columns then all right columns, bag semantics (every
+ * matching pair once), rows ordered by left row then by right row.  SEMI / ANTI: the left rows
+ * that have / lack a match, left columns only, in left order.  Key column types must match
+ * pairwise (XLB_ERR_TYPE).  An empty side yields an empty relation of the output schema. */
+xlb_status xlb_hash_join(xlb_ctx* ctx, const xlb_rel* left, const xlb_rel* right,
+                         const uint32_t* left_keys, const uint32_t* right_keys, uint32_t n_keys,
+                         xlb_join_type join_type, xlb_rel** out);
+
+/* sort (relational.rs:1881): stable, lexicographic over key_cols, first key most significant,
+ * unsigned order; all columns are carried. */
+xlb_status xlb_sort(xlb_ctx* ctx, const xlb_rel* in, const uint32_t* key_cols, uint32_t n_keys,
+                    xlb_rel** out);
+
+/* dedup (relational.rs:238).  key_cols covering every column (or n_keys == 0) is the full-row
+ * form: the result is sorted by all columns, unique, and certified canonical.  A proper subset
+ * keeps, for every distinct key, the first row in stable key order. */
+xlb_status xlb_dedup(xlb_ctx* ctx, const xlb_rel* in, const uint32_t* key_cols, uint32_t n_keys,
+                     xlb_rel** out);
+
+/* union_gpu / union_many_gpu (relational.rs:822,859): set union of n >= 1 type-compatible
+ * relations; the result is sorted, unique and certified.  n == 0 is XLB_ERR_INVALID. */
+xlb_status xlb_union(xlb_ctx* ctx, const xlb_rel* const* ins, uint32_t n, xlb_rel** out);
+
+/* diff_gpu (relational.rs:1102): a \ b with set semantics on full rows; sorted, unique. */
+xlb_status xlb_diff(xlb_ctx* ctx, const xlb_rel* a, const xlb_rel* b, xlb_rel** out);
+
+/* ---- plans: the subset of RirNode the fixpoint path uses (crates/xlog-ir/src/rir.rs:339-541) - */
+
+typedef enum xlb_node_kind {
+    XLB_NODE_SCAN = 1,    /* RirNode::Scan { rel }                                              */
+    XLB_NODE_FILTER = 2,  /* RirNode::Filter { input, predicate } with a column comparison      */
+    XLB_NODE_PROJECT = 3, /* RirNode::Project { input, columns } with pass-through columns      */
+    XLB_NODE_JOIN = 4,    /* RirNode::Join { left, right, left_keys, right_keys, Inner }        */
+    XLB_NODE_UNION = 5    /* RirNode::Union { inputs }                                          */
+} xlb_node_kind;
+
+/* CompareOp (rir.rs:296-310). */
+typedef enum xlb_cmp { XLB_EQ = 0, XLB_NE = 1, XLB_LT = 2, XLB_LE = 3, XLB_GT = 4, XLB_GE = 5 } xlb_cmp;
+
+/* A promoted node (ChainJoin, MultiWayJoin) is passed as its `fallback` tree, which the
+ * reference guarantees to be row-set equivalent (rir.rs:386-404, 449-457). */
+typedef struct xlb_node {
+    uint32_t kind;
+    uint32_t rel_id;                      /* SCAN                                             */
+    const struct xlb_node* input;         /* FILTER, PROJECT                                  */
+    const struct xlb_node* left;          /* JOIN                                             */
+    const struct xlb_node* right;         /* JOIN                                             */
+    uint32_t n_keys;                      /* JOIN                                             */
+    uint32_t left_keys[XLB_MAX_KEYS];     /* JOIN: column indices of the left input           */
+    uint32_t right_keys[XLB_MAX_KEYS];    /* JOIN: column indices of the right input          */
+    uint32_t n_cols;                      /* PROJECT                                          */
+    uint32_t cols[XLB_MAX_ARITY];         /* PROJECT: input column per output column          */
+    uint32_t cmp;                         /* FILTER: xlb_cmp                                  */
+    uint32_t cmp_lhs_col;                 /* FILTER: left operand column                      */
+    uint32_t cmp_rhs_is_const;            /* FILTER: 0 = column, 1 = constant                 */
+    uint64_t cmp_rhs;                     /* FILTER: column index or constant                 */
+    const struct xlb_node* const* inputs; /* UNION                                            */
+    uint32_t n_inputs;                    /* UNION                                            */
+} xlb_node;
+
+/* CompiledRule { head, body } (crates/xlog-ir/src/plan.rs:28-36). */
+typedef struct xlb_rule {
+    const char* head;
+    const xlb_node* body;
+    xlb_schema head_schema; /* CompiledRule.meta.schema */
+} xlb_rule;
+
+/* Scc + its rules (plan.rs:8-16, ExecutionPlan.rules_by_scc). */
+typedef struct xlb_scc {
+    uint32_t id;
+    uint32_t is_recursive;
+    const xlb_rule* rules;
+    uint32_t n_rules;
+} xlb_scc;
+
+/* ExecutionPlan with strata flattened into evaluation order (plan.rs:52-70):
+ * sccs[0..n_sccs) are executed in order. */
+typedef struct xlb_plan {
+    const xlb_scc* sccs;
+    uint32_t n_sccs;
+} xlb_plan;
+
+/* ExecutionStats subset (crates/xlog-runtime/src/profiler.rs:172-233) + data-plane counters. */
+typedef struct xlb_run_stats {
+    uint64_t iterations;       /* semi-naive iterations over all recursive SCCs                */
+    uint64_t derived_tuples;   /* sum over heads of the final row count (all ranks' shards)    */
+    uint64_t candidate_tuples; /* join outputs before dedup (bag), all ranks                   */
+    uint64_t kernel_launches;  /* kernels this library launched during the call                */
+    uint64_t peak_bytes;       /* allocator high-water mark during the call                    */
+    double ms_total;           /* device time of the whole call (CUDA events)                  */
+    double ms_join;            /* index build + probe + expand                                 */
+    double ms_sort;            /* radix sort of candidates                                     */
+    double ms_setops;          /* dedup + difference + union                                   */
+    double ms_exchange;        /* partition + all-to-all + termination vote (multi-rank)       */
+    uint64_t exchange_bytes;   /* bytes this rank sent to other ranks                          */
+    double ms_sort_kernel;     /* device time inside the radix scatter kernels (PROFILE flag)  */
+    uint64_t sort_kernel_bytes;/* algorithmic bytes those launches moved (PROFILE flag)        */
+    uint64_t sort_kernel_launches;
+} xlb_run_stats;
+
+/* ---- executor: Executor::{register_relation, put_relation, store().get, execute_plan} ----- */
+
+/* register_relation(RelId, &str) (crates/xlog-runtime/src/executor/mod.rs:1242). */
+xlb_status xlb_register_relation(xlb_ctx* ctx, uint32_t rel_id, const char* name);
+/* put_relation(&str, CudaBuffer) (executor/mod.rs:587): the store takes ownership of `rel`.
+ * With several ranks each rank puts its own slice of the relation; the relation is the union. */
+xlb_status xlb_store_put(xlb_ctx* ctx, const char* name, xlb_rel* rel);
+/* store().get(&str) (executor/mod.rs:562): borrowed handle, valid until the next put of that
+ * name, the next xlb_execute_plan or the context's destruction.  With several ranks it is this
+ * rank's shard (sorted, unique); the relation is the disjoint union of the shards. */
+xlb_status xlb_store_get(xlb_ctx* ctx, const char* name, const xlb_rel** rel);
+xlb_status xlb_store_remove(xlb_ctx* ctx, const char* name);
+/* execute_plan(&ExecutionPlan) (executor/mod.rs:1404-1469); recursive SCCs run the semi-naive
+ * loop of execute_recursive_scc (executor/recursive.rs:447-957).  `stats` may be NULL. */
+xlb_status xlb_execute_plan(xlb_ctx* ctx, const xlb_plan* plan, xlb_run_stats* stats);
+
+/* ---- several GPUs: one process and one context per GPU ------------------------------------ */
+/* No counterpart in the reference (docs/architecture/multi-gpu.mdx:45-54 marks distributed
+ * joins as not implemented).  Rank 0 obtains an id, the host program broadcasts its
+ * XLB_UNIQUE_ID_BYTES bytes to every rank by its own means, and every rank then joins.  Derived
+ * relations are hash-partitioned; joins exchange tuples with an NCCL all-to-all and the fixpoint
+ * ends on an all-reduced emptiness vote. */
+xlb_status xlb_comm_unique_id(uint8_t id[XLB_UNIQUE_ID_BYTES]);
+xlb_status xlb_comm_init(xlb_ctx* ctx, const uint8_t id[XLB_UNIQUE_ID_BYTES], uint32_t rank,
+                         uint32_t world);
+/* Owner rank of a join-key value: identical on host and device. */
+uint32_t xlb_owner_of(uint64_t key, uint32_t world);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* XLB_H */

@@ -1,0 +1,187 @@
+"""ctypes front end of the CPU oracle (test infrastructure; never imported by the package).
+
+Mirrors the operator names of the reference's provider (``hash_join_v2``, ``dedup``,
+``union_many_gpu``, ``diff_gpu``, ``sort``) and its executor (``register_relation``,
+``put_relation``, ``execute_plan``, ``get``) so tests can run the same scenario on both sides.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = os.path.join(_HERE, "_build", "libxlog_oracle.so")
+
+
+def build(force: bool = False) -> str:
+    src = os.path.join(_HERE, "xlog_oracle.cpp")
+    if force or not os.path.exists(_LIB) or os.path.getmtime(_LIB) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-C", _HERE, "-s", "-B"])
+    return _LIB
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        _lib = C.CDLL(build())
+        L = _lib
+        P = C.c_void_p
+        L.xo_rel_from_cols.restype = P
+        L.xo_rel_from_cols.argtypes = [C.c_uint32, C.c_uint32, C.POINTER(P), C.c_uint64]
+        L.xo_rel_rows.restype = C.c_uint64
+        L.xo_rel_rows.argtypes = [P]
+        L.xo_rel_arity.restype = C.c_uint32
+        L.xo_rel_arity.argtypes = [P]
+        L.xo_rel_width.restype = C.c_uint32
+        L.xo_rel_width.argtypes = [P]
+        L.xo_rel_canonical.argtypes = [P]
+        L.xo_rel_to_cols.argtypes = [P, C.POINTER(P)]
+        L.xo_rel_free.argtypes = [P]
+        U = C.POINTER(C.c_uint32)
+        for name, args in (("xo_sort", [P, U, C.c_uint32]), ("xo_dedup", [P, U, C.c_uint32]),
+                           ("xo_union", [C.POINTER(P), C.c_uint32]), ("xo_diff", [P, P]),
+                           ("xo_hash_join", [P, P, U, U, C.c_uint32, C.c_int])):
+            getattr(L, name).restype = P
+            getattr(L, name).argtypes = args
+        L.xo_exec_new.restype = P
+        L.xo_exec_new.argtypes = [C.c_uint64]
+        L.xo_exec_free.argtypes = [P]
+        L.xo_register.argtypes = [P, C.c_uint32, C.c_char_p]
+        L.xo_put.argtypes = [P, C.c_char_p, P]
+        L.xo_get.restype = P
+        L.xo_get.argtypes = [P, C.c_char_p]
+        L.xo_error.restype = C.c_char_p
+        L.xo_error.argtypes = [P]
+        L.xo_iterations.restype = C.c_uint64
+        L.xo_iterations.argtypes = [P]
+        L.xo_candidates.restype = C.c_uint64
+        L.xo_candidates.argtypes = [P]
+        L.xo_execute_plan.argtypes = [P, C.c_void_p]
+    return _lib
+
+
+def set_threads(n: int) -> None:
+    lib().xo_set_threads(int(n))
+
+
+def _u32s(xs):
+    return (C.c_uint32 * max(len(xs), 1))(*xs)
+
+
+class OracleRel:
+    """Host relation: a list of equal-length numpy columns of one width (uint32 or uint64)."""
+
+    def __init__(self, handle):
+        if not handle:
+            raise ValueError("oracle operator rejected its inputs")
+        self._h = handle
+
+    @classmethod
+    def from_columns(cls, cols, dtype=np.uint32, arity=None):
+        cols = [np.ascontiguousarray(c, dtype=dtype) for c in cols]
+        arity = len(cols) if arity is None else arity
+        rows = len(cols[0]) if cols else 0
+        ptrs = (C.c_void_p * max(arity, 1))(*[c.ctypes.data for c in cols])
+        return cls(lib().xo_rel_from_cols(arity, np.dtype(dtype).itemsize, ptrs, rows))
+
+    @property
+    def rows(self):
+        return lib().xo_rel_rows(self._h)
+
+    @property
+    def arity(self):
+        return lib().xo_rel_arity(self._h)
+
+    @property
+    def canonical(self):
+        return bool(lib().xo_rel_canonical(self._h))
+
+    def columns(self):
+        dt = np.uint32 if lib().xo_rel_width(self._h) == 4 else np.uint64
+        cols = [np.empty(self.rows, dtype=dt) for _ in range(self.arity)]
+        ptrs = (C.c_void_p * max(self.arity, 1))(*[c.ctypes.data for c in cols])
+        lib().xo_rel_to_cols(self._h, ptrs)
+        return cols
+
+    def tuples(self):
+        return list(zip(*[c.tolist() for c in self.columns()])) if self.arity else []
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            lib().xo_rel_free(self._h)
+            self._h = None
+
+
+def sort(r, keys):
+    return OracleRel(lib().xo_sort(r._h, _u32s(keys), len(keys)))
+
+
+def dedup(r, keys=()):
+    return OracleRel(lib().xo_dedup(r._h, _u32s(keys), len(keys)))
+
+
+def union_many(rels):
+    arr = (C.c_void_p * max(len(rels), 1))(*[r._h for r in rels])
+    return OracleRel(lib().xo_union(arr, len(rels)))
+
+
+def diff(a, b):
+    return OracleRel(lib().xo_diff(a._h, b._h))
+
+
+def hash_join(l, r, lk, rk, join_type=0):
+    return OracleRel(lib().xo_hash_join(l._h, r._h, _u32s(lk), _u32s(rk), len(lk), join_type))
+
+
+class OracleExecutor:
+    """Executor::{register_relation, put_relation, execute_plan, store().get}
+    (crates/xlog-runtime/src/executor/mod.rs:1242,587,1404,562) on the CPU."""
+
+    def __init__(self, max_iterations: int = 0):
+        self._h = lib().xo_exec_new(max_iterations)
+
+    def register_relation(self, rel_id, name):
+        lib().xo_register(self._h, rel_id, name.encode())
+
+    def put_relation(self, name, rel):
+        lib().xo_put(self._h, name.encode(), rel._h)
+
+    def get(self, name):
+        return OracleRel(lib().xo_get(self._h, name.encode()))
+
+    def execute_plan(self, compiled_plan):
+        st = lib().xo_execute_plan(self._h, C.addressof(compiled_plan.c))
+        if st != 0:
+            raise RuntimeError(f"oracle status {st}: {lib().xo_error(self._h).decode()}")
+
+    @property
+    def iterations(self):
+        return lib().xo_iterations(self._h)
+
+    @property
+    def candidates(self):
+        return lib().xo_candidates(self._h)
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            lib().xo_exec_free(self._h)
+            self._h = None
+
+
+def run_program(plan, inputs, outputs, max_iterations=0):
+    """Evaluate ``plan`` on ``inputs`` (name -> list of numpy columns); returns
+    (dict name -> list of columns, executor)."""
+    ex = OracleExecutor(max_iterations)
+    for name, rid in plan.rel_ids.items():
+        ex.register_relation(rid, name)
+    for name, cols in inputs.items():
+        ex.put_relation(name, OracleRel.from_columns(cols))
+    cp = plan.compile()
+    ex.execute_plan(cp)
+    return {o: ex.get(o).columns() for o in outputs}, ex

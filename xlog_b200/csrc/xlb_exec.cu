@@ -1,0 +1,728 @@
+// The executor behind xlb_execute_plan: relation store, rule flattening, join pipelines and
+// the semi-naive loop of Executor::execute_recursive_scc
+// (crates/xlog-runtime/src/executor/recursive.rs:447-957), host control in C++, all data on
+// the device.
+//
+// Differences from the reference's control flow that do not change any result:
+//   - a rule body (a tree of Scan/Join/Project/Filter nodes) is flattened to a conjunctive
+//     query and evaluated as a left-deep pipeline that starts at the delta atom, so every
+//     join probes with the small side and builds on a cached index;
+//   - scans are views, never copies (the reference deep-copies, node_dispatch.rs:68-83);
+//   - full relations stay sorted and unique, so the per-iteration difference and union are
+//     merges, never a re-sort of the full relation (relational.rs:976-999 re-sorts).
+#include <algorithm>
+#include <cstring>
+#include <functional>
+#include <set>
+
+#include "xlb_comm.h"
+#include "xlb_ops.h"
+
+void xlb_resolve_phase_timers(xlb_ctx* c);
+
+// ------------------------------------------------------------------------------ store
+struct CachedIndex {
+    Index ix;
+    uint64_t version = 0;   // store version of the relation the rows came from
+    bool table_ok = false;  // hash table matches ix.S
+    uint64_t rows_global_hint = 0;
+};
+struct IndexCache {
+    std::map<std::pair<std::string, int>, CachedIndex> m;
+};
+
+static IndexCache& cache(xlb_ctx* c) {
+    if (!c->indexes) c->indexes = new IndexCache;
+    return *c->indexes;
+}
+
+static void store_put(xlb_ctx* c, const std::string& name, xlb_rel* rel) {
+    auto it = c->store.find(name);
+    if (it != c->store.end()) delete it->second;
+    c->store[name] = rel;
+    c->versions[name]++;
+}
+
+static xlb_rel* store_get(xlb_ctx* c, const std::string& name) {
+    auto it = c->store.find(name);
+    return it == c->store.end() ? nullptr : it->second;
+}
+
+void xlb_exec_teardown(xlb_ctx* c) {
+    for (auto& kv : c->store) delete kv.second;
+    c->store.clear();
+    delete c->indexes;
+    c->indexes = nullptr;
+    comm_destroy(c);
+}
+
+#define API_BEGIN(ctxp) \
+    xlb_ctx* ctx__ = (ctxp); \
+    try {
+#define API_END()                                                \
+    }                                                            \
+    catch (const XlbError& e) {                                  \
+        if (ctx__) ctx__->last_error = e.msg;                    \
+        return e.st;                                             \
+    }                                                            \
+    catch (const std::bad_alloc&) {                              \
+        if (ctx__) ctx__->last_error = "host allocation failed"; \
+        return XLB_ERR_RESOURCE_EXHAUSTED;                       \
+    }                                                            \
+    return XLB_OK;
+
+extern "C" xlb_status xlb_register_relation(xlb_ctx* c, uint32_t rel_id, const char* name) {
+    if (!c || !name) return XLB_ERR_INVALID;
+    c->rel_names[rel_id] = name;
+    return XLB_OK;
+}
+
+extern "C" xlb_status xlb_store_put(xlb_ctx* c, const char* name, xlb_rel* rel) {
+    if (!c || !name || !rel) return XLB_ERR_INVALID;
+    API_BEGIN(c)
+    if (rel->ctx != c) xlb_fail(XLB_ERR_INVALID, "relation belongs to another context");
+    store_put(c, name, rel);
+    API_END()
+}
+
+extern "C" xlb_status xlb_store_get(xlb_ctx* c, const char* name, const xlb_rel** rel) {
+    if (!c || !name || !rel) return XLB_ERR_INVALID;
+    xlb_rel* r = store_get(c, name);
+    if (!r) {
+        c->last_error = std::string("Missing relation: ") + name;
+        return XLB_ERR_NOT_FOUND;
+    }
+    *rel = r;
+    return XLB_OK;
+}
+
+extern "C" xlb_status xlb_store_remove(xlb_ctx* c, const char* name) {
+    if (!c || !name) return XLB_ERR_INVALID;
+    auto it = c->store.find(name);
+    if (it == c->store.end()) return XLB_ERR_NOT_FOUND;
+    delete it->second;
+    c->store.erase(it);
+    c->versions[name]++;
+    return XLB_OK;
+}
+
+// ------------------------------------------------------------------------------ flattening
+struct Atom {
+    const xlb_node* scan;
+    std::string rel;
+    uint32_t arity;
+    int var[2];
+};
+struct FilterC {
+    uint32_t cmp;
+    int lhs;
+    bool rhs_const;
+    uint64_t rhs;  // constant, or a variable id
+    bool applied;
+};
+struct FlatRule {
+    std::string head;
+    xlb_schema hs;
+    std::vector<Atom> atoms;
+    std::vector<FilterC> filters;
+    std::vector<int> head_vars;
+};
+
+struct Flattener {
+    xlb_ctx* c;
+    std::vector<int> parent;
+    FlatRule fr;
+    int fresh() {
+        parent.push_back((int)parent.size());
+        return (int)parent.size() - 1;
+    }
+    int find(int x) {
+        while (parent[x] != x) x = parent[x] = parent[parent[x]];
+        return x;
+    }
+    void unite(int a, int b) { parent[find(a)] = find(b); }
+
+    std::vector<int> walk(const xlb_node* n) {
+        if (!n) xlb_fail(XLB_ERR_INVALID, "plan node is null");
+        switch (n->kind) {
+            case XLB_NODE_SCAN: {
+                auto nm = c->rel_names.find(n->rel_id);
+                if (nm == c->rel_names.end()) xlb_fail(XLB_ERR_INVALID, "scan of unregistered relation id %u", n->rel_id);
+                xlb_rel* r = store_get(c, nm->second);
+                if (!r) xlb_fail(XLB_ERR_NOT_FOUND, "Missing relation: %s", nm->second.c_str());
+                if (!rel_packable(r->schema))
+                    xlb_fail(XLB_ERR_UNSUPPORTED, "relation %s: plans take relations of one or two 32-bit columns", nm->second.c_str());
+                Atom a;
+                a.scan = n;
+                a.rel = nm->second;
+                a.arity = r->schema.arity;
+                std::vector<int> cols;
+                for (uint32_t i = 0; i < a.arity; ++i) {
+                    a.var[i] = fresh();
+                    cols.push_back(a.var[i]);
+                }
+                fr.atoms.push_back(a);
+                return cols;
+            }
+            case XLB_NODE_FILTER: {
+                auto cols = walk(n->input);
+                if (n->cmp_lhs_col >= cols.size() || (!n->cmp_rhs_is_const && n->cmp_rhs >= cols.size()))
+                    xlb_fail(XLB_ERR_INVALID, "filter column out of range");
+                FilterC f{n->cmp, cols[n->cmp_lhs_col], n->cmp_rhs_is_const != 0,
+                          n->cmp_rhs_is_const ? n->cmp_rhs : (uint64_t)cols[n->cmp_rhs], false};
+                fr.filters.push_back(f);
+                return cols;
+            }
+            case XLB_NODE_PROJECT: {
+                auto cols = walk(n->input);
+                std::vector<int> out;
+                for (uint32_t i = 0; i < n->n_cols; ++i) {
+                    if (n->cols[i] >= cols.size()) xlb_fail(XLB_ERR_INVALID, "projection column %u out of range", n->cols[i]);
+                    out.push_back(cols[n->cols[i]]);
+                }
+                return out;
+            }
+            case XLB_NODE_JOIN: {
+                auto l = walk(n->left);
+                auto r = walk(n->right);
+                if (n->n_keys < 1 || n->n_keys > XLB_MAX_KEYS) xlb_fail(XLB_ERR_INVALID, "join needs 1..%u keys", XLB_MAX_KEYS);
+                for (uint32_t i = 0; i < n->n_keys; ++i) {
+                    if (n->left_keys[i] >= l.size() || n->right_keys[i] >= r.size()) xlb_fail(XLB_ERR_INVALID, "join key column out of range");
+                    unite(l[n->left_keys[i]], r[n->right_keys[i]]);
+                }
+                l.insert(l.end(), r.begin(), r.end());
+                return l;
+            }
+            case XLB_NODE_UNION:
+                xlb_fail(XLB_ERR_UNSUPPORTED, "a Union node inside a rule body is not built; pass one rule per disjunct");
+        }
+        xlb_fail(XLB_ERR_INVALID, "unknown plan node kind %u", n->kind);
+    }
+
+    FlatRule run(const xlb_rule& rule) {
+        fr.head = rule.head;
+        fr.hs = rule.head_schema;
+        fr.head_vars = walk(rule.body);
+        for (auto& a : fr.atoms)
+            for (uint32_t i = 0; i < a.arity; ++i) a.var[i] = find(a.var[i]);
+        for (auto& f : fr.filters) {
+            f.lhs = find(f.lhs);
+            if (!f.rhs_const) f.rhs = (uint64_t)find((int)f.rhs);
+        }
+        for (auto& v : fr.head_vars) v = find(v);
+        if (fr.head_vars.size() != rule.head_schema.arity)
+            xlb_fail(XLB_ERR_INVALID, "rule for %s: body yields %zu columns, head has %u", rule.head, fr.head_vars.size(), rule.head_schema.arity);
+        if (!rel_packable(rule.head_schema))
+            xlb_fail(XLB_ERR_UNSUPPORTED, "head %s: derived relations of one or two 32-bit columns are built", rule.head);
+        return fr;
+    }
+};
+
+// ------------------------------------------------------------------------------ indexes
+struct RunState {
+    xlb_run_stats st{};
+};
+
+// Rows of relation `name` arranged for a join on column kc: (key << 32) | other, sorted.
+static Keys index_rows(xlb_ctx* c, const xlb_rel* r, int kc) {
+    Keys k = ops_rel_packed(c, r);
+    if (r->schema.arity == 1) {
+        Keys s = ops_remap(c, k, SRC_LO, SRC_ZERO);
+        if (!r->canonical) ops_sort(c, s);
+        return s;
+    }
+    if (kc == 0) {
+        if (r->canonical) return k;  // a canonical relation is already ordered by its first column
+        Keys s = ops_copy(c, k);
+        ops_sort(c, s);
+        return s;
+    }
+    Keys s = ops_remap(c, k, SRC_LO, SRC_HI);
+    ops_sort(c, s);
+    return s;
+}
+
+static const Index& get_index(xlb_ctx* c, const std::string& name, int kc, RunState& rs) {
+    xlb_rel* r = store_get(c, name);
+    if (!r) xlb_fail(XLB_ERR_NOT_FOUND, "Missing relation: %s", name.c_str());
+    CachedIndex& ci = cache(c).m[{name, kc}];
+    uint64_t ver = c->versions[name];
+    PhaseTimer t(c, &rs.st.ms_join);
+    if (ci.version != ver || !ci.ix.S) {
+        Keys local = index_rows(c, r, kc);
+        if (c->world > 1) local = comm_repartition(c, local, SRC_HI, /*sorted_unique_result=*/true, rs.st);
+        ci.ix = Index();
+        ci.ix.S = local.buf;
+        ci.ix.n = local.n;
+        ci.version = ver;
+        ci.table_ok = false;
+    }
+    if (!ci.table_ok) {
+        ci.ix = ops_index_build(c, ci.ix.S, ci.ix.n, 32, Buf());
+        ci.table_ok = true;
+    }
+    return ci.ix;
+}
+
+// The full relation `name` grew by `delta` (disjoint from it): bring cached indexes along by
+// merging instead of re-sorting.  Called before the store is updated; `new_full` is the merged
+// relation that is about to be stored under a new version.
+static void indexes_on_merge(xlb_ctx* c, const std::string& name, const xlb_rel* new_full, const Keys& delta, uint64_t new_version, RunState& rs) {
+    for (auto& kv : cache(c).m) {
+        if (kv.first.first != name) continue;
+        CachedIndex& ci = kv.second;
+        if (ci.version + 1 != new_version || !ci.ix.S) continue;  // stale already: rebuilt on demand
+        int kc = kv.first.second;
+        PhaseTimer t(c, &rs.st.ms_join);
+        if (c->world > 1) {
+            // the index copy is partitioned by its own key column: route the new rows there
+            Keys d = new_full->schema.arity == 1 ? ops_remap(c, delta, SRC_LO, SRC_ZERO) : (kc == 0 ? delta : ops_remap(c, delta, SRC_LO, SRC_HI));
+            if (d.buf == delta.buf) d = ops_copy(c, d);
+            d = comm_repartition(c, d, SRC_HI, true, rs.st);
+            Keys old;
+            old.buf = ci.ix.S;
+            old.n = ci.ix.n;
+            Keys extra = ops_diff(c, d, old);
+            Keys m = ops_merge_disjoint(c, old, extra);
+            ci.ix = Index();
+            ci.ix.S = m.buf;
+            ci.ix.n = m.n;
+        } else if (new_full->schema.arity == 2 && kc == 0) {
+            ci.ix = Index();
+            ci.ix.S = new_full->packed;  // alias: canonical order is key order
+            ci.ix.n = new_full->rows;
+        } else {
+            Keys d = new_full->schema.arity == 1 ? ops_remap(c, delta, SRC_LO, SRC_ZERO) : ops_remap(c, delta, SRC_LO, SRC_HI);
+            if (new_full->schema.arity == 2) ops_sort(c, d);
+            Keys old;
+            old.buf = ci.ix.S;
+            old.n = ci.ix.n;
+            Keys m = ops_merge_disjoint(c, old, d);
+            ci.ix = Index();
+            ci.ix.S = m.buf;
+            ci.ix.n = m.n;
+        }
+        ci.version = new_version;
+        ci.table_ok = false;
+    }
+}
+
+// ------------------------------------------------------------------------------ pipelines
+struct ChunkTooBig {};
+
+struct Bag {
+    Keys k;
+    int hi = -1, lo = -1;  // variable in each half (-1: none)
+    int part = -1;         // several ranks: the variable whose owner rank holds each row (-1: unknown)
+};
+
+static int src_of(const Bag& b, int var) { return var == b.hi ? SRC_HI : SRC_LO; }
+
+static void apply_ready_filters(xlb_ctx* c, FlatRule& fr, Bag& b) {
+    for (auto& f : fr.filters) {
+        if (f.applied) continue;
+        bool lhs_ok = f.lhs == b.hi || f.lhs == b.lo;
+        bool rhs_ok = f.rhs_const || (int)f.rhs == b.hi || (int)f.rhs == b.lo;
+        if (!lhs_ok || !rhs_ok) continue;
+        b.k = ops_filter(c, b.k, f.cmp, src_of(b, f.lhs), f.rhs_const, f.rhs_const ? f.rhs : (uint64_t)src_of(b, (int)f.rhs));
+        f.applied = true;
+    }
+}
+
+// Variables still needed once the atoms in `done` are consumed.
+static std::set<int> needed_vars(const FlatRule& fr, const std::vector<bool>& done) {
+    std::set<int> s;
+    for (size_t i = 0; i < fr.atoms.size(); ++i)
+        if (!done[i])
+            for (uint32_t j = 0; j < fr.atoms[i].arity; ++j) s.insert(fr.atoms[i].var[j]);
+    for (auto& f : fr.filters)
+        if (!f.applied) {
+            s.insert(f.lhs);
+            if (!f.rhs_const) s.insert((int)f.rhs);
+        }
+    for (int v : fr.head_vars) s.insert(v);
+    return s;
+}
+
+// Evaluate the rule with atom `start` read from `start_rows` (the delta, a chunk of it, or a
+// full relation) and every other atom from the store.  Returns candidate head tuples (a bag).
+static Keys run_pipeline(xlb_ctx* c, FlatRule fr /*by value: filter flags*/, size_t start, const Keys& start_rows, int start_part_half, uint64_t limit, RunState& rs) {
+    std::vector<bool> done(fr.atoms.size(), false);
+    Bag bag;
+    const Atom& sa = fr.atoms[start];
+    bag.k = start_rows;
+    if (sa.arity == 2) { bag.hi = sa.var[0]; bag.lo = sa.var[1]; }
+    else bag.lo = sa.var[0];
+    if (start_part_half == SRC_HI) bag.part = bag.hi;
+    else if (start_part_half == SRC_LO) bag.part = bag.lo;
+    done[start] = true;
+    if (sa.arity == 2 && sa.var[0] == sa.var[1]) {  // p(X, X)
+        bag.k = ops_filter(c, bag.k, XLB_EQ, SRC_HI, false, SRC_LO);
+        bag.hi = -1;
+    }
+    {
+        PhaseTimer t(c, &rs.st.ms_join);
+        apply_ready_filters(c, fr, bag);
+    }
+    size_t remaining = fr.atoms.size() - 1;
+    while (remaining) {
+        // next atom: exactly one of its columns is bound by the bag, and what must stay live fits two columns
+        int pick = -1, kc = -1;
+        std::set<int> keep;
+        for (size_t i = 0; i < fr.atoms.size() && pick < 0; ++i) {
+            if (done[i]) continue;
+            const Atom& a = fr.atoms[i];
+            int bound = 0, which = -1;
+            for (uint32_t j = 0; j < a.arity; ++j)
+                if (a.var[j] == bag.hi || a.var[j] == bag.lo) { bound++; which = (int)j; }
+            if (a.arity == 2 && a.var[0] == a.var[1]) continue;
+            if (bound != 1) continue;
+            done[i] = true;
+            std::set<int> need = needed_vars(fr, done);
+            done[i] = false;
+            std::set<int> avail{bag.hi, bag.lo};
+            if (a.arity == 2) avail.insert(a.var[1 - which]);
+            avail.erase(-1);
+            std::set<int> k2;
+            for (int v : need)
+                if (avail.count(v)) k2.insert(v);
+            if (k2.size() > 2) continue;
+            pick = (int)i;
+            kc = which;
+            keep = k2;
+        }
+        if (pick < 0)
+            xlb_fail(XLB_ERR_UNSUPPORTED, "rule for %s: no join order keeps at most two live columns with single-column keys", fr.head.c_str());
+        const Atom& a = fr.atoms[pick];
+        done[pick] = true;
+        remaining--;
+        int keyvar = a.var[kc];
+        int othervar = a.arity == 2 ? a.var[1 - kc] : -1;
+        const Index& ix = get_index(c, a.rel, kc, rs);
+        // output layout: the head's layout when this is the last step and nothing is pending
+        bool last = remaining == 0;
+        bool pending = false;
+        for (auto& f : fr.filters)
+            if (!f.applied) pending = true;
+        int out_hi = -1, out_lo = -1;
+        if (last && !pending) {
+            if (fr.head_vars.size() == 2) { out_hi = fr.head_vars[0]; out_lo = fr.head_vars[1]; }
+            else out_lo = fr.head_vars[0];
+        } else {
+            std::vector<int> kv(keep.begin(), keep.end());
+            if (kv.size() == 2) { out_hi = kv[0]; out_lo = kv[1]; }
+            else if (kv.size() == 1) out_lo = kv[0];
+        }
+        auto sel = [&](int var) -> int {
+            if (var < 0) return SRC_ZERO;
+            if (var == bag.hi) return SRC_HI;
+            if (var == bag.lo) return SRC_LO;
+            if (var == othervar) return SRC_OTHER;
+            xlb_fail(XLB_ERR_INVALID, "internal: variable %d is not available at this join step", var);
+        };
+        int hs = sel(out_hi), ls = sel(out_lo);
+        Bag nb;
+        Keys probe = bag.k;
+        int keysel = src_of(bag, keyvar);
+        if (c->world > 1 && bag.part != keyvar) {
+            PhaseTimer t(c, &rs.st.ms_exchange);
+            probe = comm_repartition(c, probe, keysel, false, rs.st);
+        }
+        {
+            PhaseTimer t(c, &rs.st.ms_join);
+            nb.k = ops_join_expand(c, probe, keysel, nullptr, ix, hs, ls);
+            nb.part = keyvar;
+            if (limit && nb.k.n > limit && start_rows.n > 1) throw ChunkTooBig{};
+            nb.hi = out_hi;
+            nb.lo = out_lo;
+            bag = nb;
+            apply_ready_filters(c, fr, bag);
+        }
+    }
+    // head layout
+    int want_hi = fr.head_vars.size() == 2 ? fr.head_vars[0] : -1;
+    int want_lo = fr.head_vars.size() == 2 ? fr.head_vars[1] : fr.head_vars[0];
+    for (auto& f : fr.filters)
+        if (!f.applied) xlb_fail(XLB_ERR_UNSUPPORTED, "rule for %s: a filter refers to a column that no atom binds", fr.head.c_str());
+    if (bag.hi != want_hi || bag.lo != want_lo) {
+        auto sel = [&](int var) -> int {
+            if (var < 0) return SRC_ZERO;
+            if (var == bag.hi) return SRC_HI;
+            if (var == bag.lo) return SRC_LO;
+            xlb_fail(XLB_ERR_UNSUPPORTED, "rule for %s: a head column is not bound by the body", fr.head.c_str());
+        };
+        PhaseTimer t(c, &rs.st.ms_join);
+        bag.k = ops_remap(c, bag.k, sel(want_hi), sel(want_lo));
+    }
+    return bag.k;
+}
+
+// Candidates of one rule variant -> sorted unique tuples not in `full`, merged into `novel`.
+// The start rows are processed in chunks so no join output exceeds the configured bound.
+static void eval_variant(xlb_ctx* c, const FlatRule& fr, size_t start, const Keys& start_rows, int start_part_half, const Keys& full, int home_sel, Keys& novel, RunState& rs) {
+    if (start_rows.n == 0 && c->world == 1) return;
+    uint64_t limit = c->join_chunk;
+    // with several ranks every rank runs the same sequence of exchanges, so the rows are not
+    // chunked (chunk counts would differ between ranks)
+    if (c->world > 1) limit = 0;
+    else if (!limit) {
+        uint64_t room = c->budget > c->allocated ? c->budget - c->allocated : 0;
+        limit = std::max<uint64_t>(room / (8 * 8), 1u << 20);  // a chunk is held, sorted and merged: ~8 copies
+    }
+    uint64_t chunk = std::max<uint64_t>(start_rows.n, 1), at = 0;
+    bool first = true;
+    while (at < start_rows.n || (first && c->world > 1)) {
+        first = false;
+        uint64_t hi = std::min(start_rows.n, at + chunk);
+        Keys part = (at == 0 && hi == start_rows.n) ? start_rows : ops_slice(c, start_rows, at, hi);
+        Keys cand;
+        try {
+            cand = run_pipeline(c, fr, start, part, start_part_half, limit, rs);
+        } catch (const ChunkTooBig&) {
+            chunk = std::max<uint64_t>((hi - at) / 2, 1);
+            continue;
+        }
+        at = hi;
+        rs.st.candidate_tuples += cand.n;
+        if (c->world > 1) {
+            PhaseTimer t(c, &rs.st.ms_exchange);
+            cand = comm_repartition(c, cand, home_sel, false, rs.st);
+        }
+        if (cand.n == 0) continue;
+        if (cand.buf == start_rows.buf) cand = ops_copy(c, cand);  // a single-atom body: never sort a stored relation in place
+        {
+            PhaseTimer t(c, &rs.st.ms_sort);
+            ops_sort(c, cand);
+        }
+        PhaseTimer t(c, &rs.st.ms_setops);
+        ops_dedup_sorted(c, cand);
+        Keys fresh = full.n ? ops_diff(c, cand, full) : cand;
+        novel = novel.n ? ops_union(c, novel, fresh) : fresh;
+    }
+}
+
+static xlb_rel* empty_rel(xlb_ctx* c, const xlb_schema& s) {
+    Keys k;
+    k.buf = make_buf(c, 0);
+    return ops_rel_from_keys(c, s, k, true);
+}
+
+static Keys canonical_keys(xlb_ctx* c, const xlb_rel* r, RunState& rs) {
+    Keys k = ops_rel_packed(c, r);
+    if (r->canonical) return k;
+    k = ops_copy(c, k);
+    {
+        PhaseTimer t(c, &rs.st.ms_sort);
+        ops_sort(c, k);
+    }
+    PhaseTimer t(c, &rs.st.ms_setops);
+    ops_dedup_sorted(c, k);
+    return k;
+}
+
+// Which half of a head tuple decides its owner rank: the column its delta is probed by first.
+static int home_half(const std::vector<FlatRule>& rules, const std::string& pred, const std::set<std::string>& rec, uint32_t arity) {
+    if (arity == 1) return SRC_LO;
+    int votes[2] = {0, 0};
+    for (auto& fr : rules)
+        for (size_t i = 0; i < fr.atoms.size(); ++i) {
+            const Atom& a = fr.atoms[i];
+            if (a.rel != pred || !rec.count(a.rel)) continue;
+            for (size_t j = 0; j < fr.atoms.size(); ++j) {
+                if (j == i) continue;
+                for (uint32_t q = 0; q < fr.atoms[j].arity; ++q)
+                    for (uint32_t p = 0; p < a.arity; ++p)
+                        if (fr.atoms[j].var[q] == a.var[p]) votes[p]++;
+            }
+        }
+    return votes[1] > votes[0] ? SRC_LO : SRC_HI;
+}
+
+// Start atom of a rule evaluated on full relations: the smallest one probes, the others build.
+static size_t pick_seed_start(xlb_ctx* c, const FlatRule& fr) {
+    if (c->world > 1) return 0;  // every rank must walk the same pipeline: shard sizes differ, so no size rule
+    size_t best = 0;
+    uint64_t rows = ~0ull;
+    for (size_t i = 0; i < fr.atoms.size(); ++i) {
+        xlb_rel* r = store_get(c, fr.atoms[i].rel);
+        uint64_t n = r ? r->rows : 0;
+        if (n < rows) { rows = n; best = i; }
+    }
+    return best;
+}
+
+static void install_full(xlb_ctx* c, const std::string& pred, const xlb_schema& hs, const Keys& full_new, const Keys* delta, RunState& rs) {
+    xlb_rel* nr = ops_rel_from_keys(c, hs, full_new, true);
+    if (delta) indexes_on_merge(c, pred, nr, *delta, c->versions[pred] + 1, rs);
+    store_put(c, pred, nr);
+}
+
+// Rules evaluated once on full relations; per head one union (recursive.rs:308-438 for a
+// non-recursive SCC, :516-609 for the seeding pass of a recursive one).
+static void seed_pass(xlb_ctx* c, const std::vector<FlatRule>& rules, const std::vector<std::string>& preds, const std::set<std::string>& rec,
+                      std::map<std::string, xlb_schema>& schema, std::map<std::string, int>& home, bool make_delta, RunState& rs) {
+    std::map<std::string, Keys> novel;
+    for (auto& fr : rules) {
+        bool any_empty = false;
+        for (auto& a : fr.atoms) {
+            xlb_rel* r = store_get(c, a.rel);
+            if (!r || (r->rows == 0 && c->world == 1)) any_empty = true;
+        }
+        if (any_empty) continue;
+        size_t start = pick_seed_start(c, fr);
+        xlb_rel* sr = store_get(c, fr.atoms[start].rel);
+        Keys rows = ops_rel_packed(c, sr);
+        Keys full_old = canonical_keys(c, store_get(c, fr.head), rs);
+        eval_variant(c, fr, start, rows, rec.count(fr.atoms[start].rel) ? home[fr.atoms[start].rel] : -1, full_old, home[fr.head], novel[fr.head], rs);
+    }
+    for (auto& p : preds) {
+        Keys full_old = canonical_keys(c, store_get(c, p), rs);
+        Keys& d = novel[p];
+        if (!d.buf) d.buf = make_buf(c, 0);
+        Keys full_new;
+        {
+            PhaseTimer t(c, &rs.st.ms_setops);
+            full_new = d.n == 0 ? full_old : (full_old.n == 0 ? d : ops_merge_disjoint(c, full_old, d));
+        }
+        if (make_delta) store_put(c, "__delta_" + p, ops_rel_from_keys(c, schema[p], d, true));
+        install_full(c, p, schema[p], full_new, nullptr, rs);
+    }
+}
+
+static void run_scc(xlb_ctx* c, const xlb_scc& scc, RunState& rs) {
+    if (!scc.rules && scc.n_rules) xlb_fail(XLB_ERR_INVALID, "SCC %u has no rule array", scc.id);
+    std::vector<std::string> preds;
+    std::map<std::string, xlb_schema> schema;
+    for (uint32_t i = 0; i < scc.n_rules; ++i) {
+        if (!scc.rules[i].head || !scc.rules[i].body) xlb_fail(XLB_ERR_INVALID, "rule %u of SCC %u is incomplete", i, scc.id);
+        std::string h = scc.rules[i].head;
+        if (!schema.count(h)) {
+            preds.push_back(h);
+            schema[h] = scc.rules[i].head_schema;
+        }
+    }
+    std::sort(preds.begin(), preds.end());
+    std::set<std::string> rec(preds.begin(), preds.end());
+    for (auto& p : preds)
+        if (!store_get(c, p)) store_put(c, p, empty_rel(c, schema[p]));  // recursive.rs:471-486
+    std::vector<FlatRule> rules;
+    for (uint32_t i = 0; i < scc.n_rules; ++i) rules.push_back(Flattener{c, {}, {}}.run(scc.rules[i]));
+    std::map<std::string, int> home;
+    for (auto& p : preds) home[p] = home_half(rules, p, rec, schema[p].arity);
+    if (c->world > 1) {
+        // a head relation that already holds rows is re-homed so that equal tuples meet on one rank
+        for (auto& p : preds) {
+            xlb_rel* r = store_get(c, p);
+            Keys k = canonical_keys(c, r, rs);
+            if (k.buf == r->packed) k = ops_copy(c, k);
+            k = comm_repartition(c, k, home[p], true, rs.st);
+            store_put(c, p, ops_rel_from_keys(c, schema[p], k, true));
+        }
+    }
+
+    seed_pass(c, rules, preds, rec, schema, home, scc.is_recursive != 0, rs);
+    if (!scc.is_recursive) return;
+
+    bool fix = false;
+    for (uint64_t it = 0; it < c->max_iterations; ++it) {  // recursive.rs:619-937
+        rs.st.iterations++;
+        std::map<std::string, Keys> novel;
+        for (auto& fr : rules) {
+            for (size_t i = 0; i < fr.atoms.size(); ++i) {  // one variant per recursive occurrence (:636-664)
+                if (!rec.count(fr.atoms[i].rel)) continue;
+                xlb_rel* d = store_get(c, "__delta_" + fr.atoms[i].rel);
+                if (!d) continue;
+                if (d->rows == 0 && c->world == 1) continue;
+                bool any_empty = false;
+                for (size_t j = 0; j < fr.atoms.size(); ++j)
+                    if (j != i && store_get(c, fr.atoms[j].rel)->rows == 0 && c->world == 1) any_empty = true;
+                if (any_empty) continue;
+                Keys full = ops_rel_packed(c, store_get(c, fr.head));
+                eval_variant(c, fr, i, ops_rel_packed(c, d), home[fr.atoms[i].rel], full, home[fr.head], novel[fr.head], rs);
+            }
+        }
+        uint64_t changed = 0;
+        for (auto& p : preds) changed += novel[p].n;
+        if (c->world > 1) {
+            PhaseTimer t(c, &rs.st.ms_exchange);
+            changed = comm_allreduce_sum(c, changed);  // the emptiness vote
+        }
+        for (auto& p : preds) {  // :735-858
+            Keys& d = novel[p];
+            if (!d.buf) d.buf = make_buf(c, 0);
+            store_put(c, "__delta_" + p, ops_rel_from_keys(c, schema[p], d, true));
+        }
+        if (changed == 0) { fix = true; break; }  // :861-865
+        for (auto& p : preds) {                    // :868-937
+            Keys& d = novel[p];
+            if (d.n == 0 && c->world == 1) continue;
+            Keys full = ops_rel_packed(c, store_get(c, p));
+            Keys merged;
+            {
+                PhaseTimer t(c, &rs.st.ms_setops);
+                merged = full.n ? ops_merge_disjoint(c, full, d) : ops_copy(c, d);
+            }
+            install_full(c, p, schema[p], merged, &d, rs);
+        }
+    }
+    for (auto& p : preds) {  // :940-945
+        auto it = c->store.find("__delta_" + p);
+        if (it != c->store.end()) {
+            delete it->second;
+            c->store.erase(it);
+        }
+    }
+    if (!fix) xlb_fail(XLB_ERR_ITER_LIMIT, "Recursive SCC iteration limit (%llu) exceeded", (unsigned long long)c->max_iterations);
+}
+
+extern "C" xlb_status xlb_execute_plan(xlb_ctx* c, const xlb_plan* plan, xlb_run_stats* stats) {
+    if (!c || !plan) return XLB_ERR_INVALID;
+    RunState rs;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    uint64_t launches0 = c->launches;
+    c->peak = c->allocated;
+    c->ms_sort_kernel = 0;
+    c->sort_bytes = 0;
+    c->sort_launches = 0;
+    xlb_status result = XLB_OK;
+    try {
+        CUDA_OK(cudaSetDevice(c->device));
+        CUDA_OK(cudaEventCreate(&e0));
+        CUDA_OK(cudaEventCreate(&e1));
+        CUDA_OK(cudaEventRecord(e0, c->stream));
+        if (!plan->sccs && plan->n_sccs) xlb_fail(XLB_ERR_INVALID, "plan has no SCC array");
+        std::set<std::string> heads;
+        for (uint32_t s = 0; s < plan->n_sccs; ++s) {
+            run_scc(c, plan->sccs[s], rs);
+            for (uint32_t i = 0; i < plan->sccs[s].n_rules; ++i) heads.insert(plan->sccs[s].rules[i].head);
+        }
+        check_dev_status(c);
+        CUDA_OK(cudaEventRecord(e1, c->stream));
+        CUDA_OK(cudaStreamSynchronize(c->stream));  // executor/mod.rs:1463
+        float ms = 0;
+        CUDA_OK(cudaEventElapsedTime(&ms, e0, e1));
+        rs.st.ms_total = ms;
+        uint64_t derived = 0;
+        for (auto& h : heads) derived += store_get(c, h)->rows;
+        if (c->world > 1) derived = comm_allreduce_sum(c, derived);
+        rs.st.derived_tuples = derived;
+        if (c->world > 1) rs.st.candidate_tuples = comm_allreduce_sum(c, rs.st.candidate_tuples);
+    } catch (const XlbError& e) {
+        c->last_error = e.msg;
+        result = e.st;
+        cudaStreamSynchronize(c->stream);
+    } catch (const std::bad_alloc&) {
+        c->last_error = "host allocation failed";
+        result = XLB_ERR_RESOURCE_EXHAUSTED;
+    }
+    xlb_resolve_phase_timers(c);
+    if (e0) cudaEventDestroy(e0);
+    if (e1) cudaEventDestroy(e1);
+    rs.st.kernel_launches = c->launches - launches0;
+    rs.st.peak_bytes = c->peak;
+    rs.st.ms_sort_kernel = c->ms_sort_kernel;
+    rs.st.sort_kernel_bytes = c->sort_bytes;
+    rs.st.sort_kernel_launches = c->sort_launches;
+    if (stats && result == XLB_OK) *stats = rs.st;
+    return result;
+}

@@ -1,0 +1,765 @@
+// Device kernels of the fixpoint data plane (sm_100a) and their launch wrappers.
+//
+//   radix sort     LSD over u64 keys (optionally with a u32 payload), 8-bit digits, shared-memory
+//                  digit counters, warp match/ballot ranking, shared-memory reorder before the
+//                  global scatter.  Replaces kernels/sort.cu:28-286 of the reference
+//                  (4-bit digits, one thread per row, host-driven per-digit scans).
+//   scan           reduce -> spine -> apply exclusive prefix sums; replaces kernels/scan.cu:133-270.
+//   select         predicate count -> scan -> compaction; replaces kernels/filter.cu:902-940 and
+//                  the mask kernels of kernels/dedup.cu:306-345.
+//   merge path     set difference and disjoint union of sorted unique key arrays; replaces the
+//                  per-row binary search of kernels/dedup.cu:515-565 and the concat + re-sort of
+//                  kernels/set_ops.cu:46-116.
+//   hash index     open-addressing table over the distinct join keys of a key-sorted relation;
+//                  probe -> compact -> scan -> load-balanced expand.  Replaces kernels/join.cu:131-252
+//                  and kernels/pack.cu:144-214.
+//
+// All arithmetic is integer; nothing here is a contraction, so no tensor-core path exists.
+#pragma once
+#include "xlb_common.cuh"
+
+namespace xk {
+
+constexpr int BLOCK = 256;
+constexpr unsigned FULL = 0xFFFFFFFFu;
+
+__device__ __forceinline__ unsigned lane_id() { return threadIdx.x & 31; }
+__device__ __forceinline__ unsigned lanemask_lt() {
+    unsigned m;
+    asm("mov.u32 %0, %%lanemask_lt;" : "=r"(m));
+    return m;
+}
+
+__device__ __forceinline__ void set_status(DevStatus* st, unsigned code, unsigned where, unsigned long long detail) {
+    if (atomicCAS(&st->code, 0u, code) == 0u) {
+        st->where = where;
+        st->detail = detail;
+    }
+}
+
+// Block-wide exclusive scan of one value per thread (BLOCK threads); returns the exclusive
+// prefix and writes the block total to `total`.
+template <class T>
+__device__ __forceinline__ T block_exclusive_scan(T v, T* total, T* smem /* >= 33 entries */) {
+    unsigned lane = lane_id(), warp = threadIdx.x >> 5;
+    T incl = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        T o = __shfl_up_sync(FULL, incl, d);
+        if (lane >= (unsigned)d) incl += o;
+    }
+    if (lane == 31) smem[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        int nw = blockDim.x >> 5;
+        T w = lane < (unsigned)nw ? smem[lane] : T(0);
+        T wi = w;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            T o = __shfl_up_sync(FULL, wi, d);
+            if (lane >= (unsigned)d) wi += o;
+        }
+        if (lane < (unsigned)nw) smem[lane] = wi - w;
+        if (lane == (unsigned)(nw - 1)) smem[32] = wi;
+    }
+    __syncthreads();
+    T res = smem[warp] + incl - v;
+    *total = smem[32];
+    __syncthreads();
+    return res;
+}
+
+// ------------------------------------------------------------------------------------ scan
+constexpr int SCAN_IPT = 8;
+constexpr int SCAN_TILE = BLOCK * SCAN_IPT;
+
+template <class Load, class Tout>
+__global__ void __launch_bounds__(BLOCK) scan_reduce_k(Load load, uint64_t n, Tout* tile_sums) {
+    __shared__ Tout sm[33];
+    uint64_t base = (uint64_t)blockIdx.x * SCAN_TILE;
+    Tout s = 0;
+#pragma unroll
+    for (int k = 0; k < SCAN_IPT; ++k) {
+        uint64_t i = base + (uint64_t)k * BLOCK + threadIdx.x;
+        if (i < n) s += (Tout)load(i);
+    }
+    Tout tot;
+    block_exclusive_scan<Tout>(s, &tot, sm);
+    if (threadIdx.x == 0) tile_sums[blockIdx.x] = tot;
+}
+
+// One block walks the tile sums in chunks of blockDim.x, turning them into exclusive offsets in
+// place; the grand total goes to *total.
+template <class Tout>
+__global__ void __launch_bounds__(1024) scan_spine_k(Tout* tile_sums, uint64_t ntiles, Tout* total) {
+    __shared__ Tout sm[33];
+    __shared__ Tout carry_s;
+    if (threadIdx.x == 0) carry_s = 0;
+    __syncthreads();
+    for (uint64_t base = 0; base < ntiles; base += blockDim.x) {
+        uint64_t i = base + threadIdx.x;
+        Tout v = i < ntiles ? tile_sums[i] : Tout(0);
+        Tout tot;
+        Tout ex = block_exclusive_scan<Tout>(v, &tot, sm);
+        Tout carry = carry_s;
+        if (i < ntiles) tile_sums[i] = carry + ex;
+        __syncthreads();
+        if (threadIdx.x == 0) carry_s = carry + tot;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) *total = carry_s;
+}
+
+// out[i] = exclusive prefix.  tile_offsets may be null for a single tile; `total` (may be null)
+// then receives the sum.  out has n entries; out_end (may be null) receives the grand total too.
+template <class Load, class Tout>
+__global__ void __launch_bounds__(BLOCK) scan_apply_k(Load load, uint64_t n, const Tout* tile_offsets, Tout* out, Tout* total) {
+    __shared__ Tout sm[33];
+    uint64_t base = (uint64_t)blockIdx.x * SCAN_TILE + (uint64_t)threadIdx.x * SCAN_IPT;
+    Tout v[SCAN_IPT];
+    Tout s = 0;
+#pragma unroll
+    for (int k = 0; k < SCAN_IPT; ++k) {
+        uint64_t i = base + k;
+        v[k] = i < n ? (Tout)load(i) : Tout(0);
+        s += v[k];
+    }
+    Tout tot;
+    Tout ex = block_exclusive_scan<Tout>(s, &tot, sm);
+    Tout run = ex + (tile_offsets ? tile_offsets[blockIdx.x] : Tout(0));
+#pragma unroll
+    for (int k = 0; k < SCAN_IPT; ++k) {
+        uint64_t i = base + k;
+        if (i < n) out[i] = run;
+        run += v[k];
+    }
+    if (!tile_offsets && total && threadIdx.x == 0) *total = tot;
+}
+
+struct LoadU32 {
+    const uint32_t* p;
+    __device__ __forceinline__ uint32_t operator()(uint64_t i) const { return p[i]; }
+};
+struct LoadLow32 {  // low half of a u64 word (the match length of a probe result)
+    const uint64_t* p;
+    __device__ __forceinline__ uint32_t operator()(uint64_t i) const { return (uint32_t)p[i]; }
+};
+
+// Exclusive scan; `d_total` (device, one Tout) receives the sum.
+template <class Load, class Tout>
+void exclusive_scan(xlb_ctx* c, Load load, uint64_t n, Tout* out, Tout* d_total) {
+    if (n == 0) {
+        CUDA_OK(cudaMemsetAsync(d_total, 0, sizeof(Tout), c->stream));
+        return;
+    }
+    uint64_t ntiles = (n + SCAN_TILE - 1) / SCAN_TILE;
+    if (ntiles == 1) {
+        scan_apply_k<Load, Tout><<<1, BLOCK, 0, c->stream>>>(load, n, nullptr, out, d_total);
+        check_launch(c, "scan_apply");
+        return;
+    }
+    Buf sums = make_buf(c, ntiles * sizeof(Tout));
+    scan_reduce_k<Load, Tout><<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(load, n, sums->as<Tout>());
+    check_launch(c, "scan_reduce");
+    scan_spine_k<Tout><<<1, 1024, 0, c->stream>>>(sums->as<Tout>(), ntiles, d_total);
+    check_launch(c, "scan_spine");
+    scan_apply_k<Load, Tout><<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(load, n, sums->as<Tout>(), out, nullptr);
+    check_launch(c, "scan_apply");
+}
+
+// ---------------------------------------------------------------------------------- select
+// Stable compaction: Pred(i) -> keep?, Emit(i, pos) stores row i at output position pos.
+template <class Pred>
+__global__ void __launch_bounds__(BLOCK) select_count_k(Pred pred, uint64_t n, uint32_t* tile_counts) {
+    __shared__ uint32_t sm[33];
+    uint64_t base = (uint64_t)blockIdx.x * SCAN_TILE;
+    uint32_t s = 0;
+#pragma unroll
+    for (int k = 0; k < SCAN_IPT; ++k) {
+        uint64_t i = base + (uint64_t)k * BLOCK + threadIdx.x;
+        if (i < n && pred(i)) s++;
+    }
+    uint32_t tot;
+    block_exclusive_scan<uint32_t>(s, &tot, sm);
+    if (threadIdx.x == 0) tile_counts[blockIdx.x] = tot;
+}
+
+template <class Pred, class Emit>
+__global__ void __launch_bounds__(BLOCK) select_write_k(Pred pred, Emit emit, uint64_t n, const uint64_t* tile_offsets, uint64_t* total) {
+    __shared__ uint32_t sm[33];
+    uint64_t base = (uint64_t)blockIdx.x * SCAN_TILE + (uint64_t)threadIdx.x * SCAN_IPT;
+    bool f[SCAN_IPT];
+    uint32_t s = 0;
+#pragma unroll
+    for (int k = 0; k < SCAN_IPT; ++k) {
+        uint64_t i = base + k;
+        f[k] = i < n && pred(i);
+        s += f[k];
+    }
+    uint32_t tot;
+    uint32_t ex = block_exclusive_scan<uint32_t>(s, &tot, sm);
+    uint64_t pos = (tile_offsets ? tile_offsets[blockIdx.x] : 0ull) + ex;
+#pragma unroll
+    for (int k = 0; k < SCAN_IPT; ++k)
+        if (f[k]) emit(base + k, pos++);
+    if (!tile_offsets && threadIdx.x == 0) *total = tot;
+}
+
+// Returns the number of selected rows (one host read-back).
+template <class Pred, class Emit>
+uint64_t select(xlb_ctx* c, Pred pred, Emit emit, uint64_t n) {
+    if (n == 0) return 0;
+    uint64_t ntiles = (n + SCAN_TILE - 1) / SCAN_TILE;
+    Buf total = make_buf(c, 8);
+    unsigned long long h;
+    if (ntiles == 1) {
+        select_write_k<Pred, Emit><<<1, BLOCK, 0, c->stream>>>(pred, emit, n, nullptr, total->as<uint64_t>());
+        check_launch(c, "select_write");
+        read_words(c, total->p, 1, &h);
+        return h;
+    }
+    Buf counts = make_buf(c, ntiles * 4);
+    Buf offs = make_buf(c, ntiles * 8);
+    select_count_k<Pred><<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(pred, n, counts->as<uint32_t>());
+    check_launch(c, "select_count");
+    exclusive_scan<LoadU32, uint64_t>(c, LoadU32{counts->as<uint32_t>()}, ntiles, offs->as<uint64_t>(), total->as<uint64_t>());
+    select_write_k<Pred, Emit><<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(pred, emit, n, offs->as<uint64_t>(), nullptr);
+    check_launch(c, "select_write");
+    read_words(c, total->p, 1, &h);
+    return h;
+}
+
+// -------------------------------------------------------------------------------- pack/unpack
+__global__ void pack2_k(const uint32_t* __restrict__ c0, const uint32_t* __restrict__ c1, uint64_t* __restrict__ out, uint64_t n) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
+        out[i] = ((uint64_t)c0[i] << 32) | c1[i];
+}
+__global__ void pack1_k(const uint32_t* __restrict__ c0, uint64_t* __restrict__ out, uint64_t n) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
+        out[i] = c0[i];
+}
+__global__ void unpack2_k(const uint64_t* __restrict__ in, uint32_t* __restrict__ c0, uint32_t* __restrict__ c1, uint64_t n) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        uint64_t k = in[i];
+        c0[i] = (uint32_t)(k >> 32);
+        c1[i] = (uint32_t)k;
+    }
+}
+__global__ void unpack1_k(const uint64_t* __restrict__ in, uint32_t* __restrict__ c0, uint64_t n) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
+        c0[i] = (uint32_t)in[i];
+}
+// out[i] = (sel(in[i], hi_src) << 32) | sel(in[i], lo_src); src: 0 = high half, 1 = low half, 2 = zero.
+__global__ void remap_k(const uint64_t* __restrict__ in, uint64_t* __restrict__ out, uint64_t n, int hi_src, int lo_src) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        uint64_t k = in[i];
+        uint32_t h = (uint32_t)(k >> 32), l = (uint32_t)k;
+        uint32_t oh = hi_src == 0 ? h : hi_src == 1 ? l : 0u;
+        uint32_t ol = lo_src == 0 ? h : lo_src == 1 ? l : 0u;
+        out[i] = ((uint64_t)oh << 32) | ol;
+    }
+}
+
+inline unsigned grid_for(xlb_ctx* c, uint64_t n, int per_block = BLOCK) {
+    uint64_t g = (n + per_block - 1) / per_block;
+    uint64_t cap = (uint64_t)c->sm_count * 16;  // grid-stride kernels: a multiple of the SM count
+    return (unsigned)(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+// ------------------------------------------------------------------------------ radix sort
+constexpr int SORT_IPT = 16;
+constexpr int SORT_TILE = BLOCK * SORT_IPT;  // 4096 keys per tile
+constexpr int SORT_WARPS = BLOCK / 32;
+
+// OR and AND of all keys in one read: a digit whose bits never vary needs no pass.
+__global__ void __launch_bounds__(BLOCK) radix_bits_k(const uint64_t* __restrict__ keys, uint64_t n, unsigned long long* __restrict__ or_and /* [2] */) {
+    uint64_t o = 0, a = ~0ull;
+    for (uint64_t i = (uint64_t)blockIdx.x * BLOCK + threadIdx.x; i < n; i += (uint64_t)gridDim.x * BLOCK) {
+        uint64_t k = keys[i];
+        o |= k;
+        a &= k;
+    }
+#pragma unroll
+    for (int d = 16; d; d >>= 1) {
+        o |= __shfl_xor_sync(FULL, o, d);
+        a &= __shfl_xor_sync(FULL, a, d);
+    }
+    if (lane_id() == 0) {
+        atomicOr(&or_and[0], (unsigned long long)o);
+        atomicAnd(&or_and[1], (unsigned long long)a);
+    }
+}
+
+// Per-tile histogram of one digit: hist[d * ntiles + tile].
+__global__ void __launch_bounds__(BLOCK) radix_tile_hist_k(const uint64_t* __restrict__ keys, uint64_t n, int shift, uint32_t* __restrict__ hist, uint32_t ntiles) {
+    __shared__ unsigned int sh[SORT_WARPS][256];
+    for (int i = threadIdx.x; i < SORT_WARPS * 256; i += BLOCK) (&sh[0][0])[i] = 0;
+    __syncthreads();
+    uint64_t base = (uint64_t)blockIdx.x * SORT_TILE;
+    unsigned warp = threadIdx.x >> 5, lane = lane_id();
+#pragma unroll
+    for (int k = 0; k < SORT_IPT; ++k) {
+        uint64_t i = base + (uint64_t)k * BLOCK + threadIdx.x;
+        // keys past the end count as digit 256 (none): match on 9 bits so they group apart
+        unsigned d = i < n ? (unsigned)((keys[i] >> shift) & 255) : 256u;
+        unsigned peers = __match_any_sync(FULL, d);
+        if (d < 256u && lane == (unsigned)(__ffs(peers) - 1)) sh[warp][d] += __popc(peers);
+        __syncwarp();
+    }
+    __syncthreads();
+    unsigned s = 0;
+#pragma unroll
+    for (int w = 0; w < SORT_WARPS; ++w) s += sh[w][threadIdx.x];
+    hist[(uint64_t)threadIdx.x * ntiles + blockIdx.x] = s;
+}
+
+// Stable scatter of one tile by one digit.  `offs` is the exclusive scan of the per-tile
+// histograms in (digit-major, tile-minor) order, i.e. the global position of the first key of
+// digit d of this tile.
+template <bool HAS_VALUES>
+__global__ void __launch_bounds__(BLOCK) radix_scatter_k(const uint64_t* __restrict__ keys_in, uint64_t* __restrict__ keys_out,
+                                                          const uint32_t* __restrict__ vals_in, uint32_t* __restrict__ vals_out,
+                                                          uint64_t n, int shift, const uint32_t* __restrict__ offs, uint32_t ntiles) {
+    __shared__ uint64_t skeys[SORT_TILE];
+    __shared__ unsigned int whist[SORT_WARPS][256];
+    __shared__ unsigned int tile_start[256];
+    __shared__ unsigned int glob_off[256];
+    __shared__ unsigned int scan_sm[33];
+
+    const unsigned lane = lane_id(), warp = threadIdx.x >> 5;
+    const uint64_t tile_base = (uint64_t)blockIdx.x * SORT_TILE;
+    const uint64_t rem = n - tile_base;
+    const unsigned valid = rem < (uint64_t)SORT_TILE ? (unsigned)rem : (unsigned)SORT_TILE;
+
+    for (int i = threadIdx.x; i < SORT_WARPS * 256; i += BLOCK) (&whist[0][0])[i] = 0;
+    glob_off[threadIdx.x] = offs[(uint64_t)threadIdx.x * ntiles + blockIdx.x];
+
+    // warp-striped load: key j of lane l sits at warp*512 + j*32 + l (memory order = (j, l))
+    uint64_t key[SORT_IPT];
+    unsigned short rank[SORT_IPT];
+    const unsigned wbase = warp * (32 * SORT_IPT);
+#pragma unroll
+    for (int j = 0; j < SORT_IPT; ++j) {
+        unsigned t = wbase + j * 32 + lane;
+        key[j] = t < valid ? keys_in[tile_base + t] : ~0ull;
+    }
+    __syncthreads();
+
+    // rank every key among the keys of its warp with the same digit, in memory order
+#pragma unroll
+    for (int j = 0; j < SORT_IPT; ++j) {
+        unsigned t = wbase + j * 32 + lane;
+        unsigned d = t < valid ? (unsigned)((key[j] >> shift) & 255) : 255u;
+        unsigned peers = __match_any_sync(FULL, d);
+        unsigned leader = __ffs(peers) - 1;
+        unsigned before = 0;
+        if (lane == leader) {
+            before = whist[warp][d];
+            whist[warp][d] = before + __popc(peers);
+        }
+        before = __shfl_sync(FULL, before, leader);
+        rank[j] = (unsigned short)(before + __popc(peers & lanemask_lt()));
+        __syncwarp();
+    }
+    __syncthreads();
+
+    // per digit: exclusive prefix over warps, then exclusive prefix over digits
+    {
+        unsigned d = threadIdx.x, run = 0;
+#pragma unroll
+        for (int w = 0; w < SORT_WARPS; ++w) {
+            unsigned v = whist[w][d];
+            whist[w][d] = run;
+            run += v;
+        }
+        unsigned tot;
+        unsigned ex = block_exclusive_scan<unsigned>(run, &tot, scan_sm);
+        tile_start[d] = ex;
+    }
+    __syncthreads();
+
+    unsigned short pos[SORT_IPT];
+#pragma unroll
+    for (int j = 0; j < SORT_IPT; ++j) {
+        unsigned t = wbase + j * 32 + lane;
+        unsigned d = t < valid ? (unsigned)((key[j] >> shift) & 255) : 255u;
+        unsigned p = tile_start[d] + whist[warp][d] + rank[j];
+        pos[j] = (unsigned short)p;
+        skeys[p] = key[j];
+    }
+    __syncthreads();
+    // coalesced runs: consecutive shared-memory slots of one digit go to consecutive addresses
+    for (unsigned i = threadIdx.x; i < valid; i += BLOCK) {
+        uint64_t k = skeys[i];
+        unsigned d = (unsigned)((k >> shift) & 255);
+        keys_out[(uint64_t)glob_off[d] + (i - tile_start[d])] = k;
+    }
+    if (HAS_VALUES) {
+        // Payloads take the same route through the (now free) shared key array: slot p gets the
+        // payload and the digit of the key that went to slot p.
+        __syncthreads();
+        uint32_t* sv = reinterpret_cast<uint32_t*>(skeys);                 // 16 KB of payloads
+        uint8_t* sd = reinterpret_cast<uint8_t*>(skeys) + SORT_TILE * 4;   // 4 KB of digits
+#pragma unroll
+        for (int j = 0; j < SORT_IPT; ++j) {
+            unsigned t = wbase + j * 32 + lane;
+            if (t < valid) {
+                sv[pos[j]] = vals_in[tile_base + t];
+                sd[pos[j]] = (uint8_t)((key[j] >> shift) & 255);
+            }
+        }
+        __syncthreads();
+        for (unsigned i = threadIdx.x; i < valid; i += BLOCK) {
+            unsigned d = sd[i];
+            vals_out[(uint64_t)glob_off[d] + (i - tile_start[d])] = sv[i];
+        }
+    }
+}
+
+struct SortPlan {
+    int npasses = 0;
+    int shifts[8];
+};
+
+// Which 8-bit digits vary over the keys (one read of the keys + one read-back).
+inline SortPlan plan_sort(xlb_ctx* c, const uint64_t* keys, uint64_t n) {
+    SortPlan p;
+    Buf oa = make_buf(c, 16);
+    CUDA_OK(cudaMemsetAsync(oa->p, 0, 8, c->stream));
+    CUDA_OK(cudaMemsetAsync((char*)oa->p + 8, 0xFF, 8, c->stream));
+    radix_bits_k<<<grid_for(c, n, BLOCK * 8), BLOCK, 0, c->stream>>>(keys, n, oa->as<unsigned long long>());
+    check_launch(c, "radix_bits");
+    unsigned long long h[2];
+    read_words(c, oa->p, 2, h);
+    uint64_t varying = h[0] & ~h[1];
+    for (int d = 0; d < 8; ++d)
+        if ((varying >> (8 * d)) & 255) p.shifts[p.npasses++] = 8 * d;
+    return p;
+}
+
+// Sorts `n` keys ascending (stable).  keys/vals are replaced by buffers holding the result;
+// vals may be empty.  n must be below 2^32.
+inline void radix_sort(xlb_ctx* c, Buf& keys, Buf* vals, uint64_t n) {
+    if (n <= 1) return;
+    if (n >= (1ull << 32)) xlb_fail(XLB_ERR_CAPACITY, "sort of %llu keys exceeds the 2^32 limit of one sort", (unsigned long long)n);
+    SortPlan p = plan_sort(c, keys->as<uint64_t>(), n);
+    if (p.npasses == 0) return;
+    uint32_t ntiles = (uint32_t)((n + SORT_TILE - 1) / SORT_TILE);
+    Buf tmpk = make_buf(c, n * 8);
+    Buf tmpv = vals ? make_buf(c, n * 4) : Buf();
+    Buf hist = make_buf(c, (uint64_t)256 * ntiles * 4);
+    Buf offs = make_buf(c, (uint64_t)256 * ntiles * 4);
+    Buf total = make_buf(c, 4);
+    bool prof = (c->flags & XLB_FLAG_PROFILE) != 0;
+    for (int q = 0; q < p.npasses; ++q) {
+        int shift = p.shifts[q];
+        radix_tile_hist_k<<<ntiles, BLOCK, 0, c->stream>>>(keys->as<uint64_t>(), n, shift, hist->as<uint32_t>(), ntiles);
+        check_launch(c, "radix_tile_hist");
+        exclusive_scan<LoadU32, uint32_t>(c, LoadU32{hist->as<uint32_t>()}, (uint64_t)256 * ntiles, offs->as<uint32_t>(), total->as<uint32_t>());
+        cudaEvent_t e0 = nullptr, e1 = nullptr;
+        if (prof) {
+            CUDA_OK(cudaEventCreate(&e0));
+            CUDA_OK(cudaEventCreate(&e1));
+            CUDA_OK(cudaEventRecord(e0, c->stream));
+        }
+        if (vals)
+            radix_scatter_k<true><<<ntiles, BLOCK, 0, c->stream>>>(keys->as<uint64_t>(), tmpk->as<uint64_t>(), (*vals)->as<uint32_t>(), tmpv->as<uint32_t>(), n, shift, offs->as<uint32_t>(), ntiles);
+        else
+            radix_scatter_k<false><<<ntiles, BLOCK, 0, c->stream>>>(keys->as<uint64_t>(), tmpk->as<uint64_t>(), nullptr, nullptr, n, shift, offs->as<uint32_t>(), ntiles);
+        check_launch(c, "radix_scatter");
+        if (prof) {
+            CUDA_OK(cudaEventRecord(e1, c->stream));
+            c->sort_events.emplace_back(e0, e1);
+            c->sort_bytes += n * (vals ? 24ull : 16ull);
+            c->sort_launches++;
+        }
+        std::swap(keys, tmpk);
+        if (vals) std::swap(*vals, tmpv);
+    }
+}
+
+// ------------------------------------------------------------------------------ merge path
+constexpr int MP_IPT = 8;
+constexpr int MP_TILE = BLOCK * MP_IPT;  // 2048 merged elements per tile
+
+// Number of A elements among the first `diag` merged elements (A first on ties).
+__device__ __forceinline__ uint64_t merge_path(const uint64_t* A, uint64_t na, const uint64_t* B, uint64_t nb, uint64_t diag) {
+    uint64_t lo = diag > nb ? diag - nb : 0, hi = diag < na ? diag : na;
+    while (lo < hi) {
+        uint64_t mid = (lo + hi) >> 1;
+        if (A[mid] <= B[diag - 1 - mid]) lo = mid + 1;
+        else hi = mid;
+    }
+    return lo;
+}
+
+__global__ void mp_partition_k(const uint64_t* __restrict__ A, uint64_t na, const uint64_t* __restrict__ B, uint64_t nb, uint64_t* __restrict__ splits, uint64_t ntiles) {
+    uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t > ntiles) return;
+    uint64_t diag = t * MP_TILE;
+    if (diag > na + nb) diag = na + nb;
+    splits[t] = merge_path(A, na, B, nb, diag);
+}
+
+// MODE 0: keep[i] = 1 iff A[i] is not in B (A, B sorted unique).
+// MODE 1: out = merge of A and B (disjoint), out has na + nb entries.
+template <int MODE>
+__global__ void __launch_bounds__(BLOCK) mp_tile_k(const uint64_t* __restrict__ A, uint64_t na, const uint64_t* __restrict__ B, uint64_t nb,
+                                                    const uint64_t* __restrict__ splits, uint8_t* __restrict__ keep, uint64_t* __restrict__ out) {
+    __shared__ uint64_t sA[MP_TILE + 1];
+    __shared__ uint64_t sB[MP_TILE + 2];
+    uint64_t t = blockIdx.x;
+    uint64_t d0 = t * MP_TILE, d1 = d0 + MP_TILE;
+    if (d1 > na + nb) d1 = na + nb;
+    uint64_t a0 = splits[t], a1 = splits[t + 1];
+    uint64_t b0 = d0 - a0, b1 = d1 - a1;
+    unsigned la = (unsigned)(a1 - a0), lb = (unsigned)(b1 - b0);
+    unsigned lbx = lb + ((b1 < nb) ? 1u : 0u);  // one look-ahead element of B for a match across the tile edge
+    for (unsigned i = threadIdx.x; i < la; i += BLOCK) sA[i] = A[a0 + i];
+    for (unsigned i = threadIdx.x; i < lbx; i += BLOCK) sB[i] = B[b0 + i];
+    __syncthreads();
+    unsigned diag = threadIdx.x * MP_IPT;
+    unsigned total = la + lb;
+    if (diag > total) diag = total;
+    // local merge path (A first on ties)
+    unsigned lo = diag > lb ? diag - lb : 0, hi = diag < la ? diag : la;
+    while (lo < hi) {
+        unsigned mid = (lo + hi) >> 1;
+        if (sA[mid] <= sB[diag - 1 - mid]) lo = mid + 1;
+        else hi = mid;
+    }
+    unsigned ai = lo, bi = diag - lo;
+    uint64_t res[MP_IPT];
+#pragma unroll
+    for (int k = 0; k < MP_IPT; ++k) {
+        unsigned o = diag + k;
+        res[k] = 0;
+        if (o >= total) continue;
+        bool takeA = ai < la && (bi >= lb || sA[ai] <= sB[bi]);
+        if (takeA) {
+            uint64_t a = sA[ai];
+            if (MODE == 0) keep[a0 + ai] = (bi < lbx && sB[bi] == a) ? 0 : 1;
+            res[k] = a;
+            ai++;
+        } else {
+            res[k] = sB[bi];
+            bi++;
+        }
+    }
+    if (MODE == 1) {
+        // stage the merged run through shared memory (the inputs are consumed) for coalesced stores
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < MP_IPT; ++k)
+            if (diag + k < total) sA[diag + k] = res[k];
+        __syncthreads();
+        for (unsigned i = threadIdx.x; i < total; i += BLOCK) out[d0 + i] = sA[i];
+    }
+}
+
+struct PredKeep {
+    const uint8_t* keep;
+    __device__ __forceinline__ bool operator()(uint64_t i) const { return keep[i] != 0; }
+};
+struct EmitKey {
+    const uint64_t* in;
+    uint64_t* out;
+    __device__ __forceinline__ void operator()(uint64_t i, uint64_t pos) const { out[pos] = in[i]; }
+};
+struct PredHead {  // first element of every run of equal keys
+    const uint64_t* k;
+    __device__ __forceinline__ bool operator()(uint64_t i) const { return i == 0 || k[i] != k[i - 1]; }
+};
+
+// Sorted keys -> sorted unique keys.  Returns the unique count; `out` has room for n keys.
+inline uint64_t dedup_sorted(xlb_ctx* c, const uint64_t* in, uint64_t n, uint64_t* out) {
+    return select(c, PredHead{in}, EmitKey{in, out}, n);
+}
+
+// A \ B for sorted unique arrays.  Returns the result (exactly sized) and its length.
+inline Buf set_difference(xlb_ctx* c, const uint64_t* A, uint64_t na, const uint64_t* B, uint64_t nb, uint64_t* n_out) {
+    if (na == 0) { *n_out = 0; return make_buf(c, 0); }
+    if (nb == 0) {
+        Buf o = make_buf(c, na * 8);
+        CUDA_OK(cudaMemcpyAsync(o->p, A, na * 8, cudaMemcpyDeviceToDevice, c->stream));
+        *n_out = na;
+        return o;
+    }
+    uint64_t ntiles = (na + nb + MP_TILE - 1) / MP_TILE;
+    Buf splits = make_buf(c, (ntiles + 1) * 8);
+    Buf keep = make_buf(c, na);
+    mp_partition_k<<<(unsigned)((ntiles + 1 + 127) / 128), 128, 0, c->stream>>>(A, na, B, nb, splits->as<uint64_t>(), ntiles);
+    check_launch(c, "mp_partition");
+    mp_tile_k<0><<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(A, na, B, nb, splits->as<uint64_t>(), keep->as<uint8_t>(), nullptr);
+    check_launch(c, "mp_diff");
+    Buf tmp = make_buf(c, na * 8);
+    uint64_t m = select(c, PredKeep{keep->as<uint8_t>()}, EmitKey{A, tmp->as<uint64_t>()}, na);
+    *n_out = m;
+    return tmp;
+}
+
+// Merge of two sorted arrays with no common element.
+inline Buf merge_disjoint(xlb_ctx* c, const uint64_t* A, uint64_t na, const uint64_t* B, uint64_t nb) {
+    Buf o = make_buf(c, (na + nb) * 8);
+    if (na == 0 || nb == 0) {
+        if (na + nb) CUDA_OK(cudaMemcpyAsync(o->p, na ? A : B, (na + nb) * 8, cudaMemcpyDeviceToDevice, c->stream));
+        return o;
+    }
+    uint64_t ntiles = (na + nb + MP_TILE - 1) / MP_TILE;
+    Buf splits = make_buf(c, (ntiles + 1) * 8);
+    mp_partition_k<<<(unsigned)((ntiles + 1 + 127) / 128), 128, 0, c->stream>>>(A, na, B, nb, splits->as<uint64_t>(), ntiles);
+    check_launch(c, "mp_partition");
+    mp_tile_k<1><<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(A, na, B, nb, splits->as<uint64_t>(), nullptr, o->as<uint64_t>());
+    check_launch(c, "mp_union");
+    return o;
+}
+
+// ------------------------------------------------------------------------------ hash index
+// 64-bit finaliser (the mixer family the reference hashes join keys with, kernels/join.cu:18-25).
+__host__ __device__ __forceinline__ uint64_t mix64(uint64_t x) {
+    x ^= x >> 33;
+    x *= 0xff51afd7ed558ccdull;
+    x ^= x >> 33;
+    x *= 0xc4ceb9fe1a85ec53ull;
+    x ^= x >> 33;
+    return x;
+}
+
+// Slot: x = key, y = (start << 32) | len of the key's run in the key-sorted relation; y == 0 is
+// an empty slot (a run has at least one row).
+struct PredRunHead {  // S sorted by (key << 32 | other): a run starts where the high half changes
+    const uint64_t* s;
+    __device__ __forceinline__ bool operator()(uint64_t i) const { return i == 0 || (s[i] >> 32) != (s[i - 1] >> 32); }
+};
+struct EmitRunHead {
+    uint32_t* starts;
+    __device__ __forceinline__ void operator()(uint64_t i, uint64_t pos) const { starts[pos] = (uint32_t)i; }
+};
+
+__global__ void hash_insert_k(const uint64_t* __restrict__ S, uint64_t n, int key_shift, const uint32_t* __restrict__ starts, uint64_t nu,
+                              ulonglong2* __restrict__ table, uint64_t mask, DevStatus* st) {
+    for (uint64_t u = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; u < nu; u += (uint64_t)gridDim.x * blockDim.x) {
+        uint64_t s = starts[u];
+        uint64_t e = u + 1 < nu ? starts[u + 1] : n;
+        uint64_t key = S[s] >> key_shift;
+        unsigned long long val = (s << 32) | (e - s);
+        uint64_t h = mix64(key) & mask;
+        bool done = false;
+        for (uint64_t probe = 0; probe <= mask; ++probe) {  // bounded by the table size
+            unsigned long long* vp = &table[h].y;
+            if (atomicCAS(vp, 0ull, val) == 0ull) {
+                table[h].x = key;
+                done = true;
+                break;
+            }
+            h = (h + 1) & mask;
+        }
+        if (!done) set_status(st, XLB_ERR_CAPACITY, 1, key);
+    }
+}
+
+struct LoadKeyHalf {  // join key = one half of the probe tuple (sel 0: high, 1: low)
+    const uint64_t* bag;
+    int sel;
+    __device__ __forceinline__ uint64_t operator()(uint64_t i) const {
+        uint64_t t = bag[i];
+        return sel == 0 ? (t >> 32) : (t & 0xFFFFFFFFull);
+    }
+};
+struct LoadKey64 {  // join key from a separate array of key words
+    const uint64_t* keys;
+    __device__ __forceinline__ uint64_t operator()(uint64_t i) const { return keys[i]; }
+};
+
+// match[i] = (start << 32) | len, or 0 when the key is absent.  Keys are compared, not only
+// their hashes (the reference pins this in crates/xlog-cuda/tests/join_collision_test.rs:19-53).
+template <class LoadKey>
+__global__ void __launch_bounds__(BLOCK) hash_probe_k(LoadKey load_key, uint64_t n, const ulonglong2* __restrict__ table, uint64_t mask, uint64_t* __restrict__ match) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        uint64_t key = load_key(i);
+        uint64_t h = mix64(key) & mask;
+        uint64_t m = 0;
+        for (uint64_t probe = 0; probe <= mask; ++probe) {  // bounded by the table size
+            ulonglong2 s = __ldg(&table[h]);
+            if (s.y == 0) break;
+            if (s.x == key) { m = s.y; break; }
+            h = (h + 1) & mask;
+        }
+        match[i] = m;
+    }
+}
+
+struct PredMatched {
+    const uint64_t* match;
+    __device__ __forceinline__ bool operator()(uint64_t i) const { return match[i] != 0; }
+};
+struct EmitMatched {
+    const uint64_t* bag;
+    const uint64_t* match;
+    uint64_t* mbag;
+    uint64_t* mmatch;
+    __device__ __forceinline__ void operator()(uint64_t i, uint64_t pos) const {
+        mbag[pos] = bag[i];
+        mmatch[pos] = match[i];
+    }
+};
+
+constexpr int EX_IPT = 8;
+constexpr int EX_TILE = BLOCK * EX_IPT;
+
+// tile_row[t] = index of the matched row that owns output t * EX_TILE (last row with off <= o).
+__global__ void expand_partition_k(const uint64_t* __restrict__ off, uint64_t nrows, uint64_t total, uint64_t* __restrict__ tile_row, uint64_t ntiles) {
+    uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t > ntiles) return;
+    uint64_t o = t * EX_TILE;
+    if (o >= total) { tile_row[t] = nrows; return; }
+    uint64_t lo = 0, hi = nrows;  // first row with off > o
+    while (lo < hi) {
+        uint64_t mid = (lo + hi) >> 1;
+        if (off[mid] <= o) lo = mid + 1;
+        else hi = mid;
+    }
+    tile_row[t] = lo - 1;
+}
+
+// Output column source: 0 = probe high half, 1 = probe low half, 2 = the build row's other
+// column, 3 = zero (arity-1 output keeps the value in the low half).
+__device__ __forceinline__ uint32_t ex_pick(int src, uint64_t probe, uint32_t other) {
+    return src == 0 ? (uint32_t)(probe >> 32) : src == 1 ? (uint32_t)probe : src == 2 ? other : 0u;
+}
+
+// Load-balanced expansion: every matched probe row contributes len outputs; each tile of EX_TILE
+// outputs finds its rows by a search over the row offsets held in shared memory, so writes are
+// coalesced whatever the degree skew.  Output order: probe row order, then build order.
+__global__ void __launch_bounds__(BLOCK) expand_k(const uint64_t* __restrict__ mbag, const uint64_t* __restrict__ mmatch, const uint64_t* __restrict__ off,
+                                                   uint64_t nrows, uint64_t total, const uint64_t* __restrict__ tile_row, const uint64_t* __restrict__ S,
+                                                   const uint32_t* __restrict__ pay, int hi_src, int lo_src, uint64_t* __restrict__ out) {
+    __shared__ uint64_t soff[EX_TILE + 2];
+    uint64_t o0 = (uint64_t)blockIdx.x * EX_TILE;
+    uint64_t o1 = o0 + EX_TILE < total ? o0 + EX_TILE : total;
+    uint64_t r0 = tile_row[blockIdx.x];
+    uint64_t r1 = tile_row[blockIdx.x + 1];  // row owning the first output of the next tile (or nrows)
+    if (r1 >= nrows) r1 = nrows - 1;
+    unsigned nr = (unsigned)(r1 - r0 + 1);  // every matched row has len >= 1, so nr <= EX_TILE + 1
+    for (unsigned i = threadIdx.x; i < nr; i += BLOCK) soff[i] = off[r0 + i];
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < EX_IPT; ++k) {
+        uint64_t o = o0 + (uint64_t)k * BLOCK + threadIdx.x;
+        if (o >= o1) break;
+        unsigned lo = 0, hi = nr;  // first local row with soff > o
+        while (lo < hi) {
+            unsigned mid = (lo + hi) >> 1;
+            if (soff[mid] <= o) lo = mid + 1;
+            else hi = mid;
+        }
+        unsigned r = lo - 1;
+        uint64_t probe = mbag[r0 + r];
+        uint64_t start = mmatch[r0 + r] >> 32;
+        uint64_t j = start + (o - soff[r]);
+        uint32_t other = pay ? pay[j] : (uint32_t)S[j];
+        out[o] = ((uint64_t)ex_pick(hi_src, probe, other) << 32) | ex_pick(lo_src, probe, other);
+    }
+}
+
+}  // namespace xk

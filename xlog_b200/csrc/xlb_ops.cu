@@ -1,0 +1,897 @@
+// Context, relations and relational operators of the C ABI (include/xlb.h), plus the host-level
+// key-array operations the executor uses.  Every device loop lives in xlb_kernels.cuh.
+#include <algorithm>
+#include <cstring>
+
+#include "xlb_kernels.cuh"
+#include "xlb_ops.h"
+
+using namespace xk;
+
+// ------------------------------------------------------------------------------ small kernels
+namespace {
+
+__global__ void iota_k(uint32_t* out, uint64_t n) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) out[i] = (uint32_t)i;
+}
+__global__ void iota64_k(uint64_t* out, uint64_t n) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) out[i] = i;
+}
+// key word of a row from up to two columns: (a << 32 | b) for two 32-bit columns, the value itself otherwise
+__global__ void build_key_k(const void* c0, int w0, const void* c1, int w1, const uint32_t* idx, uint64_t* out, uint64_t n) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        uint64_t r = idx ? idx[i] : i;
+        uint64_t a = w0 == 4 ? ((const uint32_t*)c0)[r] : ((const uint64_t*)c0)[r];
+        if (c1) {
+            uint64_t b = ((const uint32_t*)c1)[r];
+            a = (a << 32) | b;
+        }
+        out[i] = a;
+    }
+}
+template <class T>
+__global__ void gather_k(const T* __restrict__ in, const uint32_t* __restrict__ idx, T* __restrict__ out, uint64_t n) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) out[i] = in[idx[i]];
+}
+// gather by one half of a u64 pair array (hi: left row, lo: right row)
+template <class T>
+__global__ void gather_pair_k(const T* __restrict__ in, const uint64_t* __restrict__ pairs, int half, T* __restrict__ out, uint64_t n) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        uint64_t p = pairs[i];
+        out[i] = in[half == 0 ? (p >> 32) : (p & 0xFFFFFFFFull)];
+    }
+}
+
+struct ColSet {  // columns of a gathered (sorted) relation for multi-column run detection
+    const void* col[XLB_MAX_ARITY];
+    int width[XLB_MAX_ARITY];
+    int n;
+};
+__device__ __forceinline__ bool rows_equal(const ColSet& cs, uint64_t a, uint64_t b) {
+    for (int c = 0; c < cs.n; ++c) {
+        uint64_t x = cs.width[c] == 4 ? ((const uint32_t*)cs.col[c])[a] : ((const uint64_t*)cs.col[c])[a];
+        uint64_t y = cs.width[c] == 4 ? ((const uint32_t*)cs.col[c])[b] : ((const uint64_t*)cs.col[c])[b];
+        if (x != y) return false;
+    }
+    return true;
+}
+struct PredRowHead {
+    ColSet cs;
+    __device__ __forceinline__ bool operator()(uint64_t i) const { return i == 0 || !rows_equal(cs, i, i - 1); }
+};
+// run head whose run does not start with a row of the excluded input (origin index < n_excl)
+struct PredRowHeadNotExcluded {
+    ColSet cs;
+    const uint32_t* origin;
+    uint32_t n_excl;
+    __device__ __forceinline__ bool operator()(uint64_t i) const {
+        if (i != 0 && rows_equal(cs, i, i - 1)) return false;
+        return origin[i] >= n_excl;
+    }
+};
+struct EmitIndex {
+    uint32_t* out;
+    __device__ __forceinline__ void operator()(uint64_t i, uint64_t pos) const { out[pos] = (uint32_t)i; }
+};
+struct PredCmp {
+    const uint64_t* in;
+    uint32_t cmp;
+    int lhs;
+    bool rhs_const;
+    uint64_t rhs;
+    __device__ __forceinline__ bool operator()(uint64_t i) const {
+        uint64_t k = in[i];
+        uint64_t a = lhs == SRC_HI ? (k >> 32) : (k & 0xFFFFFFFFull);
+        uint64_t b = rhs_const ? rhs : (rhs == SRC_HI ? (k >> 32) : (k & 0xFFFFFFFFull));
+        switch (cmp) {
+            case XLB_EQ: return a == b;
+            case XLB_NE: return a != b;
+            case XLB_LT: return a < b;
+            case XLB_LE: return a <= b;
+            case XLB_GT: return a > b;
+            default: return a >= b;
+        }
+    }
+};
+struct PredFlag {
+    const uint64_t* match;
+    bool want;
+    __device__ __forceinline__ bool operator()(uint64_t i) const { return (match[i] != 0) == want; }
+};
+
+// stable partition by owner rank
+__global__ void owner_count_k(const uint64_t* __restrict__ in, uint64_t n, int keysel, uint32_t world, unsigned long long* __restrict__ counts) {
+    __shared__ unsigned int sh[64];
+    if (threadIdx.x < 64) sh[threadIdx.x] = 0;
+    __syncthreads();
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        uint64_t k = in[i];
+        uint64_t key = keysel == 0 ? (k >> 32) : (k & 0xFFFFFFFFull);
+        atomicAdd(&sh[(uint32_t)(mix64(key) % world)], 1u);
+    }
+    __syncthreads();
+    if (threadIdx.x < world && sh[threadIdx.x]) atomicAdd(&counts[threadIdx.x], (unsigned long long)sh[threadIdx.x]);
+}
+struct PredOwner {
+    const uint64_t* in;
+    int keysel;
+    uint32_t world, want;
+    __device__ __forceinline__ bool operator()(uint64_t i) const {
+        uint64_t k = in[i];
+        uint64_t key = keysel == 0 ? (k >> 32) : (k & 0xFFFFFFFFull);
+        return (uint32_t)(mix64(key) % world) == want;
+    }
+};
+
+}  // namespace
+
+extern "C" uint32_t xlb_owner_of(uint64_t key, uint32_t world) { return world ? (uint32_t)(xk::mix64(key) % world) : 0; }
+
+// ------------------------------------------------------------------------------ phase timing
+struct PhaseRec {
+    cudaEvent_t e0, e1;
+    double* acc;
+};
+static thread_local std::vector<PhaseRec> g_phase_recs;
+
+PhaseTimer::PhaseTimer(xlb_ctx* ctx, double* into) : c(ctx), acc(into) {
+    if (!(c->flags & XLB_FLAG_PROFILE) || !into) return;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    cudaEventRecord(e0, c->stream);
+}
+PhaseTimer::~PhaseTimer() {
+    if (!e0) return;
+    cudaEventRecord(e1, c->stream);
+    g_phase_recs.push_back({e0, e1, acc});
+}
+void xlb_resolve_phase_timers(xlb_ctx* c) {
+    cudaStreamSynchronize(c->stream);
+    for (auto& r : g_phase_recs) {
+        float ms = 0;
+        if (cudaEventElapsedTime(&ms, r.e0, r.e1) == cudaSuccess) *r.acc += ms;
+        cudaEventDestroy(r.e0);
+        cudaEventDestroy(r.e1);
+    }
+    g_phase_recs.clear();
+    for (auto& e : c->sort_events) {
+        float ms = 0;
+        if (cudaEventElapsedTime(&ms, e.first, e.second) == cudaSuccess) c->ms_sort_kernel += ms;
+        cudaEventDestroy(e.first);
+        cudaEventDestroy(e.second);
+    }
+    c->sort_events.clear();
+}
+
+// ------------------------------------------------------------------------------ key-array ops
+Keys ops_rel_packed(xlb_ctx* c, const xlb_rel* r) {
+    Keys k;
+    k.n = r->rows;
+    if (r->packed) { k.buf = r->packed; return k; }
+    if (!rel_packable(r->schema)) xlb_fail(XLB_ERR_UNSUPPORTED, "relation is not a one- or two-column 32-bit relation");
+    Buf b = make_buf(c, r->rows * 8);
+    if (r->rows) {
+        if (r->schema.arity == 2) pack2_k<<<grid_for(c, r->rows), BLOCK, 0, c->stream>>>(r->cols[0]->as<uint32_t>(), r->cols[1]->as<uint32_t>(), b->as<uint64_t>(), r->rows);
+        else pack1_k<<<grid_for(c, r->rows), BLOCK, 0, c->stream>>>(r->cols[0]->as<uint32_t>(), b->as<uint64_t>(), r->rows);
+        check_launch(c, "pack");
+    }
+    r->packed = b;
+    k.buf = b;
+    return k;
+}
+
+void ops_rel_columns(xlb_ctx* c, const xlb_rel* r) {
+    if (r->schema.arity == 0 || r->cols[0]) return;
+    for (uint32_t i = 0; i < r->schema.arity; ++i) r->cols[i] = make_buf(c, r->rows * 4);
+    if (!r->rows) return;
+    if (r->schema.arity == 2) unpack2_k<<<grid_for(c, r->rows), BLOCK, 0, c->stream>>>(r->packed->as<uint64_t>(), r->cols[0]->as<uint32_t>(), r->cols[1]->as<uint32_t>(), r->rows);
+    else unpack1_k<<<grid_for(c, r->rows), BLOCK, 0, c->stream>>>(r->packed->as<uint64_t>(), r->cols[0]->as<uint32_t>(), r->rows);
+    check_launch(c, "unpack");
+}
+
+xlb_rel* ops_rel_from_keys(xlb_ctx* c, const xlb_schema& s, Keys k, bool canonical) {
+    auto* r = new xlb_rel;
+    r->ctx = c;
+    r->schema = s;
+    r->rows = k.n;
+    r->packed = k.buf ? k.buf : make_buf(c, 0);
+    r->canonical = canonical;
+    return r;
+}
+
+Keys ops_copy(xlb_ctx* c, const Keys& in) {
+    Keys o;
+    o.n = in.n;
+    o.buf = make_buf(c, in.n * 8);
+    if (in.n) CUDA_OK(cudaMemcpyAsync(o.buf->p, in.buf->p, in.n * 8, cudaMemcpyDeviceToDevice, c->stream));
+    return o;
+}
+
+Keys ops_slice(xlb_ctx* c, const Keys& in, uint64_t lo, uint64_t hi) {
+    Keys o;
+    o.n = hi - lo;
+    o.buf = make_buf(c, o.n * 8);
+    if (o.n) CUDA_OK(cudaMemcpyAsync(o.buf->p, in.ptr() + lo, o.n * 8, cudaMemcpyDeviceToDevice, c->stream));
+    return o;
+}
+
+Keys ops_concat(xlb_ctx* c, const std::vector<Keys>& parts) {
+    Keys o;
+    for (auto& p : parts) o.n += p.n;
+    o.buf = make_buf(c, o.n * 8);
+    uint64_t at = 0;
+    for (auto& p : parts) {
+        if (p.n) CUDA_OK(cudaMemcpyAsync(o.buf->as<uint64_t>() + at, p.buf->p, p.n * 8, cudaMemcpyDeviceToDevice, c->stream));
+        at += p.n;
+    }
+    return o;
+}
+
+void ops_sort(xlb_ctx* c, Keys& k) { radix_sort(c, k.buf, nullptr, k.n); }
+
+void ops_dedup_sorted(xlb_ctx* c, Keys& k) {
+    if (k.n <= 1) return;
+    Buf out = make_buf(c, k.n * 8);
+    k.n = dedup_sorted(c, k.ptr(), k.n, out->as<uint64_t>());
+    k.buf = out;
+}
+
+Keys ops_diff(xlb_ctx* c, const Keys& a, const Keys& b) {
+    Keys o;
+    o.buf = set_difference(c, a.ptr(), a.n, b.ptr(), b.n, &o.n);
+    return o;
+}
+
+Keys ops_merge_disjoint(xlb_ctx* c, const Keys& a, const Keys& b) {
+    Keys o;
+    o.n = a.n + b.n;
+    o.buf = merge_disjoint(c, a.ptr(), a.n, b.ptr(), b.n);
+    return o;
+}
+
+Keys ops_union(xlb_ctx* c, const Keys& a, const Keys& b) {
+    if (b.n == 0) return a;
+    if (a.n == 0) return b;
+    const Keys& small = a.n <= b.n ? a : b;
+    const Keys& big = a.n <= b.n ? b : a;
+    Keys extra = ops_diff(c, small, big);
+    return ops_merge_disjoint(c, big, extra);
+}
+
+Keys ops_remap(xlb_ctx* c, const Keys& in, int hi_src, int lo_src) {
+    Keys o;
+    o.n = in.n;
+    o.buf = make_buf(c, in.n * 8);
+    if (in.n) {
+        remap_k<<<grid_for(c, in.n), BLOCK, 0, c->stream>>>(in.ptr(), o.buf->as<uint64_t>(), in.n, hi_src == SRC_ZERO ? 2 : hi_src, lo_src == SRC_ZERO ? 2 : lo_src);
+        check_launch(c, "remap");
+    }
+    return o;
+}
+
+Keys ops_filter(xlb_ctx* c, const Keys& in, uint32_t cmp, int lhs_src, bool rhs_is_const, uint64_t rhs) {
+    Keys o;
+    o.buf = make_buf(c, in.n * 8);
+    o.n = select(c, PredCmp{in.ptr(), cmp, lhs_src, rhs_is_const, rhs}, EmitKey{in.ptr(), o.buf->as<uint64_t>()}, in.n);
+    return o;
+}
+
+Index ops_index_build(xlb_ctx* c, Buf S, uint64_t n, int key_shift, Buf pay) {
+    Index ix;
+    ix.S = S;
+    ix.pay = pay;
+    ix.n = n;
+    ix.key_shift = key_shift;
+    if (n >= 0xFFFFFFFFull) xlb_fail(XLB_ERR_CAPACITY, "join build side of %llu rows exceeds the 2^32 - 1 row limit", (unsigned long long)n);
+    Buf starts = make_buf(c, (n + 1) * 4);
+    uint64_t nu = 0;
+    if (n) {
+        if (key_shift == 32) nu = select(c, PredRunHead{S->as<uint64_t>()}, EmitRunHead{starts->as<uint32_t>()}, n);
+        else nu = select(c, PredHead{S->as<uint64_t>()}, EmitRunHead{starts->as<uint32_t>()}, n);
+    }
+    ix.nkeys = nu;
+    uint64_t cap = 1024;
+    while (cap < 2 * nu) cap <<= 1;
+    ix.mask = cap - 1;
+    ix.table = make_buf(c, cap * 16);
+    CUDA_OK(cudaMemsetAsync(ix.table->p, 0, cap * 16, c->stream));
+    if (nu) {
+        hash_insert_k<<<grid_for(c, nu), BLOCK, 0, c->stream>>>(S->as<uint64_t>(), n, key_shift, starts->as<uint32_t>(), nu, ix.table->as<ulonglong2>(), ix.mask, c->d_status);
+        check_launch(c, "hash_insert");
+    }
+    return ix;
+}
+
+Buf ops_probe_match(xlb_ctx* c, const Keys& bag, int keysel, const uint64_t* pkeys, const Index& ix) {
+    Buf match = make_buf(c, bag.n * 8);
+    if (bag.n) {
+        if (pkeys) hash_probe_k<LoadKey64><<<grid_for(c, bag.n), BLOCK, 0, c->stream>>>(LoadKey64{pkeys}, bag.n, ix.table->as<ulonglong2>(), ix.mask, match->as<uint64_t>());
+        else hash_probe_k<LoadKeyHalf><<<grid_for(c, bag.n), BLOCK, 0, c->stream>>>(LoadKeyHalf{bag.ptr(), keysel}, bag.n, ix.table->as<ulonglong2>(), ix.mask, match->as<uint64_t>());
+        check_launch(c, "hash_probe");
+    }
+    return match;
+}
+
+Keys ops_join_expand(xlb_ctx* c, const Keys& bag, int keysel, const uint64_t* pkeys, const Index& ix, int hi_src, int lo_src) {
+    Keys out;
+    if (bag.n == 0 || ix.n == 0) { out.buf = make_buf(c, 0); return out; }
+    Buf match = ops_probe_match(c, bag, keysel, pkeys, ix);
+    // keep the probe rows that matched, so every remaining row expands to at least one output
+    Buf mbag = make_buf(c, bag.n * 8), mmatch = make_buf(c, bag.n * 8);
+    uint64_t nm = select(c, PredMatched{match->as<uint64_t>()}, EmitMatched{bag.ptr(), match->as<uint64_t>(), mbag->as<uint64_t>(), mmatch->as<uint64_t>()}, bag.n);
+    match.reset();
+    if (nm == 0) { out.buf = make_buf(c, 0); return out; }
+    Buf off = make_buf(c, nm * 8);
+    Buf total = make_buf(c, 8);
+    exclusive_scan<LoadLow32, uint64_t>(c, LoadLow32{mmatch->as<uint64_t>()}, nm, off->as<uint64_t>(), total->as<uint64_t>());
+    unsigned long long tot;
+    read_words(c, total->p, 1, &tot);
+    out.n = tot;
+    out.buf = make_buf(c, tot * 8);
+    uint64_t ntiles = (tot + EX_TILE - 1) / EX_TILE;
+    Buf tile_row = make_buf(c, (ntiles + 1) * 8);
+    expand_partition_k<<<(unsigned)((ntiles + 1 + 127) / 128), 128, 0, c->stream>>>(off->as<uint64_t>(), nm, tot, tile_row->as<uint64_t>(), ntiles);
+    check_launch(c, "expand_partition");
+    expand_k<<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(mbag->as<uint64_t>(), mmatch->as<uint64_t>(), off->as<uint64_t>(), nm, tot, tile_row->as<uint64_t>(),
+                                                         ix.S->as<uint64_t>(), ix.pay ? ix.pay->as<uint32_t>() : nullptr, hi_src, lo_src, out.buf->as<uint64_t>());
+    check_launch(c, "expand");
+    return out;
+}
+
+Keys ops_partition_by_owner(xlb_ctx* c, const Keys& in, int keysel, uint32_t world, std::vector<uint64_t>& counts_out) {
+    counts_out.assign(world, 0);
+    Keys out;
+    out.n = in.n;
+    out.buf = make_buf(c, in.n * 8);
+    if (in.n == 0) return out;
+    uint64_t at = 0;
+    for (uint32_t r = 0; r < world; ++r) {  // one stable compaction per destination rank
+        uint64_t m = select(c, PredOwner{in.ptr(), keysel, world, r}, EmitKey{in.ptr(), out.buf->as<uint64_t>() + at}, in.n);
+        counts_out[r] = m;
+        at += m;
+    }
+    return out;
+}
+
+// ------------------------------------------------------------------------------ C ABI: context
+#define API_BEGIN(ctxp) \
+    xlb_ctx* ctx__ = (ctxp); \
+    try {
+#define API_END()                                  \
+    }                                              \
+    catch (const XlbError& e) {                    \
+        if (ctx__) ctx__->last_error = e.msg;      \
+        return e.st;                               \
+    }                                              \
+    catch (const std::bad_alloc&) {                \
+        if (ctx__) ctx__->last_error = "host allocation failed"; \
+        return XLB_ERR_RESOURCE_EXHAUSTED;         \
+    }                                              \
+    return XLB_OK;
+
+static thread_local std::string g_create_error;
+
+extern "C" xlb_status xlb_ctx_create(const xlb_config* cfg, xlb_ctx** out) {
+    if (!out) return XLB_ERR_INVALID;
+    xlb_ctx* c = nullptr;
+    try {
+        int ndev = 0;
+        cudaError_t e = cudaGetDeviceCount(&ndev);
+        if (e != cudaSuccess || ndev == 0)
+            xlb_fail(XLB_ERR_CUDA, "no CUDA device: %s (this library has no CPU path)", cudaGetErrorString(e));
+        c = new xlb_ctx;
+        int dev = cfg ? cfg->device : -1;
+        if (dev < 0) CUDA_OK(cudaGetDevice(&dev));
+        if (dev >= ndev) xlb_fail(XLB_ERR_INVALID, "device %d out of range (%d devices)", dev, ndev);
+        c->device = dev;
+        CUDA_OK(cudaSetDevice(dev));
+        CUDA_OK(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+        cudaMemPoolProps props{};
+        props.allocType = cudaMemAllocationTypePinned;
+        props.handleTypes = cudaMemHandleTypeNone;
+        props.location.type = cudaMemLocationTypeDevice;
+        props.location.id = dev;
+        CUDA_OK(cudaMemPoolCreate(&c->pool, &props));
+        uint64_t thresh = ~0ull;
+        CUDA_OK(cudaMemPoolSetAttribute(c->pool, cudaMemPoolAttrReleaseThreshold, &thresh));
+        size_t fr = 0, tot = 0;
+        CUDA_OK(cudaMemGetInfo(&fr, &tot));
+        c->budget = cfg && cfg->memory_budget_bytes ? cfg->memory_budget_bytes : (uint64_t)(fr * 0.9);
+        c->max_iterations = cfg && cfg->max_iterations ? cfg->max_iterations : 1000000ull;
+        c->join_chunk = cfg ? cfg->join_chunk_tuples : 0;
+        c->flags = cfg ? cfg->flags : 0;
+        CUDA_OK(cudaMallocHost(&c->h_scalar, 64 * 8));
+        CUDA_OK(cudaMalloc(&c->d_status, sizeof(DevStatus)));
+        CUDA_OK(cudaMemset(c->d_status, 0, sizeof(DevStatus)));
+        cudaDeviceProp prop;
+        CUDA_OK(cudaGetDeviceProperties(&prop, dev));
+        c->sm_count = prop.multiProcessorCount;
+        *out = c;
+    } catch (const XlbError& e) {
+        g_create_error = e.msg;
+        delete c;
+        return e.st;
+    }
+    return XLB_OK;
+}
+
+void xlb_exec_teardown(xlb_ctx* c);  // xlb_exec.cu: store, indexes, communicator
+
+extern "C" void xlb_ctx_destroy(xlb_ctx* c) {
+    if (!c) return;
+    cudaSetDevice(c->device);
+    xlb_exec_teardown(c);
+    cudaStreamSynchronize(c->stream);
+    if (c->h_scalar) cudaFreeHost(c->h_scalar);
+    if (c->d_status) cudaFree(c->d_status);
+    if (c->pool) cudaMemPoolDestroy(c->pool);
+    if (c->stream) cudaStreamDestroy(c->stream);
+    delete c;
+}
+
+extern "C" const char* xlb_last_error(const xlb_ctx* c) { return c ? c->last_error.c_str() : g_create_error.c_str(); }
+
+extern "C" xlb_status xlb_memory_stats(const xlb_ctx* c, uint64_t* allocated, uint64_t* peak) {
+    if (!c) return XLB_ERR_INVALID;
+    if (allocated) *allocated = c->allocated;
+    if (peak) *peak = c->peak;
+    return XLB_OK;
+}
+
+// ------------------------------------------------------------------------------ C ABI: relations
+static void check_schema(const xlb_schema* s) {
+    if (!s || s->arity > XLB_MAX_ARITY) xlb_fail(XLB_ERR_INVALID, "schema missing or arity above %u", XLB_MAX_ARITY);
+    for (uint32_t i = 0; i < s->arity; ++i)
+        if (!type_built(s->types[i])) xlb_fail(XLB_ERR_UNSUPPORTED, "column %u: type code %u is not built (u32, u64 and symbol are)", i, s->types[i]);
+}
+
+static xlb_rel* rel_empty(xlb_ctx* c, const xlb_schema& s) {
+    auto* r = new xlb_rel;
+    r->ctx = c;
+    r->schema = s;
+    r->rows = 0;
+    for (uint32_t i = 0; i < s.arity; ++i) r->cols[i] = make_buf(c, 0);
+    r->canonical = true;
+    return r;
+}
+
+extern "C" xlb_status xlb_rel_from_host(xlb_ctx* c, const xlb_schema* s, const void* const* cols, uint64_t rows, xlb_rel** out) {
+    if (!c || !out) return XLB_ERR_INVALID;
+    API_BEGIN(c)
+    check_schema(s);
+    if (rows && s->arity && !cols) xlb_fail(XLB_ERR_INVALID, "column pointers missing");
+    std::unique_ptr<xlb_rel> r(new xlb_rel);
+    r->ctx = c;
+    r->schema = *s;
+    r->rows = s->arity ? rows : std::min<uint64_t>(rows, 1);
+    for (uint32_t i = 0; i < s->arity; ++i) {
+        uint64_t bytes = rows * type_width(s->types[i]);
+        r->cols[i] = make_buf(c, bytes);
+        if (bytes) {
+            if (!cols[i]) xlb_fail(XLB_ERR_INVALID, "column %u pointer is null", i);
+            CUDA_OK(cudaMemcpyAsync(r->cols[i]->p, cols[i], bytes, cudaMemcpyHostToDevice, c->stream));
+        }
+    }
+    CUDA_OK(cudaStreamSynchronize(c->stream));
+    r->canonical = r->rows == 0;
+    *out = r.release();
+    API_END()
+}
+
+extern "C" xlb_status xlb_rel_empty(xlb_ctx* c, const xlb_schema* s, xlb_rel** out) {
+    if (!c || !out) return XLB_ERR_INVALID;
+    API_BEGIN(c)
+    check_schema(s);
+    *out = rel_empty(c, *s);
+    API_END()
+}
+
+extern "C" xlb_status xlb_rel_rows(const xlb_rel* r, uint64_t* rows) {
+    if (!r || !rows) return XLB_ERR_INVALID;
+    *rows = r->rows;
+    return XLB_OK;
+}
+extern "C" xlb_status xlb_rel_schema(const xlb_rel* r, xlb_schema* s) {
+    if (!r || !s) return XLB_ERR_INVALID;
+    *s = r->schema;
+    return XLB_OK;
+}
+extern "C" xlb_status xlb_rel_is_canonical(const xlb_rel* r, int* canonical) {
+    if (!r || !canonical) return XLB_ERR_INVALID;
+    *canonical = r->canonical ? 1 : 0;
+    return XLB_OK;
+}
+
+extern "C" xlb_status xlb_rel_to_host(xlb_ctx* c, const xlb_rel* r, void* const* cols, uint64_t cap_rows, uint64_t* rows) {
+    if (!c || !r) return XLB_ERR_INVALID;
+    API_BEGIN(c)
+    uint64_t n = std::min(r->rows, cap_rows);
+    if (n && r->schema.arity) {
+        if (!cols) xlb_fail(XLB_ERR_INVALID, "column pointers missing");
+        ops_rel_columns(c, r);
+        for (uint32_t i = 0; i < r->schema.arity; ++i) {
+            if (!cols[i]) xlb_fail(XLB_ERR_INVALID, "column %u pointer is null", i);
+            CUDA_OK(cudaMemcpyAsync(cols[i], r->cols[i]->p, n * type_width(r->schema.types[i]), cudaMemcpyDeviceToHost, c->stream));
+        }
+    }
+    CUDA_OK(cudaStreamSynchronize(c->stream));
+    if (rows) *rows = r->rows;
+    API_END()
+}
+
+static xlb_rel* rel_clone(xlb_ctx* c, const xlb_rel* r) {
+    std::unique_ptr<xlb_rel> o(new xlb_rel);
+    o->ctx = c;
+    o->schema = r->schema;
+    o->rows = r->rows;
+    o->canonical = r->canonical;
+    if (r->packed) {
+        Keys k;
+        k.buf = r->packed;
+        k.n = r->rows;
+        o->packed = ops_copy(c, k).buf;
+    } else {
+        for (uint32_t i = 0; i < r->schema.arity; ++i) {
+            uint64_t bytes = r->rows * type_width(r->schema.types[i]);
+            o->cols[i] = make_buf(c, bytes);
+            if (bytes) CUDA_OK(cudaMemcpyAsync(o->cols[i]->p, r->cols[i]->p, bytes, cudaMemcpyDeviceToDevice, c->stream));
+        }
+    }
+    return o.release();
+}
+
+extern "C" xlb_status xlb_rel_clone(xlb_ctx* c, const xlb_rel* r, xlb_rel** out) {
+    if (!c || !r || !out) return XLB_ERR_INVALID;
+    API_BEGIN(c)
+    *out = rel_clone(c, r);
+    CUDA_OK(cudaStreamSynchronize(c->stream));
+    API_END()
+}
+
+extern "C" void xlb_rel_free(xlb_rel* r) {
+    if (!r) return;
+    cudaSetDevice(r->ctx->device);
+    delete r;
+}
+
+// ------------------------------------------------------------------------------ operators
+static bool schemas_compatible(const xlb_schema& a, const xlb_schema& b) {
+    if (a.arity != b.arity) return false;
+    for (uint32_t i = 0; i < a.arity; ++i) {
+        uint8_t x = a.types[i] == XLB_SYMBOL ? XLB_U32 : a.types[i];
+        uint8_t y = b.types[i] == XLB_SYMBOL ? XLB_U32 : b.types[i];
+        if (x != y) return false;
+    }
+    return true;
+}
+
+// rows that fit one u64 word: (u32), (u32,u32) as packed keys, or a single u64 column as is
+static bool single_word(const xlb_schema& s) { return rel_packable(s) || (s.arity == 1 && type_width(s.types[0]) == 8); }
+
+static Keys rel_word_keys(xlb_ctx* c, const xlb_rel* r) {
+    if (rel_packable(r->schema)) return ops_rel_packed(c, r);
+    Keys k;
+    k.buf = r->cols[0];
+    k.n = r->rows;
+    return k;
+}
+static xlb_rel* rel_from_word_keys(xlb_ctx* c, const xlb_schema& s, Keys k, bool canonical) {
+    if (rel_packable(s)) return ops_rel_from_keys(c, s, k, canonical);
+    auto* r = new xlb_rel;
+    r->ctx = c;
+    r->schema = s;
+    r->rows = k.n;
+    r->cols[0] = k.buf ? k.buf : make_buf(c, 0);
+    r->canonical = canonical;
+    return r;
+}
+
+static ColSet colset_of(const xlb_rel* r) {
+    ColSet cs{};
+    cs.n = (int)r->schema.arity;
+    for (int i = 0; i < cs.n; ++i) {
+        cs.col[i] = r->cols[i]->p;
+        cs.width[i] = (int)type_width(r->schema.types[i]);
+    }
+    return cs;
+}
+
+// Stable sort permutation by key columns (first key most significant): LSD over the key
+// columns, least significant first, each a stable (key word, row index) radix sort.
+static Buf sort_permutation(xlb_ctx* c, const xlb_rel* r, const uint32_t* keys, uint32_t nk) {
+    uint64_t n = r->rows;
+    Buf idx = make_buf(c, n * 4);
+    if (n == 0) return idx;
+    if (n >= (1ull << 32)) xlb_fail(XLB_ERR_CAPACITY, "sort of %llu rows exceeds the 2^32 row limit", (unsigned long long)n);
+    iota_k<<<grid_for(c, n), BLOCK, 0, c->stream>>>(idx->as<uint32_t>(), n);
+    check_launch(c, "iota");
+    int k = (int)nk - 1;
+    while (k >= 0) {
+        // fuse two adjacent 32-bit key columns into one 64-bit key word
+        int w1 = (int)type_width(r->schema.types[keys[k]]);
+        const void* lo = nullptr;
+        int hi_col = k;
+        if (w1 == 4 && k >= 1 && type_width(r->schema.types[keys[k - 1]]) == 4) {
+            lo = r->cols[keys[k]]->p;
+            hi_col = k - 1;
+        }
+        Buf kw = make_buf(c, n * 8);
+        const xlb_rel* rr = r;
+        build_key_k<<<grid_for(c, n), BLOCK, 0, c->stream>>>(rr->cols[keys[hi_col]]->p, (int)type_width(r->schema.types[keys[hi_col]]), lo, 4, idx->as<uint32_t>(), kw->as<uint64_t>(), n);
+        check_launch(c, "build_key");
+        radix_sort(c, kw, &idx, n);
+        k = hi_col - 1;
+    }
+    return idx;
+}
+
+static xlb_rel* gather_rel(xlb_ctx* c, const xlb_rel* r, const uint32_t* idx, uint64_t n) {
+    std::unique_ptr<xlb_rel> o(new xlb_rel);
+    o->ctx = c;
+    o->schema = r->schema;
+    o->rows = n;
+    for (uint32_t i = 0; i < r->schema.arity; ++i) {
+        uint32_t w = type_width(r->schema.types[i]);
+        o->cols[i] = make_buf(c, n * w);
+        if (!n) continue;
+        if (w == 4) gather_k<uint32_t><<<grid_for(c, n), BLOCK, 0, c->stream>>>(r->cols[i]->as<uint32_t>(), idx, o->cols[i]->as<uint32_t>(), n);
+        else gather_k<uint64_t><<<grid_for(c, n), BLOCK, 0, c->stream>>>(r->cols[i]->as<uint64_t>(), idx, o->cols[i]->as<uint64_t>(), n);
+        check_launch(c, "gather");
+    }
+    return o.release();
+}
+
+extern "C" xlb_status xlb_sort(xlb_ctx* c, const xlb_rel* in, const uint32_t* key_cols, uint32_t nk, xlb_rel** out) {
+    if (!c || !in || !out) return XLB_ERR_INVALID;
+    API_BEGIN(c)
+    for (uint32_t i = 0; i < nk; ++i)
+        if (key_cols[i] >= in->schema.arity) xlb_fail(XLB_ERR_INVALID, "sort key column %u out of range", key_cols[i]);
+    ops_rel_columns(c, in);
+    Buf idx = sort_permutation(c, in, key_cols, nk);
+    *out = gather_rel(c, in, idx->as<uint32_t>(), in->rows);
+    CUDA_OK(cudaStreamSynchronize(c->stream));
+    API_END()
+}
+
+// Full-row canonicalisation of a wide relation (more than one 64-bit word per row).
+static xlb_rel* wide_dedup(xlb_ctx* c, const xlb_rel* in, const uint32_t* origin_excl, uint32_t n_excl) {
+    (void)origin_excl;
+    uint32_t all[XLB_MAX_ARITY];
+    for (uint32_t i = 0; i < in->schema.arity; ++i) all[i] = i;
+    Buf idx = sort_permutation(c, in, all, in->schema.arity);
+    std::unique_ptr<xlb_rel> sorted(gather_rel(c, in, idx->as<uint32_t>(), in->rows));
+    Buf heads = make_buf(c, in->rows * 4);
+    uint64_t m;
+    if (n_excl) m = select(c, PredRowHeadNotExcluded{colset_of(sorted.get()), idx->as<uint32_t>(), n_excl}, EmitIndex{heads->as<uint32_t>()}, in->rows);
+    else m = select(c, PredRowHead{colset_of(sorted.get())}, EmitIndex{heads->as<uint32_t>()}, in->rows);
+    xlb_rel* o = gather_rel(c, sorted.get(), heads->as<uint32_t>(), m);
+    o->canonical = true;
+    return o;
+}
+
+static xlb_rel* concat_cols(xlb_ctx* c, const xlb_rel* const* ins, uint32_t n) {
+    std::unique_ptr<xlb_rel> o(new xlb_rel);
+    o->ctx = c;
+    o->schema = ins[0]->schema;
+    uint64_t rows = 0;
+    for (uint32_t i = 0; i < n; ++i) rows += ins[i]->rows;
+    o->rows = rows;
+    for (uint32_t col = 0; col < o->schema.arity; ++col) {
+        uint32_t w = type_width(o->schema.types[col]);
+        o->cols[col] = make_buf(c, rows * w);
+        uint64_t at = 0;
+        for (uint32_t i = 0; i < n; ++i) {
+            if (ins[i]->rows) {
+                ops_rel_columns(c, ins[i]);
+                CUDA_OK(cudaMemcpyAsync((char*)o->cols[col]->p + at * w, ins[i]->cols[col]->p, ins[i]->rows * w, cudaMemcpyDeviceToDevice, c->stream));
+            }
+            at += ins[i]->rows;
+        }
+    }
+    return o.release();
+}
+
+static xlb_rel* canonicalize(xlb_ctx* c, const xlb_rel* in) {
+    if (in->schema.arity == 0) {  // the 0-arity relation is {} or {()} (set_ops_tests.rs:160-183)
+        xlb_rel* o = rel_empty(c, in->schema);
+        o->rows = in->rows ? 1 : 0;
+        return o;
+    }
+    if (in->canonical) return rel_clone(c, in);
+    if (single_word(in->schema)) {
+        Keys k = ops_copy(c, rel_word_keys(c, in));
+        ops_sort(c, k);
+        ops_dedup_sorted(c, k);
+        return rel_from_word_keys(c, in->schema, k, true);
+    }
+    ops_rel_columns(c, in);
+    return wide_dedup(c, in, nullptr, 0);
+}
+
+extern "C" xlb_status xlb_dedup(xlb_ctx* c, const xlb_rel* in, const uint32_t* key_cols, uint32_t nk, xlb_rel** out) {
+    if (!c || !in || !out) return XLB_ERR_INVALID;
+    API_BEGIN(c)
+    bool full = nk == 0 || nk >= in->schema.arity;
+    if (full) {
+        *out = canonicalize(c, in);
+    } else {
+        for (uint32_t i = 0; i < nk; ++i)
+            if (key_cols[i] >= in->schema.arity) xlb_fail(XLB_ERR_INVALID, "dedup key column %u out of range", key_cols[i]);
+        ops_rel_columns(c, in);
+        Buf idx = sort_permutation(c, in, key_cols, nk);
+        std::unique_ptr<xlb_rel> sorted(gather_rel(c, in, idx->as<uint32_t>(), in->rows));
+        ColSet cs{};
+        cs.n = (int)nk;
+        for (uint32_t i = 0; i < nk; ++i) {
+            cs.col[i] = sorted->cols[key_cols[i]]->p;
+            cs.width[i] = (int)type_width(in->schema.types[key_cols[i]]);
+        }
+        Buf heads = make_buf(c, in->rows * 4);
+        uint64_t m = select(c, PredRowHead{cs}, EmitIndex{heads->as<uint32_t>()}, in->rows);
+        *out = gather_rel(c, sorted.get(), heads->as<uint32_t>(), m);
+    }
+    CUDA_OK(cudaStreamSynchronize(c->stream));
+    API_END()
+}
+
+extern "C" xlb_status xlb_union(xlb_ctx* c, const xlb_rel* const* ins, uint32_t n, xlb_rel** out) {
+    if (!c || !out) return XLB_ERR_INVALID;
+    API_BEGIN(c)
+    if (n == 0 || !ins) xlb_fail(XLB_ERR_INVALID, "union of no inputs");
+    for (uint32_t i = 0; i < n; ++i) {
+        if (!ins[i]) xlb_fail(XLB_ERR_INVALID, "union input %u is null", i);
+        if (!schemas_compatible(ins[0]->schema, ins[i]->schema)) xlb_fail(XLB_ERR_TYPE, "union input %u has an incompatible schema", i);
+    }
+    const xlb_schema& s = ins[0]->schema;
+    if (s.arity == 0) {
+        xlb_rel* o = rel_empty(c, s);
+        for (uint32_t i = 0; i < n; ++i)
+            if (ins[i]->rows) o->rows = 1;
+        *out = o;
+    } else if (single_word(s)) {
+        // canonical inputs are merged; the rest are concatenated, sorted and deduplicated once
+        std::vector<Keys> loose;
+        Keys acc;
+        bool have_acc = false;
+        for (uint32_t i = 0; i < n; ++i) {
+            if (ins[i]->rows == 0) continue;
+            Keys k = rel_word_keys(c, ins[i]);
+            if (ins[i]->canonical) {
+                acc = have_acc ? ops_union(c, acc, k) : k;
+                have_acc = true;
+            } else loose.push_back(k);
+        }
+        if (!loose.empty()) {
+            Keys cat = ops_concat(c, loose);
+            ops_sort(c, cat);
+            ops_dedup_sorted(c, cat);
+            acc = have_acc ? ops_union(c, acc, cat) : cat;
+            have_acc = true;
+        }
+        if (!have_acc) *out = rel_empty(c, s);
+        else {
+            bool aliased = false;
+            for (uint32_t i = 0; i < n; ++i) {
+                if (!ins[i]->rows) continue;
+                Keys k = rel_word_keys(c, ins[i]);
+                if (k.buf == acc.buf) aliased = true;
+            }
+            if (aliased) acc = ops_copy(c, acc);
+            *out = rel_from_word_keys(c, s, acc, true);
+        }
+    } else {
+        std::unique_ptr<xlb_rel> cat(concat_cols(c, ins, n));
+        *out = wide_dedup(c, cat.get(), nullptr, 0);
+    }
+    CUDA_OK(cudaStreamSynchronize(c->stream));
+    API_END()
+}
+
+extern "C" xlb_status xlb_diff(xlb_ctx* c, const xlb_rel* a, const xlb_rel* b, xlb_rel** out) {
+    if (!c || !a || !b || !out) return XLB_ERR_INVALID;
+    API_BEGIN(c)
+    if (!schemas_compatible(a->schema, b->schema)) xlb_fail(XLB_ERR_TYPE, "difference of incompatible schemas");
+    const xlb_schema& s = a->schema;
+    if (s.arity == 0) {
+        xlb_rel* o = rel_empty(c, s);
+        o->rows = (a->rows && !b->rows) ? 1 : 0;
+        *out = o;
+    } else if (a->rows == 0) {
+        *out = rel_empty(c, s);
+    } else if (single_word(s)) {
+        std::unique_ptr<xlb_rel> ca(canonicalize(c, a)), cb(canonicalize(c, b));
+        Keys d = ops_diff(c, rel_word_keys(c, ca.get()), rel_word_keys(c, cb.get()));
+        *out = rel_from_word_keys(c, s, d, true);
+    } else {
+        // rows of b first: a run of equal rows that starts with a row of b is dropped whole
+        const xlb_rel* both[2] = {b, a};
+        std::unique_ptr<xlb_rel> cat(concat_cols(c, both, 2));
+        if (b->rows >= (1ull << 32)) xlb_fail(XLB_ERR_CAPACITY, "difference input exceeds the 2^32 row limit");
+        *out = wide_dedup(c, cat.get(), nullptr, (uint32_t)b->rows);
+    }
+    CUDA_OK(cudaStreamSynchronize(c->stream));
+    API_END()
+}
+
+// key word per row for a join side; two 32-bit key columns fuse into one word
+static Buf join_keys(xlb_ctx* c, const xlb_rel* r, const uint32_t* keys, uint32_t nk) {
+    Buf kw = make_buf(c, r->rows * 8);
+    if (!r->rows) return kw;
+    int w0 = (int)type_width(r->schema.types[keys[0]]);
+    const void* c1 = nullptr;
+    if (nk == 2) {
+        if (w0 != 4 || type_width(r->schema.types[keys[1]]) != 4) xlb_fail(XLB_ERR_UNSUPPORTED, "two-column join keys must both be 32-bit");
+        c1 = r->cols[keys[1]]->p;
+    }
+    build_key_k<<<grid_for(c, r->rows), BLOCK, 0, c->stream>>>(r->cols[keys[0]]->p, w0, c1, 4, nullptr, kw->as<uint64_t>(), r->rows);
+    check_launch(c, "build_key");
+    return kw;
+}
+
+extern "C" xlb_status xlb_hash_join(xlb_ctx* c, const xlb_rel* l, const xlb_rel* r, const uint32_t* lk, const uint32_t* rk, uint32_t nk,
+                                    xlb_join_type type, xlb_rel** out) {
+    if (!c || !l || !r || !out) return XLB_ERR_INVALID;
+    API_BEGIN(c)
+    if (nk < 1 || nk > XLB_MAX_KEYS || !lk || !rk) xlb_fail(XLB_ERR_INVALID, "join needs 1..%u key columns", XLB_MAX_KEYS);
+    for (uint32_t i = 0; i < nk; ++i) {
+        if (lk[i] >= l->schema.arity || rk[i] >= r->schema.arity) xlb_fail(XLB_ERR_INVALID, "join key column out of range");
+        uint8_t a = l->schema.types[lk[i]] == XLB_SYMBOL ? XLB_U32 : l->schema.types[lk[i]];
+        uint8_t b = r->schema.types[rk[i]] == XLB_SYMBOL ? XLB_U32 : r->schema.types[rk[i]];
+        if (a != b) xlb_fail(XLB_ERR_TYPE, "join key %u: type mismatch", i);
+    }
+    xlb_schema os = l->schema;
+    if (type == XLB_JOIN_INNER) {
+        if (l->schema.arity + r->schema.arity > XLB_MAX_ARITY) xlb_fail(XLB_ERR_UNSUPPORTED, "join output arity above %u", XLB_MAX_ARITY);
+        for (uint32_t i = 0; i < r->schema.arity; ++i) os.types[os.arity++] = r->schema.types[i];
+    }
+    bool empty = l->rows == 0 || (r->rows == 0 && type != XLB_JOIN_ANTI);
+    if (empty) {
+        *out = rel_empty(c, os);
+        (*out)->canonical = false;
+    } else {
+        if (l->rows >= (1ull << 32)) xlb_fail(XLB_ERR_CAPACITY, "join probe side exceeds the 2^32 row limit");
+        ops_rel_columns(c, l);
+        ops_rel_columns(c, r);
+        // build side: rows ordered by key word (stable, so equal keys keep right-row order)
+        Buf rkeys = join_keys(c, r, rk, nk);
+        Buf ridx = make_buf(c, r->rows * 4);
+        if (r->rows) {
+            iota_k<<<grid_for(c, r->rows), BLOCK, 0, c->stream>>>(ridx->as<uint32_t>(), r->rows);
+            check_launch(c, "iota");
+            radix_sort(c, rkeys, &ridx, r->rows);
+        }
+        Index ix = ops_index_build(c, rkeys, r->rows, 0, ridx);
+        Buf lkeys = join_keys(c, l, lk, nk);
+        Keys lrows;
+        lrows.n = l->rows;
+        lrows.buf = make_buf(c, l->rows * 8);
+        iota64_k<<<grid_for(c, l->rows), BLOCK, 0, c->stream>>>(lrows.buf->as<uint64_t>(), l->rows);
+        check_launch(c, "iota64");
+        if (type == XLB_JOIN_INNER) {
+            Keys pairs = ops_join_expand(c, lrows, SRC_LO, lkeys->as<uint64_t>(), ix, SRC_LO, SRC_OTHER);
+            std::unique_ptr<xlb_rel> o(new xlb_rel);
+            o->ctx = c;
+            o->schema = os;
+            o->rows = pairs.n;
+            for (uint32_t i = 0; i < os.arity; ++i) {
+                bool left = i < l->schema.arity;
+                const xlb_rel* src = left ? l : r;
+                uint32_t sc = left ? i : i - l->schema.arity;
+                uint32_t w = type_width(os.types[i]);
+                o->cols[i] = make_buf(c, pairs.n * w);
+                if (!pairs.n) continue;
+                if (w == 4) gather_pair_k<uint32_t><<<grid_for(c, pairs.n), BLOCK, 0, c->stream>>>(src->cols[sc]->as<uint32_t>(), pairs.ptr(), left ? 0 : 1, o->cols[i]->as<uint32_t>(), pairs.n);
+                else gather_pair_k<uint64_t><<<grid_for(c, pairs.n), BLOCK, 0, c->stream>>>(src->cols[sc]->as<uint64_t>(), pairs.ptr(), left ? 0 : 1, o->cols[i]->as<uint64_t>(), pairs.n);
+                check_launch(c, "gather_pair");
+            }
+            *out = o.release();
+        } else {
+            Buf match = ops_probe_match(c, lrows, SRC_LO, lkeys->as<uint64_t>(), ix);
+            Buf sel = make_buf(c, l->rows * 4);
+            uint64_t m = select(c, PredFlag{match->as<uint64_t>(), type == XLB_JOIN_SEMI}, EmitIndex{sel->as<uint32_t>()}, l->rows);
+            *out = gather_rel(c, l, sel->as<uint32_t>(), m);
+        }
+    }
+    check_dev_status(c);
+    API_END()
+}

@@ -1,0 +1,63 @@
+// Host-level operations on device key arrays: the vocabulary the executor is written in.
+// Implemented in xlb_ops.cu on top of the kernels of xlb_kernels.cuh.
+#pragma once
+#include "xlb_common.cuh"
+
+// A bag or set of rows of at most two 32-bit columns, one u64 per row:
+// arity 2 -> (c0 << 32) | c1, arity 1 -> c0 in the low half.
+struct Keys {
+    Buf buf;
+    uint64_t n = 0;
+    const uint64_t* ptr() const { return buf ? buf->as<uint64_t>() : nullptr; }
+};
+
+// Column source selectors for remap / expand: which 32-bit value lands in an output half.
+enum Src { SRC_HI = 0, SRC_LO = 1, SRC_OTHER = 2, SRC_ZERO = 3 };
+
+// Join index over a relation sorted by its join key: distinct keys live in an open-addressing
+// table whose slots carry (start, length) of the key's run in `S`.
+struct Index {
+    Buf S;             // sorted u64 words; join key = S[i] >> key_shift
+    Buf pay;           // optional 32-bit payload per row; when absent the payload is the low half of S
+    uint64_t n = 0;    // rows
+    int key_shift = 32;
+    Buf table;         // ulonglong2 slots
+    uint64_t mask = 0; // capacity - 1
+    uint64_t nkeys = 0;
+};
+
+Keys ops_rel_packed(xlb_ctx* c, const xlb_rel* r);             // packed view (cached on the relation)
+void ops_rel_columns(xlb_ctx* c, const xlb_rel* r);            // materialise column view (cached)
+xlb_rel* ops_rel_from_keys(xlb_ctx* c, const xlb_schema& s, Keys k, bool canonical);
+
+Keys ops_copy(xlb_ctx* c, const Keys& in);
+Keys ops_concat(xlb_ctx* c, const std::vector<Keys>& parts);
+Keys ops_slice(xlb_ctx* c, const Keys& in, uint64_t lo, uint64_t hi);  // copy of rows [lo, hi)
+void ops_sort(xlb_ctx* c, Keys& k);                              // ascending
+void ops_dedup_sorted(xlb_ctx* c, Keys& k);                      // sorted -> sorted unique
+Keys ops_diff(xlb_ctx* c, const Keys& a, const Keys& b);         // sorted unique a \ sorted unique b
+Keys ops_merge_disjoint(xlb_ctx* c, const Keys& a, const Keys& b);
+Keys ops_union(xlb_ctx* c, const Keys& a, const Keys& b);        // sorted unique a U b
+Keys ops_remap(xlb_ctx* c, const Keys& in, int hi_src, int lo_src);
+// rows where half(lhs_src) <cmp> (rhs_is_const ? rhs : half(rhs))
+Keys ops_filter(xlb_ctx* c, const Keys& in, uint32_t cmp, int lhs_src, bool rhs_is_const, uint64_t rhs);
+
+Index ops_index_build(xlb_ctx* c, Buf S, uint64_t n, int key_shift, Buf pay);
+// Probe `bag` (key = the half named by keysel, or pkeys[i] when given) and expand every match:
+// out row = (pick(hi_src) << 32) | pick(lo_src) with SRC_OTHER = the build row's payload.
+Keys ops_join_expand(xlb_ctx* c, const Keys& bag, int keysel, const uint64_t* pkeys, const Index& ix, int hi_src, int lo_src);
+// match[i] != 0 flags for semi / anti joins (device array of bag.n words)
+Buf ops_probe_match(xlb_ctx* c, const Keys& bag, int keysel, const uint64_t* pkeys, const Index& ix);
+
+// owner rank of every row by the half `keysel`; stable partition into `world` runs.
+// counts_out[world] (host) receives the run lengths; returns the partitioned copy.
+Keys ops_partition_by_owner(xlb_ctx* c, const Keys& in, int keysel, uint32_t world, std::vector<uint64_t>& counts_out);
+
+// Per-phase event timing (XLB_FLAG_PROFILE): bracket with phase_begin / phase_end.
+struct PhaseTimer {
+    xlb_ctx* c;
+    double* acc;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    PhaseTimer(xlb_ctx* ctx, double* into);
+    ~PhaseTimer();
+};
