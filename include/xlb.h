@@ -84,7 +84,7 @@ typedef struct xlb_config {
 } xlb_config;
 
 #define XLB_FLAG_PROFILE 1u        /* time every phase with CUDA events (RuntimeConfig.profile)     */
-#define XLB_FLAG_UNFUSED_SETOPS 2u /* use separate difference and union passes instead of the fused one */
+
 
 /* ---- context ------------------------------------------------------------------------------ */
 
@@ -221,9 +221,6 @@ typedef struct xlb_run_stats {
     double ms_setops;          /* dedup + difference + union                                   */
     double ms_exchange;        /* partition + all-to-all + termination vote (multi-rank)       */
     uint64_t exchange_bytes;   /* bytes this rank sent to other ranks                          */
-    double ms_sort_kernel;     /* device time inside the radix scatter kernels (PROFILE flag)  */
-    uint64_t sort_kernel_bytes;/* algorithmic bytes those launches moved (PROFILE flag)        */
-    uint64_t sort_kernel_launches;
 } xlb_run_stats;
 
 /* ---- executor: Executor::{register_relation, put_relation, store().get, execute_plan} ----- */
@@ -241,6 +238,21 @@ xlb_status xlb_store_remove(xlb_ctx* ctx, const char* name);
 /* execute_plan(&ExecutionPlan) (executor/mod.rs:1404-1469); recursive SCCs run the semi-naive
  * loop of execute_recursive_scc (executor/recursive.rs:447-957).  `stats` may be NULL. */
 xlb_status xlb_execute_plan(xlb_ctx* ctx, const xlb_plan* plan, xlb_run_stats* stats);
+
+/* ---- per-kernel timing -------------------------------------------------------------------- */
+/* Counterpart of the reference's feature-gated per-phase CUDA-event timing
+ * (crates/xlog-runtime/src/profiler.rs:355-640, feature `wcoj-phase-timing`): brackets every
+ * launch of the named kernel ("*" = every kernel, NULL = off) with CUDA events on the launching
+ * stream.  xlb_profile_read waits for the stream, then reports per kernel its launches, device
+ * time and algorithmic bytes since xlb_profile_enable. */
+typedef struct xlb_kernel_profile {
+    char name[32];
+    uint64_t launches;
+    uint64_t bytes;
+    double ms;
+} xlb_kernel_profile;
+xlb_status xlb_profile_enable(xlb_ctx* ctx, const char* kernel);
+xlb_status xlb_profile_read(xlb_ctx* ctx, xlb_kernel_profile* out, uint32_t cap, uint32_t* n);
 
 /* ---- several GPUs: one process and one context per GPU ------------------------------------ */
 /* No counterpart in the reference (docs/architecture/multi-gpu.mdx:45-54 marks distributed

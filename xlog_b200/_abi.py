@@ -23,7 +23,6 @@ NODE_SCAN, NODE_FILTER, NODE_PROJECT, NODE_JOIN, NODE_UNION = 1, 2, 3, 4, 5
 EQ, NE, LT, LE, GT, GE = range(6)
 
 FLAG_PROFILE = 1
-FLAG_UNFUSED_SETOPS = 2
 
 
 class Schema(C.Structure):
@@ -78,8 +77,11 @@ class RunStats(C.Structure):
                 ("candidate_tuples", C.c_uint64), ("kernel_launches", C.c_uint64),
                 ("peak_bytes", C.c_uint64), ("ms_total", C.c_double), ("ms_join", C.c_double),
                 ("ms_sort", C.c_double), ("ms_setops", C.c_double), ("ms_exchange", C.c_double),
-                ("exchange_bytes", C.c_uint64), ("ms_sort_kernel", C.c_double),
-                ("sort_kernel_bytes", C.c_uint64), ("sort_kernel_launches", C.c_uint64)]
+                ("exchange_bytes", C.c_uint64)]
 
     def as_dict(self):
         return {k: getattr(self, k) for k, _ in self._fields_}
+
+
+class KernelProfile(C.Structure):
+    _fields_ = [("name", C.c_char * 32), ("launches", C.c_uint64), ("bytes", C.c_uint64), ("ms", C.c_double)]

@@ -66,12 +66,29 @@ struct xlb_ctx {
     struct IndexCache* indexes = nullptr;
     Comm* comm = nullptr;
     uint32_t rank = 0, world = 1;
-    // profiling of the radix scatter kernel (XLB_FLAG_PROFILE)
-    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> sort_events;
-    uint64_t sort_bytes = 0;
-    double ms_sort_kernel = 0;
-    uint64_t sort_launches = 0;
+    // per-kernel event timing (xlb_profile_enable)
+    struct ProfEntry {
+        uint64_t launches = 0, bytes = 0;
+        double ms = 0;
+        std::vector<std::pair<cudaEvent_t, cudaEvent_t>> pending;
+    };
+    std::map<std::string, ProfEntry> prof;
+    std::string prof_filter;  // "" = off, "*" = every kernel, else one kernel name
+    ProfEntry* prof_open = nullptr;
+    cudaEvent_t prof_e0 = nullptr;
 };
+
+// Bracket one launch with CUDA events on the launching stream when its kernel is profiled.
+inline void prof_begin(xlb_ctx* c, const char* name, uint64_t bytes) {
+    if (c->prof_filter.empty()) return;
+    if (c->prof_filter != "*" && c->prof_filter != name) return;
+    auto& e = c->prof[name];
+    e.launches++;
+    e.bytes += bytes;
+    cudaEventCreate(&c->prof_e0);
+    cudaEventRecord(c->prof_e0, c->stream);
+    c->prof_open = &e;
+}
 
 // A device allocation charged to the context's budget (GpuMemoryManager::alloc with a
 // MemoryBudget, crates/xlog-cuda/src/memory.rs:57-1350).  Freed stream-ordered.
@@ -104,6 +121,13 @@ inline Buf make_buf(xlb_ctx* c, uint64_t bytes) { return std::make_shared<DevBuf
 
 inline void check_launch(xlb_ctx* c, const char* what) {
     c->launches++;
+    if (c->prof_open) {
+        cudaEvent_t e1;
+        cudaEventCreate(&e1);
+        cudaEventRecord(e1, c->stream);
+        c->prof_open->pending.emplace_back(c->prof_e0, e1);
+        c->prof_open = nullptr;
+    }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) xlb_fail(XLB_ERR_CUDA, "launch of %s failed: %s", what, cudaGetErrorString(e));
 }

@@ -681,9 +681,6 @@ extern "C" xlb_status xlb_execute_plan(xlb_ctx* c, const xlb_plan* plan, xlb_run
     cudaEvent_t e0 = nullptr, e1 = nullptr;
     uint64_t launches0 = c->launches;
     c->peak = c->allocated;
-    c->ms_sort_kernel = 0;
-    c->sort_bytes = 0;
-    c->sort_launches = 0;
     xlb_status result = XLB_OK;
     try {
         CUDA_OK(cudaSetDevice(c->device));
@@ -720,9 +717,6 @@ extern "C" xlb_status xlb_execute_plan(xlb_ctx* c, const xlb_plan* plan, xlb_run
     if (e1) cudaEventDestroy(e1);
     rs.st.kernel_launches = c->launches - launches0;
     rs.st.peak_bytes = c->peak;
-    rs.st.ms_sort_kernel = c->ms_sort_kernel;
-    rs.st.sort_kernel_bytes = c->sort_bytes;
-    rs.st.sort_kernel_launches = c->sort_launches;
     if (stats && result == XLB_OK) *stats = rs.st;
     return result;
 }

@@ -30,6 +30,24 @@ __device__ __forceinline__ unsigned lanemask_lt() {
     return m;
 }
 
+// Lanes of the warp whose 8-bit value equals this lane's: eight ballots.  (The match.any
+// instruction does the same but its cost grows with the number of distinct values in the warp,
+// and radix digits are close to all-distinct.)
+__device__ __forceinline__ unsigned match_digit(unsigned d) {
+#ifdef XLB_RANK_MATCH
+    return __match_any_sync(FULL, d);
+#else
+    unsigned peers = FULL;
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+        bool bit = (d >> b) & 1u;
+        unsigned vote = __ballot_sync(FULL, bit);
+        peers &= bit ? vote : ~vote;
+    }
+    return peers;
+#endif
+}
+
 __device__ __forceinline__ void set_status(DevStatus* st, unsigned code, unsigned where, unsigned long long detail) {
     if (atomicCAS(&st->code, 0u, code) == 0u) {
         st->where = where;
@@ -154,15 +172,19 @@ void exclusive_scan(xlb_ctx* c, Load load, uint64_t n, Tout* out, Tout* d_total)
     }
     uint64_t ntiles = (n + SCAN_TILE - 1) / SCAN_TILE;
     if (ntiles == 1) {
+        prof_begin(c, "scan_apply", 0);
         scan_apply_k<Load, Tout><<<1, BLOCK, 0, c->stream>>>(load, n, nullptr, out, d_total);
         check_launch(c, "scan_apply");
         return;
     }
     Buf sums = make_buf(c, ntiles * sizeof(Tout));
+    prof_begin(c, "scan_reduce", 0);
     scan_reduce_k<Load, Tout><<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(load, n, sums->as<Tout>());
     check_launch(c, "scan_reduce");
+    prof_begin(c, "scan_spine", 0);
     scan_spine_k<Tout><<<1, 1024, 0, c->stream>>>(sums->as<Tout>(), ntiles, d_total);
     check_launch(c, "scan_spine");
+    prof_begin(c, "scan_apply", 0);
     scan_apply_k<Load, Tout><<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(load, n, sums->as<Tout>(), out, nullptr);
     check_launch(c, "scan_apply");
 }
@@ -213,6 +235,7 @@ uint64_t select(xlb_ctx* c, Pred pred, Emit emit, uint64_t n) {
     Buf total = make_buf(c, 8);
     unsigned long long h;
     if (ntiles == 1) {
+        prof_begin(c, "select_write", 0);
         select_write_k<Pred, Emit><<<1, BLOCK, 0, c->stream>>>(pred, emit, n, nullptr, total->as<uint64_t>());
         check_launch(c, "select_write");
         read_words(c, total->p, 1, &h);
@@ -220,9 +243,11 @@ uint64_t select(xlb_ctx* c, Pred pred, Emit emit, uint64_t n) {
     }
     Buf counts = make_buf(c, ntiles * 4);
     Buf offs = make_buf(c, ntiles * 8);
+    prof_begin(c, "select_count", 0);
     select_count_k<Pred><<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(pred, n, counts->as<uint32_t>());
     check_launch(c, "select_count");
     exclusive_scan<LoadU32, uint64_t>(c, LoadU32{counts->as<uint32_t>()}, ntiles, offs->as<uint64_t>(), total->as<uint64_t>());
+    prof_begin(c, "select_write", 0);
     select_write_k<Pred, Emit><<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(pred, emit, n, offs->as<uint64_t>(), nullptr);
     check_launch(c, "select_write");
     read_words(c, total->p, 1, &h);
@@ -267,9 +292,16 @@ inline unsigned grid_for(xlb_ctx* c, uint64_t n, int per_block = BLOCK) {
 }
 
 // ------------------------------------------------------------------------------ radix sort
-constexpr int SORT_IPT = 16;
-constexpr int SORT_TILE = BLOCK * SORT_IPT;  // 4096 keys per tile
-constexpr int SORT_WARPS = BLOCK / 32;
+#ifndef XLB_SORT_THREADS
+#define XLB_SORT_THREADS 256
+#endif
+#ifndef XLB_SORT_IPT
+#define XLB_SORT_IPT 16
+#endif
+constexpr int SORT_THREADS = XLB_SORT_THREADS;
+constexpr int SORT_IPT = XLB_SORT_IPT;
+constexpr int SORT_TILE = SORT_THREADS * SORT_IPT;  // keys per tile
+constexpr int SORT_WARPS = SORT_THREADS / 32;
 
 // OR and AND of all keys in one read: a digit whose bits never vary needs no pass.
 __global__ void __launch_bounds__(BLOCK) radix_bits_k(const uint64_t* __restrict__ keys, uint64_t n, unsigned long long* __restrict__ or_and /* [2] */) {
@@ -290,15 +322,60 @@ __global__ void __launch_bounds__(BLOCK) radix_bits_k(const uint64_t* __restrict
     }
 }
 
+// Histograms of all eight digits in one read of the keys.  A digit on which a whole warp agrees
+// (constant high bytes are the common case) costs one shared-memory add per warp.
+__global__ void __launch_bounds__(BLOCK) radix_upfront_k(const uint64_t* __restrict__ keys, uint64_t n, unsigned int* __restrict__ ghist /* 8*256 */) {
+    __shared__ unsigned int sh[8 * 256];
+    for (int i = threadIdx.x; i < 8 * 256; i += BLOCK) sh[i] = 0;
+    __syncthreads();
+    const unsigned lane = lane_id();
+    const uint64_t stride = (uint64_t)gridDim.x * BLOCK;
+    for (uint64_t base = (uint64_t)blockIdx.x * BLOCK + (threadIdx.x & ~31u); base < n; base += stride) {
+        uint64_t i = base + lane;
+        bool ok = i < n;
+        uint64_t k = ok ? keys[i] : 0;
+        unsigned live = __ballot_sync(FULL, ok);
+        unsigned first_lane = __ffs(live) - 1;
+#pragma unroll
+        for (int d = 0; d < 8; ++d) {
+            unsigned dig = (unsigned)((k >> (8 * d)) & 255);
+            unsigned first = __shfl_sync(FULL, dig, first_lane);
+            bool uni = __all_sync(FULL, !ok || dig == first);
+            if (uni) {
+                if (lane == first_lane) atomicAdd(&sh[d * 256 + first], (unsigned)__popc(live));
+            } else if (ok) {
+                atomicAdd(&sh[d * 256 + dig], 1u);
+            }
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 8 * 256; i += BLOCK)
+        if (sh[i]) atomicAdd(&ghist[i], sh[i]);
+}
+
+// Exclusive scan of each digit histogram (the digit bases of the sweep) and, per digit, whether
+// more than one bin is occupied.
+__global__ void __launch_bounds__(BLOCK) radix_bases_k(const unsigned int* __restrict__ ghist, unsigned long long n, unsigned int* __restrict__ bases, unsigned long long* __restrict__ varies) {
+    __shared__ unsigned int sm[33];
+    for (int d = 0; d < 8; ++d) {
+        unsigned v = ghist[d * 256 + threadIdx.x];
+        unsigned tot;
+        unsigned ex = block_exclusive_scan<unsigned>(v, &tot, sm);
+        bases[d * 256 + threadIdx.x] = ex;
+        int constant = __syncthreads_or(v == n);
+        if (threadIdx.x == 0) varies[d] = constant ? 0ull : 1ull;
+    }
+}
+
 // Per-tile histogram of one digit: hist[d * ntiles + tile].
 __global__ void __launch_bounds__(BLOCK) radix_tile_hist_k(const uint64_t* __restrict__ keys, uint64_t n, int shift, uint32_t* __restrict__ hist, uint32_t ntiles) {
-    __shared__ unsigned int sh[SORT_WARPS][256];
-    for (int i = threadIdx.x; i < SORT_WARPS * 256; i += BLOCK) (&sh[0][0])[i] = 0;
+    __shared__ unsigned int sh[BLOCK / 32][256];
+    for (int i = threadIdx.x; i < (BLOCK / 32) * 256; i += BLOCK) (&sh[0][0])[i] = 0;
     __syncthreads();
     uint64_t base = (uint64_t)blockIdx.x * SORT_TILE;
     unsigned warp = threadIdx.x >> 5, lane = lane_id();
 #pragma unroll
-    for (int k = 0; k < SORT_IPT; ++k) {
+    for (int k = 0; k < SORT_TILE / BLOCK; ++k) {
         uint64_t i = base + (uint64_t)k * BLOCK + threadIdx.x;
         // keys past the end count as digit 256 (none): match on 9 bits so they group apart
         unsigned d = i < n ? (unsigned)((keys[i] >> shift) & 255) : 256u;
@@ -309,30 +386,53 @@ __global__ void __launch_bounds__(BLOCK) radix_tile_hist_k(const uint64_t* __res
     __syncthreads();
     unsigned s = 0;
 #pragma unroll
-    for (int w = 0; w < SORT_WARPS; ++w) s += sh[w][threadIdx.x];
+    for (int w = 0; w < BLOCK / 32; ++w) s += sh[w][threadIdx.x];
     hist[(uint64_t)threadIdx.x * ntiles + blockIdx.x] = s;
 }
 
 // Stable scatter of one tile by one digit.  `offs` is the exclusive scan of the per-tile
 // histograms in (digit-major, tile-minor) order, i.e. the global position of the first key of
 // digit d of this tile.
-template <bool HAS_VALUES>
-__global__ void __launch_bounds__(BLOCK) radix_scatter_k(const uint64_t* __restrict__ keys_in, uint64_t* __restrict__ keys_out,
-                                                          const uint32_t* __restrict__ vals_in, uint32_t* __restrict__ vals_out,
-                                                          uint64_t n, int shift, const uint32_t* __restrict__ offs, uint32_t ntiles) {
-    __shared__ uint64_t skeys[SORT_TILE];
-    __shared__ unsigned int whist[SORT_WARPS][256];
-    __shared__ unsigned int tile_start[256];
-    __shared__ unsigned int glob_off[256];
-    __shared__ unsigned int scan_sm[33];
+//
+// LOOKBACK = false: `offs` is the exclusive scan of the per-tile histograms in (digit-major,
+// tile-minor) order, i.e. the global position of the first key of digit d of this tile.
+// LOOKBACK = true ("one sweep"): `offs` holds the 256 global digit bases; tiles take their
+// number from an atomic counter, publish their digit counts in `status` and obtain the sum over
+// all earlier tiles by a decoupled look-back, so the pass reads and writes every key once.
+// A tile only waits for tiles that took an earlier number, which are running already; every
+// wait is bounded and reports XLB_ERR_TIMEOUT through `dst` instead of spinning for ever.
+constexpr unsigned LB_FLAG_AGG = 1u << 30, LB_FLAG_INC = 2u << 30, LB_MASK = (1u << 30) - 1;
+constexpr unsigned LB_SPIN_LIMIT = 1u << 22;
 
+#ifndef XLB_SORT_MINB
+#define XLB_SORT_MINB 4
+#endif
+template <bool HAS_VALUES, bool LOOKBACK>
+__global__ void __launch_bounds__(SORT_THREADS, XLB_SORT_MINB) radix_scatter_k(const uint64_t* __restrict__ keys_in, uint64_t* __restrict__ keys_out,
+                                                          const uint32_t* __restrict__ vals_in, uint32_t* __restrict__ vals_out,
+                                                          uint64_t n, int shift, const uint32_t* __restrict__ offs, uint32_t ntiles,
+                                                          unsigned int* __restrict__ tile_counter, volatile unsigned int* status, DevStatus* dst) {
+    extern __shared__ __align__(16) unsigned char sort_smem[];
+    uint64_t* skeys = reinterpret_cast<uint64_t*>(sort_smem);
+    unsigned int (*whist)[256] = reinterpret_cast<unsigned int (*)[256]>(sort_smem + SORT_TILE * 8);
+    unsigned int* tile_start = reinterpret_cast<unsigned int*>(sort_smem + SORT_TILE * 8 + SORT_WARPS * 1024);
+    unsigned int* glob_off = tile_start + 256;
+    unsigned int* scan_sm = glob_off + 256;
+
+    __shared__ unsigned int tile_s;
     const unsigned lane = lane_id(), warp = threadIdx.x >> 5;
-    const uint64_t tile_base = (uint64_t)blockIdx.x * SORT_TILE;
+    unsigned tile = blockIdx.x;
+    if (LOOKBACK) {
+        if (threadIdx.x == 0) tile_s = atomicAdd(tile_counter, 1u);
+        __syncthreads();
+        tile = tile_s;
+    }
+    const uint64_t tile_base = (uint64_t)tile * SORT_TILE;
     const uint64_t rem = n - tile_base;
     const unsigned valid = rem < (uint64_t)SORT_TILE ? (unsigned)rem : (unsigned)SORT_TILE;
 
-    for (int i = threadIdx.x; i < SORT_WARPS * 256; i += BLOCK) (&whist[0][0])[i] = 0;
-    glob_off[threadIdx.x] = offs[(uint64_t)threadIdx.x * ntiles + blockIdx.x];
+    for (int i = threadIdx.x; i < SORT_WARPS * 256; i += SORT_THREADS) (&whist[0][0])[i] = 0;
+    if (!LOOKBACK && threadIdx.x < 256) glob_off[threadIdx.x] = offs[(uint64_t)threadIdx.x * ntiles + tile];
 
     // warp-striped load: key j of lane l sits at warp*512 + j*32 + l (memory order = (j, l))
     uint64_t key[SORT_IPT];
@@ -345,12 +445,41 @@ __global__ void __launch_bounds__(BLOCK) radix_scatter_k(const uint64_t* __restr
     }
     __syncthreads();
 
+#ifdef XLB_RANK_PIPE
+    // Rank every key among the keys of its warp with the same digit, in memory order.  Three
+    // unrolled phases keep the shared-memory latency off the critical path: all matches, then one
+    // returning shared atomic per (round, digit group) issued back to back (the unit applies one
+    // warp's atomics in program order, so the returned value is the count of earlier rounds),
+    // then all broadcasts.
+    unsigned peers[SORT_IPT];
+#pragma unroll
+    for (int j = 0; j < SORT_IPT; ++j) {
+        unsigned t = wbase + j * 32 + lane;
+        unsigned d = t < valid ? (unsigned)((key[j] >> shift) & 255) : 255u;
+        peers[j] = match_digit(d);
+    }
+    unsigned before[SORT_IPT];
+#pragma unroll
+    for (int j = 0; j < SORT_IPT; ++j) {
+        unsigned t = wbase + j * 32 + lane;
+        unsigned d = t < valid ? (unsigned)((key[j] >> shift) & 255) : 255u;
+        before[j] = 0;
+        if (lane == (unsigned)(__ffs(peers[j]) - 1)) before[j] = atomicAdd(&whist[warp][d], (unsigned)__popc(peers[j]));
+    }
+#pragma unroll
+    for (int j = 0; j < SORT_IPT; ++j) {
+        unsigned b = __shfl_sync(FULL, before[j], __ffs(peers[j]) - 1);
+        rank[j] = (unsigned short)(b + __popc(peers[j] & lanemask_lt()));
+    }
+    __syncthreads();
+
+#else
     // rank every key among the keys of its warp with the same digit, in memory order
 #pragma unroll
     for (int j = 0; j < SORT_IPT; ++j) {
         unsigned t = wbase + j * 32 + lane;
         unsigned d = t < valid ? (unsigned)((key[j] >> shift) & 255) : 255u;
-        unsigned peers = __match_any_sync(FULL, d);
+        unsigned peers = match_digit(d);
         unsigned leader = __ffs(peers) - 1;
         unsigned before = 0;
         if (lane == leader) {
@@ -363,18 +492,52 @@ __global__ void __launch_bounds__(BLOCK) radix_scatter_k(const uint64_t* __restr
     }
     __syncthreads();
 
+#endif
     // per digit: exclusive prefix over warps, then exclusive prefix over digits
     {
-        unsigned d = threadIdx.x, run = 0;
+        const bool dig = threadIdx.x < 256;
+        unsigned d = threadIdx.x & 255, run = 0;
+        if (dig) {
 #pragma unroll
-        for (int w = 0; w < SORT_WARPS; ++w) {
-            unsigned v = whist[w][d];
-            whist[w][d] = run;
-            run += v;
+            for (int w = 0; w < SORT_WARPS; ++w) {
+                unsigned v = whist[w][d];
+                whist[w][d] = run;
+                run += v;
+            }
+        }
+        if (LOOKBACK && dig) {
+            // keys past the end were counted under digit 255: take them out of the published count
+            unsigned cnt = run - (d == 255 ? (unsigned)SORT_TILE - valid : 0u);
+            volatile unsigned int* mine = status + (uint64_t)tile * 256 + d;
+            unsigned excl = 0;
+            if (tile == 0) {
+                *mine = cnt | LB_FLAG_INC;
+            } else {
+                *mine = cnt | LB_FLAG_AGG;
+                int64_t t = (int64_t)tile - 1;
+                unsigned spins = 0;
+                while (t >= 0) {
+                    unsigned v = status[(uint64_t)t * 256 + d];
+                    unsigned f = v & ~LB_MASK;
+                    if (f == 0) {
+                        if (++spins > LB_SPIN_LIMIT) {
+                            set_status(dst, XLB_ERR_TIMEOUT, 2, tile);
+                            break;
+                        }
+                        __nanosleep(20);
+                        continue;
+                    }
+                    excl += v & LB_MASK;
+                    if (f == LB_FLAG_INC) break;
+                    --t;
+                }
+                *mine = (excl + cnt) | LB_FLAG_INC;
+            }
+            glob_off[d] = offs[d] + excl;
         }
         unsigned tot;
         unsigned ex = block_exclusive_scan<unsigned>(run, &tot, scan_sm);
-        tile_start[d] = ex;
+        if (dig) tile_start[d] = ex;
     }
     __syncthreads();
 
@@ -389,7 +552,7 @@ __global__ void __launch_bounds__(BLOCK) radix_scatter_k(const uint64_t* __restr
     }
     __syncthreads();
     // coalesced runs: consecutive shared-memory slots of one digit go to consecutive addresses
-    for (unsigned i = threadIdx.x; i < valid; i += BLOCK) {
+    for (unsigned i = threadIdx.x; i < valid; i += SORT_THREADS) {
         uint64_t k = skeys[i];
         unsigned d = (unsigned)((k >> shift) & 255);
         keys_out[(uint64_t)glob_off[d] + (i - tile_start[d])] = k;
@@ -409,11 +572,24 @@ __global__ void __launch_bounds__(BLOCK) radix_scatter_k(const uint64_t* __restr
             }
         }
         __syncthreads();
-        for (unsigned i = threadIdx.x; i < valid; i += BLOCK) {
+        for (unsigned i = threadIdx.x; i < valid; i += SORT_THREADS) {
             unsigned d = sd[i];
             vals_out[(uint64_t)glob_off[d] + (i - tile_start[d])] = sv[i];
         }
     }
+}
+
+constexpr size_t SORT_SMEM = (size_t)SORT_TILE * 8 + SORT_WARPS * 1024 + 256 * 4 * 2 + 64 * 4;
+
+// The scatter kernel takes more than the 48 KB a launch gets by default: opt in once per process.
+inline void radix_sort_setup() {
+    static bool done = false;
+    if (done) return;
+    cudaFuncSetAttribute(radix_scatter_k<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SORT_SMEM);
+    cudaFuncSetAttribute(radix_scatter_k<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SORT_SMEM);
+    cudaFuncSetAttribute(radix_scatter_k<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SORT_SMEM);
+    cudaFuncSetAttribute(radix_scatter_k<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SORT_SMEM);
+    done = true;
 }
 
 struct SortPlan {
@@ -427,6 +603,7 @@ inline SortPlan plan_sort(xlb_ctx* c, const uint64_t* keys, uint64_t n) {
     Buf oa = make_buf(c, 16);
     CUDA_OK(cudaMemsetAsync(oa->p, 0, 8, c->stream));
     CUDA_OK(cudaMemsetAsync((char*)oa->p + 8, 0xFF, 8, c->stream));
+    prof_begin(c, "radix_bits", n * 8ull);
     radix_bits_k<<<grid_for(c, n, BLOCK * 8), BLOCK, 0, c->stream>>>(keys, n, oa->as<unsigned long long>());
     check_launch(c, "radix_bits");
     unsigned long long h[2];
@@ -442,37 +619,66 @@ inline SortPlan plan_sort(xlb_ctx* c, const uint64_t* keys, uint64_t n) {
 inline void radix_sort(xlb_ctx* c, Buf& keys, Buf* vals, uint64_t n) {
     if (n <= 1) return;
     if (n >= (1ull << 32)) xlb_fail(XLB_ERR_CAPACITY, "sort of %llu keys exceeds the 2^32 limit of one sort", (unsigned long long)n);
-    SortPlan p = plan_sort(c, keys->as<uint64_t>(), n);
-    if (p.npasses == 0) return;
+    radix_sort_setup();
     uint32_t ntiles = (uint32_t)((n + SORT_TILE - 1) / SORT_TILE);
     Buf tmpk = make_buf(c, n * 8);
     Buf tmpv = vals ? make_buf(c, n * 4) : Buf();
+    if (n < (1ull << 30)) {
+        // one sweep: a histogram read, then one read + one write of the keys per varying digit
+        Buf gh = make_buf(c, 8 * 256 * 4 * 2 + 64);  // histograms | bases | varies
+        unsigned int* ghist = gh->as<unsigned int>();
+        unsigned int* bases = ghist + 8 * 256;
+        unsigned long long* varies = (unsigned long long*)(bases + 8 * 256);
+        CUDA_OK(cudaMemsetAsync(ghist, 0, 8 * 256 * 4, c->stream));
+        prof_begin(c, "radix_upfront", n * 8ull);
+        radix_upfront_k<<<grid_for(c, n, BLOCK * 8), BLOCK, 0, c->stream>>>(keys->as<uint64_t>(), n, ghist);
+        check_launch(c, "radix_upfront");
+        prof_begin(c, "radix_bases", 0);
+        radix_bases_k<<<1, BLOCK, 0, c->stream>>>(ghist, n, bases, varies);
+        check_launch(c, "radix_bases");
+        unsigned long long v[8];
+        read_words(c, varies, 8, v);
+        int np = 0, digits[8];
+        for (int d = 0; d < 8; ++d)
+            if (v[d]) digits[np++] = d;
+        if (np == 0) return;
+        uint64_t status_words = (uint64_t)ntiles * 256;
+        Buf status = make_buf(c, (status_words * np + 8) * 4);  // per pass: tile status; then 8 tile counters
+        CUDA_OK(cudaMemsetAsync(status->p, 0, (status_words * np + 8) * 4, c->stream));
+        unsigned int* counters = status->as<unsigned int>() + status_words * np;
+        for (int q = 0; q < np; ++q) {
+            int d = digits[q];
+            unsigned int* st = status->as<unsigned int>() + status_words * q;
+            prof_begin(c, "radix_scatter", n * (vals ? 24ull : 16ull));
+            if (vals)
+                radix_scatter_k<true, true><<<ntiles, SORT_THREADS, SORT_SMEM, c->stream>>>(keys->as<uint64_t>(), tmpk->as<uint64_t>(), (*vals)->as<uint32_t>(), tmpv->as<uint32_t>(), n, 8 * d, bases + d * 256, ntiles, counters + q, st, c->d_status);
+            else
+                radix_scatter_k<false, true><<<ntiles, SORT_THREADS, SORT_SMEM, c->stream>>>(keys->as<uint64_t>(), tmpk->as<uint64_t>(), nullptr, nullptr, n, 8 * d, bases + d * 256, ntiles, counters + q, st, c->d_status);
+            check_launch(c, "radix_scatter");
+            std::swap(keys, tmpk);
+            if (vals) std::swap(*vals, tmpv);
+        }
+        return;
+    }
+    // 2^30 keys and more: per-tile histograms, a scan, then the scatter (counts exceed the
+    // 30 bits of a look-back status word)
+    SortPlan p = plan_sort(c, keys->as<uint64_t>(), n);
+    if (p.npasses == 0) return;
     Buf hist = make_buf(c, (uint64_t)256 * ntiles * 4);
     Buf offs = make_buf(c, (uint64_t)256 * ntiles * 4);
     Buf total = make_buf(c, 4);
-    bool prof = (c->flags & XLB_FLAG_PROFILE) != 0;
     for (int q = 0; q < p.npasses; ++q) {
         int shift = p.shifts[q];
+        prof_begin(c, "radix_tile_hist", n * 8ull);
         radix_tile_hist_k<<<ntiles, BLOCK, 0, c->stream>>>(keys->as<uint64_t>(), n, shift, hist->as<uint32_t>(), ntiles);
         check_launch(c, "radix_tile_hist");
         exclusive_scan<LoadU32, uint32_t>(c, LoadU32{hist->as<uint32_t>()}, (uint64_t)256 * ntiles, offs->as<uint32_t>(), total->as<uint32_t>());
-        cudaEvent_t e0 = nullptr, e1 = nullptr;
-        if (prof) {
-            CUDA_OK(cudaEventCreate(&e0));
-            CUDA_OK(cudaEventCreate(&e1));
-            CUDA_OK(cudaEventRecord(e0, c->stream));
-        }
+        prof_begin(c, "radix_scatter", n * (vals ? 24ull : 16ull));
         if (vals)
-            radix_scatter_k<true><<<ntiles, BLOCK, 0, c->stream>>>(keys->as<uint64_t>(), tmpk->as<uint64_t>(), (*vals)->as<uint32_t>(), tmpv->as<uint32_t>(), n, shift, offs->as<uint32_t>(), ntiles);
+            radix_scatter_k<true, false><<<ntiles, SORT_THREADS, SORT_SMEM, c->stream>>>(keys->as<uint64_t>(), tmpk->as<uint64_t>(), (*vals)->as<uint32_t>(), tmpv->as<uint32_t>(), n, shift, offs->as<uint32_t>(), ntiles, nullptr, nullptr, c->d_status);
         else
-            radix_scatter_k<false><<<ntiles, BLOCK, 0, c->stream>>>(keys->as<uint64_t>(), tmpk->as<uint64_t>(), nullptr, nullptr, n, shift, offs->as<uint32_t>(), ntiles);
+            radix_scatter_k<false, false><<<ntiles, SORT_THREADS, SORT_SMEM, c->stream>>>(keys->as<uint64_t>(), tmpk->as<uint64_t>(), nullptr, nullptr, n, shift, offs->as<uint32_t>(), ntiles, nullptr, nullptr, c->d_status);
         check_launch(c, "radix_scatter");
-        if (prof) {
-            CUDA_OK(cudaEventRecord(e1, c->stream));
-            c->sort_events.emplace_back(e0, e1);
-            c->sort_bytes += n * (vals ? 24ull : 16ull);
-            c->sort_launches++;
-        }
         std::swap(keys, tmpk);
         if (vals) std::swap(*vals, tmpv);
     }
@@ -588,8 +794,10 @@ inline Buf set_difference(xlb_ctx* c, const uint64_t* A, uint64_t na, const uint
     uint64_t ntiles = (na + nb + MP_TILE - 1) / MP_TILE;
     Buf splits = make_buf(c, (ntiles + 1) * 8);
     Buf keep = make_buf(c, na);
+    prof_begin(c, "mp_partition", 0);
     mp_partition_k<<<(unsigned)((ntiles + 1 + 127) / 128), 128, 0, c->stream>>>(A, na, B, nb, splits->as<uint64_t>(), ntiles);
     check_launch(c, "mp_partition");
+    prof_begin(c, "mp_diff", (na + nb) * 8ull + na);
     mp_tile_k<0><<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(A, na, B, nb, splits->as<uint64_t>(), keep->as<uint8_t>(), nullptr);
     check_launch(c, "mp_diff");
     Buf tmp = make_buf(c, na * 8);
@@ -607,8 +815,10 @@ inline Buf merge_disjoint(xlb_ctx* c, const uint64_t* A, uint64_t na, const uint
     }
     uint64_t ntiles = (na + nb + MP_TILE - 1) / MP_TILE;
     Buf splits = make_buf(c, (ntiles + 1) * 8);
+    prof_begin(c, "mp_partition", 0);
     mp_partition_k<<<(unsigned)((ntiles + 1 + 127) / 128), 128, 0, c->stream>>>(A, na, B, nb, splits->as<uint64_t>(), ntiles);
     check_launch(c, "mp_partition");
+    prof_begin(c, "mp_union", (na + nb) * 16ull);
     mp_tile_k<1><<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(A, na, B, nb, splits->as<uint64_t>(), nullptr, o->as<uint64_t>());
     check_launch(c, "mp_union");
     return o;

@@ -154,13 +154,41 @@ void xlb_resolve_phase_timers(xlb_ctx* c) {
         cudaEventDestroy(r.e1);
     }
     g_phase_recs.clear();
-    for (auto& e : c->sort_events) {
-        float ms = 0;
-        if (cudaEventElapsedTime(&ms, e.first, e.second) == cudaSuccess) c->ms_sort_kernel += ms;
-        cudaEventDestroy(e.first);
-        cudaEventDestroy(e.second);
+    for (auto& kv : c->prof) {
+        for (auto& e : kv.second.pending) {
+            float ms = 0;
+            if (cudaEventElapsedTime(&ms, e.first, e.second) == cudaSuccess) kv.second.ms += ms;
+            cudaEventDestroy(e.first);
+            cudaEventDestroy(e.second);
+        }
+        kv.second.pending.clear();
     }
-    c->sort_events.clear();
+}
+
+extern "C" xlb_status xlb_profile_enable(xlb_ctx* c, const char* kernel) {
+    if (!c) return XLB_ERR_INVALID;
+    xlb_resolve_phase_timers(c);
+    c->prof.clear();
+    c->prof_filter = kernel ? kernel : "";
+    return XLB_OK;
+}
+
+extern "C" xlb_status xlb_profile_read(xlb_ctx* c, xlb_kernel_profile* out, uint32_t cap, uint32_t* n) {
+    if (!c || !n) return XLB_ERR_INVALID;
+    xlb_resolve_phase_timers(c);
+    uint32_t i = 0;
+    for (auto& kv : c->prof) {
+        if (out && i < cap) {
+            memset(&out[i], 0, sizeof out[i]);
+            strncpy(out[i].name, kv.first.c_str(), sizeof(out[i].name) - 1);
+            out[i].launches = kv.second.launches;
+            out[i].ms = kv.second.ms;
+            out[i].bytes = kv.second.bytes;
+        }
+        ++i;
+    }
+    *n = i;
+    return XLB_OK;
 }
 
 // ------------------------------------------------------------------------------ key-array ops
@@ -171,6 +199,7 @@ Keys ops_rel_packed(xlb_ctx* c, const xlb_rel* r) {
     if (!rel_packable(r->schema)) xlb_fail(XLB_ERR_UNSUPPORTED, "relation is not a one- or two-column 32-bit relation");
     Buf b = make_buf(c, r->rows * 8);
     if (r->rows) {
+        prof_begin(c, "pack", 0);
         if (r->schema.arity == 2) pack2_k<<<grid_for(c, r->rows), BLOCK, 0, c->stream>>>(r->cols[0]->as<uint32_t>(), r->cols[1]->as<uint32_t>(), b->as<uint64_t>(), r->rows);
         else pack1_k<<<grid_for(c, r->rows), BLOCK, 0, c->stream>>>(r->cols[0]->as<uint32_t>(), b->as<uint64_t>(), r->rows);
         check_launch(c, "pack");
@@ -184,6 +213,7 @@ void ops_rel_columns(xlb_ctx* c, const xlb_rel* r) {
     if (r->schema.arity == 0 || r->cols[0]) return;
     for (uint32_t i = 0; i < r->schema.arity; ++i) r->cols[i] = make_buf(c, r->rows * 4);
     if (!r->rows) return;
+    prof_begin(c, "unpack", 0);
     if (r->schema.arity == 2) unpack2_k<<<grid_for(c, r->rows), BLOCK, 0, c->stream>>>(r->packed->as<uint64_t>(), r->cols[0]->as<uint32_t>(), r->cols[1]->as<uint32_t>(), r->rows);
     else unpack1_k<<<grid_for(c, r->rows), BLOCK, 0, c->stream>>>(r->packed->as<uint64_t>(), r->cols[0]->as<uint32_t>(), r->rows);
     check_launch(c, "unpack");
@@ -263,6 +293,7 @@ Keys ops_remap(xlb_ctx* c, const Keys& in, int hi_src, int lo_src) {
     o.n = in.n;
     o.buf = make_buf(c, in.n * 8);
     if (in.n) {
+        prof_begin(c, "remap", 0);
         remap_k<<<grid_for(c, in.n), BLOCK, 0, c->stream>>>(in.ptr(), o.buf->as<uint64_t>(), in.n, hi_src == SRC_ZERO ? 2 : hi_src, lo_src == SRC_ZERO ? 2 : lo_src);
         check_launch(c, "remap");
     }
@@ -296,6 +327,7 @@ Index ops_index_build(xlb_ctx* c, Buf S, uint64_t n, int key_shift, Buf pay) {
     ix.table = make_buf(c, cap * 16);
     CUDA_OK(cudaMemsetAsync(ix.table->p, 0, cap * 16, c->stream));
     if (nu) {
+        prof_begin(c, "hash_insert", 0);
         hash_insert_k<<<grid_for(c, nu), BLOCK, 0, c->stream>>>(S->as<uint64_t>(), n, key_shift, starts->as<uint32_t>(), nu, ix.table->as<ulonglong2>(), ix.mask, c->d_status);
         check_launch(c, "hash_insert");
     }
@@ -305,6 +337,7 @@ Index ops_index_build(xlb_ctx* c, Buf S, uint64_t n, int key_shift, Buf pay) {
 Buf ops_probe_match(xlb_ctx* c, const Keys& bag, int keysel, const uint64_t* pkeys, const Index& ix) {
     Buf match = make_buf(c, bag.n * 8);
     if (bag.n) {
+        prof_begin(c, "hash_probe", bag.n * 32ull);
         if (pkeys) hash_probe_k<LoadKey64><<<grid_for(c, bag.n), BLOCK, 0, c->stream>>>(LoadKey64{pkeys}, bag.n, ix.table->as<ulonglong2>(), ix.mask, match->as<uint64_t>());
         else hash_probe_k<LoadKeyHalf><<<grid_for(c, bag.n), BLOCK, 0, c->stream>>>(LoadKeyHalf{bag.ptr(), keysel}, bag.n, ix.table->as<ulonglong2>(), ix.mask, match->as<uint64_t>());
         check_launch(c, "hash_probe");
@@ -330,8 +363,10 @@ Keys ops_join_expand(xlb_ctx* c, const Keys& bag, int keysel, const uint64_t* pk
     out.buf = make_buf(c, tot * 8);
     uint64_t ntiles = (tot + EX_TILE - 1) / EX_TILE;
     Buf tile_row = make_buf(c, (ntiles + 1) * 8);
+    prof_begin(c, "expand_partition", 0);
     expand_partition_k<<<(unsigned)((ntiles + 1 + 127) / 128), 128, 0, c->stream>>>(off->as<uint64_t>(), nm, tot, tile_row->as<uint64_t>(), ntiles);
     check_launch(c, "expand_partition");
+    prof_begin(c, "expand", tot * 12ull + nm * 24ull);
     expand_k<<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(mbag->as<uint64_t>(), mmatch->as<uint64_t>(), off->as<uint64_t>(), nm, tot, tile_row->as<uint64_t>(),
                                                          ix.S->as<uint64_t>(), ix.pay ? ix.pay->as<uint32_t>() : nullptr, hi_src, lo_src, out.buf->as<uint64_t>());
     check_launch(c, "expand");
@@ -603,6 +638,7 @@ static Buf sort_permutation(xlb_ctx* c, const xlb_rel* r, const uint32_t* keys, 
     Buf idx = make_buf(c, n * 4);
     if (n == 0) return idx;
     if (n >= (1ull << 32)) xlb_fail(XLB_ERR_CAPACITY, "sort of %llu rows exceeds the 2^32 row limit", (unsigned long long)n);
+    prof_begin(c, "iota", 0);
     iota_k<<<grid_for(c, n), BLOCK, 0, c->stream>>>(idx->as<uint32_t>(), n);
     check_launch(c, "iota");
     int k = (int)nk - 1;
@@ -617,6 +653,7 @@ static Buf sort_permutation(xlb_ctx* c, const xlb_rel* r, const uint32_t* keys, 
         }
         Buf kw = make_buf(c, n * 8);
         const xlb_rel* rr = r;
+        prof_begin(c, "build_key", 0);
         build_key_k<<<grid_for(c, n), BLOCK, 0, c->stream>>>(rr->cols[keys[hi_col]]->p, (int)type_width(r->schema.types[keys[hi_col]]), lo, 4, idx->as<uint32_t>(), kw->as<uint64_t>(), n);
         check_launch(c, "build_key");
         radix_sort(c, kw, &idx, n);
@@ -634,6 +671,7 @@ static xlb_rel* gather_rel(xlb_ctx* c, const xlb_rel* r, const uint32_t* idx, ui
         uint32_t w = type_width(r->schema.types[i]);
         o->cols[i] = make_buf(c, n * w);
         if (!n) continue;
+        prof_begin(c, "gather", 0);
         if (w == 4) gather_k<uint32_t><<<grid_for(c, n), BLOCK, 0, c->stream>>>(r->cols[i]->as<uint32_t>(), idx, o->cols[i]->as<uint32_t>(), n);
         else gather_k<uint64_t><<<grid_for(c, n), BLOCK, 0, c->stream>>>(r->cols[i]->as<uint64_t>(), idx, o->cols[i]->as<uint64_t>(), n);
         check_launch(c, "gather");
@@ -823,6 +861,7 @@ static Buf join_keys(xlb_ctx* c, const xlb_rel* r, const uint32_t* keys, uint32_
         if (w0 != 4 || type_width(r->schema.types[keys[1]]) != 4) xlb_fail(XLB_ERR_UNSUPPORTED, "two-column join keys must both be 32-bit");
         c1 = r->cols[keys[1]]->p;
     }
+    prof_begin(c, "build_key", 0);
     build_key_k<<<grid_for(c, r->rows), BLOCK, 0, c->stream>>>(r->cols[keys[0]]->p, w0, c1, 4, nullptr, kw->as<uint64_t>(), r->rows);
     check_launch(c, "build_key");
     return kw;
@@ -856,6 +895,7 @@ extern "C" xlb_status xlb_hash_join(xlb_ctx* c, const xlb_rel* l, const xlb_rel*
         Buf rkeys = join_keys(c, r, rk, nk);
         Buf ridx = make_buf(c, r->rows * 4);
         if (r->rows) {
+            prof_begin(c, "iota", 0);
             iota_k<<<grid_for(c, r->rows), BLOCK, 0, c->stream>>>(ridx->as<uint32_t>(), r->rows);
             check_launch(c, "iota");
             radix_sort(c, rkeys, &ridx, r->rows);
@@ -865,6 +905,7 @@ extern "C" xlb_status xlb_hash_join(xlb_ctx* c, const xlb_rel* l, const xlb_rel*
         Keys lrows;
         lrows.n = l->rows;
         lrows.buf = make_buf(c, l->rows * 8);
+        prof_begin(c, "iota64", 0);
         iota64_k<<<grid_for(c, l->rows), BLOCK, 0, c->stream>>>(lrows.buf->as<uint64_t>(), l->rows);
         check_launch(c, "iota64");
         if (type == XLB_JOIN_INNER) {
@@ -880,6 +921,7 @@ extern "C" xlb_status xlb_hash_join(xlb_ctx* c, const xlb_rel* l, const xlb_rel*
                 uint32_t w = type_width(os.types[i]);
                 o->cols[i] = make_buf(c, pairs.n * w);
                 if (!pairs.n) continue;
+                prof_begin(c, "gather_pair", 0);
                 if (w == 4) gather_pair_k<uint32_t><<<grid_for(c, pairs.n), BLOCK, 0, c->stream>>>(src->cols[sc]->as<uint32_t>(), pairs.ptr(), left ? 0 : 1, o->cols[i]->as<uint32_t>(), pairs.n);
                 else gather_pair_k<uint64_t><<<grid_for(c, pairs.n), BLOCK, 0, c->stream>>>(src->cols[sc]->as<uint64_t>(), pairs.ptr(), left ? 0 : 1, o->cols[i]->as<uint64_t>(), pairs.n);
                 check_launch(c, "gather_pair");

@@ -12,7 +12,7 @@ import subprocess
 from . import _abi as A
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libxlb.so")
+LIB_PATH = os.environ.get("XLB_LIB") or os.path.join(_HERE, "libxlb.so")  # XLB_LIB: an alternative build, for A/B runs
 
 P = C.c_void_p
 U32P = C.POINTER(C.c_uint32)
@@ -41,6 +41,8 @@ PROTOTYPES = {
     "xlb_store_get": (C.c_int, [P, C.c_char_p, C.POINTER(P)]),
     "xlb_store_remove": (C.c_int, [P, C.c_char_p]),
     "xlb_execute_plan": (C.c_int, [P, C.POINTER(A.Plan), C.POINTER(A.RunStats)]),
+    "xlb_profile_enable": (C.c_int, [P, C.c_char_p]),
+    "xlb_profile_read": (C.c_int, [P, C.POINTER(A.KernelProfile), C.c_uint32, C.POINTER(C.c_uint32)]),
     "xlb_comm_unique_id": (C.c_int, [C.POINTER(C.c_uint8)]),
     "xlb_comm_init": (C.c_int, [P, C.POINTER(C.c_uint8), C.c_uint32, C.c_uint32]),
     "xlb_owner_of": (C.c_uint32, [C.c_uint64, C.c_uint32]),

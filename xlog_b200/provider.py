@@ -170,3 +170,15 @@ class KernelProvider:
         a, p = C.c_uint64(), C.c_uint64()
         self._check(self._lib.xlb_memory_stats(self._ctx, C.byref(a), C.byref(p)))
         return a.value, p.value
+
+    def profile_enable(self, kernel: str | None) -> None:
+        """Time every launch of ``kernel`` ("*" = all kernels, None = off) with CUDA events."""
+        self._check(self._lib.xlb_profile_enable(self._ctx, kernel.encode() if kernel else None))
+
+    def profile_read(self) -> dict:
+        """name -> {launches, ms, bytes} since ``profile_enable``."""
+        arr = (A.KernelProfile * 64)()
+        n = C.c_uint32()
+        self._check(self._lib.xlb_profile_read(self._ctx, arr, 64, C.byref(n)))
+        return {arr[i].name.decode(): {"launches": arr[i].launches, "ms": arr[i].ms, "bytes": arr[i].bytes}
+                for i in range(min(n.value, 64))}
