@@ -239,6 +239,30 @@ xlb_status xlb_store_remove(xlb_ctx* ctx, const char* name);
  * loop of execute_recursive_scc (executor/recursive.rs:447-957).  `stats` may be NULL. */
 xlb_status xlb_execute_plan(xlb_ctx* ctx, const xlb_plan* plan, xlb_run_stats* stats);
 
+/* ---- allocation-free entry point ---------------------------------------------------------- */
+/* No counterpart in the reference.  For callers that may not allocate device memory when they
+ * call in (a host runtime that owns the whole GPU through its own arena and forbids cudaMalloc
+ * in plug-ins; a section where an allocation could stall the device; a caller with no allocator
+ * to hand down): removes duplicates from `n` ascending keys at `d_sorted` (device memory),
+ * writing the distinct keys, ascending, to `d_unique` (room for n keys) and their number to
+ * `*d_count` (device memory), on `cuda_stream` (a cudaStream_t; NULL = the default stream).  Same
+ * result as the full-row xlb_dedup of a sorted single-column u64 relation.
+ *   - needs no context and calls no cudaMalloc/cudaFree or any allocating routine: its scratch
+ *     (tile counts, tile offsets, scan partials) is a fixed array of about 385 KiB inside the
+ *     library image, held by every GPU that loads the library until the process exits;
+ *   - n above xlb_dedup_sorted_u64_static_max() (2^26 keys) is refused with XLB_ERR_CAPACITY;
+ *   - the first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress); make that first call before starting any stream capture;
+ *   - every call shares the one array: calls that may overlap on the GPU (different streams,
+ *     different host threads) race on it and must be serialised by the caller.  The array
+ *     keeps the last call's contents; each call overwrites every word it later reads;
+ *   - returns after the stream has been synchronised.  xlb_static_last_error() gives the
+ *     message of the calling thread's last failing call. */
+xlb_status xlb_dedup_sorted_u64_static(const uint64_t* d_sorted, uint64_t n, uint64_t* d_unique,
+                                       uint64_t* d_count, void* cuda_stream);
+uint64_t xlb_dedup_sorted_u64_static_max(void);
+const char* xlb_static_last_error(void);
+
 /* ---- per-kernel timing -------------------------------------------------------------------- */
 /* Counterpart of the reference's feature-gated per-phase CUDA-event timing
  * (crates/xlog-runtime/src/profiler.rs:355-640, feature `wcoj-phase-timing`): brackets every

@@ -92,7 +92,7 @@ constexpr int SCAN_IPT = 8;
 constexpr int SCAN_TILE = BLOCK * SCAN_IPT;
 
 template <class Load, class Tout>
-__global__ void __launch_bounds__(BLOCK) scan_reduce_k(Load load, uint64_t n, Tout* tile_sums) {
+static __global__ void __launch_bounds__(BLOCK) scan_reduce_k(Load load, uint64_t n, Tout* tile_sums) {
     __shared__ Tout sm[33];
     uint64_t base = (uint64_t)blockIdx.x * SCAN_TILE;
     Tout s = 0;
@@ -109,7 +109,7 @@ __global__ void __launch_bounds__(BLOCK) scan_reduce_k(Load load, uint64_t n, To
 // One block walks the tile sums in chunks of blockDim.x, turning them into exclusive offsets in
 // place; the grand total goes to *total.
 template <class Tout>
-__global__ void __launch_bounds__(1024) scan_spine_k(Tout* tile_sums, uint64_t ntiles, Tout* total) {
+static __global__ void __launch_bounds__(1024) scan_spine_k(Tout* tile_sums, uint64_t ntiles, Tout* total) {
     __shared__ Tout sm[33];
     __shared__ Tout carry_s;
     if (threadIdx.x == 0) carry_s = 0;
@@ -131,7 +131,7 @@ __global__ void __launch_bounds__(1024) scan_spine_k(Tout* tile_sums, uint64_t n
 // out[i] = exclusive prefix.  tile_offsets may be null for a single tile; `total` (may be null)
 // then receives the sum.  out has n entries; out_end (may be null) receives the grand total too.
 template <class Load, class Tout>
-__global__ void __launch_bounds__(BLOCK) scan_apply_k(Load load, uint64_t n, const Tout* tile_offsets, Tout* out, Tout* total) {
+static __global__ void __launch_bounds__(BLOCK) scan_apply_k(Load load, uint64_t n, const Tout* tile_offsets, Tout* out, Tout* total) {
     __shared__ Tout sm[33];
     uint64_t base = (uint64_t)blockIdx.x * SCAN_TILE + (uint64_t)threadIdx.x * SCAN_IPT;
     Tout v[SCAN_IPT];
@@ -192,7 +192,7 @@ void exclusive_scan(xlb_ctx* c, Load load, uint64_t n, Tout* out, Tout* d_total)
 // ---------------------------------------------------------------------------------- select
 // Stable compaction: Pred(i) -> keep?, Emit(i, pos) stores row i at output position pos.
 template <class Pred>
-__global__ void __launch_bounds__(BLOCK) select_count_k(Pred pred, uint64_t n, uint32_t* tile_counts) {
+static __global__ void __launch_bounds__(BLOCK) select_count_k(Pred pred, uint64_t n, uint32_t* tile_counts) {
     __shared__ uint32_t sm[33];
     uint64_t base = (uint64_t)blockIdx.x * SCAN_TILE;
     uint32_t s = 0;
@@ -207,7 +207,7 @@ __global__ void __launch_bounds__(BLOCK) select_count_k(Pred pred, uint64_t n, u
 }
 
 template <class Pred, class Emit>
-__global__ void __launch_bounds__(BLOCK) select_write_k(Pred pred, Emit emit, uint64_t n, const uint64_t* tile_offsets, uint64_t* total) {
+static __global__ void __launch_bounds__(BLOCK) select_write_k(Pred pred, Emit emit, uint64_t n, const uint64_t* tile_offsets, uint64_t* total) {
     __shared__ uint32_t sm[33];
     uint64_t base = (uint64_t)blockIdx.x * SCAN_TILE + (uint64_t)threadIdx.x * SCAN_IPT;
     bool f[SCAN_IPT];
@@ -255,27 +255,27 @@ uint64_t select(xlb_ctx* c, Pred pred, Emit emit, uint64_t n) {
 }
 
 // -------------------------------------------------------------------------------- pack/unpack
-__global__ void pack2_k(const uint32_t* __restrict__ c0, const uint32_t* __restrict__ c1, uint64_t* __restrict__ out, uint64_t n) {
+static __global__ void pack2_k(const uint32_t* __restrict__ c0, const uint32_t* __restrict__ c1, uint64_t* __restrict__ out, uint64_t n) {
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
         out[i] = ((uint64_t)c0[i] << 32) | c1[i];
 }
-__global__ void pack1_k(const uint32_t* __restrict__ c0, uint64_t* __restrict__ out, uint64_t n) {
+static __global__ void pack1_k(const uint32_t* __restrict__ c0, uint64_t* __restrict__ out, uint64_t n) {
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
         out[i] = c0[i];
 }
-__global__ void unpack2_k(const uint64_t* __restrict__ in, uint32_t* __restrict__ c0, uint32_t* __restrict__ c1, uint64_t n) {
+static __global__ void unpack2_k(const uint64_t* __restrict__ in, uint32_t* __restrict__ c0, uint32_t* __restrict__ c1, uint64_t n) {
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
         uint64_t k = in[i];
         c0[i] = (uint32_t)(k >> 32);
         c1[i] = (uint32_t)k;
     }
 }
-__global__ void unpack1_k(const uint64_t* __restrict__ in, uint32_t* __restrict__ c0, uint64_t n) {
+static __global__ void unpack1_k(const uint64_t* __restrict__ in, uint32_t* __restrict__ c0, uint64_t n) {
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
         c0[i] = (uint32_t)in[i];
 }
 // out[i] = (sel(in[i], hi_src) << 32) | sel(in[i], lo_src); src: 0 = high half, 1 = low half, 2 = zero.
-__global__ void remap_k(const uint64_t* __restrict__ in, uint64_t* __restrict__ out, uint64_t n, int hi_src, int lo_src) {
+static __global__ void remap_k(const uint64_t* __restrict__ in, uint64_t* __restrict__ out, uint64_t n, int hi_src, int lo_src) {
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
         uint64_t k = in[i];
         uint32_t h = (uint32_t)(k >> 32), l = (uint32_t)k;
@@ -304,7 +304,7 @@ constexpr int SORT_TILE = SORT_THREADS * SORT_IPT;  // keys per tile
 constexpr int SORT_WARPS = SORT_THREADS / 32;
 
 // OR and AND of all keys in one read: a digit whose bits never vary needs no pass.
-__global__ void __launch_bounds__(BLOCK) radix_bits_k(const uint64_t* __restrict__ keys, uint64_t n, unsigned long long* __restrict__ or_and /* [2] */) {
+static __global__ void __launch_bounds__(BLOCK) radix_bits_k(const uint64_t* __restrict__ keys, uint64_t n, unsigned long long* __restrict__ or_and /* [2] */) {
     uint64_t o = 0, a = ~0ull;
     for (uint64_t i = (uint64_t)blockIdx.x * BLOCK + threadIdx.x; i < n; i += (uint64_t)gridDim.x * BLOCK) {
         uint64_t k = keys[i];
@@ -324,7 +324,7 @@ __global__ void __launch_bounds__(BLOCK) radix_bits_k(const uint64_t* __restrict
 
 // Histograms of all eight digits in one read of the keys.  A digit on which a whole warp agrees
 // (constant high bytes are the common case) costs one shared-memory add per warp.
-__global__ void __launch_bounds__(BLOCK) radix_upfront_k(const uint64_t* __restrict__ keys, uint64_t n, unsigned int* __restrict__ ghist /* 8*256 */) {
+static __global__ void __launch_bounds__(BLOCK) radix_upfront_k(const uint64_t* __restrict__ keys, uint64_t n, unsigned int* __restrict__ ghist /* 8*256 */) {
     __shared__ unsigned int sh[8 * 256];
     for (int i = threadIdx.x; i < 8 * 256; i += BLOCK) sh[i] = 0;
     __syncthreads();
@@ -355,7 +355,7 @@ __global__ void __launch_bounds__(BLOCK) radix_upfront_k(const uint64_t* __restr
 
 // Exclusive scan of each digit histogram (the digit bases of the sweep) and, per digit, whether
 // more than one bin is occupied.
-__global__ void __launch_bounds__(BLOCK) radix_bases_k(const unsigned int* __restrict__ ghist, unsigned long long n, unsigned int* __restrict__ bases, unsigned long long* __restrict__ varies) {
+static __global__ void __launch_bounds__(BLOCK) radix_bases_k(const unsigned int* __restrict__ ghist, unsigned long long n, unsigned int* __restrict__ bases, unsigned long long* __restrict__ varies) {
     __shared__ unsigned int sm[33];
     for (int d = 0; d < 8; ++d) {
         unsigned v = ghist[d * 256 + threadIdx.x];
@@ -368,7 +368,7 @@ __global__ void __launch_bounds__(BLOCK) radix_bases_k(const unsigned int* __res
 }
 
 // Per-tile histogram of one digit: hist[d * ntiles + tile].
-__global__ void __launch_bounds__(BLOCK) radix_tile_hist_k(const uint64_t* __restrict__ keys, uint64_t n, int shift, uint32_t* __restrict__ hist, uint32_t ntiles) {
+static __global__ void __launch_bounds__(BLOCK) radix_tile_hist_k(const uint64_t* __restrict__ keys, uint64_t n, int shift, uint32_t* __restrict__ hist, uint32_t ntiles) {
     __shared__ unsigned int sh[BLOCK / 32][256];
     for (int i = threadIdx.x; i < (BLOCK / 32) * 256; i += BLOCK) (&sh[0][0])[i] = 0;
     __syncthreads();
@@ -408,7 +408,7 @@ constexpr unsigned LB_SPIN_LIMIT = 1u << 22;
 #define XLB_SORT_MINB 4
 #endif
 template <bool HAS_VALUES, bool LOOKBACK>
-__global__ void __launch_bounds__(SORT_THREADS, XLB_SORT_MINB) radix_scatter_k(const uint64_t* __restrict__ keys_in, uint64_t* __restrict__ keys_out,
+static __global__ void __launch_bounds__(SORT_THREADS, XLB_SORT_MINB) radix_scatter_k(const uint64_t* __restrict__ keys_in, uint64_t* __restrict__ keys_out,
                                                           const uint32_t* __restrict__ vals_in, uint32_t* __restrict__ vals_out,
                                                           uint64_t n, int shift, const uint32_t* __restrict__ offs, uint32_t ntiles,
                                                           unsigned int* __restrict__ tile_counter, volatile unsigned int* status, DevStatus* dst) {
@@ -699,7 +699,7 @@ __device__ __forceinline__ uint64_t merge_path(const uint64_t* A, uint64_t na, c
     return lo;
 }
 
-__global__ void mp_partition_k(const uint64_t* __restrict__ A, uint64_t na, const uint64_t* __restrict__ B, uint64_t nb, uint64_t* __restrict__ splits, uint64_t ntiles) {
+static __global__ void mp_partition_k(const uint64_t* __restrict__ A, uint64_t na, const uint64_t* __restrict__ B, uint64_t nb, uint64_t* __restrict__ splits, uint64_t ntiles) {
     uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (t > ntiles) return;
     uint64_t diag = t * MP_TILE;
@@ -710,7 +710,7 @@ __global__ void mp_partition_k(const uint64_t* __restrict__ A, uint64_t na, cons
 // MODE 0: keep[i] = 1 iff A[i] is not in B (A, B sorted unique).
 // MODE 1: out = merge of A and B (disjoint), out has na + nb entries.
 template <int MODE>
-__global__ void __launch_bounds__(BLOCK) mp_tile_k(const uint64_t* __restrict__ A, uint64_t na, const uint64_t* __restrict__ B, uint64_t nb,
+static __global__ void __launch_bounds__(BLOCK) mp_tile_k(const uint64_t* __restrict__ A, uint64_t na, const uint64_t* __restrict__ B, uint64_t nb,
                                                     const uint64_t* __restrict__ splits, uint8_t* __restrict__ keep, uint64_t* __restrict__ out) {
     __shared__ uint64_t sA[MP_TILE + 1];
     __shared__ uint64_t sB[MP_TILE + 2];
@@ -846,7 +846,7 @@ struct EmitRunHead {
     __device__ __forceinline__ void operator()(uint64_t i, uint64_t pos) const { starts[pos] = (uint32_t)i; }
 };
 
-__global__ void hash_insert_k(const uint64_t* __restrict__ S, uint64_t n, int key_shift, const uint32_t* __restrict__ starts, uint64_t nu,
+static __global__ void hash_insert_k(const uint64_t* __restrict__ S, uint64_t n, int key_shift, const uint32_t* __restrict__ starts, uint64_t nu,
                               ulonglong2* __restrict__ table, uint64_t mask, DevStatus* st) {
     for (uint64_t u = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; u < nu; u += (uint64_t)gridDim.x * blockDim.x) {
         uint64_t s = starts[u];
@@ -884,7 +884,7 @@ struct LoadKey64 {  // join key from a separate array of key words
 // match[i] = (start << 32) | len, or 0 when the key is absent.  Keys are compared, not only
 // their hashes (the reference pins this in crates/xlog-cuda/tests/join_collision_test.rs:19-53).
 template <class LoadKey>
-__global__ void __launch_bounds__(BLOCK) hash_probe_k(LoadKey load_key, uint64_t n, const ulonglong2* __restrict__ table, uint64_t mask, uint64_t* __restrict__ match) {
+static __global__ void __launch_bounds__(BLOCK) hash_probe_k(LoadKey load_key, uint64_t n, const ulonglong2* __restrict__ table, uint64_t mask, uint64_t* __restrict__ match) {
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
         uint64_t key = load_key(i);
         uint64_t h = mix64(key) & mask;
@@ -918,7 +918,7 @@ constexpr int EX_IPT = 8;
 constexpr int EX_TILE = BLOCK * EX_IPT;
 
 // tile_row[t] = index of the matched row that owns output t * EX_TILE (last row with off <= o).
-__global__ void expand_partition_k(const uint64_t* __restrict__ off, uint64_t nrows, uint64_t total, uint64_t* __restrict__ tile_row, uint64_t ntiles) {
+static __global__ void expand_partition_k(const uint64_t* __restrict__ off, uint64_t nrows, uint64_t total, uint64_t* __restrict__ tile_row, uint64_t ntiles) {
     uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (t > ntiles) return;
     uint64_t o = t * EX_TILE;
@@ -941,7 +941,7 @@ __device__ __forceinline__ uint32_t ex_pick(int src, uint64_t probe, uint32_t ot
 // Load-balanced expansion: every matched probe row contributes len outputs; each tile of EX_TILE
 // outputs finds its rows by a search over the row offsets held in shared memory, so writes are
 // coalesced whatever the degree skew.  Output order: probe row order, then build order.
-__global__ void __launch_bounds__(BLOCK) expand_k(const uint64_t* __restrict__ mbag, const uint64_t* __restrict__ mmatch, const uint64_t* __restrict__ off,
+static __global__ void __launch_bounds__(BLOCK) expand_k(const uint64_t* __restrict__ mbag, const uint64_t* __restrict__ mmatch, const uint64_t* __restrict__ off,
                                                    uint64_t nrows, uint64_t total, const uint64_t* __restrict__ tile_row, const uint64_t* __restrict__ S,
                                                    const uint32_t* __restrict__ pay, int hi_src, int lo_src, uint64_t* __restrict__ out) {
     __shared__ uint64_t soff[EX_TILE + 2];

@@ -41,6 +41,9 @@ PROTOTYPES = {
     "xlb_store_get": (C.c_int, [P, C.c_char_p, C.POINTER(P)]),
     "xlb_store_remove": (C.c_int, [P, C.c_char_p]),
     "xlb_execute_plan": (C.c_int, [P, C.POINTER(A.Plan), C.POINTER(A.RunStats)]),
+    "xlb_dedup_sorted_u64_static": (C.c_int, [P, C.c_uint64, P, P, P]),
+    "xlb_dedup_sorted_u64_static_max": (C.c_uint64, []),
+    "xlb_static_last_error": (C.c_char_p, []),
     "xlb_profile_enable": (C.c_int, [P, C.c_char_p]),
     "xlb_profile_read": (C.c_int, [P, C.POINTER(A.KernelProfile), C.c_uint32, C.POINTER(C.c_uint32)]),
     "xlb_comm_unique_id": (C.c_int, [C.POINTER(C.c_uint8)]),
