@@ -78,3 +78,83 @@ def test_chunked_join_matches_unchunked(oracle):
     want, _ = oracle.run_program(programs.transitive_closure(), {"edge": [c0, c1]}, ["reach"])
     assert all(np.array_equal(g, w) for g, w in zip(got["reach"], want["reach"]))
     p.close()
+
+
+# ---- the reference's end-to-end fixtures -------------------------------------------------------
+from test_oracle_golden import PROGS, program_inputs, rows_of  # noqa: E402
+
+
+@pytest.mark.parametrize("case", PROGS["programs"], ids=lambda c: c["name"])
+def test_program_kat(case):
+    plan, facts, out = program_inputs(case)
+    p = fresh()
+    got, _ = run_program(p, plan, facts, [out])
+    assert rows_of(got[out]) == case["expected"], case["cite"]
+    p.close()
+
+
+def test_novel_step_emits_sorted_unique_rows(provider):
+    from test_oracle_golden import cols_of
+    ns = PROGS["novel_step"]
+    t2 = ["u32", "u32"]
+    mk = lambda rows: provider.create_buffer_from_slices(cols_of(rows, t2))
+    joined = provider.download(provider.hash_join_v2(mk(ns["delta"]), mk(ns["edge"]), [1], [0]))
+    cand = provider.create_buffer_from_slices([joined[0], joined[3]])
+    novel = provider.diff_gpu(cand, mk(ns["full"]))
+    assert rows_of(provider.download(novel)) == ns["expected"] and novel.is_canonical()
+
+
+def test_iteration_limit_is_an_error_with_the_reference_message():
+    from xlog_b200.lib import XlbError
+    from xlog_b200 import _abi as A
+    c0 = np.arange(0, 50, dtype=np.uint32)
+    p = KernelProvider(device=0, max_iterations=3)
+    with pytest.raises(XlbError) as e:
+        run_program(p, programs.transitive_closure(), {"edge": [c0, c0 + 1]}, ["reach"])
+    assert e.value.status == A.ERR_ITER_LIMIT and "iteration limit (3) exceeded" in e.value.message
+    p.close()
+
+
+def test_missing_input_relation_is_reported():
+    from xlog_b200.lib import XlbError
+    from xlog_b200 import _abi as A
+    p = fresh()
+    with pytest.raises(XlbError) as e:
+        run_program(p, programs.transitive_closure(), {}, ["reach"])
+    assert e.value.status == A.ERR_NOT_FOUND and "Missing relation: edge" in e.value.message
+    p.close()
+
+
+def test_rerun_after_new_facts_extends_the_fixpoint(oracle):
+    """Running the plan again after an input grew continues from the stored relation, as the
+    reference's seeding pass does (executor/recursive.rs:525-566)."""
+    from xlog_b200.executor import Executor
+    c0, c1 = workloads.uniform_digraph(150, 400, 5)
+    plan = programs.transitive_closure()
+    p = fresh()
+    ex = Executor(p)
+    for name, rid in plan.rel_ids.items():
+        ex.register_relation(rid, name)
+    ex.put_relation("edge", p.create_buffer_from_slices([c0[:300], c1[:300]]))
+    ex.execute_plan(plan)
+    ex.put_relation("edge", p.create_buffer_from_slices([c0, c1]))
+    ex.execute_plan(plan)
+    got = p.download(ex.get("reach"))
+    want, _ = oracle.run_program(plan, {"edge": [c0, c1]}, ["reach"])
+    assert all(np.array_equal(g, w) for g, w in zip(got, want["reach"]))
+    p.close()
+
+
+def test_unsupported_rule_shape_is_refused_not_miscomputed():
+    """A triangle body needs an atom with both columns bound: outside the built scope."""
+    from xlog_b200.lib import XlbError
+    from xlog_b200 import _abi as A
+    from xlog_b200.plan import CompiledRule, ExecutionPlan, Join, Project, Scan, Scc
+    body = Project(Join(Join(Scan(0), Scan(0), [1], [0]), Scan(0), [3, 0], [0, 1]), [0, 1])
+    plan = ExecutionPlan([Scc(0, False, [CompiledRule("tri", body)])], {"edge": 0, "tri": 1})
+    c0, c1 = workloads.uniform_digraph(50, 200, 2)
+    p = fresh()
+    with pytest.raises(XlbError) as e:
+        run_program(p, plan, {"edge": [c0, c1]}, ["tri"])
+    assert e.value.status == A.ERR_UNSUPPORTED
+    p.close()
