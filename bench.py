@@ -59,7 +59,7 @@ class ClockSampler:
         self.proc = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(gpu_index)], stdout=subprocess.PIPE, text=True)
+                                          "-lms", "50", "-i", str(gpu_index)], stdout=subprocess.PIPE, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
         except OSError:
@@ -144,6 +144,7 @@ def main():
     ap.add_argument("--scale", type=int, default=20)
     ap.add_argument("--kernel", default="radix_scatter", help="kernel whose launches are timed for the roofline object")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-clocks", action="store_true", help="do not run nvidia-smi beside the timed region")
     ap.add_argument("--breakdown", action="store_true", help="extra untimed pass with every kernel timed, to stderr")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
@@ -156,7 +157,6 @@ def main():
     import torch.distributed as dist
 
     from xlog_b200.executor import Executor
-    from xlog_b200.lib import load
     from xlog_b200.provider import KernelProvider
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -185,17 +185,9 @@ def main():
         host_cols.append(a)
 
     prov = KernelProvider(device=local)
-    lib = load()
     if world > 1:
-        import ctypes as C
-        idt = torch.zeros(128, dtype=torch.uint8, device="cuda")
-        if rank == 0:
-            buf = (C.c_uint8 * 128)()
-            assert lib.xlb_comm_unique_id(buf) == 0
-            idt.copy_(torch.tensor(list(buf), dtype=torch.uint8))
-        dist.broadcast(idt, 0)
-        arr = (C.c_uint8 * 128)(*idt.cpu().tolist())
-        prov._check(lib.xlb_comm_init(prov._ctx, arr, rank, world))
+        from xlog_b200 import dist as D
+        D.init_comm(prov, rank, world, device="cuda")
 
     ex = Executor(prov)
     for name, rid in plan.rel_ids.items():
@@ -224,10 +216,12 @@ def main():
         return ex.execute_plan(cplan)
 
     # ---- device-resident steps: warm-up, then K timed steps ---------------------------------
+    # clocks are sampled from the first warm-up step to the last end-to-end step: the timed region
+    # alone lasts tens of milliseconds, less than one nvidia-smi sampling period
+    sampler = ClockSampler(local) if rank == 0 and not args.no_clocks else None
     for _ in range(args.warmup):
         device_step()
     prov.profile_enable(args.kernel)
-    sampler = ClockSampler(local) if rank == 0 else None
     ms_steps, stats = [], None
     launches = 0
     barrier()
@@ -236,7 +230,6 @@ def main():
         ms_steps.append(stats["ms_total"])
         launches += stats["kernel_launches"]
     barrier()
-    clocks = sampler.stop() if sampler else None
     prof = prov.profile_read()
     prov.profile_enable(None)
     ms_t = torch.tensor(ms_steps, dtype=torch.float64, device="cuda")
@@ -264,6 +257,7 @@ def main():
         d2h_bytes = sum(c.nbytes for c in res)
         if i >= args.warmup:
             e2e_ms.append(dt)
+    clocks = sampler.stop() if sampler else None
     e2e_t = torch.tensor(e2e_ms, dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
@@ -320,7 +314,7 @@ def main():
         "clocks": clocks,
         "roofline": roof,
         "cpu_baseline": cpu,
-        "phases_ms_last_step": {k: stats[k] for k in ("ms_join", "ms_sort", "ms_setops", "ms_exchange")},
+        "host_last_step": {k: stats[k] for k in ("host_syncs", "ms_host_wait", "ms_host_total")},
     }
     print(json.dumps(line), flush=True)
     if world > 1:

@@ -221,6 +221,9 @@ typedef struct xlb_run_stats {
     double ms_setops;          /* dedup + difference + union                                   */
     double ms_exchange;        /* partition + all-to-all + termination vote (multi-rank)       */
     uint64_t exchange_bytes;   /* bytes this rank sent to other ranks                          */
+    uint64_t host_syncs;       /* times the host waited for the stream (row-count read-backs)  */
+    double ms_host_wait;       /* host wall time inside those waits                            */
+    double ms_host_total;      /* host wall time of the whole call                             */
 } xlb_run_stats;
 
 /* ---- executor: Executor::{register_relation, put_relation, store().get, execute_plan} ----- */

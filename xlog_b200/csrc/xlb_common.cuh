@@ -2,7 +2,9 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include <chrono>
 #include <cstdarg>
+#include <cstring>
 #include <cstdint>
 #include <cstdio>
 #include <map>
@@ -54,6 +56,8 @@ struct xlb_ctx {
     uint64_t join_chunk = 0;
     uint32_t flags = 0;
     uint64_t launches = 0;
+    uint64_t syncs = 0;       // host waits on the stream (count read-backs)
+    double ms_sync_wait = 0;  // wall time spent inside those waits
     std::string last_error;
     // pinned scratch for scalar read-backs
     unsigned long long* h_scalar = nullptr;  // 64 words
@@ -133,16 +137,23 @@ inline void check_launch(xlb_ctx* c, const char* what) {
 }
 
 // Read `n` 64-bit words from device memory (one stream synchronisation).
+inline void stream_wait(xlb_ctx* c) {
+    auto t0 = std::chrono::steady_clock::now();
+    CUDA_OK(cudaStreamSynchronize(c->stream));
+    c->ms_sync_wait += std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+    c->syncs++;
+}
+
 inline void read_words(xlb_ctx* c, const void* dptr, int n, unsigned long long* out) {
     CUDA_OK(cudaMemcpyAsync(c->h_scalar, dptr, (size_t)n * 8, cudaMemcpyDeviceToHost, c->stream));
-    CUDA_OK(cudaStreamSynchronize(c->stream));
+    stream_wait(c);
     for (int i = 0; i < n; ++i) out[i] = c->h_scalar[i];
 }
 
 inline void check_dev_status(xlb_ctx* c) {
     DevStatus s;
     CUDA_OK(cudaMemcpyAsync(c->h_scalar, c->d_status, sizeof s, cudaMemcpyDeviceToHost, c->stream));
-    CUDA_OK(cudaStreamSynchronize(c->stream));
+    stream_wait(c);
     memcpy(&s, c->h_scalar, sizeof s);
     if (s.code != 0) {
         CUDA_OK(cudaMemsetAsync(c->d_status, 0, sizeof s, c->stream));

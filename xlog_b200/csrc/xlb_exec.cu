@@ -234,11 +234,12 @@ static Keys index_rows(xlb_ctx* c, const xlb_rel* r, int kc) {
     if (kc == 0) {
         if (r->canonical) return k;  // a canonical relation is already ordered by its first column
         Keys s = ops_copy(c, k);
-        ops_sort(c, s);
+        ops_sort_by_high_half(c, s);
         return s;
     }
     Keys s = ops_remap(c, k, SRC_LO, SRC_HI);
-    ops_sort(c, s);
+    if (r->canonical) ops_sort(c, s);           // kept fully sorted: later deltas are merged in
+    else ops_sort_by_high_half(c, s);           // an index only needs its rows grouped by key
     return s;
 }
 
@@ -459,7 +460,35 @@ static Keys run_pipeline(xlb_ctx* c, FlatRule fr /*by value: filter flags*/, siz
 
 // Candidates of one rule variant -> sorted unique tuples not in `full`, merged into `novel`.
 // The start rows are processed in chunks so no join output exceeds the configured bound.
-static void eval_variant(xlb_ctx* c, const FlatRule& fr, size_t start, const Keys& start_rows, int start_part_half, const Keys& full, int home_sel, Keys& novel, RunState& rs) {
+static void eval_variant(xlb_ctx* c, const FlatRule& fr_in, size_t start, const Keys& start_rows_in, bool start_is_stored, int start_part_half,
+                         const Keys& full, int home_sel, Keys& novel, RunState& rs) {
+    FlatRule fr = fr_in;
+    Keys start_rows = start_rows_in;
+    if (start_is_stored) {
+        // `atom(.., c, ..)` with a constant: fetch the matching rows through the atom's join index
+        // instead of filtering the whole relation
+        const Atom& sa = fr.atoms[start];
+        for (auto& f : fr.filters) {
+            if (f.applied || f.cmp != XLB_EQ || !f.rhs_const || f.rhs > 0xFFFFFFFFull) continue;
+            int kc = -1;
+            for (uint32_t j = 0; j < sa.arity; ++j)
+                if (sa.var[j] == f.lhs) kc = (int)j;
+            if (kc < 0 || (sa.arity == 2 && sa.var[0] == sa.var[1])) continue;
+            const Index& ix = get_index(c, sa.rel, kc, rs);
+            uint64_t key = f.rhs;
+            Keys probe = ops_from_host(c, &key, 1);
+            int hs = SRC_ZERO, ls = SRC_LO;
+            if (sa.arity == 2) {
+                hs = kc == 0 ? SRC_LO : SRC_OTHER;
+                ls = kc == 1 ? SRC_LO : SRC_OTHER;
+            }
+            PhaseTimer t(c, &rs.st.ms_join);
+            start_rows = ops_join_expand(c, probe, SRC_LO, nullptr, ix, hs, ls);
+            start_part_half = sa.arity == 2 ? (kc == 0 ? SRC_HI : SRC_LO) : SRC_LO;
+            f.applied = true;
+            break;
+        }
+    }
     if (start_rows.n == 0 && c->world == 1) return;
     uint64_t limit = c->join_chunk;
     // with several ranks every rank runs the same sequence of exchanges, so the rows are not
@@ -495,8 +524,7 @@ static void eval_variant(xlb_ctx* c, const FlatRule& fr, size_t start, const Key
             ops_sort(c, cand);
         }
         PhaseTimer t(c, &rs.st.ms_setops);
-        ops_dedup_sorted(c, cand);
-        Keys fresh = full.n ? ops_diff(c, cand, full) : cand;
+        Keys fresh = ops_dedup_diff(c, cand, full);  // duplicates dropped and `full` subtracted in one merge pass
         novel = novel.n ? ops_union(c, novel, fresh) : fresh;
     }
 }
@@ -573,7 +601,7 @@ static void seed_pass(xlb_ctx* c, const std::vector<FlatRule>& rules, const std:
         xlb_rel* sr = store_get(c, fr.atoms[start].rel);
         Keys rows = ops_rel_packed(c, sr);
         Keys full_old = canonical_keys(c, store_get(c, fr.head), rs);
-        eval_variant(c, fr, start, rows, rec.count(fr.atoms[start].rel) ? home[fr.atoms[start].rel] : -1, full_old, home[fr.head], novel[fr.head], rs);
+        eval_variant(c, fr, start, rows, true, rec.count(fr.atoms[start].rel) ? home[fr.atoms[start].rel] : -1, full_old, home[fr.head], novel[fr.head], rs);
     }
     for (auto& p : preds) {
         Keys full_old = canonical_keys(c, store_get(c, p), rs);
@@ -638,7 +666,7 @@ static void run_scc(xlb_ctx* c, const xlb_scc& scc, RunState& rs) {
                     if (j != i && store_get(c, fr.atoms[j].rel)->rows == 0 && c->world == 1) any_empty = true;
                 if (any_empty) continue;
                 Keys full = ops_rel_packed(c, store_get(c, fr.head));
-                eval_variant(c, fr, i, ops_rel_packed(c, d), home[fr.atoms[i].rel], full, home[fr.head], novel[fr.head], rs);
+                eval_variant(c, fr, i, ops_rel_packed(c, d), false, home[fr.atoms[i].rel], full, home[fr.head], novel[fr.head], rs);
             }
         }
         uint64_t changed = 0;
@@ -679,7 +707,9 @@ extern "C" xlb_status xlb_execute_plan(xlb_ctx* c, const xlb_plan* plan, xlb_run
     if (!c || !plan) return XLB_ERR_INVALID;
     RunState rs;
     cudaEvent_t e0 = nullptr, e1 = nullptr;
-    uint64_t launches0 = c->launches;
+    uint64_t launches0 = c->launches, syncs0 = c->syncs;
+    double wait0 = c->ms_sync_wait;
+    auto host_t0 = std::chrono::steady_clock::now();
     c->peak = c->allocated;
     xlb_status result = XLB_OK;
     try {
@@ -716,6 +746,9 @@ extern "C" xlb_status xlb_execute_plan(xlb_ctx* c, const xlb_plan* plan, xlb_run
     if (e0) cudaEventDestroy(e0);
     if (e1) cudaEventDestroy(e1);
     rs.st.kernel_launches = c->launches - launches0;
+    rs.st.host_syncs = c->syncs - syncs0;
+    rs.st.ms_host_wait = c->ms_sync_wait - wait0;
+    rs.st.ms_host_total = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - host_t0).count();
     rs.st.peak_bytes = c->peak;
     if (stats && result == XLB_OK) *stats = rs.st;
     return result;

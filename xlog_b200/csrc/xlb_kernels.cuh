@@ -206,24 +206,34 @@ static __global__ void __launch_bounds__(BLOCK) select_count_k(Pred pred, uint64
     if (threadIdx.x == 0) tile_counts[blockIdx.x] = tot;
 }
 
+// Each warp owns 256 consecutive rows and walks them 32 at a time, so reads are coalesced and
+// the predicate runs once per row; ballots give the stable position inside the warp.
 template <class Pred, class Emit>
 static __global__ void __launch_bounds__(BLOCK) select_write_k(Pred pred, Emit emit, uint64_t n, const uint64_t* tile_offsets, uint64_t* total) {
     __shared__ uint32_t sm[33];
-    uint64_t base = (uint64_t)blockIdx.x * SCAN_TILE + (uint64_t)threadIdx.x * SCAN_IPT;
-    bool f[SCAN_IPT];
-    uint32_t s = 0;
+    constexpr int ROUNDS = SCAN_TILE / BLOCK;  // 8 rounds of 32 rows per warp
+    const unsigned lane = lane_id(), warp = threadIdx.x >> 5;
+    const uint64_t wbase = (uint64_t)blockIdx.x * SCAN_TILE + (uint64_t)warp * (32 * ROUNDS);
+    unsigned flags[ROUNDS];
+    uint32_t cnt = 0;
 #pragma unroll
-    for (int k = 0; k < SCAN_IPT; ++k) {
-        uint64_t i = base + k;
-        f[k] = i < n && pred(i);
-        s += f[k];
+    for (int r = 0; r < ROUNDS; ++r) {
+        uint64_t i = wbase + r * 32 + lane;
+        bool f = i < n && pred(i);
+        flags[r] = __ballot_sync(FULL, f);
+        cnt += __popc(flags[r]);
     }
+    // every lane of a warp holds the warp's count: scan one value per warp
     uint32_t tot;
-    uint32_t ex = block_exclusive_scan<uint32_t>(s, &tot, sm);
+    uint32_t ex = block_exclusive_scan<uint32_t>(lane == 0 ? cnt : 0u, &tot, sm);
+    ex = __shfl_sync(FULL, ex, 0);
     uint64_t pos = (tile_offsets ? tile_offsets[blockIdx.x] : 0ull) + ex;
 #pragma unroll
-    for (int k = 0; k < SCAN_IPT; ++k)
-        if (f[k]) emit(base + k, pos++);
+    for (int r = 0; r < ROUNDS; ++r) {
+        unsigned b = flags[r];
+        if ((b >> lane) & 1u) emit(wbase + r * 32 + lane, pos + __popc(b & lanemask_lt()));
+        pos += __popc(b);
+    }
     if (!tile_offsets && threadIdx.x == 0) *total = tot;
 }
 
@@ -616,7 +626,9 @@ inline SortPlan plan_sort(xlb_ctx* c, const uint64_t* keys, uint64_t n) {
 
 // Sorts `n` keys ascending (stable).  keys/vals are replaced by buffers holding the result;
 // vals may be empty.  n must be below 2^32.
-inline void radix_sort(xlb_ctx* c, Buf& keys, Buf* vals, uint64_t n) {
+// `digit_mask` bit d set = digit d (bits 8d..8d+7) takes part in the order; a join index only
+// needs its rows grouped by the key half, i.e. digits 4..7.
+inline void radix_sort(xlb_ctx* c, Buf& keys, Buf* vals, uint64_t n, unsigned digit_mask = 0xFFu) {
     if (n <= 1) return;
     if (n >= (1ull << 32)) xlb_fail(XLB_ERR_CAPACITY, "sort of %llu keys exceeds the 2^32 limit of one sort", (unsigned long long)n);
     radix_sort_setup();
@@ -640,7 +652,7 @@ inline void radix_sort(xlb_ctx* c, Buf& keys, Buf* vals, uint64_t n) {
         read_words(c, varies, 8, v);
         int np = 0, digits[8];
         for (int d = 0; d < 8; ++d)
-            if (v[d]) digits[np++] = d;
+            if (v[d] && ((digit_mask >> d) & 1u)) digits[np++] = d;
         if (np == 0) return;
         uint64_t status_words = (uint64_t)ntiles * 256;
         Buf status = make_buf(c, (status_words * np + 8) * 4);  // per pass: tile status; then 8 tile counters
@@ -662,7 +674,9 @@ inline void radix_sort(xlb_ctx* c, Buf& keys, Buf* vals, uint64_t n) {
     }
     // 2^30 keys and more: per-tile histograms, a scan, then the scatter (counts exceed the
     // 30 bits of a look-back status word)
-    SortPlan p = plan_sort(c, keys->as<uint64_t>(), n);
+    SortPlan p0 = plan_sort(c, keys->as<uint64_t>(), n), p;
+    for (int q = 0; q < p0.npasses; ++q)
+        if ((digit_mask >> (p0.shifts[q] / 8)) & 1u) p.shifts[p.npasses++] = p0.shifts[q];
     if (p.npasses == 0) return;
     Buf hist = make_buf(c, (uint64_t)256 * ntiles * 4);
     Buf offs = make_buf(c, (uint64_t)256 * ntiles * 4);
@@ -767,6 +781,11 @@ struct PredKeep {
     const uint8_t* keep;
     __device__ __forceinline__ bool operator()(uint64_t i) const { return keep[i] != 0; }
 };
+struct PredKeepHead {  // first of a run of equal keys, and not found in the other set
+    const uint8_t* keep;
+    const uint64_t* k;
+    __device__ __forceinline__ bool operator()(uint64_t i) const { return keep[i] != 0 && (i == 0 || k[i] != k[i - 1]); }
+};
 struct EmitKey {
     const uint64_t* in;
     uint64_t* out;
@@ -782,13 +801,17 @@ inline uint64_t dedup_sorted(xlb_ctx* c, const uint64_t* in, uint64_t n, uint64_
     return select(c, PredHead{in}, EmitKey{in, out}, n);
 }
 
-// A \ B for sorted unique arrays.  Returns the result (exactly sized) and its length.
-inline Buf set_difference(xlb_ctx* c, const uint64_t* A, uint64_t na, const uint64_t* B, uint64_t nb, uint64_t* n_out) {
+// A \ B for a sorted array A (duplicates allowed when `a_has_dups`: they are dropped in the same
+// pass) and a sorted unique array B.  Returns the result and its length.
+inline Buf set_difference(xlb_ctx* c, const uint64_t* A, uint64_t na, const uint64_t* B, uint64_t nb, uint64_t* n_out, bool a_has_dups = false) {
     if (na == 0) { *n_out = 0; return make_buf(c, 0); }
     if (nb == 0) {
         Buf o = make_buf(c, na * 8);
-        CUDA_OK(cudaMemcpyAsync(o->p, A, na * 8, cudaMemcpyDeviceToDevice, c->stream));
-        *n_out = na;
+        if (a_has_dups) *n_out = dedup_sorted(c, A, na, o->as<uint64_t>());
+        else {
+            CUDA_OK(cudaMemcpyAsync(o->p, A, na * 8, cudaMemcpyDeviceToDevice, c->stream));
+            *n_out = na;
+        }
         return o;
     }
     uint64_t ntiles = (na + nb + MP_TILE - 1) / MP_TILE;
@@ -801,7 +824,8 @@ inline Buf set_difference(xlb_ctx* c, const uint64_t* A, uint64_t na, const uint
     mp_tile_k<0><<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(A, na, B, nb, splits->as<uint64_t>(), keep->as<uint8_t>(), nullptr);
     check_launch(c, "mp_diff");
     Buf tmp = make_buf(c, na * 8);
-    uint64_t m = select(c, PredKeep{keep->as<uint8_t>()}, EmitKey{A, tmp->as<uint64_t>()}, na);
+    uint64_t m = a_has_dups ? select(c, PredKeepHead{keep->as<uint8_t>(), A}, EmitKey{A, tmp->as<uint64_t>()}, na)
+                            : select(c, PredKeep{keep->as<uint8_t>()}, EmitKey{A, tmp->as<uint64_t>()}, na);
     *n_out = m;
     return tmp;
 }

@@ -237,6 +237,19 @@ Keys ops_copy(xlb_ctx* c, const Keys& in) {
     return o;
 }
 
+Keys ops_from_host(xlb_ctx* c, const uint64_t* rows, uint64_t n) {
+    if (n > 16) xlb_fail(XLB_ERR_INVALID, "internal: ops_from_host is for a handful of rows");
+    Keys o;
+    o.n = n;
+    o.buf = make_buf(c, n * 8);
+    for (uint64_t i = 0; i < n; ++i) c->h_scalar[40 + i] = rows[i];  // pinned staging words
+    if (n) {
+        CUDA_OK(cudaMemcpyAsync(o.buf->p, &c->h_scalar[40], n * 8, cudaMemcpyHostToDevice, c->stream));
+        stream_wait(c);
+    }
+    return o;
+}
+
 Keys ops_slice(xlb_ctx* c, const Keys& in, uint64_t lo, uint64_t hi) {
     Keys o;
     o.n = hi - lo;
@@ -258,6 +271,7 @@ Keys ops_concat(xlb_ctx* c, const std::vector<Keys>& parts) {
 }
 
 void ops_sort(xlb_ctx* c, Keys& k) { radix_sort(c, k.buf, nullptr, k.n); }
+void ops_sort_by_high_half(xlb_ctx* c, Keys& k) { radix_sort(c, k.buf, nullptr, k.n, 0xF0u); }
 
 void ops_dedup_sorted(xlb_ctx* c, Keys& k) {
     if (k.n <= 1) return;
@@ -269,6 +283,12 @@ void ops_dedup_sorted(xlb_ctx* c, Keys& k) {
 Keys ops_diff(xlb_ctx* c, const Keys& a, const Keys& b) {
     Keys o;
     o.buf = set_difference(c, a.ptr(), a.n, b.ptr(), b.n, &o.n);
+    return o;
+}
+
+Keys ops_dedup_diff(xlb_ctx* c, const Keys& a, const Keys& b) {
+    Keys o;
+    o.buf = set_difference(c, a.ptr(), a.n, b.ptr(), b.n, &o.n, true);
     return o;
 }
 

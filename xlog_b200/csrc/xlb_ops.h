@@ -31,11 +31,14 @@ void ops_rel_columns(xlb_ctx* c, const xlb_rel* r);            // materialise co
 xlb_rel* ops_rel_from_keys(xlb_ctx* c, const xlb_schema& s, Keys k, bool canonical);
 
 Keys ops_copy(xlb_ctx* c, const Keys& in);
+Keys ops_from_host(xlb_ctx* c, const uint64_t* rows, uint64_t n);  // small host arrays only (n <= 16)
 Keys ops_concat(xlb_ctx* c, const std::vector<Keys>& parts);
 Keys ops_slice(xlb_ctx* c, const Keys& in, uint64_t lo, uint64_t hi);  // copy of rows [lo, hi)
 void ops_sort(xlb_ctx* c, Keys& k);                              // ascending
+void ops_sort_by_high_half(xlb_ctx* c, Keys& k);                 // stable, by bits 32..63 only (groups rows by join key)
 void ops_dedup_sorted(xlb_ctx* c, Keys& k);                      // sorted -> sorted unique
 Keys ops_diff(xlb_ctx* c, const Keys& a, const Keys& b);         // sorted unique a \ sorted unique b
+Keys ops_dedup_diff(xlb_ctx* c, const Keys& a, const Keys& b);   // distinct rows of sorted a that are not in sorted unique b
 Keys ops_merge_disjoint(xlb_ctx* c, const Keys& a, const Keys& b);
 Keys ops_union(xlb_ctx* c, const Keys& a, const Keys& b);        // sorted unique a U b
 Keys ops_remap(xlb_ctx* c, const Keys& in, int hi_src, int lo_src);

@@ -122,15 +122,21 @@ def rmat_edges(scale: int, edge_factor: int, seed: int, a=0.57, b=0.19, c=0.19,
     return src, dst
 
 
-def rmat_graph(scale: int = 20, edge_factor: int = 16, seed: int | None = None):
-    """Config 2 input: R-MAT (a=.57 b=.19 c=.19 d=.05), self-loops and duplicates removed.
+def shuffle_rows(cols, seed: int):
+    """The same rows in a seeded pseudo-random order (deduplication leaves them sorted; a
+    consumer must not be handed that order for free)."""
+    perm = np.argsort(splitmix64(seed ^ 0x0DDC0FFEE, 0, len(cols[0])), kind="stable")
+    return tuple(np.ascontiguousarray(c[perm]) for c in cols)
 
-    Returned sorted by (src, dst) because deduplication sorts; the consumers do
-    not rely on that.
-    """
+
+def rmat_graph(scale: int = 20, edge_factor: int = 16, seed: int | None = None, shuffle: bool = True):
+    """Config 2 input: R-MAT (a=.57 b=.19 c=.19 d=.05), self-loops and duplicates removed,
+    rows in a seeded pseudo-random order (``shuffle=False`` keeps the (src, dst) order that
+    deduplication leaves)."""
     seed = config_seed(2) if seed is None else seed
     s, d = rmat_edges(scale, edge_factor, seed)
-    return _dedup_pairs(s, d)
+    out = _dedup_pairs(s, d)
+    return shuffle_rows(out, seed) if shuffle else out
 
 
 def rmat_dag(scale: int = 24, edge_factor: int = 8, bands: int = 64, seed: int | None = None):
