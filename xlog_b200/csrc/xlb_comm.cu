@@ -170,6 +170,7 @@ Keys comm_repartition(xlb_ctx* c, const Keys& in, int keysel, bool sorted_unique
     }
     Keys out;
     out.n = total;
+    out.bound = ~0ull;  // rows of other ranks: their bits are not known here
     out.buf = make_buf(c, total * 8);
     NCCL_OK(api().GroupStart());
     uint64_t so = 0, ro = 0;

@@ -171,6 +171,7 @@ struct xlb_rel {
     uint64_t rows = 0;
     mutable Buf cols[XLB_MAX_ARITY];
     mutable Buf packed;
+    mutable uint64_t or_bound = ~0ull;  // host-known upper bound of the OR of the packed rows (~0: unknown)
     bool canonical = false;
 };
 

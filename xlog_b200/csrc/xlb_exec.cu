@@ -255,11 +255,14 @@ static const Index& get_index(xlb_ctx* c, const std::string& name, int kc, RunSt
         ci.ix = Index();
         ci.ix.S = local.buf;
         ci.ix.n = local.n;
+        ci.ix.bound = local.bound;
         ci.version = ver;
         ci.table_ok = false;
     }
     if (!ci.table_ok) {
+        uint64_t b = ci.ix.bound;
         ci.ix = ops_index_build(c, ci.ix.S, ci.ix.n, 32, Buf());
+        ci.ix.bound = b;
         ci.table_ok = true;
     }
     return ci.ix;
@@ -283,25 +286,30 @@ static void indexes_on_merge(xlb_ctx* c, const std::string& name, const xlb_rel*
             Keys old;
             old.buf = ci.ix.S;
             old.n = ci.ix.n;
+            old.bound = ci.ix.bound;
             Keys extra = ops_diff(c, d, old);
             Keys m = ops_merge_disjoint(c, old, extra);
             ci.ix = Index();
             ci.ix.S = m.buf;
             ci.ix.n = m.n;
+            ci.ix.bound = m.bound;
         } else if (new_full->schema.arity == 2 && kc == 0) {
             ci.ix = Index();
             ci.ix.S = new_full->packed;  // alias: canonical order is key order
             ci.ix.n = new_full->rows;
+            ci.ix.bound = new_full->or_bound;
         } else {
             Keys d = new_full->schema.arity == 1 ? ops_remap(c, delta, SRC_LO, SRC_ZERO) : ops_remap(c, delta, SRC_LO, SRC_HI);
             if (new_full->schema.arity == 2) ops_sort(c, d);
             Keys old;
             old.buf = ci.ix.S;
             old.n = ci.ix.n;
+            old.bound = ci.ix.bound;
             Keys m = ops_merge_disjoint(c, old, d);
             ci.ix = Index();
             ci.ix.S = m.buf;
             ci.ix.n = m.n;
+            ci.ix.bound = m.bound;
         }
         ci.version = new_version;
         ci.table_ok = false;

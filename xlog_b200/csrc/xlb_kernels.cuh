@@ -455,35 +455,6 @@ static __global__ void __launch_bounds__(SORT_THREADS, XLB_SORT_MINB) radix_scat
     }
     __syncthreads();
 
-#ifdef XLB_RANK_PIPE
-    // Rank every key among the keys of its warp with the same digit, in memory order.  Three
-    // unrolled phases keep the shared-memory latency off the critical path: all matches, then one
-    // returning shared atomic per (round, digit group) issued back to back (the unit applies one
-    // warp's atomics in program order, so the returned value is the count of earlier rounds),
-    // then all broadcasts.
-    unsigned peers[SORT_IPT];
-#pragma unroll
-    for (int j = 0; j < SORT_IPT; ++j) {
-        unsigned t = wbase + j * 32 + lane;
-        unsigned d = t < valid ? (unsigned)((key[j] >> shift) & 255) : 255u;
-        peers[j] = match_digit(d);
-    }
-    unsigned before[SORT_IPT];
-#pragma unroll
-    for (int j = 0; j < SORT_IPT; ++j) {
-        unsigned t = wbase + j * 32 + lane;
-        unsigned d = t < valid ? (unsigned)((key[j] >> shift) & 255) : 255u;
-        before[j] = 0;
-        if (lane == (unsigned)(__ffs(peers[j]) - 1)) before[j] = atomicAdd(&whist[warp][d], (unsigned)__popc(peers[j]));
-    }
-#pragma unroll
-    for (int j = 0; j < SORT_IPT; ++j) {
-        unsigned b = __shfl_sync(FULL, before[j], __ffs(peers[j]) - 1);
-        rank[j] = (unsigned short)(b + __popc(peers[j] & lanemask_lt()));
-    }
-    __syncthreads();
-
-#else
     // rank every key among the keys of its warp with the same digit, in memory order
 #pragma unroll
     for (int j = 0; j < SORT_IPT; ++j) {
@@ -502,7 +473,6 @@ static __global__ void __launch_bounds__(SORT_THREADS, XLB_SORT_MINB) radix_scat
     }
     __syncthreads();
 
-#endif
     // per digit: exclusive prefix over warps, then exclusive prefix over digits
     {
         const bool dig = threadIdx.x < 256;
@@ -628,7 +598,9 @@ inline SortPlan plan_sort(xlb_ctx* c, const uint64_t* keys, uint64_t n) {
 // vals may be empty.  n must be below 2^32.
 // `digit_mask` bit d set = digit d (bits 8d..8d+7) takes part in the order; a join index only
 // needs its rows grouped by the key half, i.e. digits 4..7.
-inline void radix_sort(xlb_ctx* c, Buf& keys, Buf* vals, uint64_t n, unsigned digit_mask = 0xFFu) {
+// `known_bound` != ~0: an upper bound of the OR of all keys that the host already holds; digits
+// outside it are constant, so the digit plan needs no read-back.
+inline void radix_sort(xlb_ctx* c, Buf& keys, Buf* vals, uint64_t n, unsigned digit_mask = 0xFFu, uint64_t known_bound = ~0ull) {
     if (n <= 1) return;
     if (n >= (1ull << 32)) xlb_fail(XLB_ERR_CAPACITY, "sort of %llu keys exceeds the 2^32 limit of one sort", (unsigned long long)n);
     radix_sort_setup();
@@ -649,7 +621,11 @@ inline void radix_sort(xlb_ctx* c, Buf& keys, Buf* vals, uint64_t n, unsigned di
         radix_bases_k<<<1, BLOCK, 0, c->stream>>>(ghist, n, bases, varies);
         check_launch(c, "radix_bases");
         unsigned long long v[8];
-        read_words(c, varies, 8, v);
+        if (known_bound != ~0ull) {
+            for (int d = 0; d < 8; ++d) v[d] = (known_bound >> (8 * d)) & 255 ? 1 : 0;
+        } else {
+            read_words(c, varies, 8, v);
+        }
         int np = 0, digits[8];
         for (int d = 0; d < 8; ++d)
             if (v[d] && ((digit_mask >> d) & 1u)) digits[np++] = d;
@@ -974,23 +950,35 @@ static __global__ void __launch_bounds__(BLOCK) expand_k(const uint64_t* __restr
     uint64_t r0 = tile_row[blockIdx.x];
     uint64_t r1 = tile_row[blockIdx.x + 1];  // row owning the first output of the next tile (or nrows)
     if (r1 >= nrows) r1 = nrows - 1;
-    unsigned nr = (unsigned)(r1 - r0 + 1);  // every matched row has len >= 1, so nr <= EX_TILE + 1
-    for (unsigned i = threadIdx.x; i < nr; i += BLOCK) soff[i] = off[r0 + i];
+    // Probe rows without a match stay in the arrays (equal consecutive offsets), so a tile may span
+    // any number of rows; the usual span fits shared memory, a longer one is searched in place.
+    const uint64_t span = r1 - r0 + 1;
+    const bool in_smem = span <= (uint64_t)(EX_TILE + 2);
+    if (in_smem)
+        for (unsigned i = threadIdx.x; i < (unsigned)span; i += BLOCK) soff[i] = off[r0 + i];
     __syncthreads();
 #pragma unroll
     for (int k = 0; k < EX_IPT; ++k) {
         uint64_t o = o0 + (uint64_t)k * BLOCK + threadIdx.x;
         if (o >= o1) break;
-        unsigned lo = 0, hi = nr;  // first local row with soff > o
-        while (lo < hi) {
-            unsigned mid = (lo + hi) >> 1;
-            if (soff[mid] <= o) lo = mid + 1;
-            else hi = mid;
+        uint64_t lo = 0, hi = span;  // first row of the span with offset > o; the one before it owns o
+        if (in_smem) {
+            while (lo < hi) {
+                uint64_t mid = (lo + hi) >> 1;
+                if (soff[mid] <= o) lo = mid + 1;
+                else hi = mid;
+            }
+        } else {
+            while (lo < hi) {
+                uint64_t mid = (lo + hi) >> 1;
+                if (off[r0 + mid] <= o) lo = mid + 1;
+                else hi = mid;
+            }
         }
-        unsigned r = lo - 1;
-        uint64_t probe = mbag[r0 + r];
-        uint64_t start = mmatch[r0 + r] >> 32;
-        uint64_t j = start + (o - soff[r]);
+        uint64_t r = r0 + lo - 1;
+        uint64_t probe = mbag[r];
+        uint64_t start = mmatch[r] >> 32;
+        uint64_t j = start + (o - (in_smem ? soff[lo - 1] : off[r]));
         uint32_t other = pay ? pay[j] : (uint32_t)S[j];
         out[o] = ((uint64_t)ex_pick(hi_src, probe, other) << 32) | ex_pick(lo_src, probe, other);
     }

@@ -99,29 +99,65 @@ struct PredFlag {
     __device__ __forceinline__ bool operator()(uint64_t i) const { return (match[i] != 0) == want; }
 };
 
-// stable partition by owner rank
-__global__ void owner_count_k(const uint64_t* __restrict__ in, uint64_t n, int keysel, uint32_t world, unsigned long long* __restrict__ counts) {
+// Partition by owner rank in two sweeps: count per destination, then scatter.  Counters are kept
+// per block in shared memory; a block claims its slice of every destination's segment with one
+// global atomic per destination, so the hot counters see one update per 2048 rows.  Rows keep no
+// particular order inside a destination (they are sorted or re-indexed on arrival).
+constexpr int OWN_IPT = 8;
+__global__ void __launch_bounds__(BLOCK) owner_count_k(const uint64_t* __restrict__ in, uint64_t n, int keysel, uint32_t world, unsigned long long* __restrict__ counts) {
     __shared__ unsigned int sh[64];
     if (threadIdx.x < 64) sh[threadIdx.x] = 0;
     __syncthreads();
-    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
-        uint64_t k = in[i];
-        uint64_t key = keysel == 0 ? (k >> 32) : (k & 0xFFFFFFFFull);
-        atomicAdd(&sh[(uint32_t)(mix64(key) % world)], 1u);
+    uint64_t base = (uint64_t)blockIdx.x * (BLOCK * OWN_IPT);
+#pragma unroll
+    for (int k = 0; k < OWN_IPT; ++k) {
+        uint64_t i = base + (uint64_t)k * BLOCK + threadIdx.x;
+        if (i < n) {
+            uint64_t w = in[i];
+            uint64_t key = keysel == 0 ? (w >> 32) : (w & 0xFFFFFFFFull);
+            atomicAdd(&sh[(uint32_t)(mix64(key) % world)], 1u);
+        }
     }
     __syncthreads();
     if (threadIdx.x < world && sh[threadIdx.x]) atomicAdd(&counts[threadIdx.x], (unsigned long long)sh[threadIdx.x]);
 }
-struct PredOwner {
-    const uint64_t* in;
-    int keysel;
-    uint32_t world, want;
-    __device__ __forceinline__ bool operator()(uint64_t i) const {
-        uint64_t k = in[i];
-        uint64_t key = keysel == 0 ? (k >> 32) : (k & 0xFFFFFFFFull);
-        return (uint32_t)(mix64(key) % world) == want;
+// cursors[d] = start of destination d's segment (exclusive scan of the counts; world <= 64)
+__global__ void owner_starts_k(const unsigned long long* __restrict__ counts, uint32_t world, unsigned long long* __restrict__ cursors) {
+    if (threadIdx.x == 0) {
+        unsigned long long run = 0;
+        for (uint32_t d = 0; d < world; ++d) {
+            cursors[d] = run;
+            run += counts[d];
+        }
     }
-};
+}
+__global__ void __launch_bounds__(BLOCK) owner_scatter_k(const uint64_t* __restrict__ in, uint64_t n, int keysel, uint32_t world,
+                                                         unsigned long long* __restrict__ cursors, uint64_t* __restrict__ out) {
+    __shared__ unsigned int sh[64];
+    __shared__ unsigned long long sbase[64];
+    if (threadIdx.x < 64) sh[threadIdx.x] = 0;
+    __syncthreads();
+    uint64_t base = (uint64_t)blockIdx.x * (BLOCK * OWN_IPT);
+    uint64_t row[OWN_IPT];
+    unsigned dest[OWN_IPT], local[OWN_IPT];
+#pragma unroll
+    for (int k = 0; k < OWN_IPT; ++k) {
+        uint64_t i = base + (uint64_t)k * BLOCK + threadIdx.x;
+        dest[k] = 0xFFFFFFFFu;
+        if (i < n) {
+            row[k] = in[i];
+            uint64_t key = keysel == 0 ? (row[k] >> 32) : (row[k] & 0xFFFFFFFFull);
+            dest[k] = (uint32_t)(mix64(key) % world);
+            local[k] = atomicAdd(&sh[dest[k]], 1u);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x < world) sbase[threadIdx.x] = sh[threadIdx.x] ? atomicAdd(&cursors[threadIdx.x], (unsigned long long)sh[threadIdx.x]) : 0ull;
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < OWN_IPT; ++k)
+        if (dest[k] != 0xFFFFFFFFu) out[sbase[dest[k]] + local[k]] = row[k];
+}
 
 }  // namespace
 
@@ -195,6 +231,7 @@ extern "C" xlb_status xlb_profile_read(xlb_ctx* c, xlb_kernel_profile* out, uint
 Keys ops_rel_packed(xlb_ctx* c, const xlb_rel* r) {
     Keys k;
     k.n = r->rows;
+    k.bound = r->or_bound;
     if (r->packed) { k.buf = r->packed; return k; }
     if (!rel_packable(r->schema)) xlb_fail(XLB_ERR_UNSUPPORTED, "relation is not a one- or two-column 32-bit relation");
     Buf b = make_buf(c, r->rows * 8);
@@ -206,6 +243,18 @@ Keys ops_rel_packed(xlb_ctx* c, const xlb_rel* r) {
     }
     r->packed = b;
     k.buf = b;
+    if (r->rows) {  // one reduction per loaded relation: later sorts of anything derived from it skip a read-back
+        Buf oa = make_buf(c, 16);
+        CUDA_OK(cudaMemsetAsync(oa->p, 0, 8, c->stream));
+        CUDA_OK(cudaMemsetAsync((char*)oa->p + 8, 0xFF, 8, c->stream));
+        prof_begin(c, "radix_bits", r->rows * 8ull);
+        radix_bits_k<<<grid_for(c, r->rows, BLOCK * 8), BLOCK, 0, c->stream>>>(b->as<uint64_t>(), r->rows, oa->as<unsigned long long>());
+        check_launch(c, "radix_bits");
+        unsigned long long h[2];
+        read_words(c, oa->p, 2, h);
+        r->or_bound = h[0];
+    } else r->or_bound = 0;
+    k.bound = r->or_bound;
     return k;
 }
 
@@ -225,6 +274,7 @@ xlb_rel* ops_rel_from_keys(xlb_ctx* c, const xlb_schema& s, Keys k, bool canonic
     r->schema = s;
     r->rows = k.n;
     r->packed = k.buf ? k.buf : make_buf(c, 0);
+    r->or_bound = k.n ? k.bound : 0;
     r->canonical = canonical;
     return r;
 }
@@ -232,6 +282,7 @@ xlb_rel* ops_rel_from_keys(xlb_ctx* c, const xlb_schema& s, Keys k, bool canonic
 Keys ops_copy(xlb_ctx* c, const Keys& in) {
     Keys o;
     o.n = in.n;
+    o.bound = in.bound;
     o.buf = make_buf(c, in.n * 8);
     if (in.n) CUDA_OK(cudaMemcpyAsync(o.buf->p, in.buf->p, in.n * 8, cudaMemcpyDeviceToDevice, c->stream));
     return o;
@@ -241,6 +292,8 @@ Keys ops_from_host(xlb_ctx* c, const uint64_t* rows, uint64_t n) {
     if (n > 16) xlb_fail(XLB_ERR_INVALID, "internal: ops_from_host is for a handful of rows");
     Keys o;
     o.n = n;
+    o.bound = 0;
+    for (uint64_t i = 0; i < n; ++i) o.bound |= rows[i];
     o.buf = make_buf(c, n * 8);
     for (uint64_t i = 0; i < n; ++i) c->h_scalar[40 + i] = rows[i];  // pinned staging words
     if (n) {
@@ -253,6 +306,7 @@ Keys ops_from_host(xlb_ctx* c, const uint64_t* rows, uint64_t n) {
 Keys ops_slice(xlb_ctx* c, const Keys& in, uint64_t lo, uint64_t hi) {
     Keys o;
     o.n = hi - lo;
+    o.bound = in.bound;
     o.buf = make_buf(c, o.n * 8);
     if (o.n) CUDA_OK(cudaMemcpyAsync(o.buf->p, in.ptr() + lo, o.n * 8, cudaMemcpyDeviceToDevice, c->stream));
     return o;
@@ -260,7 +314,11 @@ Keys ops_slice(xlb_ctx* c, const Keys& in, uint64_t lo, uint64_t hi) {
 
 Keys ops_concat(xlb_ctx* c, const std::vector<Keys>& parts) {
     Keys o;
-    for (auto& p : parts) o.n += p.n;
+    o.bound = 0;
+    for (auto& p : parts) {
+        o.n += p.n;
+        if (p.n) o.bound |= p.bound;
+    }
     o.buf = make_buf(c, o.n * 8);
     uint64_t at = 0;
     for (auto& p : parts) {
@@ -270,8 +328,8 @@ Keys ops_concat(xlb_ctx* c, const std::vector<Keys>& parts) {
     return o;
 }
 
-void ops_sort(xlb_ctx* c, Keys& k) { radix_sort(c, k.buf, nullptr, k.n); }
-void ops_sort_by_high_half(xlb_ctx* c, Keys& k) { radix_sort(c, k.buf, nullptr, k.n, 0xF0u); }
+void ops_sort(xlb_ctx* c, Keys& k) { radix_sort(c, k.buf, nullptr, k.n, 0xFFu, k.bound); }
+void ops_sort_by_high_half(xlb_ctx* c, Keys& k) { radix_sort(c, k.buf, nullptr, k.n, 0xF0u, k.bound); }
 
 void ops_dedup_sorted(xlb_ctx* c, Keys& k) {
     if (k.n <= 1) return;
@@ -282,18 +340,21 @@ void ops_dedup_sorted(xlb_ctx* c, Keys& k) {
 
 Keys ops_diff(xlb_ctx* c, const Keys& a, const Keys& b) {
     Keys o;
+    o.bound = a.bound;
     o.buf = set_difference(c, a.ptr(), a.n, b.ptr(), b.n, &o.n);
     return o;
 }
 
 Keys ops_dedup_diff(xlb_ctx* c, const Keys& a, const Keys& b) {
     Keys o;
+    o.bound = a.bound;
     o.buf = set_difference(c, a.ptr(), a.n, b.ptr(), b.n, &o.n, true);
     return o;
 }
 
 Keys ops_merge_disjoint(xlb_ctx* c, const Keys& a, const Keys& b) {
     Keys o;
+    o.bound = (a.n ? a.bound : 0) | (b.n ? b.bound : 0);
     o.n = a.n + b.n;
     o.buf = merge_disjoint(c, a.ptr(), a.n, b.ptr(), b.n);
     return o;
@@ -308,9 +369,15 @@ Keys ops_union(xlb_ctx* c, const Keys& a, const Keys& b) {
     return ops_merge_disjoint(c, big, extra);
 }
 
+static uint64_t half_bound(uint64_t bound, int src, uint64_t other) {
+    if (bound == ~0ull && src != SRC_OTHER && src != SRC_ZERO) return 0xFFFFFFFFull;
+    return src == SRC_HI ? (bound >> 32) : src == SRC_LO ? (bound & 0xFFFFFFFFull) : src == SRC_OTHER ? other : 0;
+}
+
 Keys ops_remap(xlb_ctx* c, const Keys& in, int hi_src, int lo_src) {
     Keys o;
     o.n = in.n;
+    o.bound = (half_bound(in.bound, hi_src, 0) << 32) | half_bound(in.bound, lo_src, 0);
     o.buf = make_buf(c, in.n * 8);
     if (in.n) {
         prof_begin(c, "remap", 0);
@@ -322,6 +389,7 @@ Keys ops_remap(xlb_ctx* c, const Keys& in, int hi_src, int lo_src) {
 
 Keys ops_filter(xlb_ctx* c, const Keys& in, uint32_t cmp, int lhs_src, bool rhs_is_const, uint64_t rhs) {
     Keys o;
+    o.bound = in.bound;
     o.buf = make_buf(c, in.n * 8);
     o.n = select(c, PredCmp{in.ptr(), cmp, lhs_src, rhs_is_const, rhs}, EmitKey{in.ptr(), o.buf->as<uint64_t>()}, in.n);
     return o;
@@ -367,27 +435,27 @@ Buf ops_probe_match(xlb_ctx* c, const Keys& bag, int keysel, const uint64_t* pke
 
 Keys ops_join_expand(xlb_ctx* c, const Keys& bag, int keysel, const uint64_t* pkeys, const Index& ix, int hi_src, int lo_src) {
     Keys out;
+    uint64_t other_bound = ix.pay ? 0xFFFFFFFFull : (ix.bound == ~0ull ? 0xFFFFFFFFull : (ix.bound & 0xFFFFFFFFull));
+    out.bound = (half_bound(bag.bound, hi_src, other_bound) << 32) | half_bound(bag.bound, lo_src, other_bound);
     if (bag.n == 0 || ix.n == 0) { out.buf = make_buf(c, 0); return out; }
+    // probe, prefix-sum the match lengths over all probe rows (rows without a match keep length 0),
+    // then a load-balanced expansion: one count read-back per join step
     Buf match = ops_probe_match(c, bag, keysel, pkeys, ix);
-    // keep the probe rows that matched, so every remaining row expands to at least one output
-    Buf mbag = make_buf(c, bag.n * 8), mmatch = make_buf(c, bag.n * 8);
-    uint64_t nm = select(c, PredMatched{match->as<uint64_t>()}, EmitMatched{bag.ptr(), match->as<uint64_t>(), mbag->as<uint64_t>(), mmatch->as<uint64_t>()}, bag.n);
-    match.reset();
-    if (nm == 0) { out.buf = make_buf(c, 0); return out; }
-    Buf off = make_buf(c, nm * 8);
+    Buf off = make_buf(c, bag.n * 8);
     Buf total = make_buf(c, 8);
-    exclusive_scan<LoadLow32, uint64_t>(c, LoadLow32{mmatch->as<uint64_t>()}, nm, off->as<uint64_t>(), total->as<uint64_t>());
+    exclusive_scan<LoadLow32, uint64_t>(c, LoadLow32{match->as<uint64_t>()}, bag.n, off->as<uint64_t>(), total->as<uint64_t>());
     unsigned long long tot;
     read_words(c, total->p, 1, &tot);
     out.n = tot;
     out.buf = make_buf(c, tot * 8);
+    if (tot == 0) return out;
     uint64_t ntiles = (tot + EX_TILE - 1) / EX_TILE;
     Buf tile_row = make_buf(c, (ntiles + 1) * 8);
     prof_begin(c, "expand_partition", 0);
-    expand_partition_k<<<(unsigned)((ntiles + 1 + 127) / 128), 128, 0, c->stream>>>(off->as<uint64_t>(), nm, tot, tile_row->as<uint64_t>(), ntiles);
+    expand_partition_k<<<(unsigned)((ntiles + 1 + 127) / 128), 128, 0, c->stream>>>(off->as<uint64_t>(), bag.n, tot, tile_row->as<uint64_t>(), ntiles);
     check_launch(c, "expand_partition");
-    prof_begin(c, "expand", tot * 12ull + nm * 24ull);
-    expand_k<<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(mbag->as<uint64_t>(), mmatch->as<uint64_t>(), off->as<uint64_t>(), nm, tot, tile_row->as<uint64_t>(),
+    prof_begin(c, "expand", tot * 12ull + bag.n * 24ull);
+    expand_k<<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(bag.ptr(), match->as<uint64_t>(), off->as<uint64_t>(), bag.n, tot, tile_row->as<uint64_t>(),
                                                          ix.S->as<uint64_t>(), ix.pay ? ix.pay->as<uint32_t>() : nullptr, hi_src, lo_src, out.buf->as<uint64_t>());
     check_launch(c, "expand");
     return out;
@@ -396,15 +464,28 @@ Keys ops_join_expand(xlb_ctx* c, const Keys& bag, int keysel, const uint64_t* pk
 Keys ops_partition_by_owner(xlb_ctx* c, const Keys& in, int keysel, uint32_t world, std::vector<uint64_t>& counts_out) {
     counts_out.assign(world, 0);
     Keys out;
+    out.bound = in.bound;
     out.n = in.n;
     out.buf = make_buf(c, in.n * 8);
     if (in.n == 0) return out;
-    uint64_t at = 0;
-    for (uint32_t r = 0; r < world; ++r) {  // one stable compaction per destination rank
-        uint64_t m = select(c, PredOwner{in.ptr(), keysel, world, r}, EmitKey{in.ptr(), out.buf->as<uint64_t>() + at}, in.n);
-        counts_out[r] = m;
-        at += m;
-    }
+    if (world > 64) xlb_fail(XLB_ERR_UNSUPPORTED, "at most 64 ranks");
+    Buf cnt = make_buf(c, 2 * 64 * 8);  // counts | cursors
+    unsigned long long* counts = cnt->as<unsigned long long>();
+    unsigned long long* cursors = counts + 64;
+    CUDA_OK(cudaMemsetAsync(counts, 0, 64 * 8, c->stream));
+    unsigned grid = (unsigned)((in.n + BLOCK * OWN_IPT - 1) / (BLOCK * OWN_IPT));
+    prof_begin(c, "owner_count", in.n * 8ull);
+    owner_count_k<<<grid, BLOCK, 0, c->stream>>>(in.ptr(), in.n, keysel, world, counts);
+    check_launch(c, "owner_count");
+    prof_begin(c, "owner_starts", 0);
+    owner_starts_k<<<1, 32, 0, c->stream>>>(counts, world, cursors);
+    check_launch(c, "owner_starts");
+    prof_begin(c, "owner_scatter", in.n * 16ull);
+    owner_scatter_k<<<grid, BLOCK, 0, c->stream>>>(in.ptr(), in.n, keysel, world, cursors, out.buf->as<uint64_t>());
+    check_launch(c, "owner_scatter");
+    unsigned long long h[64];
+    read_words(c, counts, (int)world, h);
+    for (uint32_t r = 0; r < world; ++r) counts_out[r] = h[r];
     return out;
 }
 

@@ -8,6 +8,7 @@
 struct Keys {
     Buf buf;
     uint64_t n = 0;
+    uint64_t bound = ~0ull;  // host-known upper bound of the OR of all rows (~0: unknown)
     const uint64_t* ptr() const { return buf ? buf->as<uint64_t>() : nullptr; }
 };
 
@@ -24,6 +25,7 @@ struct Index {
     Buf table;         // ulonglong2 slots
     uint64_t mask = 0; // capacity - 1
     uint64_t nkeys = 0;
+    uint64_t bound = ~0ull;  // OR bound of the rows of S
 };
 
 Keys ops_rel_packed(xlb_ctx* c, const xlb_rel* r);             // packed view (cached on the relation)
