@@ -74,21 +74,58 @@ def _u32s(xs):
     return (C.c_uint32 * max(len(xs), 1))(*xs)
 
 
-class OracleRel:
-    """Host relation: a list of equal-length numpy columns of one width (uint32 or uint64)."""
+def _to_ordered(c: np.ndarray) -> np.ndarray:
+    """Order-preserving unsigned image of a typed column: sign flip for signed integers, IEEE
+    totalOrder for floats (the reference's key transforms, kernels/sort.cu:296-448,
+    kernels/totalorder.cuh); unsigned columns pass through."""
+    k = c.dtype.kind
+    if k == "u":
+        return c
+    u = c.view(np.uint32 if c.dtype.itemsize == 4 else np.uint64)
+    sign = u.dtype.type(1) << u.dtype.type(c.dtype.itemsize * 8 - 1)
+    if k == "i":
+        return u ^ sign
+    return np.where(u & sign, ~u, u | sign)
 
-    def __init__(self, handle):
+
+def _from_ordered(u: np.ndarray, dtype) -> np.ndarray:
+    dtype = np.dtype(dtype)
+    if dtype.kind == "u":
+        return u
+    sign = u.dtype.type(1) << u.dtype.type(dtype.itemsize * 8 - 1)
+    raw = (u ^ sign) if dtype.kind == "i" else np.where(u & sign, u ^ sign, ~u)
+    return raw.astype(u.dtype).view(dtype)
+
+
+class OracleRel:
+    """Host relation: equal-length numpy columns of one width class (4 or 8 bytes).  Signed and
+    floating columns are held as their order-preserving unsigned images."""
+
+    def __init__(self, handle, dtypes=None):
         if not handle:
             raise ValueError("oracle operator rejected its inputs")
         self._h = handle
+        self.dtypes = dtypes
 
     @classmethod
-    def from_columns(cls, cols, dtype=np.uint32, arity=None):
-        cols = [np.ascontiguousarray(c, dtype=dtype) for c in cols]
+    def from_columns(cls, cols, dtype=None, arity=None):
+        if dtype is not None:
+            cols = [np.ascontiguousarray(c, dtype=dtype) for c in cols]
+        else:
+            cols = [np.ascontiguousarray(c) for c in cols]
+            cols = [c if c.dtype.itemsize in (4, 8) and c.dtype.kind in "uif" else c.astype(np.uint32) for c in cols]
+        dtypes = [c.dtype for c in cols]
+        width = dtypes[0].itemsize if dtypes else (np.dtype(dtype).itemsize if dtype is not None else 4)
+        if any(d.itemsize != width for d in dtypes):
+            raise ValueError("the oracle takes columns of one width class")
+        ucols = [np.ascontiguousarray(_to_ordered(c)) for c in cols]
         arity = len(cols) if arity is None else arity
         rows = len(cols[0]) if cols else 0
-        ptrs = (C.c_void_p * max(arity, 1))(*[c.ctypes.data for c in cols])
-        return cls(lib().xo_rel_from_cols(arity, np.dtype(dtype).itemsize, ptrs, rows))
+        ptrs = (C.c_void_p * max(arity, 1))(*[c.ctypes.data for c in ucols])
+        return cls(lib().xo_rel_from_cols(arity, width, ptrs, rows), dtypes)
+
+    def _like(self, handle, dtypes=None):
+        return OracleRel(handle, self.dtypes if dtypes is None else dtypes)
 
     @property
     def rows(self):
@@ -107,6 +144,8 @@ class OracleRel:
         cols = [np.empty(self.rows, dtype=dt) for _ in range(self.arity)]
         ptrs = (C.c_void_p * max(self.arity, 1))(*[c.ctypes.data for c in cols])
         lib().xo_rel_to_cols(self._h, ptrs)
+        if self.dtypes and len(self.dtypes) == len(cols):
+            cols = [_from_ordered(c, d) for c, d in zip(cols, self.dtypes)]
         return cols
 
     def tuples(self):
@@ -118,25 +157,37 @@ class OracleRel:
             self._h = None
 
 
+def _same_types(rels):
+    d0 = [np.dtype(d) for d in (rels[0].dtypes or [])]
+    for r in rels[1:]:
+        if [np.dtype(d) for d in (r.dtypes or [])] != d0:
+            raise ValueError("incompatible column types")
+
+
 def sort(r, keys):
-    return OracleRel(lib().xo_sort(r._h, _u32s(keys), len(keys)))
+    return r._like(lib().xo_sort(r._h, _u32s(keys), len(keys)))
 
 
 def dedup(r, keys=()):
-    return OracleRel(lib().xo_dedup(r._h, _u32s(keys), len(keys)))
+    return r._like(lib().xo_dedup(r._h, _u32s(keys), len(keys)))
 
 
 def union_many(rels):
+    if not rels:
+        raise ValueError("union of no inputs")
+    _same_types(rels)
     arr = (C.c_void_p * max(len(rels), 1))(*[r._h for r in rels])
-    return OracleRel(lib().xo_union(arr, len(rels)))
+    return rels[0]._like(lib().xo_union(arr, len(rels)))
 
 
 def diff(a, b):
-    return OracleRel(lib().xo_diff(a._h, b._h))
+    _same_types([a, b])
+    return a._like(lib().xo_diff(a._h, b._h))
 
 
 def hash_join(l, r, lk, rk, join_type=0):
-    return OracleRel(lib().xo_hash_join(l._h, r._h, _u32s(lk), _u32s(rk), len(lk), join_type))
+    dt = (l.dtypes or []) + (r.dtypes or []) if join_type == 0 else l.dtypes
+    return OracleRel(lib().xo_hash_join(l._h, r._h, _u32s(lk), _u32s(rk), len(lk), join_type), dt)
 
 
 class OracleExecutor:

@@ -94,6 +94,29 @@ def operators():
     add("union", SO + ":452-478 (rows shifted to non-negative values)", [[0, 12, 13], [6, 7, 8], [8, 35, 4], [14, 5, 1]],
         types=["u64", "u64", "u64"],
         ins=[[[8, 35, 4], [0, 12, 13]], [[6, 7, 8], [8, 35, 4]], [[0, 12, 13], [14, 5, 1], [6, 7, 8]]])
+    # ---- typed order: signed integers and floats ------------------------------------------------
+    i8, f8, i4 = ["i64"], ["f64"], ["i32"]
+    add("union", SO + ":1400-1423", rows1([-10, -5, 0, 5, 10, 20]), types=i8, ins=[rows1([-10, -5, 0, 5]), rows1([-5, 0, 10, 20])])
+    add("union", SO + ":1426-1450", rows1([-5, 0, 5]), types=i8, ins=[rows1([-5, -5, 0]), rows1([0, 5, 5])])
+    add("union", SO + ":1453-1475", rows1([1.5, 2.5, 3.5, 4.5]), types=f8, ins=[rows1([1.5, 2.5, 3.5]), rows1([2.5, 3.5, 4.5])])
+    add("union", SO + ":1478-1502", rows1([1.5, 2.5, 3.5]), types=f8, ins=[rows1([1.5, 1.5, 2.5]), rows1([2.5, 3.5, 3.5])])
+    add("diff", SO + ":1505-1527", rows1([-10, 0, 10]), types=i8, a=rows1([-10, -5, 0, 5, 10]), b=rows1([-5, 5]))
+    add("diff", SO + ":1530-1554", rows1([-10, -5, 0]), types=i8, a=rows1([-10, -5, 0]), b=rows1([5, 10, 15]))
+    add("diff", SO + ":1557-1579", rows1([1.5, 3.5]), types=f8, a=rows1([1.5, 2.5, 3.5, 4.5]), b=rows1([2.5, 4.5]))
+    add("diff", SO + ":1582-1604", rows1([1.5, 2.5, 3.5]), types=f8, a=rows1([1.5, 2.5, 3.5]), b=rows1([4.5, 5.5, 6.5]))
+    add("union", SO + ":452-478 (i64 triples, signed order)", [[-5, 7, 8], [1, 2, 3], [3, 30, -1], [9, 0, -4]], types=["i64"] * 3,
+        ins=[[[3, 30, -1], [-5, 7, 8]], [[1, 2, 3], [3, 30, -1]], [[-5, 7, 8], [9, 0, -4], [1, 2, 3]]])
+    add("dedup", FR + ":170-183", rows1([-2, -1, 0, 1]), types=i4, a=rows1([-2, -1, 0, 1, -1, -2, 0]))
+    add("diff", FR + ":185-201", rows1([-3, 0, 3]), types=i4, a=rows1([-3, -1, 0, 1, 3]), b=rows1([-1, 1]))
+    # f32 rows are given as bit patterns; the reference compares these as sets of bit patterns
+    fb = ["f32bits"]
+    NAN_A, NAN_B, ONE, PZ, NZ, PINF, NINF = 0x7FC00001, 0x7FC00002, 0x3F800000, 0x00000000, 0x80000000, 0x7F800000, 0xFF800000
+    add("dedup", FR + ":234-245 (NaNs collapse only when bit-identical)", rows1(sorted([NAN_A, ONE])), types=fb, a=rows1([NAN_A, NAN_A, ONE]), compare="set")
+    add("dedup", FR + ":247-258", rows1(sorted([NAN_A, NAN_B])), types=fb, a=rows1([NAN_A, NAN_B]), compare="set")
+    add("dedup", FR + ":260-272 (signed zeros are distinct)", rows1(sorted([PZ, NZ])), types=fb, a=rows1([PZ, NZ, PZ]), compare="set")
+    add("dedup", FR + ":274-286", rows1(sorted([PINF, NINF, ONE])), types=fb, a=rows1([PINF, NINF, PINF, ONE]), compare="set")
+    add("diff", FR + ":288-298", rows1([NAN_A]), types=fb, a=rows1([NAN_A]), b=rows1([NAN_B]), compare="set")
+    add("diff", FR + ":300-310", rows1([PZ]), types=fb, a=rows1([PZ]), b=rows1([NZ]), compare="set")
     # ---- joins -----------------------------------------------------------------------------------
     add("join", JV + ":14-48 (2 rows, arity 4)", [[2, 20, 2, 200], [3, 30, 3, 300]], types=t2, rtypes=t2,
         a=[[1, 10], [2, 20], [3, 30]], b=[[2, 200], [3, 300], [4, 400]], lk=[0], rk=[0], join="inner")

@@ -158,3 +158,48 @@ def test_unsupported_rule_shape_is_refused_not_miscomputed():
         run_program(p, plan, {"edge": [c0, c1]}, ["tri"])
     assert e.value.status == A.ERR_UNSUPPORTED
     p.close()
+
+
+def _dag_closure_size(c0, c1, n):
+    """|TC| of a DAG whose edges go from lower to higher ids: descendant bitsets, highest id first."""
+    words = (n + 63) // 64
+    desc = np.zeros((n, words), dtype=np.uint64)
+    order = np.argsort(c0, kind="stable")
+    s, d = c0[order], c1[order]
+    starts = np.searchsorted(s, np.arange(n + 1))
+    for v in range(n - 1, -1, -1):
+        kids = d[starts[v]:starts[v + 1]]
+        if len(kids):
+            row = np.bitwise_or.reduce(desc[kids], axis=0)
+            np.bitwise_or.at(row, kids >> 6, np.uint64(1) << (kids & 63).astype(np.uint64))
+            desc[v] = row
+    return int(np.bitwise_count(desc).sum(dtype=np.uint64))
+
+
+def test_rmat_dag_closure_scale_15_properties():
+    """A closure of tens of millions of tuples: too large for the oracle in test time, so checked by
+    what does not depend on size: the count against an independent bitset closure, sorted-unique
+    order, every input edge present, and closure under one more join step on a sample of tuples."""
+    n = 1 << 15
+    c0, c1 = workloads.rmat_dag(15, 8)
+    p = fresh()
+    got, stats = run_program(p, programs.transitive_closure(), {"edge": [c0, c1]}, ["reach"])
+    r0, r1 = got["reach"]
+    assert len(r0) == _dag_closure_size(c0, c1, n) == stats["derived_tuples"]
+    k = (r0.astype(np.uint64) << np.uint64(32)) | r1
+    assert np.all(k[1:] > k[:-1])
+    assert np.all(np.isin((c0.astype(np.uint64) << np.uint64(32)) | c1, k))
+    # closure under one more step, on a sample: (x, y) in reach and edge(y, z) imply (x, z) in reach
+    order = np.argsort(c0, kind="stable")
+    s0, s1 = c0[order], c1[order]
+    starts = np.searchsorted(s0, np.arange(n + 1))
+    pick = (workloads.splitmix64(77, 0, 200_000) % np.uint64(len(r0))).astype(np.int64)
+    x, y = r0[pick], r1[pick]
+    deg = (starts[y + 1] - starts[y]).astype(np.int64)
+    xs = np.repeat(x, deg)
+    offs = np.arange(deg.sum()) - np.repeat(np.cumsum(deg) - deg, deg)
+    zs = s1[np.repeat(starts[y], deg) + offs]
+    want = (xs.astype(np.uint64) << np.uint64(32)) | zs
+    pos = np.searchsorted(k, want)
+    assert np.all(k[np.minimum(pos, len(k) - 1)] == want)
+    p.close()

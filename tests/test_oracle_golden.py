@@ -11,7 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 OPS = json.load(open(os.path.join(HERE, "golden", "operators.json")))
 PROGS = json.load(open(os.path.join(HERE, "golden", "programs.json")))
 
-DT = {"u32": np.uint32, "u64": np.uint64}
+DT = {"u32": np.uint32, "u64": np.uint64, "i32": np.int32, "i64": np.int64, "f64": np.float64, "f32bits": np.float32}
 PLANS = {"tc": programs.transitive_closure, "tc_left": programs.transitive_closure_left_linear,
          "tc_nonlinear": programs.transitive_closure_nonlinear, "tc_swapped": programs.transitive_closure_swapped_head,
          "points_to_copy": programs.points_to_copy, "same_generation": programs.same_generation,
@@ -22,12 +22,28 @@ RENAME = {"tc": {"q": "reach"}, "tc_left": {"q": "reach"}, "tc_nonlinear": {"q":
 
 
 def cols_of(rows, types):
-    dt = [DT[t] for t in types]
-    return [np.array([r[i] for r in rows], dtype=dt[i]) for i in range(len(types))]
+    out = []
+    for i, t in enumerate(types):
+        vals = [r[i] for r in rows]
+        if t == "f32bits":          # rows carry IEEE bit patterns
+            out.append(np.array(vals, dtype=np.uint32).view(np.float32))
+        else:
+            out.append(np.array(vals, dtype=DT[t]))
+    return out
 
 
 def rows_of(cols):
-    return [list(map(int, t)) for t in zip(*[c.tolist() for c in cols])] if cols and len(cols[0]) else []
+    if not cols or not len(cols[0]):
+        return []
+    lists = [c.view(np.uint32).tolist() if c.dtype == np.float32 else c.tolist() for c in cols]
+    return [list(t) for t in zip(*lists)]
+
+
+def expected_of(case, got):
+    """(got, want) in comparable form: joins and bit-pattern cases compare as sorted sets."""
+    if case["op"] == "join" or case.get("compare") == "set":
+        return sorted(got), sorted(case["expected"])
+    return got, case["expected"]
 
 
 def run_operator_case(case, make, ops):
@@ -44,7 +60,7 @@ def run_operator_case(case, make, ops):
     if op == "join":
         jt = {"inner": 0, "semi": 1, "anti": 2}[case["join"]]
         out = ops.hash_join(make(case["a"], case["types"]), make(case["b"], case["rtypes"]), case["lk"], case["rk"], jt)
-        return sorted(ops.rows(out))
+        return ops.rows(out)
     raise AssertionError(op)
 
 
@@ -53,8 +69,8 @@ class OracleOps:
         self.O = O
 
     def make(self, rows, types):
-        dt = DT[types[0]]
-        return self.O.OracleRel.from_columns(cols_of(rows, types), dtype=dt, arity=len(types))
+        return self.O.OracleRel.from_columns(cols_of(rows, types), arity=len(types)) if rows else \
+            self.O.OracleRel.from_columns([np.zeros(0, dtype=DT[t]) for t in types], arity=len(types))
 
     def rows(self, r):
         return rows_of(r.columns())
@@ -78,8 +94,7 @@ class OracleOps:
 @pytest.mark.parametrize("case", [c for c in OPS if not c["op"].endswith("_error")], ids=lambda c: c["op"] + "@" + c["cite"].split(" ")[0])
 def test_oracle_operator_kat(oracle, case):
     ops = OracleOps(oracle)
-    got = run_operator_case(case, ops.make, ops)
-    want = sorted(case["expected"]) if case["op"] == "join" else case["expected"]
+    got, want = expected_of(case, run_operator_case(case, ops.make, ops))
     assert got == want, case["cite"]
 
 

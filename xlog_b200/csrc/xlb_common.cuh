@@ -182,10 +182,11 @@ inline uint32_t type_width(uint8_t t) {
         default: return 1;
     }
 }
-inline bool type_built(uint8_t t) { return t == XLB_U32 || t == XLB_SYMBOL || t == XLB_U64; }
+inline bool type_built(uint8_t t) { return t != XLB_BOOL && t <= XLB_SYMBOL; }
+inline bool type_unsigned(uint8_t t) { return t == XLB_U32 || t == XLB_SYMBOL || t == XLB_U64; }
 inline bool rel_packable(const xlb_schema& s) {
     if (s.arity < 1 || s.arity > 2) return false;
     for (uint32_t i = 0; i < s.arity; ++i)
-        if (type_width(s.types[i]) != 4) return false;
+        if (s.types[i] != XLB_U32 && s.types[i] != XLB_SYMBOL) return false;
     return true;
 }

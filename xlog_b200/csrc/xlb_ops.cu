@@ -578,7 +578,7 @@ extern "C" xlb_status xlb_memory_stats(const xlb_ctx* c, uint64_t* allocated, ui
 static void check_schema(const xlb_schema* s) {
     if (!s || s->arity > XLB_MAX_ARITY) xlb_fail(XLB_ERR_INVALID, "schema missing or arity above %u", XLB_MAX_ARITY);
     for (uint32_t i = 0; i < s->arity; ++i)
-        if (!type_built(s->types[i])) xlb_fail(XLB_ERR_UNSUPPORTED, "column %u: type code %u is not built (u32, u64 and symbol are)", i, s->types[i]);
+        if (!type_built(s->types[i])) xlb_fail(XLB_ERR_UNSUPPORTED, "column %u: type code %u is not built (u32, u64, i32, i64, f32, f64 and symbol are)", i, s->types[i]);
 }
 
 static xlb_rel* rel_empty(xlb_ctx* c, const xlb_schema& s) {
@@ -780,7 +780,7 @@ static xlb_rel* gather_rel(xlb_ctx* c, const xlb_rel* r, const uint32_t* idx, ui
     return o.release();
 }
 
-extern "C" xlb_status xlb_sort(xlb_ctx* c, const xlb_rel* in, const uint32_t* key_cols, uint32_t nk, xlb_rel** out) {
+static xlb_status sort_unsigned(xlb_ctx* c, const xlb_rel* in, const uint32_t* key_cols, uint32_t nk, xlb_rel** out) {
     if (!c || !in || !out) return XLB_ERR_INVALID;
     API_BEGIN(c)
     for (uint32_t i = 0; i < nk; ++i)
@@ -847,7 +847,7 @@ static xlb_rel* canonicalize(xlb_ctx* c, const xlb_rel* in) {
     return wide_dedup(c, in, nullptr, 0);
 }
 
-extern "C" xlb_status xlb_dedup(xlb_ctx* c, const xlb_rel* in, const uint32_t* key_cols, uint32_t nk, xlb_rel** out) {
+static xlb_status dedup_unsigned(xlb_ctx* c, const xlb_rel* in, const uint32_t* key_cols, uint32_t nk, xlb_rel** out) {
     if (!c || !in || !out) return XLB_ERR_INVALID;
     API_BEGIN(c)
     bool full = nk == 0 || nk >= in->schema.arity;
@@ -873,7 +873,7 @@ extern "C" xlb_status xlb_dedup(xlb_ctx* c, const xlb_rel* in, const uint32_t* k
     API_END()
 }
 
-extern "C" xlb_status xlb_union(xlb_ctx* c, const xlb_rel* const* ins, uint32_t n, xlb_rel** out) {
+static xlb_status union_unsigned(xlb_ctx* c, const xlb_rel* const* ins, uint32_t n, xlb_rel** out) {
     if (!c || !out) return XLB_ERR_INVALID;
     API_BEGIN(c)
     if (n == 0 || !ins) xlb_fail(XLB_ERR_INVALID, "union of no inputs");
@@ -926,7 +926,7 @@ extern "C" xlb_status xlb_union(xlb_ctx* c, const xlb_rel* const* ins, uint32_t 
     API_END()
 }
 
-extern "C" xlb_status xlb_diff(xlb_ctx* c, const xlb_rel* a, const xlb_rel* b, xlb_rel** out) {
+static xlb_status diff_unsigned(xlb_ctx* c, const xlb_rel* a, const xlb_rel* b, xlb_rel** out) {
     if (!c || !a || !b || !out) return XLB_ERR_INVALID;
     API_BEGIN(c)
     if (!schemas_compatible(a->schema, b->schema)) xlb_fail(XLB_ERR_TYPE, "difference of incompatible schemas");
@@ -950,6 +950,114 @@ extern "C" xlb_status xlb_diff(xlb_ctx* c, const xlb_rel* a, const xlb_rel* b, x
     }
     CUDA_OK(cudaStreamSynchronize(c->stream));
     API_END()
+}
+
+// ---- typed columns ---------------------------------------------------------------------------
+// Signed and floating columns are ordered the way the reference orders them (sign flip for
+// i32/i64; IEEE totalOrder for f32/f64: crates/xlog-cuda/kernels/sort.cu:296-448, totalorder.cuh)
+// by mapping them to order-preserving unsigned words, running the unsigned operator and mapping
+// the result back.  Equality stays bitwise (NaN payloads and signed zeros are distinct), as in
+// crates/xlog-cuda/tests/test_full_row_set_algebra.rs:234-310.
+namespace {
+// kind 1: signed; kind 2: float.  Forward then inverse is the identity.
+template <class T>
+__global__ void order_map_k(const T* __restrict__ in, T* __restrict__ out, uint64_t n, int kind, int inverse) {
+    const T sign = T(1) << (sizeof(T) * 8 - 1);
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        T x = in[i];
+        if (kind == 1) x ^= sign;
+        else if (!inverse) x = (x & sign) ? ~x : (x | sign);
+        else x = (x & sign) ? (x ^ sign) : ~x;
+        out[i] = x;
+    }
+}
+}  // namespace
+
+static int order_kind(uint8_t t) { return (t == XLB_I32 || t == XLB_I64) ? 1 : (t == XLB_F32 || t == XLB_F64) ? 2 : 0; }
+static bool schema_typed(const xlb_schema& s) {
+    for (uint32_t i = 0; i < s.arity; ++i)
+        if (order_kind(s.types[i])) return true;
+    return false;
+}
+
+// forward: a view of `r` whose typed columns are mapped to unsigned words (schema becomes
+// unsigned); inverse: `r` is an unsigned result, `types` the schema to restore.
+static xlb_rel* map_rel(xlb_ctx* c, const xlb_rel* r, const xlb_schema& types, bool inverse) {
+    ops_rel_columns(c, r);
+    std::unique_ptr<xlb_rel> o(new xlb_rel);
+    o->ctx = c;
+    o->rows = r->rows;
+    o->canonical = r->canonical;
+    o->schema = types;
+    for (uint32_t i = 0; i < types.arity; ++i) {
+        int kind = order_kind(types.types[i]);
+        uint32_t w = type_width(types.types[i]);
+        if (!inverse) o->schema.types[i] = kind ? (w == 4 ? XLB_U32 : XLB_U64) : types.types[i];
+        if (!kind) { o->cols[i] = r->cols[i]; continue; }  // relations are immutable: share the column
+        o->cols[i] = make_buf(c, r->rows * w);
+        if (!r->rows) continue;
+        prof_begin(c, "order_map", r->rows * 2ull * w);
+        if (w == 4) order_map_k<uint32_t><<<grid_for(c, r->rows), BLOCK, 0, c->stream>>>(r->cols[i]->as<uint32_t>(), o->cols[i]->as<uint32_t>(), r->rows, kind, inverse);
+        else order_map_k<uint64_t><<<grid_for(c, r->rows), BLOCK, 0, c->stream>>>(r->cols[i]->as<uint64_t>(), o->cols[i]->as<uint64_t>(), r->rows, kind, inverse);
+        check_launch(c, "order_map");
+    }
+    return o.release();
+}
+
+static bool schemas_compatible(const xlb_schema& a, const xlb_schema& b);
+
+// Run `op` on unsigned views of the inputs and restore the first input's column types.
+template <class Op>
+static xlb_status with_typed(xlb_ctx* c, const xlb_rel* const* ins, uint32_t n, xlb_rel** out, Op op) {
+    bool typed = false;
+    for (uint32_t i = 0; i < n; ++i)
+        if (ins[i] && schema_typed(ins[i]->schema)) typed = true;
+    if (!typed) return op(ins, out);
+    std::vector<std::unique_ptr<xlb_rel>> mapped;
+    std::vector<const xlb_rel*> ptrs;
+    try {
+        for (uint32_t i = 0; i < n; ++i) {
+            if (!schemas_compatible(ins[0]->schema, ins[i]->schema)) xlb_fail(XLB_ERR_TYPE, "input %u has an incompatible schema", i);
+            mapped.emplace_back(map_rel(c, ins[i], ins[i]->schema, false));
+            ptrs.push_back(mapped.back().get());
+        }
+    } catch (const XlbError& e) {
+        c->last_error = e.msg;
+        return e.st;
+    }
+    xlb_rel* u = nullptr;
+    xlb_status st = op(ptrs.data(), &u);
+    if (st != XLB_OK) return st;
+    std::unique_ptr<xlb_rel> ur(u);
+    try {
+        *out = map_rel(c, u, ins[0]->schema, true);
+        CUDA_OK(cudaStreamSynchronize(c->stream));
+    } catch (const XlbError& e) {
+        c->last_error = e.msg;
+        return e.st;
+    }
+    return XLB_OK;
+}
+
+extern "C" xlb_status xlb_sort(xlb_ctx* c, const xlb_rel* in, const uint32_t* key_cols, uint32_t nk, xlb_rel** out) {
+    if (!c || !in || !out) return XLB_ERR_INVALID;
+    return with_typed(c, &in, 1, out, [&](const xlb_rel* const* v, xlb_rel** o) { return sort_unsigned(c, v[0], key_cols, nk, o); });
+}
+extern "C" xlb_status xlb_dedup(xlb_ctx* c, const xlb_rel* in, const uint32_t* key_cols, uint32_t nk, xlb_rel** out) {
+    if (!c || !in || !out) return XLB_ERR_INVALID;
+    return with_typed(c, &in, 1, out, [&](const xlb_rel* const* v, xlb_rel** o) { return dedup_unsigned(c, v[0], key_cols, nk, o); });
+}
+extern "C" xlb_status xlb_union(xlb_ctx* c, const xlb_rel* const* ins, uint32_t n, xlb_rel** out) {
+    if (!c || !out) return XLB_ERR_INVALID;
+    if (n == 0 || !ins) { c->last_error = "union of no inputs"; return XLB_ERR_INVALID; }
+    for (uint32_t i = 0; i < n; ++i)
+        if (!ins[i]) { c->last_error = "union input is null"; return XLB_ERR_INVALID; }
+    return with_typed(c, ins, n, out, [&](const xlb_rel* const* v, xlb_rel** o) { return union_unsigned(c, v, n, o); });
+}
+extern "C" xlb_status xlb_diff(xlb_ctx* c, const xlb_rel* a, const xlb_rel* b, xlb_rel** out) {
+    if (!c || !a || !b || !out) return XLB_ERR_INVALID;
+    const xlb_rel* both[2] = {a, b};
+    return with_typed(c, both, 2, out, [&](const xlb_rel* const* v, xlb_rel** o) { return diff_unsigned(c, v[0], v[1], o); });
 }
 
 // key word per row for a join side; two 32-bit key columns fuse into one word

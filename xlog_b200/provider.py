@@ -17,7 +17,10 @@ import numpy as np
 from . import _abi as A
 from .lib import XlbError, load
 
-_NP = {A.U32: np.uint32, A.SYMBOL: np.uint32, A.U64: np.uint64}
+_NP = {A.U32: np.uint32, A.SYMBOL: np.uint32, A.U64: np.uint64, A.I32: np.int32, A.I64: np.int64,
+       A.F32: np.float32, A.F64: np.float64}
+_CODE = {np.dtype(np.uint32): A.U32, np.dtype(np.uint64): A.U64, np.dtype(np.int32): A.I32, np.dtype(np.int64): A.I64,
+         np.dtype(np.float32): A.F32, np.dtype(np.float64): A.F64}
 
 
 def _u32s(xs):
@@ -104,7 +107,7 @@ class KernelProvider:
     # ---- lifecycle / transfer ---------------------------------------------------------------
     def create_buffer_from_slices(self, cols: Sequence[np.ndarray], schema: Sequence[int] | None = None) -> Buffer:
         if schema is None:
-            schema = [A.U64 if np.asarray(c).dtype == np.uint64 else A.U32 for c in cols]
+            schema = [_CODE.get(np.asarray(c).dtype, A.U32) for c in cols]
         cols = [np.ascontiguousarray(c, dtype=_NP[t]) for c, t in zip(cols, schema)]
         rows = len(cols[0]) if cols else 0
         for c in cols:
