@@ -27,6 +27,9 @@ import numpy as np
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
+# stdout carries exactly one JSON line: keep NCCL's version banner (NCCL_DEBUG=VERSION) off it
+if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+    os.environ["NCCL_DEBUG"] = "WARN"
 
 METRIC = "derived_tuples_per_sec"
 UNIT = "tuples/s"
@@ -59,7 +62,7 @@ class ClockSampler:
         self.proc = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "50", "-i", str(gpu_index)], stdout=subprocess.PIPE, text=True)
+                                          "-lms", "200", "-i", str(gpu_index)], stdout=subprocess.PIPE, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
         except OSError:
@@ -220,6 +223,8 @@ def main():
     # clocks are sampled from the first warm-up step to the last end-to-end step: the timed region
     # alone lasts tens of milliseconds, less than one nvidia-smi sampling period
     sampler = ClockSampler(local) if rank == 0 and not args.no_clocks else None
+    if sampler:
+        time.sleep(1.0)  # let nvidia-smi finish starting up: its first query stalls CUDA calls for milliseconds
     for _ in range(args.warmup):
         device_step()
     prov.profile_enable(args.kernel)

@@ -150,18 +150,16 @@ Keys comm_repartition(xlb_ctx* c, const Keys& in, int keysel, bool sorted_unique
     }
     Comm* cm = c->comm;
     uint32_t W = c->world;
-    std::vector<uint64_t> send;
-    Keys part = ops_partition_by_owner(c, in, keysel, W, send);
-    // every rank learns every rank's send counts
-    uint64_t* mine = cm->counts_dev->as<uint64_t>() + (uint64_t)c->rank * W;
-    for (uint32_t r = 0; r < W; ++r) c->h_scalar[r < 32 ? r : 31] = 0;
-    std::vector<unsigned long long> stage(send.begin(), send.end());
-    CUDA_OK(cudaMemcpyAsync(mine, stage.data(), W * 8, cudaMemcpyHostToDevice, c->stream));
-    CUDA_OK(cudaStreamSynchronize(c->stream));  // `stage` is pageable host memory
+    // partition into one run per destination; the run lengths go straight from device memory into
+    // the all-gather, so every rank learns the whole count matrix with a single host wait
+    unsigned long long* mine = cm->counts_dev->as<unsigned long long>() + (uint64_t)c->rank * W;
+    Keys part = ops_partition_by_owner_dev(c, in, keysel, W, mine);
     NCCL_OK(api().AllGather(mine, cm->counts_dev->p, W, ncclUint64, cm->comm, c->stream));
     std::vector<unsigned long long> all((size_t)W * W);
     CUDA_OK(cudaMemcpyAsync(all.data(), cm->counts_dev->p, (size_t)W * W * 8, cudaMemcpyDeviceToHost, c->stream));
     comm_wait(c);
+    std::vector<uint64_t> send(W);
+    for (uint32_t r = 0; r < W; ++r) send[r] = all[(size_t)c->rank * W + r];
     std::vector<uint64_t> recv(W);
     uint64_t total = 0;
     for (uint32_t r = 0; r < W; ++r) {

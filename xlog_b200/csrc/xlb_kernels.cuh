@@ -265,13 +265,27 @@ uint64_t select(xlb_ctx* c, Pred pred, Emit emit, uint64_t n) {
 }
 
 // -------------------------------------------------------------------------------- pack/unpack
-static __global__ void pack2_k(const uint32_t* __restrict__ c0, const uint32_t* __restrict__ c1, uint64_t* __restrict__ out, uint64_t n) {
-    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
-        out[i] = ((uint64_t)c0[i] << 32) | c1[i];
+// pack kernels also reduce the OR of the packed rows into *or_out (may be null)
+static __global__ void pack2_k(const uint32_t* __restrict__ c0, const uint32_t* __restrict__ c1, uint64_t* __restrict__ out, uint64_t n, unsigned long long* or_out) {
+    uint64_t acc = 0;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        uint64_t k = ((uint64_t)c0[i] << 32) | c1[i];
+        out[i] = k;
+        acc |= k;
+    }
+#pragma unroll
+    for (int d = 16; d; d >>= 1) acc |= __shfl_xor_sync(FULL, acc, d);
+    if (or_out && lane_id() == 0 && acc) atomicOr(or_out, (unsigned long long)acc);
 }
-static __global__ void pack1_k(const uint32_t* __restrict__ c0, uint64_t* __restrict__ out, uint64_t n) {
-    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
+static __global__ void pack1_k(const uint32_t* __restrict__ c0, uint64_t* __restrict__ out, uint64_t n, unsigned long long* or_out) {
+    uint64_t acc = 0;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
         out[i] = c0[i];
+        acc |= c0[i];
+    }
+#pragma unroll
+    for (int d = 16; d; d >>= 1) acc |= __shfl_xor_sync(FULL, acc, d);
+    if (or_out && lane_id() == 0 && acc) atomicOr(or_out, (unsigned long long)acc);
 }
 static __global__ void unpack2_k(const uint64_t* __restrict__ in, uint32_t* __restrict__ c0, uint32_t* __restrict__ c1, uint64_t n) {
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
@@ -334,7 +348,8 @@ static __global__ void __launch_bounds__(BLOCK) radix_bits_k(const uint64_t* __r
 
 // Histograms of all eight digits in one read of the keys.  A digit on which a whole warp agrees
 // (constant high bytes are the common case) costs one shared-memory add per warp.
-static __global__ void __launch_bounds__(BLOCK) radix_upfront_k(const uint64_t* __restrict__ keys, uint64_t n, unsigned int* __restrict__ ghist /* 8*256 */) {
+// `digits`: bit d set = digit d is wanted (the others are known constant or take no part).
+static __global__ void __launch_bounds__(BLOCK) radix_upfront_k(const uint64_t* __restrict__ keys, uint64_t n, unsigned int* __restrict__ ghist /* 8*256 */, unsigned digits) {
     __shared__ unsigned int sh[8 * 256];
     for (int i = threadIdx.x; i < 8 * 256; i += BLOCK) sh[i] = 0;
     __syncthreads();
@@ -348,6 +363,7 @@ static __global__ void __launch_bounds__(BLOCK) radix_upfront_k(const uint64_t* 
         unsigned first_lane = __ffs(live) - 1;
 #pragma unroll
         for (int d = 0; d < 8; ++d) {
+            if (!((digits >> d) & 1u)) continue;
             unsigned dig = (unsigned)((k >> (8 * d)) & 255);
             unsigned first = __shfl_sync(FULL, dig, first_lane);
             bool uni = __all_sync(FULL, !ok || dig == first);
@@ -615,7 +631,12 @@ inline void radix_sort(xlb_ctx* c, Buf& keys, Buf* vals, uint64_t n, unsigned di
         unsigned long long* varies = (unsigned long long*)(bases + 8 * 256);
         CUDA_OK(cudaMemsetAsync(ghist, 0, 8 * 256 * 4, c->stream));
         prof_begin(c, "radix_upfront", n * 8ull);
-        radix_upfront_k<<<grid_for(c, n, BLOCK * 8), BLOCK, 0, c->stream>>>(keys->as<uint64_t>(), n, ghist);
+        unsigned want = digit_mask & 0xFFu;
+        if (known_bound != ~0ull)
+            for (int d = 0; d < 8; ++d)
+                if (!((known_bound >> (8 * d)) & 255)) want &= ~(1u << d);
+        if (want == 0) return;
+        radix_upfront_k<<<grid_for(c, n, BLOCK * 8), BLOCK, 0, c->stream>>>(keys->as<uint64_t>(), n, ghist, want);
         check_launch(c, "radix_upfront");
         prof_begin(c, "radix_bases", 0);
         radix_bases_k<<<1, BLOCK, 0, c->stream>>>(ghist, n, bases, varies);

@@ -236,24 +236,20 @@ Keys ops_rel_packed(xlb_ctx* c, const xlb_rel* r) {
     if (!rel_packable(r->schema)) xlb_fail(XLB_ERR_UNSUPPORTED, "relation is not a one- or two-column 32-bit relation");
     Buf b = make_buf(c, r->rows * 8);
     if (r->rows) {
-        prof_begin(c, "pack", 0);
-        if (r->schema.arity == 2) pack2_k<<<grid_for(c, r->rows), BLOCK, 0, c->stream>>>(r->cols[0]->as<uint32_t>(), r->cols[1]->as<uint32_t>(), b->as<uint64_t>(), r->rows);
-        else pack1_k<<<grid_for(c, r->rows), BLOCK, 0, c->stream>>>(r->cols[0]->as<uint32_t>(), b->as<uint64_t>(), r->rows);
-        check_launch(c, "pack");
-    }
-    r->packed = b;
-    k.buf = b;
-    if (r->rows) {  // one reduction per loaded relation: later sorts of anything derived from it skip a read-back
-        Buf oa = make_buf(c, 16);
+        // pack and, in the same sweep, reduce the OR of all rows: later sorts of anything derived
+        // from this relation plan their digits from it without a read-back
+        Buf oa = make_buf(c, 8);
         CUDA_OK(cudaMemsetAsync(oa->p, 0, 8, c->stream));
-        CUDA_OK(cudaMemsetAsync((char*)oa->p + 8, 0xFF, 8, c->stream));
-        prof_begin(c, "radix_bits", r->rows * 8ull);
-        radix_bits_k<<<grid_for(c, r->rows, BLOCK * 8), BLOCK, 0, c->stream>>>(b->as<uint64_t>(), r->rows, oa->as<unsigned long long>());
-        check_launch(c, "radix_bits");
-        unsigned long long h[2];
-        read_words(c, oa->p, 2, h);
+        prof_begin(c, "pack", r->rows * 16ull);
+        if (r->schema.arity == 2) pack2_k<<<grid_for(c, r->rows), BLOCK, 0, c->stream>>>(r->cols[0]->as<uint32_t>(), r->cols[1]->as<uint32_t>(), b->as<uint64_t>(), r->rows, oa->as<unsigned long long>());
+        else pack1_k<<<grid_for(c, r->rows), BLOCK, 0, c->stream>>>(r->cols[0]->as<uint32_t>(), b->as<uint64_t>(), r->rows, oa->as<unsigned long long>());
+        check_launch(c, "pack");
+        unsigned long long h[1];
+        read_words(c, oa->p, 1, h);
         r->or_bound = h[0];
     } else r->or_bound = 0;
+    r->packed = b;
+    k.buf = b;
     k.bound = r->or_bound;
     return k;
 }
@@ -461,18 +457,16 @@ Keys ops_join_expand(xlb_ctx* c, const Keys& bag, int keysel, const uint64_t* pk
     return out;
 }
 
-Keys ops_partition_by_owner(xlb_ctx* c, const Keys& in, int keysel, uint32_t world, std::vector<uint64_t>& counts_out) {
-    counts_out.assign(world, 0);
+Keys ops_partition_by_owner_dev(xlb_ctx* c, const Keys& in, int keysel, uint32_t world, unsigned long long* counts) {
     Keys out;
     out.bound = in.bound;
     out.n = in.n;
     out.buf = make_buf(c, in.n * 8);
-    if (in.n == 0) return out;
     if (world > 64) xlb_fail(XLB_ERR_UNSUPPORTED, "at most 64 ranks");
-    Buf cnt = make_buf(c, 2 * 64 * 8);  // counts | cursors
-    unsigned long long* counts = cnt->as<unsigned long long>();
-    unsigned long long* cursors = counts + 64;
-    CUDA_OK(cudaMemsetAsync(counts, 0, 64 * 8, c->stream));
+    CUDA_OK(cudaMemsetAsync(counts, 0, (size_t)world * 8, c->stream));
+    if (in.n == 0) return out;
+    Buf cur = make_buf(c, 64 * 8);
+    unsigned long long* cursors = cur->as<unsigned long long>();
     unsigned grid = (unsigned)((in.n + BLOCK * OWN_IPT - 1) / (BLOCK * OWN_IPT));
     prof_begin(c, "owner_count", in.n * 8ull);
     owner_count_k<<<grid, BLOCK, 0, c->stream>>>(in.ptr(), in.n, keysel, world, counts);
@@ -483,8 +477,16 @@ Keys ops_partition_by_owner(xlb_ctx* c, const Keys& in, int keysel, uint32_t wor
     prof_begin(c, "owner_scatter", in.n * 16ull);
     owner_scatter_k<<<grid, BLOCK, 0, c->stream>>>(in.ptr(), in.n, keysel, world, cursors, out.buf->as<uint64_t>());
     check_launch(c, "owner_scatter");
+    return out;
+}
+
+Keys ops_partition_by_owner(xlb_ctx* c, const Keys& in, int keysel, uint32_t world, std::vector<uint64_t>& counts_out) {
+    counts_out.assign(world, 0);
+    Buf cnt = make_buf(c, 64 * 8);
+    Keys out = ops_partition_by_owner_dev(c, in, keysel, world, cnt->as<unsigned long long>());
+    if (in.n == 0) return out;
     unsigned long long h[64];
-    read_words(c, counts, (int)world, h);
+    read_words(c, cnt->p, (int)world, h);
     for (uint32_t r = 0; r < world; ++r) counts_out[r] = h[r];
     return out;
 }

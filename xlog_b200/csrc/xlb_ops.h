@@ -57,6 +57,8 @@ Buf ops_probe_match(xlb_ctx* c, const Keys& bag, int keysel, const uint64_t* pke
 // owner rank of every row by the half `keysel`; stable partition into `world` runs.
 // counts_out[world] (host) receives the run lengths; returns the partitioned copy.
 Keys ops_partition_by_owner(xlb_ctx* c, const Keys& in, int keysel, uint32_t world, std::vector<uint64_t>& counts_out);
+// The same without the read-back: the `world` run lengths are left in device memory at `counts_dev`.
+Keys ops_partition_by_owner_dev(xlb_ctx* c, const Keys& in, int keysel, uint32_t world, unsigned long long* counts_dev);
 
 // Per-phase event timing (XLB_FLAG_PROFILE): bracket with phase_begin / phase_end.
 struct PhaseTimer {
