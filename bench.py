@@ -27,9 +27,15 @@ import numpy as np
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
-# stdout carries exactly one JSON line: keep NCCL's version banner (NCCL_DEBUG=VERSION) off it
-if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-    os.environ["NCCL_DEBUG"] = "WARN"
+# stdout carries exactly one JSON line: everything else that libraries print there (NCCL's version
+# banner, for one) is sent to stderr by pointing file descriptor 1 at stderr until the line is due
+_REAL_STDOUT = os.dup(1)
+os.dup2(2, 1)
+
+
+def emit(line: dict) -> None:
+    sys.stdout.flush()
+    os.write(_REAL_STDOUT, (json.dumps(line) + "\n").encode())
 
 METRIC = "derived_tuples_per_sec"
 UNIT = "tuples/s"
@@ -134,7 +140,7 @@ def run_reference(args):
                          "sample": "the whole fixpoint of the same workload, once per step"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def main():
@@ -326,7 +332,7 @@ def main():
         "cpu_baseline": cpu,
         "host_last_step": {k: stats[k] for k in ("host_syncs", "ms_host_wait", "ms_host_total")},
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
     if world > 1:
         dist.destroy_process_group()
 

@@ -84,6 +84,9 @@ typedef struct xlb_config {
 } xlb_config;
 
 #define XLB_FLAG_PROFILE 1u        /* time every phase with CUDA events (RuntimeConfig.profile)     */
+#define XLB_FLAG_NO_DENSE 2u       /* never take the bitmap route for small dense domains (the kill
+                                      switch the reference gives its factorized routes,
+                                      XLOG_DISABLE_FACTORIZED_DELTA)                                 */
 
 
 /* ---- context ------------------------------------------------------------------------------ */

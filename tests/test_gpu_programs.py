@@ -203,3 +203,31 @@ def test_rmat_dag_closure_scale_15_properties():
     pos = np.searchsorted(k, want)
     assert np.all(k[np.minimum(pos, len(k) - 1)] == want)
     p.close()
+
+
+@pytest.mark.parametrize("name", ["tc", "reach", "sg"])
+def test_dense_route_on_and_off_agree(oracle, name):
+    """Small-domain fixpoints take the bitmap route by default; with the kill switch they take the
+    sort / merge route.  Both must give the oracle's result (the reference pins its own fast route
+    the same way: crates/xlog-integration/tests/test_factorized_delta_e2e.rs:280-308)."""
+    from xlog_b200 import _abi as A
+    if name == "tc":
+        c0, c1 = workloads.uniform_digraph(500, 2000, 4)
+        plan, inputs, out = programs.transitive_closure(), {"edge": [c0, c1]}, "reach"
+    elif name == "reach":
+        c0, c1 = workloads.rmat_graph(13, 16)
+        plan, inputs, out = programs.reach_from_source(0), {"edge": [c0, c1]}, "r"
+    else:
+        c0, c1, _ = workloads.tree_dag(1200, 0.05, 8)
+        plan, inputs, out = programs.same_generation(), {"edge": [c0, c1]}, "sg"
+    want, _ = oracle.run_program(plan, inputs, [out])
+    results = []
+    for flags in (0, A.FLAG_NO_DENSE):
+        p = KernelProvider(device=0, flags=flags)
+        p.profile_enable("*")
+        got, _ = run_program(p, plan, inputs, [out])
+        prof = p.profile_read()
+        used_dense = "dense_mark" in prof
+        assert used_dense == (flags == 0), "the route taken is not the one asked for"
+        assert all(np.array_equal(g, w) for g, w in zip(got[out], want[out]))
+        p.close()

@@ -23,6 +23,7 @@ NODE_SCAN, NODE_FILTER, NODE_PROJECT, NODE_JOIN, NODE_UNION = 1, 2, 3, 4, 5
 EQ, NE, LT, LE, GT, GE = range(6)
 
 FLAG_PROFILE = 1
+FLAG_NO_DENSE = 2
 
 
 class Schema(C.Structure):

@@ -57,7 +57,7 @@ NcclApi& api() {
 struct Comm {
     ncclComm_t comm = nullptr;
     double timeout_s = 120.0;
-    Buf counts_dev;  // world*world u64: row r = send counts of rank r
+    Buf counts_dev;  // world rows of world + 1 u64: row r = send counts of rank r, then its OR bound
 };
 
 // Wait for the stream without ever blocking for good: poll the stream and the communicator's
@@ -122,7 +122,7 @@ extern "C" xlb_status xlb_comm_init(xlb_ctx* c, const uint8_t id[XLB_UNIQUE_ID_B
         NCCL_OK(api().CommInitRank(&cm->comm, (int)world, u, (int)rank));
         c->rank = rank;
         c->world = world;
-        cm->counts_dev = make_buf(c, (uint64_t)world * world * 8);
+        cm->counts_dev = make_buf(c, (uint64_t)world * (world + 1) * 8);
     } catch (const XlbError& e) {
         c->last_error = e.msg;
         return e.st;
@@ -151,24 +151,33 @@ Keys comm_repartition(xlb_ctx* c, const Keys& in, int keysel, bool sorted_unique
     Comm* cm = c->comm;
     uint32_t W = c->world;
     // partition into one run per destination; the run lengths go straight from device memory into
-    // the all-gather, so every rank learns the whole count matrix with a single host wait
-    unsigned long long* mine = cm->counts_dev->as<unsigned long long>() + (uint64_t)c->rank * W;
+    // the all-gather, so every rank learns the whole count matrix with a single host wait.  Each
+    // row of the matrix carries one more word: the sender's OR bound of its rows, so the receiver
+    // knows the bits of what it gets without looking at it.
+    const uint32_t RW = W + 1;
+    unsigned long long* mine = cm->counts_dev->as<unsigned long long>() + (uint64_t)c->rank * RW;
     Keys part = ops_partition_by_owner_dev(c, in, keysel, W, mine);
-    NCCL_OK(api().AllGather(mine, cm->counts_dev->p, W, ncclUint64, cm->comm, c->stream));
-    std::vector<unsigned long long> all((size_t)W * W);
-    CUDA_OK(cudaMemcpyAsync(all.data(), cm->counts_dev->p, (size_t)W * W * 8, cudaMemcpyDeviceToHost, c->stream));
+    c->h_scalar[60] = in.n ? in.bound : 0;
+    CUDA_OK(cudaMemcpyAsync(mine + W, &c->h_scalar[60], 8, cudaMemcpyHostToDevice, c->stream));
+    NCCL_OK(api().AllGather(mine, cm->counts_dev->p, RW, ncclUint64, cm->comm, c->stream));
+    std::vector<unsigned long long> all((size_t)W * RW);
+    CUDA_OK(cudaMemcpyAsync(all.data(), cm->counts_dev->p, (size_t)W * RW * 8, cudaMemcpyDeviceToHost, c->stream));
     comm_wait(c);
     std::vector<uint64_t> send(W);
-    for (uint32_t r = 0; r < W; ++r) send[r] = all[(size_t)c->rank * W + r];
+    uint64_t bound = 0;
+    for (uint32_t r = 0; r < W; ++r) {
+        send[r] = all[(size_t)c->rank * RW + r];
+        bound |= all[(size_t)r * RW + W];
+    }
     std::vector<uint64_t> recv(W);
     uint64_t total = 0;
     for (uint32_t r = 0; r < W; ++r) {
-        recv[r] = all[(size_t)r * W + c->rank];
+        recv[r] = all[(size_t)r * RW + c->rank];
         total += recv[r];
     }
     Keys out;
     out.n = total;
-    out.bound = ~0ull;  // rows of other ranks: their bits are not known here
+    out.bound = bound;
     out.buf = make_buf(c, total * 8);
     NCCL_OK(api().GroupStart());
     uint64_t so = 0, ro = 0;

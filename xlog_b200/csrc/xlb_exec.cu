@@ -25,7 +25,6 @@ struct CachedIndex {
     Index ix;
     uint64_t version = 0;   // store version of the relation the rows came from
     bool table_ok = false;  // hash table matches ix.S
-    uint64_t rows_global_hint = 0;
 };
 struct IndexCache {
     std::map<std::pair<std::string, int>, CachedIndex> m;
@@ -108,7 +107,6 @@ extern "C" xlb_status xlb_store_remove(xlb_ctx* c, const char* name) {
 
 // ------------------------------------------------------------------------------ flattening
 struct Atom {
-    const xlb_node* scan;
     std::string rel;
     uint32_t arity;
     int var[2];
@@ -153,7 +151,6 @@ struct Flattener {
                 if (!rel_packable(r->schema))
                     xlb_fail(XLB_ERR_UNSUPPORTED, "relation %s: plans take relations of one or two 32-bit columns", nm->second.c_str());
                 Atom a;
-                a.scan = n;
                 a.rel = nm->second;
                 a.arity = r->schema.arity;
                 std::vector<int> cols;
@@ -526,13 +523,22 @@ static void eval_variant(xlb_ctx* c, const FlatRule& fr_in, size_t start, const 
             cand = comm_repartition(c, cand, home_sel, false, rs.st);
         }
         if (cand.n == 0) continue;
-        if (cand.buf == start_rows.buf) cand = ops_copy(c, cand);  // a single-atom body: never sort a stored relation in place
-        {
-            PhaseTimer t(c, &rs.st.ms_sort);
-            ops_sort(c, cand);
+        Keys fresh;
+        int hb = 0, lb = 0;
+        if (!(c->flags & XLB_FLAG_NO_DENSE) && ops_dense_bits(cand, full, &hb, &lb)) {
+            // small dense domain: sort + dedup + difference on a bitmap
+            PhaseTimer t(c, &rs.st.ms_setops);
+            fresh = ops_dense_novel(c, cand, full, hb, lb);
+        } else {
+            if (cand.buf == start_rows.buf) cand = ops_copy(c, cand);  // a single-atom body: never sort a stored relation in place
+            {
+                PhaseTimer t(c, &rs.st.ms_sort);
+                ops_sort(c, cand);
+            }
+            PhaseTimer t(c, &rs.st.ms_setops);
+            fresh = ops_dedup_diff(c, cand, full);  // duplicates dropped and `full` subtracted in one merge pass
         }
-        PhaseTimer t(c, &rs.st.ms_setops);
-        Keys fresh = ops_dedup_diff(c, cand, full);  // duplicates dropped and `full` subtracted in one merge pass
+        PhaseTimer t2(c, &rs.st.ms_setops);
         novel = novel.n ? ops_union(c, novel, fresh) : fresh;
     }
 }

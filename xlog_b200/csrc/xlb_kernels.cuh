@@ -163,11 +163,49 @@ struct LoadLow32 {  // low half of a u64 word (the match length of a probe resul
     __device__ __forceinline__ uint32_t operator()(uint64_t i) const { return (uint32_t)p[i]; }
 };
 
+// Up to a few hundred thousand elements one block walks the whole array (one launch instead of
+// three): 1024 threads, blocked chunks of 8 per thread, a running carry.
+constexpr uint64_t SCAN_SMALL_MAX = 1ull << 18;
+template <class Load, class Tout>
+static __global__ void __launch_bounds__(1024) scan_small_k(Load load, uint64_t n, Tout* out, Tout* total) {
+    __shared__ Tout sm[33];
+    __shared__ Tout carry_s;
+    if (threadIdx.x == 0) carry_s = 0;
+    __syncthreads();
+    for (uint64_t base = 0; base < n; base += 1024 * SCAN_IPT) {
+        uint64_t first = base + (uint64_t)threadIdx.x * SCAN_IPT;
+        Tout v[SCAN_IPT];
+        Tout s = 0;
+#pragma unroll
+        for (int k = 0; k < SCAN_IPT; ++k) {
+            v[k] = first + k < n ? (Tout)load(first + k) : Tout(0);
+            s += v[k];
+        }
+        Tout tot;
+        Tout run = block_exclusive_scan<Tout>(s, &tot, sm) + carry_s;
+#pragma unroll
+        for (int k = 0; k < SCAN_IPT; ++k) {
+            if (first + k < n) out[first + k] = run;
+            run += v[k];
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) carry_s += tot;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) *total = carry_s;
+}
+
 // Exclusive scan; `d_total` (device, one Tout) receives the sum.
 template <class Load, class Tout>
 void exclusive_scan(xlb_ctx* c, Load load, uint64_t n, Tout* out, Tout* d_total) {
     if (n == 0) {
         CUDA_OK(cudaMemsetAsync(d_total, 0, sizeof(Tout), c->stream));
+        return;
+    }
+    if (n > (uint64_t)SCAN_TILE && n <= SCAN_SMALL_MAX) {
+        prof_begin(c, "scan_small", 0);
+        scan_small_k<Load, Tout><<<1, 1024, 0, c->stream>>>(load, n, out, d_total);
+        check_launch(c, "scan_small");
         return;
     }
     uint64_t ntiles = (n + SCAN_TILE - 1) / SCAN_TILE;
@@ -843,6 +881,52 @@ inline Buf merge_disjoint(xlb_ctx* c, const uint64_t* A, uint64_t na, const uint
     mp_tile_k<1><<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(A, na, B, nb, splits->as<uint64_t>(), nullptr, o->as<uint64_t>());
     check_launch(c, "mp_union");
     return o;
+}
+
+// ------------------------------------------------------------------------------ dense sets
+// When the tuples of a relation fit a small dense domain (hi_bits + lo_bits <= 27 after dropping
+// the bits that are zero in every tuple), "sort, dedup, subtract the full relation" is done on a
+// bitmap instead: mark the candidates, clear the tuples of the full relation, then emit the
+// surviving bits in ascending order, which is the relation's lexicographic order.  The reference's
+// default route for small domains works the same way (fj_delta_mark / subtract / popcount / emit,
+// kernels/wcoj.cu:3811-3935), on a domain x domain bitmap.
+__device__ __forceinline__ uint32_t dense_index(uint64_t k, int lo_bits) {
+    return (uint32_t)(((k >> 32) << lo_bits) | (k & 0xFFFFFFFFull));
+}
+template <bool SET>
+static __global__ void __launch_bounds__(BLOCK) dense_mark_k(const uint64_t* __restrict__ keys, uint64_t n, int lo_bits, unsigned int* __restrict__ bitmap,
+                                                           uint64_t words, DevStatus* st) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        uint64_t k = keys[i];
+        uint32_t x = dense_index(k, lo_bits);
+        // a tuple outside the domain the host derived would mean a wrong bound: report, never write
+        if ((k & 0xFFFFFFFFull) >> lo_bits || (uint64_t)(x >> 5) >= words) {
+            set_status(st, XLB_ERR_CAPACITY, 3, k);
+            continue;
+        }
+        unsigned bit = 1u << (x & 31);
+        unsigned cur = bitmap[x >> 5];  // most candidates repeat a tuple already seen: skip the atomic then
+        if (SET) { if (!(cur & bit)) atomicOr(&bitmap[x >> 5], bit); }
+        else     { if (cur & bit) atomicAnd(&bitmap[x >> 5], ~bit); }
+    }
+}
+struct LoadPopc {
+    const unsigned int* w;
+    __device__ __forceinline__ uint32_t operator()(uint64_t i) const { return (uint32_t)__popc(w[i]); }
+};
+static __global__ void __launch_bounds__(BLOCK) dense_emit_k(const unsigned int* __restrict__ bitmap, uint64_t words, const uint64_t* __restrict__ offs,
+                                                           int lo_bits, uint64_t* __restrict__ out) {
+    const uint64_t lo_mask = (1ull << lo_bits) - 1;
+    for (uint64_t w = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; w < words; w += (uint64_t)gridDim.x * blockDim.x) {
+        unsigned m = bitmap[w];
+        uint64_t pos = offs[w];
+        while (m) {
+            unsigned b = __ffs(m) - 1;
+            m &= m - 1;
+            uint64_t x = (w << 5) | b;
+            out[pos++] = ((x >> lo_bits) << 32) | (x & lo_mask);
+        }
+    }
 }
 
 // ------------------------------------------------------------------------------ hash index

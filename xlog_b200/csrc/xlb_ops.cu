@@ -294,7 +294,7 @@ Keys ops_from_host(xlb_ctx* c, const uint64_t* rows, uint64_t n) {
     for (uint64_t i = 0; i < n; ++i) c->h_scalar[40 + i] = rows[i];  // pinned staging words
     if (n) {
         CUDA_OK(cudaMemcpyAsync(o.buf->p, &c->h_scalar[40], n * 8, cudaMemcpyHostToDevice, c->stream));
-        stream_wait(c);
+        stream_wait(c);  // the staging words are reused by the next call
     }
     return o;
 }
@@ -345,6 +345,48 @@ Keys ops_dedup_diff(xlb_ctx* c, const Keys& a, const Keys& b) {
     Keys o;
     o.bound = a.bound;
     o.buf = set_difference(c, a.ptr(), a.n, b.ptr(), b.n, &o.n, true);
+    return o;
+}
+
+static int bit_length(uint64_t v) { return v ? 64 - __builtin_clzll(v) : 0; }
+
+bool ops_dense_bits(const Keys& a, const Keys& b, int* hi_bits, int* lo_bits) {
+    uint64_t ba = a.n ? a.bound : 0, bb = b.n ? b.bound : 0;
+    if (ba == ~0ull || bb == ~0ull) return false;  // bits unknown
+    uint64_t all = ba | bb;
+    *hi_bits = bit_length(all >> 32);
+    *lo_bits = bit_length(all & 0xFFFFFFFFull);
+    return *hi_bits + *lo_bits <= 27 && *hi_bits + *lo_bits >= 1;
+}
+
+Keys ops_dense_novel(xlb_ctx* c, const Keys& cand, const Keys& full, int hi_bits, int lo_bits) {
+    Keys o;
+    o.bound = cand.bound;
+    uint64_t words = ((1ull << (hi_bits + lo_bits)) + 31) / 32;
+    Buf bitmap = make_buf(c, words * 4);
+    CUDA_OK(cudaMemsetAsync(bitmap->p, 0, words * 4, c->stream));
+    if (cand.n) {
+        prof_begin(c, "dense_mark", cand.n * 8ull);
+        dense_mark_k<true><<<grid_for(c, cand.n), BLOCK, 0, c->stream>>>(cand.ptr(), cand.n, lo_bits, bitmap->as<unsigned int>(), words, c->d_status);
+        check_launch(c, "dense_mark");
+    }
+    if (full.n && cand.n) {
+        prof_begin(c, "dense_clear", full.n * 8ull);
+        dense_mark_k<false><<<grid_for(c, full.n), BLOCK, 0, c->stream>>>(full.ptr(), full.n, lo_bits, bitmap->as<unsigned int>(), words, c->d_status);
+        check_launch(c, "dense_clear");
+    }
+    Buf offs = make_buf(c, words * 8);
+    Buf total = make_buf(c, 8);
+    exclusive_scan<LoadPopc, uint64_t>(c, LoadPopc{bitmap->as<unsigned int>()}, words, offs->as<uint64_t>(), total->as<uint64_t>());
+    unsigned long long tot;
+    read_words(c, total->p, 1, &tot);
+    o.n = tot;
+    o.buf = make_buf(c, tot * 8);
+    if (tot) {
+        prof_begin(c, "dense_emit", words * 12ull + tot * 8ull);
+        dense_emit_k<<<grid_for(c, words), BLOCK, 0, c->stream>>>(bitmap->as<unsigned int>(), words, offs->as<uint64_t>(), lo_bits, o.buf->as<uint64_t>());
+        check_launch(c, "dense_emit");
+    }
     return o;
 }
 

@@ -41,6 +41,10 @@ void ops_sort_by_high_half(xlb_ctx* c, Keys& k);                 // stable, by b
 void ops_dedup_sorted(xlb_ctx* c, Keys& k);                      // sorted -> sorted unique
 Keys ops_diff(xlb_ctx* c, const Keys& a, const Keys& b);         // sorted unique a \ sorted unique b
 Keys ops_dedup_diff(xlb_ctx* c, const Keys& a, const Keys& b);   // distinct rows of sorted a that are not in sorted unique b
+// The same result through a bitmap over a dense domain; `ops_dense_bits` says whether the rows of
+// both arrays fit one (returns false otherwise) and how many low-half bits to keep.
+bool ops_dense_bits(const Keys& a, const Keys& b, int* hi_bits, int* lo_bits);
+Keys ops_dense_novel(xlb_ctx* c, const Keys& cand, const Keys& full, int hi_bits, int lo_bits);
 Keys ops_merge_disjoint(xlb_ctx* c, const Keys& a, const Keys& b);
 Keys ops_union(xlb_ctx* c, const Keys& a, const Keys& b);        // sorted unique a U b
 Keys ops_remap(xlb_ctx* c, const Keys& in, int hi_src, int lo_src);
