@@ -161,8 +161,8 @@ typedef enum xlb_node_kind {
     XLB_NODE_SCAN = 1,    /* RirNode::Scan { rel }                                              */
     XLB_NODE_FILTER = 2,  /* RirNode::Filter { input, predicate } with a column comparison      */
     XLB_NODE_PROJECT = 3, /* RirNode::Project { input, columns } with pass-through columns      */
-    XLB_NODE_JOIN = 4,    /* RirNode::Join { left, right, left_keys, right_keys, Inner }        */
-    XLB_NODE_UNION = 5    /* RirNode::Union { inputs }                                          */
+    XLB_NODE_JOIN = 4,    /* RirNode::Join { left, right, left_keys, right_keys, join_type }    */
+    XLB_NODE_UNION = 5    /* RirNode::Union { inputs }: at the top of a rule body (one rule per input) */
 } xlb_node_kind;
 
 /* CompareOp (rir.rs:296-310). */
@@ -187,6 +187,8 @@ typedef struct xlb_node {
     uint64_t cmp_rhs;                     /* FILTER: column index or constant                 */
     const struct xlb_node* const* inputs; /* UNION                                            */
     uint32_t n_inputs;                    /* UNION                                            */
+    uint32_t join_type;                   /* JOIN: xlb_join_type (0 = inner).  SEMI / ANTI keep the
+                                             left columns; their right input must be a Scan     */
 } xlb_node;
 
 /* CompiledRule { head, body } (crates/xlog-ir/src/plan.rs:28-36). */

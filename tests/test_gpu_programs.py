@@ -231,3 +231,16 @@ def test_dense_route_on_and_off_agree(oracle, name):
         assert used_dense == (flags == 0), "the route taken is not the one asked for"
         assert all(np.array_equal(g, w) for g, w in zip(got[out], want[out]))
         p.close()
+
+
+def test_stratified_negation_and_union_body(oracle):
+    """Anti join against a lower stratum and a Union at the top of a rule body."""
+    from test_oracle_golden import stratified_case
+    plan, inputs, reach, unreach = stratified_case()
+    p = fresh()
+    got, _ = run_program(p, plan, inputs, ["r", "un", "either"])
+    want, _ = oracle.run_program(plan, inputs, ["r", "un", "either"])
+    for name in ("r", "un", "either"):
+        assert np.array_equal(got[name][0], want[name][0])
+    assert got["un"][0].tolist() == sorted(unreach)
+    p.close()

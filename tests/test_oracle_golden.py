@@ -135,3 +135,31 @@ def test_oracle_iteration_limit(oracle):
     c0 = np.arange(0, 50, dtype=np.uint32)
     with pytest.raises(RuntimeError, match="iteration limit"):
         oracle.run_program(programs.transitive_closure(), {"edge": [c0, c0 + 1]}, ["reach"], max_iterations=3)
+
+
+def _reachable(c0, c1, source):
+    seen, frontier = set(), {int(y) for x, y in zip(c0.tolist(), c1.tolist()) if x == source}
+    adj = {}
+    for x, y in zip(c0.tolist(), c1.tolist()):
+        adj.setdefault(x, []).append(y)
+    while frontier:
+        seen |= frontier
+        frontier = {z for y in frontier for z in adj.get(y, ())} - seen
+    return seen
+
+
+def stratified_case():
+    from xlog_b200 import workloads
+    c0, c1 = workloads.uniform_digraph(80, 160, 3)
+    source = int(c0[0])
+    node = np.arange(80, dtype=np.uint32)
+    reach = _reachable(c0, c1, source)
+    return programs.unreachable_nodes(source), {"edge": [c0, c1], "node": [node]}, reach, set(range(80)) - reach
+
+
+def test_oracle_stratified_negation_and_union_body(oracle):
+    plan, inputs, reach, unreach = stratified_case()
+    out, _ = oracle.run_program(plan, inputs, ["r", "un", "either"])
+    assert out["r"][0].tolist() == sorted(reach) and len(reach) > 3
+    assert out["un"][0].tolist() == sorted(unreach)
+    assert out["either"][0].tolist() == list(range(80))

@@ -56,7 +56,7 @@ Node._fields_ = [
     ("n_cols", C.c_uint32), ("cols", C.c_uint32 * XLB_MAX_ARITY),
     ("cmp", C.c_uint32), ("cmp_lhs_col", C.c_uint32), ("cmp_rhs_is_const", C.c_uint32),
     ("cmp_rhs", C.c_uint64),
-    ("inputs", C.POINTER(C.POINTER(Node))), ("n_inputs", C.c_uint32),
+    ("inputs", C.POINTER(C.POINTER(Node))), ("n_inputs", C.c_uint32), ("join_type", C.c_uint32),
 ]
 
 

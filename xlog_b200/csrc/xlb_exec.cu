@@ -118,11 +118,19 @@ struct FilterC {
     uint64_t rhs;  // constant, or a variable id
     bool applied;
 };
+struct CheckC {  // semi / anti join against a stored relation: keep rows whose variable has / lacks a match
+    std::string rel;
+    int kc;
+    int var;
+    bool anti;
+    bool applied;
+};
 struct FlatRule {
     std::string head;
     xlb_schema hs;
     std::vector<Atom> atoms;
     std::vector<FilterC> filters;
+    std::vector<CheckC> checks;
     std::vector<int> head_vars;
 };
 
@@ -180,6 +188,20 @@ struct Flattener {
                 return out;
             }
             case XLB_NODE_JOIN: {
+                if (n->join_type == XLB_JOIN_SEMI || n->join_type == XLB_JOIN_ANTI) {
+                    auto l = walk(n->left);
+                    if (!n->right || n->right->kind != XLB_NODE_SCAN || n->n_keys != 1)
+                        xlb_fail(XLB_ERR_UNSUPPORTED, "a semi / anti join takes a scanned relation on the right and one key column");
+                    auto nm = c->rel_names.find(n->right->rel_id);
+                    if (nm == c->rel_names.end()) xlb_fail(XLB_ERR_INVALID, "scan of unregistered relation id %u", n->right->rel_id);
+                    xlb_rel* r = store_get(c, nm->second);
+                    if (!r) xlb_fail(XLB_ERR_NOT_FOUND, "Missing relation: %s", nm->second.c_str());
+                    if (!rel_packable(r->schema)) xlb_fail(XLB_ERR_UNSUPPORTED, "relation %s: plans take relations of one or two 32-bit columns", nm->second.c_str());
+                    if (n->left_keys[0] >= l.size() || n->right_keys[0] >= r->schema.arity) xlb_fail(XLB_ERR_INVALID, "join key column out of range");
+                    fr.checks.push_back(CheckC{nm->second, (int)n->right_keys[0], l[n->left_keys[0]], n->join_type == XLB_JOIN_ANTI, false});
+                    return l;
+                }
+                if (n->join_type != XLB_JOIN_INNER) xlb_fail(XLB_ERR_UNSUPPORTED, "join type %u is not built", n->join_type);
                 auto l = walk(n->left);
                 auto r = walk(n->right);
                 if (n->n_keys < 1 || n->n_keys > XLB_MAX_KEYS) xlb_fail(XLB_ERR_INVALID, "join needs 1..%u keys", XLB_MAX_KEYS);
@@ -191,7 +213,7 @@ struct Flattener {
                 return l;
             }
             case XLB_NODE_UNION:
-                xlb_fail(XLB_ERR_UNSUPPORTED, "a Union node inside a rule body is not built; pass one rule per disjunct");
+                xlb_fail(XLB_ERR_UNSUPPORTED, "a Union node below the top of a rule body is not built");
         }
         xlb_fail(XLB_ERR_INVALID, "unknown plan node kind %u", n->kind);
     }
@@ -206,6 +228,7 @@ struct Flattener {
             f.lhs = find(f.lhs);
             if (!f.rhs_const) f.rhs = (uint64_t)find((int)f.rhs);
         }
+        for (auto& k : fr.checks) k.var = find(k.var);
         for (auto& v : fr.head_vars) v = find(v);
         if (fr.head_vars.size() != rule.head_schema.arity)
             xlb_fail(XLB_ERR_INVALID, "rule for %s: body yields %zu columns, head has %u", rule.head, fr.head_vars.size(), rule.head_schema.arity);
@@ -324,7 +347,18 @@ struct Bag {
 
 static int src_of(const Bag& b, int var) { return var == b.hi ? SRC_HI : SRC_LO; }
 
-static void apply_ready_filters(xlb_ctx* c, FlatRule& fr, Bag& b) {
+static void apply_ready_filters(xlb_ctx* c, FlatRule& fr, Bag& b, RunState& rs) {
+    for (auto& k : fr.checks) {  // semi / anti joins whose variable is bound now
+        if (k.applied || (k.var != b.hi && k.var != b.lo)) continue;
+        const Index& ix = get_index(c, k.rel, k.kc, rs);
+        int keysel = src_of(b, k.var);
+        if (c->world > 1 && b.part != k.var) {  // the index is partitioned by its key: take the rows there
+            b.k = comm_repartition(c, b.k, keysel, false, rs.st);
+            b.part = k.var;
+        }
+        b.k = ops_semi_filter(c, b.k, keysel, ix, k.anti);
+        k.applied = true;
+    }
     for (auto& f : fr.filters) {
         if (f.applied) continue;
         bool lhs_ok = f.lhs == b.hi || f.lhs == b.lo;
@@ -346,6 +380,8 @@ static std::set<int> needed_vars(const FlatRule& fr, const std::vector<bool>& do
             s.insert(f.lhs);
             if (!f.rhs_const) s.insert((int)f.rhs);
         }
+    for (auto& k : fr.checks)
+        if (!k.applied) s.insert(k.var);
     for (int v : fr.head_vars) s.insert(v);
     return s;
 }
@@ -368,7 +404,7 @@ static Keys run_pipeline(xlb_ctx* c, FlatRule fr /*by value: filter flags*/, siz
     }
     {
         PhaseTimer t(c, &rs.st.ms_join);
-        apply_ready_filters(c, fr, bag);
+        apply_ready_filters(c, fr, bag, rs);
     }
     size_t remaining = fr.atoms.size() - 1;
     while (remaining) {
@@ -410,6 +446,8 @@ static Keys run_pipeline(xlb_ctx* c, FlatRule fr /*by value: filter flags*/, siz
         bool pending = false;
         for (auto& f : fr.filters)
             if (!f.applied) pending = true;
+        for (auto& k : fr.checks)
+            if (!k.applied) pending = true;
         int out_hi = -1, out_lo = -1;
         if (last && !pending) {
             if (fr.head_vars.size() == 2) { out_hi = fr.head_vars[0]; out_lo = fr.head_vars[1]; }
@@ -442,7 +480,7 @@ static Keys run_pipeline(xlb_ctx* c, FlatRule fr /*by value: filter flags*/, siz
             nb.hi = out_hi;
             nb.lo = out_lo;
             bag = nb;
-            apply_ready_filters(c, fr, bag);
+            apply_ready_filters(c, fr, bag, rs);
         }
     }
     // head layout
@@ -450,6 +488,8 @@ static Keys run_pipeline(xlb_ctx* c, FlatRule fr /*by value: filter flags*/, siz
     int want_lo = fr.head_vars.size() == 2 ? fr.head_vars[1] : fr.head_vars[0];
     for (auto& f : fr.filters)
         if (!f.applied) xlb_fail(XLB_ERR_UNSUPPORTED, "rule for %s: a filter refers to a column that no atom binds", fr.head.c_str());
+    for (auto& k : fr.checks)
+        if (!k.applied) xlb_fail(XLB_ERR_UNSUPPORTED, "rule for %s: a semi / anti join key is not live where it could be applied", fr.head.c_str());
     if (bag.hi != want_hi || bag.lo != want_lo) {
         auto sel = [&](int var) -> int {
             if (var < 0) return SRC_ZERO;
@@ -648,7 +688,23 @@ static void run_scc(xlb_ctx* c, const xlb_scc& scc, RunState& rs) {
     for (auto& p : preds)
         if (!store_get(c, p)) store_put(c, p, empty_rel(c, schema[p]));  // recursive.rs:471-486
     std::vector<FlatRule> rules;
-    for (uint32_t i = 0; i < scc.n_rules; ++i) rules.push_back(Flattener{c, {}, {}}.run(scc.rules[i]));
+    for (uint32_t i = 0; i < scc.n_rules; ++i) {
+        // a Union at the top of a body is one rule per input (RirNode::Union concatenates its inputs)
+        std::vector<const xlb_node*> bodies{scc.rules[i].body};
+        for (size_t q = 0; q < bodies.size();) {
+            const xlb_node* b = bodies[q];
+            if (b->kind == XLB_NODE_UNION) {
+                if (!b->inputs && b->n_inputs) xlb_fail(XLB_ERR_INVALID, "Union node without inputs");
+                bodies.erase(bodies.begin() + q);
+                for (uint32_t u = 0; u < b->n_inputs; ++u) bodies.push_back(b->inputs[u]);
+            } else ++q;
+        }
+        for (const xlb_node* b : bodies) {
+            xlb_rule r = scc.rules[i];
+            r.body = b;
+            rules.push_back(Flattener{c, {}, {}}.run(r));
+        }
+    }
     std::map<std::string, int> home;
     for (auto& p : preds) home[p] = home_half(rules, p, rec, schema[p].arity);
     if (c->world > 1) {

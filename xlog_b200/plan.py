@@ -55,8 +55,11 @@ class Join(RirNode):
     right: RirNode
     left_keys: Sequence[int]
     right_keys: Sequence[int]
+    join_type: int = A.JOIN_INNER   # JOIN_SEMI / JOIN_ANTI keep the left columns only
 
     def arity(self, arities):
+        if self.join_type != A.JOIN_INNER:
+            return self.left.arity(arities)
         return self.left.arity(arities) + self.right.arity(arities)
 
 
@@ -133,6 +136,7 @@ class CompiledPlan:
             c.left = C.pointer(self._node(n.left))
             c.right = C.pointer(self._node(n.right))
             c.n_keys = len(n.left_keys)
+            c.join_type = n.join_type
             for i, (a, b) in enumerate(zip(n.left_keys, n.right_keys)):
                 c.left_keys[i], c.right_keys[i] = a, b
         elif isinstance(n, Union):

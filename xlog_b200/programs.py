@@ -89,3 +89,16 @@ def points_to_copy() -> ExecutionPlan:
     r0 = CompiledRule("points_to", Scan(0), U2)
     r1 = CompiledRule("points_to", Project(Join(Scan(1), Scan(2), [1], [0]), [0, 3]), U2)
     return ExecutionPlan([Scc(0, True, [r0, r1])], ids)
+
+
+def unreachable_nodes(source: int = 0) -> ExecutionPlan:
+    """Two strata: r(Y) :- edge(source,Y). r(Z) :- r(Y), edge(Y,Z).   then
+    un(X) :- node(X), not r(X).   (negation lowered to an anti join against the lower stratum)
+    and  either(X) :- r(X).  either(X) :- un(X).  written as one rule with a Union body."""
+    from .plan import Union
+    ids = {"edge": 0, "r": 1, "node": 2, "un": 3, "either": 4}
+    base = CompiledRule("r", Project(Filter(Scan(0), A.EQ, 0, source, True), [1]), (A.U32,))
+    rec = CompiledRule("r", Project(Join(Scan(1), Scan(0), [0], [0]), [2]), (A.U32,))
+    un = CompiledRule("un", Join(Scan(2), Scan(1), [0], [0], A.JOIN_ANTI), (A.U32,))
+    either = CompiledRule("either", Union([Scan(1), Scan(3)]), (A.U32,))
+    return ExecutionPlan([Scc(0, True, [base, rec]), Scc(1, False, [un]), Scc(2, False, [either])], ids)
