@@ -234,11 +234,12 @@ def main():
     for _ in range(args.warmup):
         device_step()
     prov.profile_enable(args.kernel)
-    ms_steps, stats = [], None
+    ms_steps, host_steps, stats = [], [], None
     launches = 0
     barrier()
     for _ in range(args.steps):
         stats = device_step()
+        host_steps.append([round(stats["ms_host_total"], 3), round(stats["ms_host_wait"], 3), round(stats["ms_host_alloc"], 3)])
         ms_steps.append(stats["ms_total"])
         launches += stats["kernel_launches"]
     barrier()
@@ -331,6 +332,7 @@ def main():
         "roofline": roof,
         "cpu_baseline": cpu,
         "host_last_step": {k: stats[k] for k in ("host_syncs", "ms_host_wait", "ms_host_total")},
+        "host_ms_total_wait_alloc_per_step": host_steps,
     }
     emit(line)
     if world > 1:

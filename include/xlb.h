@@ -229,6 +229,7 @@ typedef struct xlb_run_stats {
     uint64_t host_syncs;       /* times the host waited for the stream (row-count read-backs)  */
     double ms_host_wait;       /* host wall time inside those waits                            */
     double ms_host_total;      /* host wall time of the whole call                             */
+    double ms_host_alloc;      /* host wall time inside the device allocator                   */
 } xlb_run_stats;
 
 /* ---- executor: Executor::{register_relation, put_relation, store().get, execute_plan} ----- */

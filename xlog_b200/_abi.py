@@ -79,7 +79,7 @@ class RunStats(C.Structure):
                 ("peak_bytes", C.c_uint64), ("ms_total", C.c_double), ("ms_join", C.c_double),
                 ("ms_sort", C.c_double), ("ms_setops", C.c_double), ("ms_exchange", C.c_double),
                 ("exchange_bytes", C.c_uint64), ("host_syncs", C.c_uint64),
-                ("ms_host_wait", C.c_double), ("ms_host_total", C.c_double)]
+                ("ms_host_wait", C.c_double), ("ms_host_total", C.c_double), ("ms_host_alloc", C.c_double)]
 
     def as_dict(self):
         return {k: getattr(self, k) for k, _ in self._fields_}

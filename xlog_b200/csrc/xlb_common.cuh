@@ -3,10 +3,12 @@
 #include <cuda_runtime.h>
 
 #include <chrono>
+#include <algorithm>
 #include <cstdarg>
 #include <cstring>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <map>
 #include <memory>
 #include <string>
@@ -47,10 +49,123 @@ struct DevStatus {
     unsigned long long detail;
 };
 
+// Device memory arena.  Every buffer of a context is used on the context's one stream, so a block
+// that the host has freed can be handed out again at once: the work that used it was enqueued
+// earlier on the same stream.  That makes a plain host-side free list over a few large slabs
+// enough, and keeps the CUDA allocator off the hot path: a fixpoint allocates and frees a few
+// hundred temporaries, and the driver's stream-ordered pool was measured to spend milliseconds
+// remapping its reserve in one step out of three for the first twenty steps of a repeated workload.
+struct Arena {
+    struct Slab {
+        char* base;
+        uint64_t size;
+    };
+    std::vector<Slab> slabs;
+    std::map<char*, uint64_t> free_by_addr;
+    std::multimap<uint64_t, char*> free_by_size;
+    uint64_t reserved = 0;
+    static constexpr uint64_t ALIGN = 512, MIN_SLAB = 256ull << 20, MAX_GROW = 8ull << 30;
+
+    static uint64_t round_up(uint64_t n) { return (n + ALIGN - 1) / ALIGN * ALIGN; }
+    void insert_free(char* p, uint64_t n) {
+        free_by_addr[p] = n;
+        free_by_size.emplace(n, p);
+    }
+    void erase_free(char* p, uint64_t n) {
+        free_by_addr.erase(p);
+        auto r = free_by_size.equal_range(n);
+        for (auto it = r.first; it != r.second; ++it)
+            if (it->second == p) {
+                free_by_size.erase(it);
+                break;
+            }
+    }
+    bool add_slab(uint64_t size) {
+        void* p = nullptr;
+        if (cudaMalloc(&p, size) != cudaSuccess) {
+            cudaGetLastError();  // clear the sticky-less allocation error
+            return false;
+        }
+        slabs.push_back({(char*)p, size});
+        reserved += size;
+        insert_free((char*)p, size);
+        return true;
+    }
+    // Give back every slab that is entirely free (after the stream has drained).
+    void trim(cudaStream_t stream) {
+        cudaStreamSynchronize(stream);
+        for (size_t i = 0; i < slabs.size();) {
+            auto it = free_by_addr.find(slabs[i].base);
+            if (it != free_by_addr.end() && it->second == slabs[i].size) {
+                erase_free(slabs[i].base, slabs[i].size);
+                cudaFree(slabs[i].base);
+                reserved -= slabs[i].size;
+                slabs.erase(slabs.begin() + i);
+            } else ++i;
+        }
+    }
+    void* alloc(uint64_t n, cudaStream_t stream) {
+        n = round_up(n);
+        for (int attempt = 0; attempt < 3; ++attempt) {
+            auto it = free_by_size.lower_bound(n);  // best fit
+            if (it != free_by_size.end()) {
+                char* p = it->second;
+                uint64_t have = it->first;
+                erase_free(p, have);
+                if (have > n) insert_free(p + n, have - n);
+                return p;
+            }
+            if (attempt == 0) {
+                uint64_t grow = std::max<uint64_t>(MIN_SLAB, std::min<uint64_t>(reserved, MAX_GROW));
+                if (add_slab(std::max(n, grow)) || (grow > n && add_slab(n))) continue;
+            } else if (attempt == 1) {
+                trim(stream);
+                if (add_slab(n)) continue;
+            }
+        }
+        return nullptr;
+    }
+    void release(void* ptr, uint64_t n) {
+        char* p = (char*)ptr;
+        n = round_up(n);
+        auto next = free_by_addr.lower_bound(p);
+        // coalesce with the free block after and before, unless a slab boundary lies between
+        if (next != free_by_addr.end() && next->first == p + n && !is_slab_base(next->first)) {
+            uint64_t m = next->second;
+            erase_free(next->first, m);
+            n += m;
+        }
+        auto prev = free_by_addr.lower_bound(p);
+        if (prev != free_by_addr.begin()) {
+            --prev;
+            if (prev->first + prev->second == p && !is_slab_base(p)) {
+                char* q = prev->first;
+                uint64_t m = prev->second;
+                erase_free(q, m);
+                p = q;
+                n += m;
+            }
+        }
+        insert_free(p, n);
+    }
+    bool is_slab_base(char* p) const {
+        for (auto& s : slabs)
+            if (s.base == p) return true;
+        return false;
+    }
+    void destroy() {
+        for (auto& s : slabs) cudaFree(s.base);
+        slabs.clear();
+        free_by_addr.clear();
+        free_by_size.clear();
+        reserved = 0;
+    }
+};
+
 struct xlb_ctx {
     int device = 0;
     cudaStream_t stream = nullptr;
-    cudaMemPool_t pool = nullptr;
+    Arena arena;
     uint64_t budget = 0, allocated = 0, peak = 0;
     uint64_t max_iterations = 1000000;
     uint64_t join_chunk = 0;
@@ -58,6 +173,7 @@ struct xlb_ctx {
     uint64_t launches = 0;
     uint64_t syncs = 0;       // host waits on the stream (count read-backs)
     double ms_sync_wait = 0;  // wall time spent inside those waits
+    double ms_alloc = 0;      // wall time spent in the device allocator (allocate + free calls)
     std::string last_error;
     // pinned scratch for scalar read-backs
     unsigned long long* h_scalar = nullptr;  // 64 words
@@ -105,13 +221,18 @@ struct DevBuf {
         if (c->budget && c->allocated + n > c->budget)
             xlb_fail(XLB_ERR_RESOURCE_EXHAUSTED, "device memory budget exceeded: %llu + %llu > %llu bytes",
                      (unsigned long long)c->allocated, (unsigned long long)n, (unsigned long long)c->budget);
-        CUDA_OK(cudaMallocAsync(&p, n, c->pool, c->stream));
+        auto t0 = std::chrono::steady_clock::now();
+        p = c->arena.alloc(n, c->stream);
+        c->ms_alloc += std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+        if (!p)
+            xlb_fail(XLB_ERR_RESOURCE_EXHAUSTED, "device memory exhausted: %llu bytes requested with %llu allocated and %llu reserved",
+                     (unsigned long long)n, (unsigned long long)c->allocated, (unsigned long long)c->arena.reserved);
         c->allocated += n;
         if (c->allocated > c->peak) c->peak = c->allocated;
     }
     ~DevBuf() {
         if (p) {
-            cudaFreeAsync(p, ctx->stream);
+            ctx->arena.release(p, bytes);
             ctx->allocated -= bytes;
         }
     }
@@ -139,6 +260,16 @@ inline void check_launch(xlb_ctx* c, const char* what) {
 // Read `n` 64-bit words from device memory (one stream synchronisation).
 inline void stream_wait(xlb_ctx* c) {
     auto t0 = std::chrono::steady_clock::now();
+    static const bool spin = getenv("XLB_BLOCKING_WAIT") == nullptr;
+    if (spin) {  // poll first: a fixpoint waits for a row count many times, and a blocked thread's wake-up
+                 // costs milliseconds on a busy host; after 5 ms fall back to a blocking wait
+        for (;;) {
+            cudaError_t q = cudaStreamQuery(c->stream);
+            if (q == cudaSuccess) break;
+            if (q != cudaErrorNotReady) CUDA_OK(q);
+            if (std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count() > 5.0) break;
+        }
+    }
     CUDA_OK(cudaStreamSynchronize(c->stream));
     c->ms_sync_wait += std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
     c->syncs++;

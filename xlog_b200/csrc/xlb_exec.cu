@@ -778,7 +778,7 @@ extern "C" xlb_status xlb_execute_plan(xlb_ctx* c, const xlb_plan* plan, xlb_run
     RunState rs;
     cudaEvent_t e0 = nullptr, e1 = nullptr;
     uint64_t launches0 = c->launches, syncs0 = c->syncs;
-    double wait0 = c->ms_sync_wait;
+    double wait0 = c->ms_sync_wait, alloc0 = c->ms_alloc;
     auto host_t0 = std::chrono::steady_clock::now();
     c->peak = c->allocated;
     xlb_status result = XLB_OK;
@@ -818,6 +818,7 @@ extern "C" xlb_status xlb_execute_plan(xlb_ctx* c, const xlb_plan* plan, xlb_run
     rs.st.kernel_launches = c->launches - launches0;
     rs.st.host_syncs = c->syncs - syncs0;
     rs.st.ms_host_wait = c->ms_sync_wait - wait0;
+    rs.st.ms_host_alloc = c->ms_alloc - alloc0;
     rs.st.ms_host_total = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - host_t0).count();
     rs.st.peak_bytes = c->peak;
     if (stats && result == XLB_OK) *stats = rs.st;

@@ -163,49 +163,11 @@ struct LoadLow32 {  // low half of a u64 word (the match length of a probe resul
     __device__ __forceinline__ uint32_t operator()(uint64_t i) const { return (uint32_t)p[i]; }
 };
 
-// Up to a few hundred thousand elements one block walks the whole array (one launch instead of
-// three): 1024 threads, blocked chunks of 8 per thread, a running carry.
-constexpr uint64_t SCAN_SMALL_MAX = 1ull << 18;
-template <class Load, class Tout>
-static __global__ void __launch_bounds__(1024) scan_small_k(Load load, uint64_t n, Tout* out, Tout* total) {
-    __shared__ Tout sm[33];
-    __shared__ Tout carry_s;
-    if (threadIdx.x == 0) carry_s = 0;
-    __syncthreads();
-    for (uint64_t base = 0; base < n; base += 1024 * SCAN_IPT) {
-        uint64_t first = base + (uint64_t)threadIdx.x * SCAN_IPT;
-        Tout v[SCAN_IPT];
-        Tout s = 0;
-#pragma unroll
-        for (int k = 0; k < SCAN_IPT; ++k) {
-            v[k] = first + k < n ? (Tout)load(first + k) : Tout(0);
-            s += v[k];
-        }
-        Tout tot;
-        Tout run = block_exclusive_scan<Tout>(s, &tot, sm) + carry_s;
-#pragma unroll
-        for (int k = 0; k < SCAN_IPT; ++k) {
-            if (first + k < n) out[first + k] = run;
-            run += v[k];
-        }
-        __syncthreads();
-        if (threadIdx.x == 0) carry_s += tot;
-        __syncthreads();
-    }
-    if (threadIdx.x == 0) *total = carry_s;
-}
-
 // Exclusive scan; `d_total` (device, one Tout) receives the sum.
 template <class Load, class Tout>
 void exclusive_scan(xlb_ctx* c, Load load, uint64_t n, Tout* out, Tout* d_total) {
     if (n == 0) {
         CUDA_OK(cudaMemsetAsync(d_total, 0, sizeof(Tout), c->stream));
-        return;
-    }
-    if (n > (uint64_t)SCAN_TILE && n <= SCAN_SMALL_MAX) {
-        prof_begin(c, "scan_small", 0);
-        scan_small_k<Load, Tout><<<1, 1024, 0, c->stream>>>(load, n, out, d_total);
-        check_launch(c, "scan_small");
         return;
     }
     uint64_t ntiles = (n + SCAN_TILE - 1) / SCAN_TILE;
@@ -910,22 +872,37 @@ static __global__ void __launch_bounds__(BLOCK) dense_mark_k(const uint64_t* __r
         else     { if (cur & bit) atomicAnd(&bitmap[x >> 5], ~bit); }
     }
 }
-struct LoadPopc {
-    const unsigned int* w;
-    __device__ __forceinline__ uint32_t operator()(uint64_t i) const { return (uint32_t)__popc(w[i]); }
-};
-static __global__ void __launch_bounds__(BLOCK) dense_emit_k(const unsigned int* __restrict__ bitmap, uint64_t words, const uint64_t* __restrict__ offs,
-                                                           int lo_bits, uint64_t* __restrict__ out) {
+// The bitmap is counted and emitted in groups of 32 words (1024 tuples): one warp per group, so the
+// prefix sum that places the output runs over domain / 1024 entries only.
+static __global__ void __launch_bounds__(BLOCK) dense_count_k(const unsigned int* __restrict__ bitmap, uint64_t words, uint32_t* __restrict__ group_counts, uint64_t groups) {
+    uint64_t g = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (g >= groups) return;
+    uint64_t w = g * 32 + lane_id();
+    unsigned cnt = w < words ? __popc(bitmap[w]) : 0;
+#pragma unroll
+    for (int d = 16; d; d >>= 1) cnt += __shfl_xor_sync(FULL, cnt, d);
+    if (lane_id() == 0) group_counts[g] = cnt;
+}
+static __global__ void __launch_bounds__(BLOCK) dense_emit_k(const unsigned int* __restrict__ bitmap, uint64_t words, const uint64_t* __restrict__ group_offs,
+                                                           uint64_t groups, int lo_bits, uint64_t* __restrict__ out) {
+    uint64_t g = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (g >= groups) return;
+    const unsigned lane = lane_id();
     const uint64_t lo_mask = (1ull << lo_bits) - 1;
-    for (uint64_t w = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; w < words; w += (uint64_t)gridDim.x * blockDim.x) {
-        unsigned m = bitmap[w];
-        uint64_t pos = offs[w];
-        while (m) {
-            unsigned b = __ffs(m) - 1;
-            m &= m - 1;
-            uint64_t x = (w << 5) | b;
-            out[pos++] = ((x >> lo_bits) << 32) | (x & lo_mask);
-        }
+    uint64_t w = g * 32 + lane;
+    unsigned m = w < words ? bitmap[w] : 0;
+    unsigned cnt = __popc(m), incl = cnt;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        unsigned o = __shfl_up_sync(FULL, incl, d);
+        if (lane >= (unsigned)d) incl += o;
+    }
+    uint64_t pos = group_offs[g] + (incl - cnt);
+    while (m) {
+        unsigned b = __ffs(m) - 1;
+        m &= m - 1;
+        uint64_t x = (w << 5) | b;
+        out[pos++] = ((x >> lo_bits) << 32) | (x & lo_mask);
     }
 }
 

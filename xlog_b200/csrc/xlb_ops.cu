@@ -375,16 +375,21 @@ Keys ops_dense_novel(xlb_ctx* c, const Keys& cand, const Keys& full, int hi_bits
         dense_mark_k<false><<<grid_for(c, full.n), BLOCK, 0, c->stream>>>(full.ptr(), full.n, lo_bits, bitmap->as<unsigned int>(), words, c->d_status);
         check_launch(c, "dense_clear");
     }
-    Buf offs = make_buf(c, words * 8);
+    uint64_t groups = (words + 31) / 32;
+    Buf gcnt = make_buf(c, groups * 4);
+    Buf offs = make_buf(c, groups * 8);
     Buf total = make_buf(c, 8);
-    exclusive_scan<LoadPopc, uint64_t>(c, LoadPopc{bitmap->as<unsigned int>()}, words, offs->as<uint64_t>(), total->as<uint64_t>());
+    prof_begin(c, "dense_count", words * 4ull);
+    dense_count_k<<<(unsigned)((groups * 32 + BLOCK - 1) / BLOCK), BLOCK, 0, c->stream>>>(bitmap->as<unsigned int>(), words, gcnt->as<uint32_t>(), groups);
+    check_launch(c, "dense_count");
+    exclusive_scan<LoadU32, uint64_t>(c, LoadU32{gcnt->as<uint32_t>()}, groups, offs->as<uint64_t>(), total->as<uint64_t>());
     unsigned long long tot;
     read_words(c, total->p, 1, &tot);
     o.n = tot;
     o.buf = make_buf(c, tot * 8);
     if (tot) {
-        prof_begin(c, "dense_emit", words * 12ull + tot * 8ull);
-        dense_emit_k<<<grid_for(c, words), BLOCK, 0, c->stream>>>(bitmap->as<unsigned int>(), words, offs->as<uint64_t>(), lo_bits, o.buf->as<uint64_t>());
+        prof_begin(c, "dense_emit", words * 4ull + tot * 8ull);
+        dense_emit_k<<<(unsigned)((groups * 32 + BLOCK - 1) / BLOCK), BLOCK, 0, c->stream>>>(bitmap->as<unsigned int>(), words, offs->as<uint64_t>(), groups, lo_bits, o.buf->as<uint64_t>());
         check_launch(c, "dense_emit");
     }
     return o;
@@ -577,14 +582,6 @@ extern "C" xlb_status xlb_ctx_create(const xlb_config* cfg, xlb_ctx** out) {
         c->device = dev;
         CUDA_OK(cudaSetDevice(dev));
         CUDA_OK(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
-        cudaMemPoolProps props{};
-        props.allocType = cudaMemAllocationTypePinned;
-        props.handleTypes = cudaMemHandleTypeNone;
-        props.location.type = cudaMemLocationTypeDevice;
-        props.location.id = dev;
-        CUDA_OK(cudaMemPoolCreate(&c->pool, &props));
-        uint64_t thresh = ~0ull;
-        CUDA_OK(cudaMemPoolSetAttribute(c->pool, cudaMemPoolAttrReleaseThreshold, &thresh));
         size_t fr = 0, tot = 0;
         CUDA_OK(cudaMemGetInfo(&fr, &tot));
         c->budget = cfg && cfg->memory_budget_bytes ? cfg->memory_budget_bytes : (uint64_t)(fr * 0.9);
@@ -615,7 +612,7 @@ extern "C" void xlb_ctx_destroy(xlb_ctx* c) {
     cudaStreamSynchronize(c->stream);
     if (c->h_scalar) cudaFreeHost(c->h_scalar);
     if (c->d_status) cudaFree(c->d_status);
-    if (c->pool) cudaMemPoolDestroy(c->pool);
+    c->arena.destroy();
     if (c->stream) cudaStreamDestroy(c->stream);
     delete c;
 }
