@@ -695,6 +695,27 @@ inline void radix_sort(xlb_ctx* c, Buf& keys, Buf* vals, uint64_t n, unsigned di
     }
 }
 
+// ------------------------------------------------------------------------------ warp searches
+// A tile kernel finds its own slice of the input with a 32-way search run by one warp: a few
+// dependent rounds of loads instead of one per halving step, and no separate partition launch.
+// Number of leading indices in [0, n) for which pred holds (pred is true on a prefix).
+template <class Pred>
+__device__ __forceinline__ uint64_t warp_partition_point(uint64_t n, Pred pred) {
+    const unsigned lane = lane_id();
+    uint64_t lo = 0, hi = n;
+    while (hi - lo > 32) {
+        uint64_t step = (hi - lo + 31) / 32;
+        uint64_t idx = lo + (uint64_t)(lane + 1) * step - 1;  // last index of this lane's chunk
+        bool whole = idx < hi && pred(idx);
+        unsigned k = __popc(__ballot_sync(FULL, whole));
+        lo = lo + (uint64_t)k * step;
+        if (lo > hi) lo = hi;
+        hi = lo + step < hi ? lo + step : hi;
+    }
+    bool t = lo + lane < hi && pred(lo + lane);
+    return lo + __popc(__ballot_sync(FULL, t));
+}
+
 // ------------------------------------------------------------------------------ merge path
 constexpr int MP_IPT = 8;
 constexpr int MP_TILE = BLOCK * MP_IPT;  // 2048 merged elements per tile
@@ -710,25 +731,25 @@ __device__ __forceinline__ uint64_t merge_path(const uint64_t* A, uint64_t na, c
     return lo;
 }
 
-static __global__ void mp_partition_k(const uint64_t* __restrict__ A, uint64_t na, const uint64_t* __restrict__ B, uint64_t nb, uint64_t* __restrict__ splits, uint64_t ntiles) {
-    uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (t > ntiles) return;
-    uint64_t diag = t * MP_TILE;
-    if (diag > na + nb) diag = na + nb;
-    splits[t] = merge_path(A, na, B, nb, diag);
-}
-
 // MODE 0: keep[i] = 1 iff A[i] is not in B (A, B sorted unique).
 // MODE 1: out = merge of A and B (disjoint), out has na + nb entries.
 template <int MODE>
 static __global__ void __launch_bounds__(BLOCK) mp_tile_k(const uint64_t* __restrict__ A, uint64_t na, const uint64_t* __restrict__ B, uint64_t nb,
-                                                    const uint64_t* __restrict__ splits, uint8_t* __restrict__ keep, uint64_t* __restrict__ out) {
+                                                    uint8_t* __restrict__ keep, uint64_t* __restrict__ out) {
     __shared__ uint64_t sA[MP_TILE + 1];
     __shared__ uint64_t sB[MP_TILE + 2];
+    __shared__ uint64_t split_s[2];
     uint64_t t = blockIdx.x;
     uint64_t d0 = t * MP_TILE, d1 = d0 + MP_TILE;
     if (d1 > na + nb) d1 = na + nb;
-    uint64_t a0 = splits[t], a1 = splits[t + 1];
+    if (threadIdx.x < 64) {  // warp 0 finds the split of diagonal d0, warp 1 that of d1 (A first on ties)
+        uint64_t diag = threadIdx.x < 32 ? d0 : d1;
+        uint64_t lo = diag > nb ? diag - nb : 0, hi = diag < na ? diag : na;
+        uint64_t k = warp_partition_point(hi - lo, [&](uint64_t i) { return A[lo + i] <= B[diag - 1 - (lo + i)]; });
+        if (lane_id() == 0) split_s[threadIdx.x >> 5] = lo + k;
+    }
+    __syncthreads();
+    uint64_t a0 = split_s[0], a1 = split_s[1];
     uint64_t b0 = d0 - a0, b1 = d1 - a1;
     unsigned la = (unsigned)(a1 - a0), lb = (unsigned)(b1 - b0);
     unsigned lbx = lb + ((b1 < nb) ? 1u : 0u);  // one look-ahead element of B for a match across the tile edge
@@ -812,13 +833,9 @@ inline Buf set_difference(xlb_ctx* c, const uint64_t* A, uint64_t na, const uint
         return o;
     }
     uint64_t ntiles = (na + nb + MP_TILE - 1) / MP_TILE;
-    Buf splits = make_buf(c, (ntiles + 1) * 8);
     Buf keep = make_buf(c, na);
-    prof_begin(c, "mp_partition", 0);
-    mp_partition_k<<<(unsigned)((ntiles + 1 + 127) / 128), 128, 0, c->stream>>>(A, na, B, nb, splits->as<uint64_t>(), ntiles);
-    check_launch(c, "mp_partition");
     prof_begin(c, "mp_diff", (na + nb) * 8ull + na);
-    mp_tile_k<0><<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(A, na, B, nb, splits->as<uint64_t>(), keep->as<uint8_t>(), nullptr);
+    mp_tile_k<0><<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(A, na, B, nb, keep->as<uint8_t>(), nullptr);
     check_launch(c, "mp_diff");
     Buf tmp = make_buf(c, na * 8);
     uint64_t m = a_has_dups ? select(c, PredKeepHead{keep->as<uint8_t>(), A}, EmitKey{A, tmp->as<uint64_t>()}, na)
@@ -835,12 +852,8 @@ inline Buf merge_disjoint(xlb_ctx* c, const uint64_t* A, uint64_t na, const uint
         return o;
     }
     uint64_t ntiles = (na + nb + MP_TILE - 1) / MP_TILE;
-    Buf splits = make_buf(c, (ntiles + 1) * 8);
-    prof_begin(c, "mp_partition", 0);
-    mp_partition_k<<<(unsigned)((ntiles + 1 + 127) / 128), 128, 0, c->stream>>>(A, na, B, nb, splits->as<uint64_t>(), ntiles);
-    check_launch(c, "mp_partition");
     prof_begin(c, "mp_union", (na + nb) * 16ull);
-    mp_tile_k<1><<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(A, na, B, nb, splits->as<uint64_t>(), nullptr, o->as<uint64_t>());
+    mp_tile_k<1><<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(A, na, B, nb, nullptr, o->as<uint64_t>());
     check_launch(c, "mp_union");
     return o;
 }
@@ -999,21 +1012,6 @@ struct EmitMatched {
 constexpr int EX_IPT = 8;
 constexpr int EX_TILE = BLOCK * EX_IPT;
 
-// tile_row[t] = index of the matched row that owns output t * EX_TILE (last row with off <= o).
-static __global__ void expand_partition_k(const uint64_t* __restrict__ off, uint64_t nrows, uint64_t total, uint64_t* __restrict__ tile_row, uint64_t ntiles) {
-    uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (t > ntiles) return;
-    uint64_t o = t * EX_TILE;
-    if (o >= total) { tile_row[t] = nrows; return; }
-    uint64_t lo = 0, hi = nrows;  // first row with off > o
-    while (lo < hi) {
-        uint64_t mid = (lo + hi) >> 1;
-        if (off[mid] <= o) lo = mid + 1;
-        else hi = mid;
-    }
-    tile_row[t] = lo - 1;
-}
-
 // Output column source: 0 = probe high half, 1 = probe low half, 2 = the build row's other
 // column, 3 = zero (arity-1 output keeps the value in the low half).
 __device__ __forceinline__ uint32_t ex_pick(int src, uint64_t probe, uint32_t other) {
@@ -1024,13 +1022,19 @@ __device__ __forceinline__ uint32_t ex_pick(int src, uint64_t probe, uint32_t ot
 // outputs finds its rows by a search over the row offsets held in shared memory, so writes are
 // coalesced whatever the degree skew.  Output order: probe row order, then build order.
 static __global__ void __launch_bounds__(BLOCK) expand_k(const uint64_t* __restrict__ mbag, const uint64_t* __restrict__ mmatch, const uint64_t* __restrict__ off,
-                                                   uint64_t nrows, uint64_t total, const uint64_t* __restrict__ tile_row, const uint64_t* __restrict__ S,
+                                                   uint64_t nrows, uint64_t total, const uint64_t* __restrict__ S,
                                                    const uint32_t* __restrict__ pay, int hi_src, int lo_src, uint64_t* __restrict__ out) {
     __shared__ uint64_t soff[EX_TILE + 2];
     uint64_t o0 = (uint64_t)blockIdx.x * EX_TILE;
     uint64_t o1 = o0 + EX_TILE < total ? o0 + EX_TILE : total;
-    uint64_t r0 = tile_row[blockIdx.x];
-    uint64_t r1 = tile_row[blockIdx.x + 1];  // row owning the first output of the next tile (or nrows)
+    __shared__ uint64_t row_s[2];
+    if (threadIdx.x < 64) {  // warp 0: the row that owns output o0; warp 1: the row that owns the next tile's first output
+        uint64_t o = threadIdx.x < 32 ? o0 : o0 + EX_TILE;
+        uint64_t ub = o < total ? warp_partition_point(nrows, [&](uint64_t i) { return off[i] <= o; }) : nrows + 1;
+        if (lane_id() == 0) row_s[threadIdx.x >> 5] = ub - 1;  // last row with offset <= o
+    }
+    __syncthreads();
+    uint64_t r0 = row_s[0], r1 = row_s[1];
     if (r1 >= nrows) r1 = nrows - 1;
     // Probe rows without a match stay in the arrays (equal consecutive offsets), so a tile may span
     // any number of rows; the usual span fits shared memory, a longer one is searched in place.

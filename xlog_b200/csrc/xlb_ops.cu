@@ -504,12 +504,8 @@ Keys ops_join_expand(xlb_ctx* c, const Keys& bag, int keysel, const uint64_t* pk
     out.buf = make_buf(c, tot * 8);
     if (tot == 0) return out;
     uint64_t ntiles = (tot + EX_TILE - 1) / EX_TILE;
-    Buf tile_row = make_buf(c, (ntiles + 1) * 8);
-    prof_begin(c, "expand_partition", 0);
-    expand_partition_k<<<(unsigned)((ntiles + 1 + 127) / 128), 128, 0, c->stream>>>(off->as<uint64_t>(), bag.n, tot, tile_row->as<uint64_t>(), ntiles);
-    check_launch(c, "expand_partition");
     prof_begin(c, "expand", tot * 12ull + bag.n * 24ull);
-    expand_k<<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(bag.ptr(), match->as<uint64_t>(), off->as<uint64_t>(), bag.n, tot, tile_row->as<uint64_t>(),
+    expand_k<<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(bag.ptr(), match->as<uint64_t>(), off->as<uint64_t>(), bag.n, tot,
                                                          ix.S->as<uint64_t>(), ix.pay ? ix.pay->as<uint32_t>() : nullptr, hi_src, lo_src, out.buf->as<uint64_t>());
     check_launch(c, "expand");
     return out;
