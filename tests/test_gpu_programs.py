@@ -227,7 +227,7 @@ def test_dense_route_on_and_off_agree(oracle, name):
         p.profile_enable("*")
         got, _ = run_program(p, plan, inputs, [out])
         prof = p.profile_read()
-        used_dense = "dense_mark" in prof
+        used_dense = "dense_mark" in prof or "expand_mark" in prof
         assert used_dense == (flags == 0), "the route taken is not the one asked for"
         assert all(np.array_equal(g, w) for g, w in zip(got[out], want[out]))
         p.close()

@@ -388,7 +388,17 @@ static std::set<int> needed_vars(const FlatRule& fr, const std::vector<bool>& do
 
 // Evaluate the rule with atom `start` read from `start_rows` (the delta, a chunk of it, or a
 // full relation) and every other atom from the store.  Returns candidate head tuples (a bag).
-static Keys run_pipeline(xlb_ctx* c, FlatRule fr /*by value: filter flags*/, size_t start, const Keys& start_rows, int start_part_half, uint64_t limit, RunState& rs) {
+// `sink`: when the last join writes the head layout directly and the head fits a dense domain, its
+// output is marked into sink->set instead of being materialised (sink->used says so; the returned
+// Keys then carries only the tuple count).
+struct DenseSink {
+    const Keys* full = nullptr;
+    bool used = false;
+    DenseSet set;
+};
+
+static Keys run_pipeline(xlb_ctx* c, FlatRule fr /*by value: filter flags*/, size_t start, const Keys& start_rows, int start_part_half, uint64_t limit, RunState& rs,
+                         DenseSink* sink = nullptr) {
     std::vector<bool> done(fr.atoms.size(), false);
     Bag bag;
     const Atom& sa = fr.atoms[start];
@@ -474,6 +484,18 @@ static Keys run_pipeline(xlb_ctx* c, FlatRule fr /*by value: filter flags*/, siz
         }
         {
             PhaseTimer t(c, &rs.st.ms_join);
+            int hb = 0, lb = 0;
+            Keys shape;  // stands for the rows this step would produce: only their OR bound matters here
+            shape.n = 1;
+            shape.bound = ops_expand_bound(probe, ix, hs, ls);
+            if (sink && last && !pending && c->world == 1 && !(c->flags & XLB_FLAG_NO_DENSE) && ops_dense_bits(shape, *sink->full, &hb, &lb)) {
+                sink->set = ops_dense_begin(c, hb, lb);
+                sink->used = true;
+                Keys counted;
+                counted.n = ops_join_expand_mark(c, probe, keysel, ix, hs, ls, sink->set);
+                counted.bound = shape.bound;
+                return counted;
+            }
             nb.k = ops_join_expand(c, probe, keysel, nullptr, ix, hs, ls);
             nb.part = keyvar;
             if (limit && nb.k.n > limit && start_rows.n > 1) throw ChunkTooBig{};
@@ -550,8 +572,10 @@ static void eval_variant(xlb_ctx* c, const FlatRule& fr_in, size_t start, const 
         uint64_t hi = std::min(start_rows.n, at + chunk);
         Keys part = (at == 0 && hi == start_rows.n) ? start_rows : ops_slice(c, start_rows, at, hi);
         Keys cand;
+        DenseSink sink;
+        sink.full = &full;
         try {
-            cand = run_pipeline(c, fr, start, part, start_part_half, limit, rs);
+            cand = run_pipeline(c, fr, start, part, start_part_half, limit, rs, &sink);
         } catch (const ChunkTooBig&) {
             chunk = std::max<uint64_t>((hi - at) / 2, 1);
             continue;
@@ -565,7 +589,11 @@ static void eval_variant(xlb_ctx* c, const FlatRule& fr_in, size_t start, const 
         if (cand.n == 0) continue;
         Keys fresh;
         int hb = 0, lb = 0;
-        if (!(c->flags & XLB_FLAG_NO_DENSE) && ops_dense_bits(cand, full, &hb, &lb)) {
+        if (sink.used) {
+            // the last join marked its tuples in the bitmap already
+            PhaseTimer t(c, &rs.st.ms_setops);
+            fresh = ops_dense_finish(c, sink.set, full);
+        } else if (!(c->flags & XLB_FLAG_NO_DENSE) && ops_dense_bits(cand, full, &hb, &lb)) {
             // small dense domain: sort + dedup + difference on a bitmap
             PhaseTimer t(c, &rs.st.ms_setops);
             fresh = ops_dense_novel(c, cand, full, hb, lb);

@@ -1021,9 +1021,13 @@ __device__ __forceinline__ uint32_t ex_pick(int src, uint64_t probe, uint32_t ot
 // Load-balanced expansion: every matched probe row contributes len outputs; each tile of EX_TILE
 // outputs finds its rows by a search over the row offsets held in shared memory, so writes are
 // coalesced whatever the degree skew.  Output order: probe row order, then build order.
+// MARK = true: instead of storing the output tuples, set their bits in a dense-domain bitmap (the
+// candidates of a small-domain head never touch memory as a list).
+template <bool MARK>
 static __global__ void __launch_bounds__(BLOCK) expand_k(const uint64_t* __restrict__ mbag, const uint64_t* __restrict__ mmatch, const uint64_t* __restrict__ off,
                                                    uint64_t nrows, uint64_t total, const uint64_t* __restrict__ S,
-                                                   const uint32_t* __restrict__ pay, int hi_src, int lo_src, uint64_t* __restrict__ out) {
+                                                   const uint32_t* __restrict__ pay, int hi_src, int lo_src, uint64_t* __restrict__ out,
+                                                   unsigned int* __restrict__ bitmap, uint64_t words, int lo_bits, DevStatus* st) {
     __shared__ uint64_t soff[EX_TILE + 2];
     uint64_t o0 = (uint64_t)blockIdx.x * EX_TILE;
     uint64_t o1 = o0 + EX_TILE < total ? o0 + EX_TILE : total;
@@ -1066,7 +1070,18 @@ static __global__ void __launch_bounds__(BLOCK) expand_k(const uint64_t* __restr
         uint64_t start = mmatch[r] >> 32;
         uint64_t j = start + (o - (in_smem ? soff[lo - 1] : off[r]));
         uint32_t other = pay ? pay[j] : (uint32_t)S[j];
-        out[o] = ((uint64_t)ex_pick(hi_src, probe, other) << 32) | ex_pick(lo_src, probe, other);
+        uint64_t key = ((uint64_t)ex_pick(hi_src, probe, other) << 32) | ex_pick(lo_src, probe, other);
+        if (!MARK) {
+            out[o] = key;
+        } else {
+            uint32_t x = dense_index(key, lo_bits);
+            if ((key & 0xFFFFFFFFull) >> lo_bits || (uint64_t)(x >> 5) >= words) {
+                set_status(st, XLB_ERR_CAPACITY, 4, key);
+            } else {
+                unsigned bit = 1u << (x & 31);
+                if (!(bitmap[x >> 5] & bit)) atomicOr(&bitmap[x >> 5], bit);
+            }
+        }
     }
 }
 

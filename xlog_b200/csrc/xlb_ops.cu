@@ -359,20 +359,23 @@ bool ops_dense_bits(const Keys& a, const Keys& b, int* hi_bits, int* lo_bits) {
     return *hi_bits + *lo_bits <= 27 && *hi_bits + *lo_bits >= 1;
 }
 
-Keys ops_dense_novel(xlb_ctx* c, const Keys& cand, const Keys& full, int hi_bits, int lo_bits) {
+DenseSet ops_dense_begin(xlb_ctx* c, int hi_bits, int lo_bits) {
+    DenseSet d;
+    d.hi_bits = hi_bits;
+    d.lo_bits = lo_bits;
+    d.words = ((1ull << (hi_bits + lo_bits)) + 31) / 32;
+    d.bitmap = make_buf(c, d.words * 4);
+    CUDA_OK(cudaMemsetAsync(d.bitmap->p, 0, d.words * 4, c->stream));
+    return d;
+}
+
+Keys ops_dense_finish(xlb_ctx* c, DenseSet& d, const Keys& full) {
     Keys o;
-    o.bound = cand.bound;
-    uint64_t words = ((1ull << (hi_bits + lo_bits)) + 31) / 32;
-    Buf bitmap = make_buf(c, words * 4);
-    CUDA_OK(cudaMemsetAsync(bitmap->p, 0, words * 4, c->stream));
-    if (cand.n) {
-        prof_begin(c, "dense_mark", cand.n * 8ull);
-        dense_mark_k<true><<<grid_for(c, cand.n), BLOCK, 0, c->stream>>>(cand.ptr(), cand.n, lo_bits, bitmap->as<unsigned int>(), words, c->d_status);
-        check_launch(c, "dense_mark");
-    }
-    if (full.n && cand.n) {
+    o.bound = d.bound;
+    const uint64_t words = d.words;
+    if (full.n) {
         prof_begin(c, "dense_clear", full.n * 8ull);
-        dense_mark_k<false><<<grid_for(c, full.n), BLOCK, 0, c->stream>>>(full.ptr(), full.n, lo_bits, bitmap->as<unsigned int>(), words, c->d_status);
+        dense_mark_k<false><<<grid_for(c, full.n), BLOCK, 0, c->stream>>>(full.ptr(), full.n, d.lo_bits, d.bitmap->as<unsigned int>(), words, c->d_status);
         check_launch(c, "dense_clear");
     }
     uint64_t groups = (words + 31) / 32;
@@ -380,7 +383,7 @@ Keys ops_dense_novel(xlb_ctx* c, const Keys& cand, const Keys& full, int hi_bits
     Buf offs = make_buf(c, groups * 8);
     Buf total = make_buf(c, 8);
     prof_begin(c, "dense_count", words * 4ull);
-    dense_count_k<<<(unsigned)((groups * 32 + BLOCK - 1) / BLOCK), BLOCK, 0, c->stream>>>(bitmap->as<unsigned int>(), words, gcnt->as<uint32_t>(), groups);
+    dense_count_k<<<(unsigned)((groups * 32 + BLOCK - 1) / BLOCK), BLOCK, 0, c->stream>>>(d.bitmap->as<unsigned int>(), words, gcnt->as<uint32_t>(), groups);
     check_launch(c, "dense_count");
     exclusive_scan<LoadU32, uint64_t>(c, LoadU32{gcnt->as<uint32_t>()}, groups, offs->as<uint64_t>(), total->as<uint64_t>());
     unsigned long long tot;
@@ -389,10 +392,22 @@ Keys ops_dense_novel(xlb_ctx* c, const Keys& cand, const Keys& full, int hi_bits
     o.buf = make_buf(c, tot * 8);
     if (tot) {
         prof_begin(c, "dense_emit", words * 4ull + tot * 8ull);
-        dense_emit_k<<<(unsigned)((groups * 32 + BLOCK - 1) / BLOCK), BLOCK, 0, c->stream>>>(bitmap->as<unsigned int>(), words, offs->as<uint64_t>(), groups, lo_bits, o.buf->as<uint64_t>());
+        dense_emit_k<<<(unsigned)((groups * 32 + BLOCK - 1) / BLOCK), BLOCK, 0, c->stream>>>(d.bitmap->as<unsigned int>(), words, offs->as<uint64_t>(), groups, d.lo_bits, o.buf->as<uint64_t>());
         check_launch(c, "dense_emit");
     }
     return o;
+}
+
+Keys ops_dense_novel(xlb_ctx* c, const Keys& cand, const Keys& full, int hi_bits, int lo_bits) {
+    DenseSet d = ops_dense_begin(c, hi_bits, lo_bits);
+    d.bound = cand.bound;
+    if (cand.n) {
+        prof_begin(c, "dense_mark", cand.n * 8ull);
+        dense_mark_k<true><<<grid_for(c, cand.n), BLOCK, 0, c->stream>>>(cand.ptr(), cand.n, lo_bits, d.bitmap->as<unsigned int>(), d.words, c->d_status);
+        check_launch(c, "dense_mark");
+    }
+    Keys none;
+    return ops_dense_finish(c, d, cand.n ? full : none);
 }
 
 Keys ops_merge_disjoint(xlb_ctx* c, const Keys& a, const Keys& b) {
@@ -487,13 +502,18 @@ Keys ops_semi_filter(xlb_ctx* c, const Keys& bag, int keysel, const Index& ix, b
     return o;
 }
 
-Keys ops_join_expand(xlb_ctx* c, const Keys& bag, int keysel, const uint64_t* pkeys, const Index& ix, int hi_src, int lo_src) {
-    Keys out;
+uint64_t ops_expand_bound(const Keys& bag, const Index& ix, int hi_src, int lo_src) {
     uint64_t other_bound = ix.pay ? 0xFFFFFFFFull : (ix.bound == ~0ull ? 0xFFFFFFFFull : (ix.bound & 0xFFFFFFFFull));
-    out.bound = (half_bound(bag.bound, hi_src, other_bound) << 32) | half_bound(bag.bound, lo_src, other_bound);
+    return (half_bound(bag.bound, hi_src, other_bound) << 32) | half_bound(bag.bound, lo_src, other_bound);
+}
+
+// Probe, prefix-sum the match lengths over all probe rows (rows without a match keep length 0),
+// then a load-balanced expansion: one count read-back per join step.  With `dense` the output
+// tuples are marked in its bitmap and no list is produced.
+static Keys join_expand(xlb_ctx* c, const Keys& bag, int keysel, const uint64_t* pkeys, const Index& ix, int hi_src, int lo_src, DenseSet* dense) {
+    Keys out;
+    out.bound = ops_expand_bound(bag, ix, hi_src, lo_src);
     if (bag.n == 0 || ix.n == 0) { out.buf = make_buf(c, 0); return out; }
-    // probe, prefix-sum the match lengths over all probe rows (rows without a match keep length 0),
-    // then a load-balanced expansion: one count read-back per join step
     Buf match = ops_probe_match(c, bag, keysel, pkeys, ix);
     Buf off = make_buf(c, bag.n * 8);
     Buf total = make_buf(c, 8);
@@ -501,14 +521,31 @@ Keys ops_join_expand(xlb_ctx* c, const Keys& bag, int keysel, const uint64_t* pk
     unsigned long long tot;
     read_words(c, total->p, 1, &tot);
     out.n = tot;
-    out.buf = make_buf(c, tot * 8);
+    if (!dense) out.buf = make_buf(c, tot * 8);
     if (tot == 0) return out;
     uint64_t ntiles = (tot + EX_TILE - 1) / EX_TILE;
-    prof_begin(c, "expand", tot * 12ull + bag.n * 24ull);
-    expand_k<<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(bag.ptr(), match->as<uint64_t>(), off->as<uint64_t>(), bag.n, tot,
-                                                         ix.S->as<uint64_t>(), ix.pay ? ix.pay->as<uint32_t>() : nullptr, hi_src, lo_src, out.buf->as<uint64_t>());
-    check_launch(c, "expand");
+    const uint32_t* pay = ix.pay ? ix.pay->as<uint32_t>() : nullptr;
+    if (!dense) {
+        prof_begin(c, "expand", tot * 12ull + bag.n * 24ull);
+        expand_k<false><<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(bag.ptr(), match->as<uint64_t>(), off->as<uint64_t>(), bag.n, tot, ix.S->as<uint64_t>(), pay, hi_src, lo_src,
+                                                                    out.buf->as<uint64_t>(), nullptr, 0, 0, c->d_status);
+        check_launch(c, "expand");
+    } else {
+        prof_begin(c, "expand_mark", tot * 4ull + bag.n * 24ull);
+        expand_k<true><<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(bag.ptr(), match->as<uint64_t>(), off->as<uint64_t>(), bag.n, tot, ix.S->as<uint64_t>(), pay, hi_src, lo_src,
+                                                                   nullptr, dense->bitmap->as<unsigned int>(), dense->words, dense->lo_bits, c->d_status);
+        check_launch(c, "expand_mark");
+        dense->bound |= out.bound;
+    }
     return out;
+}
+
+Keys ops_join_expand(xlb_ctx* c, const Keys& bag, int keysel, const uint64_t* pkeys, const Index& ix, int hi_src, int lo_src) {
+    return join_expand(c, bag, keysel, pkeys, ix, hi_src, lo_src, nullptr);
+}
+
+uint64_t ops_join_expand_mark(xlb_ctx* c, const Keys& bag, int keysel, const Index& ix, int hi_src, int lo_src, DenseSet& d) {
+    return join_expand(c, bag, keysel, nullptr, ix, hi_src, lo_src, &d).n;
 }
 
 Keys ops_partition_by_owner_dev(xlb_ctx* c, const Keys& in, int keysel, uint32_t world, unsigned long long* counts) {

@@ -45,6 +45,19 @@ Keys ops_dedup_diff(xlb_ctx* c, const Keys& a, const Keys& b);   // distinct row
 // both arrays fit one (returns false otherwise) and how many low-half bits to keep.
 bool ops_dense_bits(const Keys& a, const Keys& b, int* hi_bits, int* lo_bits);
 Keys ops_dense_novel(xlb_ctx* c, const Keys& cand, const Keys& full, int hi_bits, int lo_bits);
+// The same in pieces, so that a join can mark its output tuples straight into the bitmap:
+struct DenseSet {
+    Buf bitmap;
+    uint64_t words = 0;
+    int hi_bits = 0, lo_bits = 0;
+    uint64_t bound = 0;  // OR bound of what was marked
+};
+DenseSet ops_dense_begin(xlb_ctx* c, int hi_bits, int lo_bits);
+Keys ops_dense_finish(xlb_ctx* c, DenseSet& d, const Keys& full);  // clear `full`, emit the rest in order
+// OR bound of the rows ops_join_expand would produce
+uint64_t ops_expand_bound(const Keys& bag, const Index& ix, int hi_src, int lo_src);
+// ops_join_expand that marks instead of materialising; returns the number of (bag) tuples marked
+uint64_t ops_join_expand_mark(xlb_ctx* c, const Keys& bag, int keysel, const Index& ix, int hi_src, int lo_src, DenseSet& d);
 Keys ops_merge_disjoint(xlb_ctx* c, const Keys& a, const Keys& b);
 Keys ops_union(xlb_ctx* c, const Keys& a, const Keys& b);        // sorted unique a U b
 Keys ops_remap(xlb_ctx* c, const Keys& in, int hi_src, int lo_src);
