@@ -253,8 +253,8 @@ static Keys index_rows(xlb_ctx* c, const xlb_rel* r, int kc) {
     }
     if (kc == 0) {
         if (r->canonical) return k;  // a canonical relation is already ordered by its first column
-        Keys s = ops_copy(c, k);
-        ops_sort_by_high_half(c, s);
+        Keys s = k;
+        ops_sort_by_high_half(c, s, /*keep_input=*/true);
         return s;
     }
     Keys s = ops_remap(c, k, SRC_LO, SRC_HI);
@@ -598,10 +598,9 @@ static void eval_variant(xlb_ctx* c, const FlatRule& fr_in, size_t start, const 
             PhaseTimer t(c, &rs.st.ms_setops);
             fresh = ops_dense_novel(c, cand, full, hb, lb);
         } else {
-            if (cand.buf == start_rows.buf) cand = ops_copy(c, cand);  // a single-atom body: never sort a stored relation in place
             {
                 PhaseTimer t(c, &rs.st.ms_sort);
-                ops_sort(c, cand);
+                ops_sort(c, cand, /*keep_input=*/cand.buf == start_rows.buf);  // a single-atom body hands over a stored relation
             }
             PhaseTimer t(c, &rs.st.ms_setops);
             fresh = ops_dedup_diff(c, cand, full);  // duplicates dropped and `full` subtracted in one merge pass
@@ -620,10 +619,9 @@ static xlb_rel* empty_rel(xlb_ctx* c, const xlb_schema& s) {
 static Keys canonical_keys(xlb_ctx* c, const xlb_rel* r, RunState& rs) {
     Keys k = ops_rel_packed(c, r);
     if (r->canonical) return k;
-    k = ops_copy(c, k);
     {
         PhaseTimer t(c, &rs.st.ms_sort);
-        ops_sort(c, k);
+        ops_sort(c, k, /*keep_input=*/true);
     }
     PhaseTimer t(c, &rs.st.ms_setops);
     ops_dedup_sorted(c, k);

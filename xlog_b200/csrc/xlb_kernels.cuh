@@ -616,7 +616,9 @@ inline SortPlan plan_sort(xlb_ctx* c, const uint64_t* keys, uint64_t n) {
 // needs its rows grouped by the key half, i.e. digits 4..7.
 // `known_bound` != ~0: an upper bound of the OR of all keys that the host already holds; digits
 // outside it are constant, so the digit plan needs no read-back.
-inline void radix_sort(xlb_ctx* c, Buf& keys, Buf* vals, uint64_t n, unsigned digit_mask = 0xFFu, uint64_t known_bound = ~0ull) {
+// `keep_input`: the buffer `keys` names on entry is left untouched (it may belong to a stored
+// relation); the first pass reads it and later passes ping-pong between two fresh buffers.
+inline void radix_sort(xlb_ctx* c, Buf& keys, Buf* vals, uint64_t n, unsigned digit_mask = 0xFFu, uint64_t known_bound = ~0ull, bool keep_input = false) {
     if (n <= 1) return;
     if (n >= (1ull << 32)) xlb_fail(XLB_ERR_CAPACITY, "sort of %llu keys exceeds the 2^32 limit of one sort", (unsigned long long)n);
     radix_sort_setup();
@@ -664,7 +666,10 @@ inline void radix_sort(xlb_ctx* c, Buf& keys, Buf* vals, uint64_t n, unsigned di
             else
                 radix_scatter_k<false, true><<<ntiles, SORT_THREADS, SORT_SMEM, c->stream>>>(keys->as<uint64_t>(), tmpk->as<uint64_t>(), nullptr, nullptr, n, 8 * d, bases + d * 256, ntiles, counters + q, st, c->d_status);
             check_launch(c, "radix_scatter");
-            std::swap(keys, tmpk);
+            if (keep_input && q == 0) {
+                keys = tmpk;
+                tmpk = np > 1 ? make_buf(c, n * 8) : Buf();
+            } else std::swap(keys, tmpk);
             if (vals) std::swap(*vals, tmpv);
         }
         return;
@@ -690,7 +695,10 @@ inline void radix_sort(xlb_ctx* c, Buf& keys, Buf* vals, uint64_t n, unsigned di
         else
             radix_scatter_k<false, false><<<ntiles, SORT_THREADS, SORT_SMEM, c->stream>>>(keys->as<uint64_t>(), tmpk->as<uint64_t>(), nullptr, nullptr, n, shift, offs->as<uint32_t>(), ntiles, nullptr, nullptr, c->d_status);
         check_launch(c, "radix_scatter");
-        std::swap(keys, tmpk);
+        if (keep_input && q == 0) {
+            keys = tmpk;
+            tmpk = p.npasses > 1 ? make_buf(c, n * 8) : Buf();
+        } else std::swap(keys, tmpk);
         if (vals) std::swap(*vals, tmpv);
     }
 }

@@ -324,8 +324,8 @@ Keys ops_concat(xlb_ctx* c, const std::vector<Keys>& parts) {
     return o;
 }
 
-void ops_sort(xlb_ctx* c, Keys& k) { radix_sort(c, k.buf, nullptr, k.n, 0xFFu, k.bound); }
-void ops_sort_by_high_half(xlb_ctx* c, Keys& k) { radix_sort(c, k.buf, nullptr, k.n, 0xF0u, k.bound); }
+void ops_sort(xlb_ctx* c, Keys& k, bool keep_input) { radix_sort(c, k.buf, nullptr, k.n, 0xFFu, k.bound, keep_input); }
+void ops_sort_by_high_half(xlb_ctx* c, Keys& k, bool keep_input) { radix_sort(c, k.buf, nullptr, k.n, 0xF0u, k.bound, keep_input); }
 
 void ops_dedup_sorted(xlb_ctx* c, Keys& k) {
     if (k.n <= 1) return;

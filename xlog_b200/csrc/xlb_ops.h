@@ -36,8 +36,10 @@ Keys ops_copy(xlb_ctx* c, const Keys& in);
 Keys ops_from_host(xlb_ctx* c, const uint64_t* rows, uint64_t n);  // small host arrays only (n <= 16)
 Keys ops_concat(xlb_ctx* c, const std::vector<Keys>& parts);
 Keys ops_slice(xlb_ctx* c, const Keys& in, uint64_t lo, uint64_t hi);  // copy of rows [lo, hi)
-void ops_sort(xlb_ctx* c, Keys& k);                              // ascending
-void ops_sort_by_high_half(xlb_ctx* c, Keys& k);                 // stable, by bits 32..63 only (groups rows by join key)
+// Sorts replace k.buf by a buffer holding the result.  With keep_input the buffer k.buf named on
+// entry is not written (it may be a stored relation's); without it, it is used as scratch.
+void ops_sort(xlb_ctx* c, Keys& k, bool keep_input = false);                 // ascending
+void ops_sort_by_high_half(xlb_ctx* c, Keys& k, bool keep_input = false);    // stable, by bits 32..63 only (groups rows by join key)
 void ops_dedup_sorted(xlb_ctx* c, Keys& k);                      // sorted -> sorted unique
 Keys ops_diff(xlb_ctx* c, const Keys& a, const Keys& b);         // sorted unique a \ sorted unique b
 Keys ops_dedup_diff(xlb_ctx* c, const Keys& a, const Keys& b);   // distinct rows of sorted a that are not in sorted unique b
