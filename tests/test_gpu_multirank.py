@@ -22,6 +22,13 @@ def _free_port():
     return p
 
 
+def _triangle_plan():
+    from xlog_b200 import _abi as A
+    from xlog_b200.plan import CompiledRule, ExecutionPlan, Join, Project, Scan, Scc
+    body = Project(Join(Join(Scan(0), Scan(0), [1], [0]), Scan(0), [3, 0], [0, 1]), [0])   # tri(X): nodes on a triangle
+    return ExecutionPlan([Scc(0, False, [CompiledRule("tri", body, (A.U32,))])], {"edge": 0, "tri": 1})
+
+
 def _cases():
     from xlog_b200 import programs, workloads
     c0, c1 = workloads.uniform_digraph(400, 1500, 13)
@@ -34,6 +41,7 @@ def _cases():
         ("reach0", programs.reach_from_source(0), {"edge": [r0, r1]}, "r"),
         ("sg", programs.same_generation(), {"edge": [t0, t1]}, "sg"),
         ("andersen", programs.andersen(), {k: list(v) for k, v in workloads.andersen_program(0.0002).items()}, "pt"),
+        ("triangle", _triangle_plan(), {"edge": [c0, c1]}, "tri"),
         ("negation", programs.unreachable_nodes(int(c0[0])), {"edge": [c0, c1], "node": [np.arange(400, dtype=np.uint32)]}, "un"),
     ]
 

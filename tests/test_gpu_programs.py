@@ -146,62 +146,47 @@ def test_rerun_after_new_facts_extends_the_fixpoint(oracle):
 
 
 def test_unsupported_rule_shape_is_refused_not_miscomputed():
-    """A triangle body needs an atom with both columns bound: outside the built scope."""
+    """A three-column head is outside the built scope: refused with a message, never miscomputed."""
     from xlog_b200.lib import XlbError
     from xlog_b200 import _abi as A
     from xlog_b200.plan import CompiledRule, ExecutionPlan, Join, Project, Scan, Scc
-    body = Project(Join(Join(Scan(0), Scan(0), [1], [0]), Scan(0), [3, 0], [0, 1]), [0, 1])
-    plan = ExecutionPlan([Scc(0, False, [CompiledRule("tri", body)])], {"edge": 0, "tri": 1})
+    body = Project(Join(Scan(0), Scan(0), [1], [0]), [0, 1, 3])
+    plan = ExecutionPlan([Scc(0, False, [CompiledRule("path3", body, (A.U32, A.U32, A.U32))])], {"edge": 0, "path3": 1})
     c0, c1 = workloads.uniform_digraph(50, 200, 2)
     p = fresh()
     with pytest.raises(XlbError) as e:
-        run_program(p, plan, {"edge": [c0, c1]}, ["tri"])
-    assert e.value.status == A.ERR_UNSUPPORTED
+        run_program(p, plan, {"edge": [c0, c1]}, ["path3"])
+    assert e.value.status == A.ERR_UNSUPPORTED and "path3" in e.value.message
     p.close()
 
 
-def _dag_closure_size(c0, c1, n):
-    """|TC| of a DAG whose edges go from lower to higher ids: descendant bitsets, highest id first."""
-    words = (n + 63) // 64
-    desc = np.zeros((n, words), dtype=np.uint64)
-    order = np.argsort(c0, kind="stable")
-    s, d = c0[order], c1[order]
-    starts = np.searchsorted(s, np.arange(n + 1))
-    for v in range(n - 1, -1, -1):
-        kids = d[starts[v]:starts[v + 1]]
-        if len(kids):
-            row = np.bitwise_or.reduce(desc[kids], axis=0)
-            np.bitwise_or.at(row, kids >> 6, np.uint64(1) << (kids & 63).astype(np.uint64))
-            desc[v] = row
-    return int(np.bitwise_count(desc).sum(dtype=np.uint64))
-
-
-def test_rmat_dag_closure_scale_15_properties():
-    """A closure of tens of millions of tuples: too large for the oracle in test time, so checked by
-    what does not depend on size: the count against an independent bitset closure, sorted-unique
-    order, every input edge present, and closure under one more join step on a sample of tuples."""
-    n = 1 << 15
-    c0, c1 = workloads.rmat_dag(15, 8)
+def test_triangle_body_with_a_closing_atom(oracle):
+    """tri(X) :- edge(X,Y), edge(Y,Z), edge(Z,X): the last atom has both columns bound and is
+    evaluated as a membership test on the row index; also as a recursive rule's filter atom."""
+    from xlog_b200.plan import CompiledRule, ExecutionPlan, Join, Project, Scan, Scc
+    from xlog_b200 import _abi as A
+    c0, c1 = workloads.uniform_digraph(300, 4000, 6)
+    # columns: X Y | Y Z | Z X  -> join keys (Z, X) against (col0, col1) of the third atom
+    body = Project(Join(Join(Scan(0), Scan(0), [1], [0]), Scan(0), [3, 0], [0, 1]), [0])
+    plan = ExecutionPlan([Scc(0, False, [CompiledRule("tri", body, (A.U32,))])], {"edge": 0, "tri": 1})
+    want, _ = oracle.run_program(plan, {"edge": [c0, c1]}, ["tri"])
+    assert len(want["tri"][0]) > 50
+    for flags in (0, A.FLAG_NO_DENSE):
+        p = KernelProvider(device=0, flags=flags)
+        got, _ = run_program(p, plan, {"edge": [c0, c1]}, ["tri"])
+        assert all(np.array_equal(g, w) for g, w in zip(got["tri"], want["tri"]))
+        p.close()
+    # recursive use: reach restricted to pairs that are also edges of a second relation
+    base = CompiledRule("r", Scan(0), (A.U32, A.U32))
+    rec = CompiledRule("r", Project(Join(Join(Scan(2), Scan(0), [1], [0]), Scan(1), [0, 3], [0, 1]), [0, 3]), (A.U32, A.U32))
+    plan2 = ExecutionPlan([Scc(0, True, [base, rec])], {"edge": 0, "allow": 1, "r": 2})
+    a0, a1 = workloads.uniform_digraph(300, 30000, 9)
+    inputs = {"edge": [c0[:1500], c1[:1500]], "allow": [a0, a1]}
+    want2, _ = oracle.run_program(plan2, inputs, ["r"])
     p = fresh()
-    got, stats = run_program(p, programs.transitive_closure(), {"edge": [c0, c1]}, ["reach"])
-    r0, r1 = got["reach"]
-    assert len(r0) == _dag_closure_size(c0, c1, n) == stats["derived_tuples"]
-    k = (r0.astype(np.uint64) << np.uint64(32)) | r1
-    assert np.all(k[1:] > k[:-1])
-    assert np.all(np.isin((c0.astype(np.uint64) << np.uint64(32)) | c1, k))
-    # closure under one more step, on a sample: (x, y) in reach and edge(y, z) imply (x, z) in reach
-    order = np.argsort(c0, kind="stable")
-    s0, s1 = c0[order], c1[order]
-    starts = np.searchsorted(s0, np.arange(n + 1))
-    pick = (workloads.splitmix64(77, 0, 200_000) % np.uint64(len(r0))).astype(np.int64)
-    x, y = r0[pick], r1[pick]
-    deg = (starts[y + 1] - starts[y]).astype(np.int64)
-    xs = np.repeat(x, deg)
-    offs = np.arange(deg.sum()) - np.repeat(np.cumsum(deg) - deg, deg)
-    zs = s1[np.repeat(starts[y], deg) + offs]
-    want = (xs.astype(np.uint64) << np.uint64(32)) | zs
-    pos = np.searchsorted(k, want)
-    assert np.all(k[np.minimum(pos, len(k) - 1)] == want)
+    got2, _ = run_program(p, plan2, inputs, ["r"])
+    assert all(np.array_equal(g, w) for g, w in zip(got2["r"], want2["r"]))
+    assert len(got2["r"][0]) > 1500
     p.close()
 
 

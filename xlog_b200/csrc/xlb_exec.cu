@@ -244,8 +244,18 @@ struct RunState {
 };
 
 // Rows of relation `name` arranged for a join on column kc: (key << 32) | other, sorted.
+// kc 0 / 1: join index on that column.  kc == ROW_INDEX: the whole row is the key (membership of a
+// pair whose two columns are both bound, as in the closing atom of a triangle).
+constexpr int ROW_INDEX = 2;
+
 static Keys index_rows(xlb_ctx* c, const xlb_rel* r, int kc) {
     Keys k = ops_rel_packed(c, r);
+    if (kc == ROW_INDEX) {
+        if (r->canonical) return k;
+        Keys s = k;
+        ops_sort(c, s, /*keep_input=*/true);
+        return s;
+    }
     if (r->schema.arity == 1) {
         Keys s = ops_remap(c, k, SRC_LO, SRC_ZERO);
         if (!r->canonical) ops_sort(c, s);
@@ -281,7 +291,7 @@ static const Index& get_index(xlb_ctx* c, const std::string& name, int kc, RunSt
     }
     if (!ci.table_ok) {
         uint64_t b = ci.ix.bound;
-        ci.ix = ops_index_build(c, ci.ix.S, ci.ix.n, 32, Buf());
+        ci.ix = ops_index_build(c, ci.ix.S, ci.ix.n, kc == ROW_INDEX ? 0 : 32, Buf());
         ci.ix.bound = b;
         ci.table_ok = true;
     }
@@ -300,7 +310,7 @@ static void indexes_on_merge(xlb_ctx* c, const std::string& name, const xlb_rel*
         PhaseTimer t(c, &rs.st.ms_join);
         if (c->world > 1) {
             // the index copy is partitioned by its own key column: route the new rows there
-            Keys d = new_full->schema.arity == 1 ? ops_remap(c, delta, SRC_LO, SRC_ZERO) : (kc == 0 ? delta : ops_remap(c, delta, SRC_LO, SRC_HI));
+            Keys d = new_full->schema.arity == 1 ? ops_remap(c, delta, SRC_LO, SRC_ZERO) : (kc != 1 ? delta : ops_remap(c, delta, SRC_LO, SRC_HI));
             if (d.buf == delta.buf) d = ops_copy(c, d);
             d = comm_repartition(c, d, SRC_HI, true, rs.st);
             Keys old;
@@ -313,7 +323,7 @@ static void indexes_on_merge(xlb_ctx* c, const std::string& name, const xlb_rel*
             ci.ix.S = m.buf;
             ci.ix.n = m.n;
             ci.ix.bound = m.bound;
-        } else if (new_full->schema.arity == 2 && kc == 0) {
+        } else if (new_full->schema.arity == 2 && (kc == 0 || kc == ROW_INDEX)) {
             ci.ix = Index();
             ci.ix.S = new_full->packed;  // alias: canonical order is key order
             ci.ix.n = new_full->rows;
@@ -418,6 +428,31 @@ static Keys run_pipeline(xlb_ctx* c, FlatRule fr /*by value: filter flags*/, siz
     }
     size_t remaining = fr.atoms.size() - 1;
     while (remaining) {
+        // atoms with both columns bound are membership tests on the bag: apply them first
+        bool filtered = false;
+        for (size_t i = 0; i < fr.atoms.size(); ++i) {
+            const Atom& a = fr.atoms[i];
+            if (done[i] || a.arity != 2 || a.var[0] == a.var[1]) continue;
+            bool b0 = a.var[0] == bag.hi || a.var[0] == bag.lo, b1 = a.var[1] == bag.hi || a.var[1] == bag.lo;
+            if (!b0 || !b1) continue;
+            const Index& ix = get_index(c, a.rel, ROW_INDEX, rs);
+            Keys probe = bag.k;
+            if (c->world > 1 && bag.part != a.var[0]) {  // the row index is partitioned by its first column
+                PhaseTimer t(c, &rs.st.ms_exchange);
+                probe = comm_repartition(c, probe, src_of(bag, a.var[0]), false, rs.st);
+                bag.part = a.var[0];
+            }
+            PhaseTimer t(c, &rs.st.ms_join);
+            Keys rowkeys = (a.var[0] == bag.hi) ? probe : ops_remap(c, probe, SRC_LO, SRC_HI);  // the atom's (col0, col1) order
+            bag.k = ops_semi_filter(c, probe, SRC_HI, ix, false, rowkeys.ptr());
+            done[i] = true;
+            remaining--;
+            filtered = true;
+        }
+        if (filtered) {
+            apply_ready_filters(c, fr, bag, rs);
+            continue;
+        }
         // next atom: exactly one of its columns is bound by the bag, and what must stay live fits two columns
         int pick = -1, kc = -1;
         std::set<int> keep;

@@ -491,13 +491,13 @@ Buf ops_probe_match(xlb_ctx* c, const Keys& bag, int keysel, const uint64_t* pke
     return match;
 }
 
-Keys ops_semi_filter(xlb_ctx* c, const Keys& bag, int keysel, const Index& ix, bool anti) {
+Keys ops_semi_filter(xlb_ctx* c, const Keys& bag, int keysel, const Index& ix, bool anti, const uint64_t* pkeys) {
     Keys o;
     o.bound = bag.bound;
     o.buf = make_buf(c, bag.n * 8);
     if (bag.n == 0) return o;
     if (ix.n == 0) return anti ? ops_copy(c, bag) : o;
-    Buf match = ops_probe_match(c, bag, keysel, nullptr, ix);
+    Buf match = ops_probe_match(c, bag, keysel, pkeys, ix);
     o.n = select(c, PredFlag{match->as<uint64_t>(), !anti}, EmitKey{bag.ptr(), o.buf->as<uint64_t>()}, bag.n);
     return o;
 }

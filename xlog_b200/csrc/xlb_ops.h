@@ -71,7 +71,8 @@ Index ops_index_build(xlb_ctx* c, Buf S, uint64_t n, int key_shift, Buf pay);
 // out row = (pick(hi_src) << 32) | pick(lo_src) with SRC_OTHER = the build row's payload.
 Keys ops_join_expand(xlb_ctx* c, const Keys& bag, int keysel, const uint64_t* pkeys, const Index& ix, int hi_src, int lo_src);
 // rows of `bag` whose key has (semi) or lacks (anti) a match in the index, in bag order
-Keys ops_semi_filter(xlb_ctx* c, const Keys& bag, int keysel, const Index& ix, bool anti);
+// (pkeys, when given, holds the key word of every bag row instead of a half named by keysel)
+Keys ops_semi_filter(xlb_ctx* c, const Keys& bag, int keysel, const Index& ix, bool anti, const uint64_t* pkeys = nullptr);
 // match[i] != 0 flags for semi / anti joins (device array of bag.n words)
 Buf ops_probe_match(xlb_ctx* c, const Keys& bag, int keysel, const uint64_t* pkeys, const Index& ix);
 
