@@ -1,5 +1,7 @@
 // Shared host-side plumbing: status handling, the context, the stream-ordered device arena.
 #pragma once
+#include <cuda.h>
+#include <cudaTypedefs.h>
 #include <cuda_runtime.h>
 
 #include <chrono>
@@ -49,22 +51,71 @@ struct DevStatus {
     unsigned long long detail;
 };
 
+// Driver entry points of the virtual-memory API, looked up through the runtime so that the
+// library does not link against the driver library (it must load on a machine without one).
+struct VmmApi {
+    PFN_cuMemAddressReserve reserve = nullptr;
+    PFN_cuMemAddressFree addr_free = nullptr;
+    PFN_cuMemCreate create = nullptr;
+    PFN_cuMemRelease release = nullptr;
+    PFN_cuMemMap map = nullptr;
+    PFN_cuMemUnmap unmap = nullptr;
+    PFN_cuMemSetAccess set_access = nullptr;
+    PFN_cuMemGetAllocationGranularity granularity = nullptr;
+    bool ok = false;
+    static const VmmApi& get() {
+        static const VmmApi api = load();
+        return api;
+    }
+    static VmmApi load() {
+        VmmApi a;
+        auto sym = [](const char* name, void** fn) {
+            cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+            return cudaGetDriverEntryPoint(name, fn, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess && *fn != nullptr;
+        };
+        a.ok = sym("cuMemAddressReserve", (void**)&a.reserve) && sym("cuMemAddressFree", (void**)&a.addr_free) && sym("cuMemCreate", (void**)&a.create) &&
+               sym("cuMemRelease", (void**)&a.release) && sym("cuMemMap", (void**)&a.map) && sym("cuMemUnmap", (void**)&a.unmap) &&
+               sym("cuMemSetAccess", (void**)&a.set_access) && sym("cuMemGetAllocationGranularity", (void**)&a.granularity);
+        if (!a.ok) cudaGetLastError();
+        return a;
+    }
+};
+
 // Device memory arena.  Every buffer of a context is used on the context's one stream, so a block
 // that the host has freed can be handed out again at once: the work that used it was enqueued
-// earlier on the same stream.  That makes a plain host-side free list over a few large slabs
-// enough, and keeps the CUDA allocator off the hot path: a fixpoint allocates and frees a few
-// hundred temporaries, and the driver's stream-ordered pool was measured to spend milliseconds
-// remapping its reserve in one step out of three for the first twenty steps of a repeated workload.
+// earlier on the same stream.  That makes a plain host-side free list enough, and keeps the CUDA
+// allocator off the hot path: a fixpoint allocates and frees a few hundred temporaries, and the
+// driver's stream-ordered pool was measured to spend milliseconds remapping its reserve in one
+// step out of three for the first twenty steps of a repeated workload.
+//
+// Backing store: one reserved virtual address range as large as the device's memory, with physical
+// memory mapped at its front chunk by chunk (the driver's virtual-memory API).  The arena is then
+// one contiguous block that grows at its end, free neighbours always coalesce, and a request that
+// does not fit extends the last free block by the missing part only.  With separate cudaMalloc
+// slabs instead, a repeated workload with 128 MB buffers was seen to need a new 1 GB slab (a 4 to
+// 11 ms stall) in its eighth repetition with 380 MB free in six pieces.  Slabs remain as the
+// fallback where the virtual-memory API is unavailable (or XLB_ARENA_SLABS is set).
 struct Arena {
     struct Slab {
         char* base;
         uint64_t size;
     };
-    std::vector<Slab> slabs;
+    struct Chunk {
+        CUmemGenericAllocationHandle handle;
+        uint64_t size;
+    };
+    std::vector<Slab> slabs;    // fallback backing
+    std::vector<Chunk> chunks;  // virtual-memory backing: mapped back to back from va_base
+    char* va_base = nullptr;
+    uint64_t va_size = 0, mapped = 0, gran = 0;
+    int device = 0;
+    bool vmm = false, vmm_tried = false;
     std::map<char*, uint64_t> free_by_addr;
     std::multimap<uint64_t, char*> free_by_size;
     uint64_t reserved = 0;
+    bool trace = getenv("XLB_ARENA_TRACE") != nullptr;  // report every time the arena has to grow
     static constexpr uint64_t ALIGN = 512, MIN_SLAB = 256ull << 20, MAX_GROW = 8ull << 30;
+    static constexpr uint64_t VMM_MIN_STEP = 64ull << 20, VMM_MAX_STEP = 2ull << 30;
 
     static uint64_t round_up(uint64_t n) { return (n + ALIGN - 1) / ALIGN * ALIGN; }
     void insert_free(char* p, uint64_t n) {
@@ -80,6 +131,101 @@ struct Arena {
                 break;
             }
     }
+    CUmemAllocationProp vmm_prop() const {
+        CUmemAllocationProp prop;
+        memset(&prop, 0, sizeof prop);
+        prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+        prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+        prop.location.id = device;
+        return prop;
+    }
+    // Reserve the address range (once).  False: use slabs.
+    bool vmm_start() {
+        if (vmm_tried) return vmm;
+        vmm_tried = true;
+        if (getenv("XLB_ARENA_SLABS")) return false;
+        const VmmApi& api = VmmApi::get();
+        int supported = 0;
+        if (!api.ok || cudaDeviceGetAttribute(&supported, cudaDevAttrMemoryPoolsSupported, device) != cudaSuccess || !supported) {
+            cudaGetLastError();
+            return false;
+        }
+        CUmemAllocationProp prop = vmm_prop();
+        size_t g = 0;
+        if (api.granularity(&g, &prop, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED) != CUDA_SUCCESS || g == 0) return false;
+        size_t free_b = 0, total_b = 0;
+        if (cudaMemGetInfo(&free_b, &total_b) != cudaSuccess) {
+            cudaGetLastError();
+            return false;
+        }
+        gran = g;
+        va_size = (total_b + gran - 1) / gran * gran;
+        CUdeviceptr base = 0;
+        if (api.reserve(&base, va_size, 0, 0, 0) != CUDA_SUCCESS) return false;
+        va_base = (char*)base;
+        vmm = true;
+        return true;
+    }
+    // Map `step` more bytes at the end of the mapped part and hand them to the free list.
+    bool vmm_map(uint64_t step) {
+        const VmmApi& api = VmmApi::get();
+        if (mapped + step > va_size) return false;
+        CUmemAllocationProp prop = vmm_prop();
+        CUmemGenericAllocationHandle h;
+        if (api.create(&h, step, &prop, 0) != CUDA_SUCCESS) return false;
+        CUdeviceptr at = (CUdeviceptr)(va_base + mapped);
+        if (api.map(at, step, 0, h, 0) != CUDA_SUCCESS) {
+            api.release(h);
+            return false;
+        }
+        CUmemAccessDesc acc;
+        memset(&acc, 0, sizeof acc);
+        acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+        acc.location.id = device;
+        acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+        if (api.set_access(at, step, &acc, 1) != CUDA_SUCCESS) {
+            api.unmap(at, step);
+            api.release(h);
+            return false;
+        }
+        chunks.push_back({h, step});
+        char* p = va_base + mapped;
+        mapped += step;
+        reserved += step;
+        release(p, step);  // coalesces with a free block that ended at the old end
+        return true;
+    }
+    // size of the free block that ends where the mapped part ends (0: none)
+    uint64_t vmm_tail_free() const {
+        if (free_by_addr.empty()) return 0;
+        auto last = std::prev(free_by_addr.end());
+        return last->first + last->second == va_base + mapped ? last->second : 0;
+    }
+    bool vmm_grow(uint64_t n) {
+        const uint64_t tail = vmm_tail_free();
+        const uint64_t need = ((n > tail ? n - tail : 0) + gran - 1) / gran * gran;
+        if (need == 0) return true;
+        // grow by half of what is mapped, within [64 MB, 2 GB], or by the request if that is more
+        uint64_t step = std::max<uint64_t>(need, std::min<uint64_t>(std::max<uint64_t>(mapped / 2, VMM_MIN_STEP), VMM_MAX_STEP));
+        step = (step + gran - 1) / gran * gran;
+        return vmm_map(step) || (step > need && vmm_map(need));
+    }
+    // Unmap whole chunks at the end that are entirely free (after the stream has drained).
+    void vmm_trim() {
+        const VmmApi& api = VmmApi::get();
+        while (!chunks.empty()) {
+            const uint64_t tail = vmm_tail_free(), sz = chunks.back().size;
+            if (tail < sz) break;
+            char* tail_at = va_base + mapped - tail;
+            erase_free(tail_at, tail);
+            if (tail > sz) insert_free(tail_at, tail - sz);
+            api.unmap((CUdeviceptr)(va_base + mapped - sz), sz);
+            api.release(chunks.back().handle);
+            chunks.pop_back();
+            mapped -= sz;
+            reserved -= sz;
+        }
+    }
     bool add_slab(uint64_t size) {
         void* p = nullptr;
         if (cudaMalloc(&p, size) != cudaSuccess) {
@@ -91,9 +237,13 @@ struct Arena {
         insert_free((char*)p, size);
         return true;
     }
-    // Give back every slab that is entirely free (after the stream has drained).
+    // Give back every part of the backing store that is entirely free (after the stream has drained).
     void trim(cudaStream_t stream) {
         cudaStreamSynchronize(stream);
+        if (vmm) {
+            vmm_trim();
+            return;
+        }
         for (size_t i = 0; i < slabs.size();) {
             auto it = free_by_addr.find(slabs[i].base);
             if (it != free_by_addr.end() && it->second == slabs[i].size) {
@@ -114,6 +264,17 @@ struct Arena {
                 erase_free(p, have);
                 if (have > n) insert_free(p + n, have - n);
                 return p;
+            }
+            if (trace) {
+                uint64_t free_total = 0;
+                for (auto& f : free_by_size) free_total += f.first;
+                fprintf(stderr, "[xlb arena] attempt %d: no block of %llu bytes; reserved %llu in %zu pieces, free %llu in %zu blocks, largest %llu\n", attempt,
+                        (unsigned long long)n, (unsigned long long)reserved, vmm ? chunks.size() : slabs.size(), (unsigned long long)free_total, free_by_size.size(),
+                        (unsigned long long)(free_by_size.empty() ? 0 : free_by_size.rbegin()->first));
+            }
+            if (vmm_start()) {
+                if (attempt == 0 && vmm_grow(n)) continue;
+                return nullptr;  // the device (or the address range) is full: trimming this arena cannot help it
             }
             if (attempt == 0) {
                 uint64_t grow = std::max<uint64_t>(MIN_SLAB, std::min<uint64_t>(reserved, MAX_GROW));
@@ -156,6 +317,20 @@ struct Arena {
     void destroy() {
         for (auto& s : slabs) cudaFree(s.base);
         slabs.clear();
+        if (vmm) {
+            const VmmApi& api = VmmApi::get();
+            uint64_t at = mapped;
+            for (size_t i = chunks.size(); i-- > 0;) {
+                at -= chunks[i].size;
+                api.unmap((CUdeviceptr)(va_base + at), chunks[i].size);
+                api.release(chunks[i].handle);
+            }
+            chunks.clear();
+            api.addr_free((CUdeviceptr)va_base, va_size);
+            va_base = nullptr;
+            va_size = mapped = 0;
+            vmm = vmm_tried = false;
+        }
         free_by_addr.clear();
         free_by_size.clear();
         reserved = 0;
@@ -208,6 +383,13 @@ inline void prof_begin(xlb_ctx* c, const char* name, uint64_t bytes) {
     cudaEventCreate(&c->prof_e0);
     cudaEventRecord(c->prof_e0, c->stream);
     c->prof_open = &e;
+}
+
+// Bytes of a launch that the host learns only later (a count read back after the launch).
+inline void prof_add_bytes(xlb_ctx* c, const char* name, uint64_t bytes) {
+    if (c->prof_filter.empty()) return;
+    auto it = c->prof.find(name);
+    if (it != c->prof.end()) it->second.bytes += bytes;
 }
 
 // A device allocation charged to the context's budget (GpuMemoryManager::alloc with a

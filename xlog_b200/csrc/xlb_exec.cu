@@ -526,10 +526,10 @@ static Keys run_pipeline(xlb_ctx* c, FlatRule fr /*by value: filter flags*/, siz
             if (sink && last && !pending && c->world == 1 && !(c->flags & XLB_FLAG_NO_DENSE) && ops_dense_bits(shape, *sink->full, &hb, &lb)) {
                 sink->set = ops_dense_begin(c, hb, lb);
                 sink->used = true;
-                Keys counted;
-                counted.n = ops_join_expand_mark(c, probe, keysel, ix, hs, ls, sink->set);
-                counted.bound = shape.bound;
-                return counted;
+                ops_join_expand_mark(c, probe, keysel, ix, hs, ls, sink->set);
+                Keys marked;  // no rows and no count: both are in the sink
+                marked.bound = shape.bound;
+                return marked;
             }
             nb.k = ops_join_expand(c, probe, keysel, nullptr, ix, hs, ls);
             nb.part = keyvar;
@@ -616,6 +616,15 @@ static void eval_variant(xlb_ctx* c, const FlatRule& fr_in, size_t start, const 
             continue;
         }
         at = hi;
+        if (sink.used) {
+            // the last join marked its tuples in the bitmap already (single rank only); how many
+            // there were comes back with the count of the new ones
+            PhaseTimer t(c, &rs.st.ms_setops);
+            Keys fresh = ops_dense_finish(c, sink.set, full);
+            rs.st.candidate_tuples += sink.set.marked;
+            novel = novel.n ? ops_union(c, novel, fresh) : fresh;
+            continue;
+        }
         rs.st.candidate_tuples += cand.n;
         if (c->world > 1) {
             PhaseTimer t(c, &rs.st.ms_exchange);
@@ -624,11 +633,7 @@ static void eval_variant(xlb_ctx* c, const FlatRule& fr_in, size_t start, const 
         if (cand.n == 0) continue;
         Keys fresh;
         int hb = 0, lb = 0;
-        if (sink.used) {
-            // the last join marked its tuples in the bitmap already
-            PhaseTimer t(c, &rs.st.ms_setops);
-            fresh = ops_dense_finish(c, sink.set, full);
-        } else if (!(c->flags & XLB_FLAG_NO_DENSE) && ops_dense_bits(cand, full, &hb, &lb)) {
+        if (!(c->flags & XLB_FLAG_NO_DENSE) && ops_dense_bits(cand, full, &hb, &lb)) {
             // small dense domain: sort + dedup + difference on a bitmap
             PhaseTimer t(c, &rs.st.ms_setops);
             fresh = ops_dense_novel(c, cand, full, hb, lb);

@@ -1035,11 +1035,16 @@ template <bool MARK>
 static __global__ void __launch_bounds__(BLOCK) expand_k(const uint64_t* __restrict__ mbag, const uint64_t* __restrict__ mmatch, const uint64_t* __restrict__ off,
                                                    uint64_t nrows, uint64_t total, const uint64_t* __restrict__ S,
                                                    const uint32_t* __restrict__ pay, int hi_src, int lo_src, uint64_t* __restrict__ out,
-                                                   unsigned int* __restrict__ bitmap, uint64_t words, int lo_bits, DevStatus* st) {
+                                                   unsigned int* __restrict__ bitmap, uint64_t words, int lo_bits, DevStatus* st,
+                                                   const uint64_t* __restrict__ total_dev) {
     __shared__ uint64_t soff[EX_TILE + 2];
-    uint64_t o0 = (uint64_t)blockIdx.x * EX_TILE;
-    uint64_t o1 = o0 + EX_TILE < total ? o0 + EX_TILE : total;
     __shared__ uint64_t row_s[2];
+    // With total_dev the output count is still on the device (the host launched a fixed grid
+    // without reading it back): tiles are then walked grid-strided.
+    if (total_dev) total = *total_dev;
+  for (uint64_t tile = blockIdx.x; tile * EX_TILE < total; tile += gridDim.x) {
+    uint64_t o0 = tile * EX_TILE;
+    uint64_t o1 = o0 + EX_TILE < total ? o0 + EX_TILE : total;
     if (threadIdx.x < 64) {  // warp 0: the row that owns output o0; warp 1: the row that owns the next tile's first output
         uint64_t o = threadIdx.x < 32 ? o0 : o0 + EX_TILE;
         uint64_t ub = o < total ? warp_partition_point(nrows, [&](uint64_t i) { return off[i] <= o; }) : nrows + 1;
@@ -1091,6 +1096,8 @@ static __global__ void __launch_bounds__(BLOCK) expand_k(const uint64_t* __restr
             }
         }
     }
+    __syncthreads();  // the next tile refills soff / row_s
+  }
 }
 
 }  // namespace xk

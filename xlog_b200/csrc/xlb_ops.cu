@@ -364,8 +364,10 @@ DenseSet ops_dense_begin(xlb_ctx* c, int hi_bits, int lo_bits) {
     d.hi_bits = hi_bits;
     d.lo_bits = lo_bits;
     d.words = ((1ull << (hi_bits + lo_bits)) + 31) / 32;
-    d.bitmap = make_buf(c, d.words * 4);
-    CUDA_OK(cudaMemsetAsync(d.bitmap->p, 0, d.words * 4, c->stream));
+    const uint64_t bitmap_bytes = (d.words * 4 + 7) & ~7ull;
+    d.bitmap = make_buf(c, bitmap_bytes + 16);
+    d.counts = (uint64_t*)((char*)d.bitmap->p + bitmap_bytes);
+    CUDA_OK(cudaMemsetAsync(d.bitmap->p, 0, bitmap_bytes + 16, c->stream));
     return d;
 }
 
@@ -381,13 +383,15 @@ Keys ops_dense_finish(xlb_ctx* c, DenseSet& d, const Keys& full) {
     uint64_t groups = (words + 31) / 32;
     Buf gcnt = make_buf(c, groups * 4);
     Buf offs = make_buf(c, groups * 8);
-    Buf total = make_buf(c, 8);
     prof_begin(c, "dense_count", words * 4ull);
     dense_count_k<<<(unsigned)((groups * 32 + BLOCK - 1) / BLOCK), BLOCK, 0, c->stream>>>(d.bitmap->as<unsigned int>(), words, gcnt->as<uint32_t>(), groups);
     check_launch(c, "dense_count");
-    exclusive_scan<LoadU32, uint64_t>(c, LoadU32{gcnt->as<uint32_t>()}, groups, offs->as<uint64_t>(), total->as<uint64_t>());
-    unsigned long long tot;
-    read_words(c, total->p, 1, &tot);
+    exclusive_scan<LoadU32, uint64_t>(c, LoadU32{gcnt->as<uint32_t>()}, groups, offs->as<uint64_t>(), d.counts);
+    unsigned long long both[2];
+    read_words(c, d.counts, 2, both);
+    const uint64_t tot = both[0];
+    d.marked = both[1];
+    prof_add_bytes(c, "expand_mark", d.marked * 4ull);
     o.n = tot;
     o.buf = make_buf(c, tot * 8);
     if (tot) {
@@ -516,27 +520,32 @@ static Keys join_expand(xlb_ctx* c, const Keys& bag, int keysel, const uint64_t*
     if (bag.n == 0 || ix.n == 0) { out.buf = make_buf(c, 0); return out; }
     Buf match = ops_probe_match(c, bag, keysel, pkeys, ix);
     Buf off = make_buf(c, bag.n * 8);
+    const uint32_t* pay = ix.pay ? ix.pay->as<uint32_t>() : nullptr;
+    if (dense) {
+        // Nothing is allocated by the count, so it stays on the device: a fixed grid walks the
+        // tiles and the host reads the count later, together with the bitmap's.
+        // (one marking join per DenseSet: the scan leaves its total in the set's count word)
+        exclusive_scan<LoadLow32, uint64_t>(c, LoadLow32{match->as<uint64_t>()}, bag.n, off->as<uint64_t>(), dense->counts + 1);
+        const unsigned grid = (unsigned)c->sm_count * 8;
+        prof_begin(c, "expand_mark", bag.n * 24ull);
+        expand_k<true><<<grid, BLOCK, 0, c->stream>>>(bag.ptr(), match->as<uint64_t>(), off->as<uint64_t>(), bag.n, 0, ix.S->as<uint64_t>(), pay, hi_src, lo_src,
+                                                       nullptr, dense->bitmap->as<unsigned int>(), dense->words, dense->lo_bits, c->d_status, dense->counts + 1);
+        check_launch(c, "expand_mark");
+        dense->bound |= out.bound;
+        return out;
+    }
     Buf total = make_buf(c, 8);
     exclusive_scan<LoadLow32, uint64_t>(c, LoadLow32{match->as<uint64_t>()}, bag.n, off->as<uint64_t>(), total->as<uint64_t>());
     unsigned long long tot;
     read_words(c, total->p, 1, &tot);
     out.n = tot;
-    if (!dense) out.buf = make_buf(c, tot * 8);
+    out.buf = make_buf(c, tot * 8);
     if (tot == 0) return out;
     uint64_t ntiles = (tot + EX_TILE - 1) / EX_TILE;
-    const uint32_t* pay = ix.pay ? ix.pay->as<uint32_t>() : nullptr;
-    if (!dense) {
-        prof_begin(c, "expand", tot * 12ull + bag.n * 24ull);
-        expand_k<false><<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(bag.ptr(), match->as<uint64_t>(), off->as<uint64_t>(), bag.n, tot, ix.S->as<uint64_t>(), pay, hi_src, lo_src,
-                                                                    out.buf->as<uint64_t>(), nullptr, 0, 0, c->d_status);
-        check_launch(c, "expand");
-    } else {
-        prof_begin(c, "expand_mark", tot * 4ull + bag.n * 24ull);
-        expand_k<true><<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(bag.ptr(), match->as<uint64_t>(), off->as<uint64_t>(), bag.n, tot, ix.S->as<uint64_t>(), pay, hi_src, lo_src,
-                                                                   nullptr, dense->bitmap->as<unsigned int>(), dense->words, dense->lo_bits, c->d_status);
-        check_launch(c, "expand_mark");
-        dense->bound |= out.bound;
-    }
+    prof_begin(c, "expand", tot * 12ull + bag.n * 24ull);
+    expand_k<false><<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(bag.ptr(), match->as<uint64_t>(), off->as<uint64_t>(), bag.n, tot, ix.S->as<uint64_t>(), pay, hi_src, lo_src,
+                                                                out.buf->as<uint64_t>(), nullptr, 0, 0, c->d_status, nullptr);
+    check_launch(c, "expand");
     return out;
 }
 
@@ -544,8 +553,8 @@ Keys ops_join_expand(xlb_ctx* c, const Keys& bag, int keysel, const uint64_t* pk
     return join_expand(c, bag, keysel, pkeys, ix, hi_src, lo_src, nullptr);
 }
 
-uint64_t ops_join_expand_mark(xlb_ctx* c, const Keys& bag, int keysel, const Index& ix, int hi_src, int lo_src, DenseSet& d) {
-    return join_expand(c, bag, keysel, nullptr, ix, hi_src, lo_src, &d).n;
+void ops_join_expand_mark(xlb_ctx* c, const Keys& bag, int keysel, const Index& ix, int hi_src, int lo_src, DenseSet& d) {
+    join_expand(c, bag, keysel, nullptr, ix, hi_src, lo_src, &d);
 }
 
 Keys ops_partition_by_owner_dev(xlb_ctx* c, const Keys& in, int keysel, uint32_t world, unsigned long long* counts) {
@@ -615,6 +624,7 @@ extern "C" xlb_status xlb_ctx_create(const xlb_config* cfg, xlb_ctx** out) {
         c->device = dev;
         CUDA_OK(cudaSetDevice(dev));
         CUDA_OK(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+        c->arena.device = dev;
         size_t fr = 0, tot = 0;
         CUDA_OK(cudaMemGetInfo(&fr, &tot));
         c->budget = cfg && cfg->memory_budget_bytes ? cfg->memory_budget_bytes : (uint64_t)(fr * 0.9);

@@ -53,13 +53,18 @@ struct DenseSet {
     uint64_t words = 0;
     int hi_bits = 0, lo_bits = 0;
     uint64_t bound = 0;  // OR bound of what was marked
+    // two words behind the bitmap: [0] rows ops_dense_finish emits, [1] sum of the tuple counts of
+    // the marking joins, which stay on the device until ops_dense_finish reads both at once
+    uint64_t* counts = nullptr;
+    uint64_t marked = 0;  // host copy of counts[1], valid after ops_dense_finish
 };
 DenseSet ops_dense_begin(xlb_ctx* c, int hi_bits, int lo_bits);
 Keys ops_dense_finish(xlb_ctx* c, DenseSet& d, const Keys& full);  // clear `full`, emit the rest in order
 // OR bound of the rows ops_join_expand would produce
 uint64_t ops_expand_bound(const Keys& bag, const Index& ix, int hi_src, int lo_src);
-// ops_join_expand that marks instead of materialising; returns the number of (bag) tuples marked
-uint64_t ops_join_expand_mark(xlb_ctx* c, const Keys& bag, int keysel, const Index& ix, int hi_src, int lo_src, DenseSet& d);
+// ops_join_expand that marks instead of materialising.  No count comes back to the host here:
+// the number of tuples marked is d.marked after ops_dense_finish.
+void ops_join_expand_mark(xlb_ctx* c, const Keys& bag, int keysel, const Index& ix, int hi_src, int lo_src, DenseSet& d);
 Keys ops_merge_disjoint(xlb_ctx* c, const Keys& a, const Keys& b);
 Keys ops_union(xlb_ctx* c, const Keys& a, const Keys& b);        // sorted unique a U b
 Keys ops_remap(xlb_ctx* c, const Keys& in, int hi_src, int lo_src);
