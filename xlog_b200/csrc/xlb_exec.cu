@@ -241,6 +241,8 @@ struct Flattener {
 // ------------------------------------------------------------------------------ indexes
 struct RunState {
     xlb_run_stats st{};
+    std::map<std::string, DenseState> dense;  // per head relation: its tuples as a bitmap, while they fit one
+    std::map<std::pair<std::string, int>, int> scans;  // scan joins run so far per (relation, key column)
 };
 
 // Rows of relation `name` arranged for a join on column kc: (key << 32) | other, sorted.
@@ -273,13 +275,33 @@ static Keys index_rows(xlb_ctx* c, const xlb_rel* r, int kc) {
     return s;
 }
 
+// Is a current index of `name` on column kc in the cache?
+static bool index_ready(xlb_ctx* c, const std::string& name, int kc) {
+    auto it = cache(c).m.find({name, kc});
+    return it != cache(c).m.end() && it->second.version == c->versions[name] && it->second.ix.built();
+}
+
 static const Index& get_index(xlb_ctx* c, const std::string& name, int kc, RunState& rs) {
     xlb_rel* r = store_get(c, name);
     if (!r) xlb_fail(XLB_ERR_NOT_FOUND, "Missing relation: %s", name.c_str());
     CachedIndex& ci = cache(c).m[{name, kc}];
     uint64_t ver = c->versions[name];
     PhaseTimer t(c, &rs.st.ms_join);
-    if (ci.version != ver || !ci.ix.S) {
+    if ((ci.version != ver || !ci.ix.built()) && (kc == 0 || kc == 1) && r->schema.arity == 2 && !r->canonical && c->world == 1 && !(c->flags & XLB_FLAG_NO_DENSE)) {
+        // A stored relation in no particular order whose join keys come from a small dense domain:
+        // group its rows by counting instead of sorting them, and address the groups directly.
+        Keys rows = ops_rel_packed(c, r);
+        const uint64_t kb = rows.bound == ~0ull ? ~0ull : (kc == 0 ? rows.bound >> 32 : rows.bound & 0xFFFFFFFFull);
+        int bits = 0;
+        while (bits < 32 && (kb >> bits)) ++bits;
+        if (kb != ~0ull && bits <= 26 && (1ull << bits) <= 4 * rows.n + 4096) {
+            ci.ix = ops_index_build_direct(c, rows, kc == 0 ? SRC_HI : SRC_LO, bits);
+            ci.version = ver;
+            ci.table_ok = true;
+            return ci.ix;
+        }
+    }
+    if (ci.version != ver || !ci.ix.built()) {
         Keys local = index_rows(c, r, kc);
         if (c->world > 1) local = comm_repartition(c, local, SRC_HI, /*sorted_unique_result=*/true, rs.st);
         ci.ix = Index();
@@ -402,16 +424,49 @@ static std::set<int> needed_vars(const FlatRule& fr, const std::vector<bool>& do
 // output is marked into sink->set instead of being materialised (sink->used says so; the returned
 // Keys then carries only the tuple count).
 struct DenseSink {
-    const Keys* full = nullptr;
+    std::string head;
+    const Keys* full = nullptr;   // the head relation before this iteration
+    const Keys* novel = nullptr;  // what the iteration has found for it so far (disjoint from full)
     bool used = false;
     DenseSet set;
+    DenseState* state = nullptr;
+    Keys known() const {  // stands for full + novel: row count and OR bound
+        Keys k;
+        k.n = full->n + novel->n;
+        k.bound = (full->n ? full->bound : 0) | (novel->n ? novel->bound : 0);
+        return k;
+    }
 };
 
-static Keys run_pipeline(xlb_ctx* c, FlatRule fr /*by value: filter flags*/, size_t start, const Keys& start_rows, int start_part_half, uint64_t limit, RunState& rs,
-                         DenseSink* sink = nullptr) {
+// The bitmap of `head` = full + novel over a domain of at least (hb, lb) bits, built or rebuilt
+// when it is missing, too narrow, or out of step with the rows (a route that does not keep it up
+// to date has added tuples).
+static DenseState* dense_state(xlb_ctx* c, RunState& rs, const std::string& head, int hb, int lb, const Keys& full, const Keys& novel) {
+    DenseState& ds = rs.dense[head];
+    if (ds.valid && ds.hi_bits >= hb && ds.lo_bits >= lb && ds.rows == full.n + novel.n) return &ds;
+    int nh = hb, nl = lb;
+    if (ds.valid && std::max(hb, ds.hi_bits) + std::max(lb, ds.lo_bits) <= 27) {
+        nh = std::max(hb, ds.hi_bits);
+        nl = std::max(lb, ds.lo_bits);
+    }
+    ops_dense_state_build(c, ds, nh, nl, full, novel);
+    return &ds;
+}
+
+static void dense_sink_begin(xlb_ctx* c, RunState& rs, DenseSink* sink, int hb, int lb) {
+    sink->state = dense_state(c, rs, sink->head, hb, lb, *sink->full, *sink->novel);
+    sink->set = ops_dense_begin(c, sink->state->hi_bits, sink->state->lo_bits);
+    sink->set.visited = sink->state->visited->as<unsigned int>();
+    sink->used = true;
+}
+
+static Keys run_pipeline(xlb_ctx* c, FlatRule fr /*by value: filter flags*/, size_t start, const Keys& start_rows, bool start_is_set, int start_part_half, uint64_t limit,
+                         RunState& rs, DenseSink* sink = nullptr) {
     std::vector<bool> done(fr.atoms.size(), false);
     Bag bag;
     const Atom& sa = fr.atoms[start];
+    // every key of the bag occurs once: rows of a one-column set (a join output may repeat keys)
+    bool bag_keys_unique = start_is_set && sa.arity == 1;
     bag.k = start_rows;
     if (sa.arity == 2) { bag.hi = sa.var[0]; bag.lo = sa.var[1]; }
     else bag.lo = sa.var[0];
@@ -485,7 +540,6 @@ static Keys run_pipeline(xlb_ctx* c, FlatRule fr /*by value: filter flags*/, siz
         remaining--;
         int keyvar = a.var[kc];
         int othervar = a.arity == 2 ? a.var[1 - kc] : -1;
-        const Index& ix = get_index(c, a.rel, kc, rs);
         // output layout: the head's layout when this is the last step and nothing is pending
         bool last = remaining == 0;
         bool pending = false;
@@ -517,15 +571,56 @@ static Keys run_pipeline(xlb_ctx* c, FlatRule fr /*by value: filter flags*/, siz
             PhaseTimer t(c, &rs.st.ms_exchange);
             probe = comm_repartition(c, probe, keysel, false, rs.st);
         }
+        // Sides swapped: when the bag gives nothing but the join key and the relation has no index
+        // yet, stream over the relation instead of building one.  An index costs about a dozen
+        // such scans (three when the relation is already in key order), so scan that often, then
+        // build it: at most twice the cost of the better choice, whatever the number of iterations.
+        auto rel_src = [&](int src) { return src == keysel ? 0 : src == SRC_OTHER ? 1 : src == SRC_ZERO ? 2 : -1; };
+        // (a bag that repeats keys would yield every row once per repeat through an index: keep to
+        // bags without repeats so that both routes count the same candidates)
+        if (c->world == 1 && bag_keys_unique && !(c->flags & XLB_FLAG_NO_DENSE) && a.arity == 2 && rel_src(hs) >= 0 && rel_src(ls) >= 0 && probe.bound != ~0ull) {
+            xlb_rel* r = store_get(c, a.rel);
+            const uint64_t kb = keysel == SRC_HI ? probe.bound >> 32 : probe.bound & 0xFFFFFFFFull;
+            int key_bits = 0;
+            while (key_bits < 32 && (kb >> key_bits)) ++key_bits;
+            const bool indexed = index_ready(c, a.rel, kc);
+            int& scans = rs.scans[{a.rel, kc}];
+            if (r && !indexed && key_bits <= 27 && scans < (r->canonical && kc == 0 ? 3 : 12)) {
+                ++scans;
+                PhaseTimer t(c, &rs.st.ms_join);
+                Keys rows = ops_rel_packed(c, r);
+                const int rel_keysel = kc == 0 ? SRC_HI : SRC_LO;
+                int hb = 0, lb = 0;
+                Keys shape;
+                shape.n = 1;
+                shape.bound = ops_scan_join_bound(probe, keysel, rows, rel_keysel, rel_src(hs), rel_src(ls));
+                if (sink && last && !pending && ops_dense_bits(shape, sink->known(), &hb, &lb)) {
+                    dense_sink_begin(c, rs, sink, hb, lb);
+                    ops_scan_join_mark(c, probe, keysel, key_bits, rows, rel_keysel, rel_src(hs), rel_src(ls), sink->set);
+                    Keys marked;  // no rows and no count: both are in the sink
+                    marked.bound = shape.bound;
+                    return marked;
+                }
+                nb.k = ops_scan_join(c, probe, keysel, key_bits, rows, rel_keysel, rel_src(hs), rel_src(ls));
+                nb.part = keyvar;
+                if (limit && nb.k.n > limit && start_rows.n > 1) throw ChunkTooBig{};
+                nb.hi = out_hi;
+                nb.lo = out_lo;
+                bag = nb;
+                bag_keys_unique = false;
+                apply_ready_filters(c, fr, bag, rs);
+                continue;
+            }
+        }
+        const Index& ix = get_index(c, a.rel, kc, rs);
         {
             PhaseTimer t(c, &rs.st.ms_join);
             int hb = 0, lb = 0;
             Keys shape;  // stands for the rows this step would produce: only their OR bound matters here
             shape.n = 1;
             shape.bound = ops_expand_bound(probe, ix, hs, ls);
-            if (sink && last && !pending && c->world == 1 && !(c->flags & XLB_FLAG_NO_DENSE) && ops_dense_bits(shape, *sink->full, &hb, &lb)) {
-                sink->set = ops_dense_begin(c, hb, lb);
-                sink->used = true;
+            if (sink && last && !pending && c->world == 1 && !(c->flags & XLB_FLAG_NO_DENSE) && ops_dense_bits(shape, sink->known(), &hb, &lb)) {
+                dense_sink_begin(c, rs, sink, hb, lb);
                 ops_join_expand_mark(c, probe, keysel, ix, hs, ls, sink->set);
                 Keys marked;  // no rows and no count: both are in the sink
                 marked.bound = shape.bound;
@@ -537,6 +632,7 @@ static Keys run_pipeline(xlb_ctx* c, FlatRule fr /*by value: filter flags*/, siz
             nb.hi = out_hi;
             nb.lo = out_lo;
             bag = nb;
+            bag_keys_unique = false;
             apply_ready_filters(c, fr, bag, rs);
         }
     }
@@ -576,6 +672,8 @@ static void eval_variant(xlb_ctx* c, const FlatRule& fr_in, size_t start, const 
             for (uint32_t j = 0; j < sa.arity; ++j)
                 if (sa.var[j] == f.lhs) kc = (int)j;
             if (kc < 0 || (sa.arity == 2 && sa.var[0] == sa.var[1])) continue;
+            // one filtering pass over the relation costs far less than building its index
+            if (c->world == 1 && !index_ready(c, sa.rel, kc)) continue;
             const Index& ix = get_index(c, sa.rel, kc, rs);
             uint64_t key = f.rhs;
             Keys probe = ops_from_host(c, &key, 1);
@@ -592,6 +690,11 @@ static void eval_variant(xlb_ctx* c, const FlatRule& fr_in, size_t start, const 
         }
     }
     if (start_rows.n == 0 && c->world == 1) return;
+    bool start_is_set = true;  // a delta is; a stored relation when it is certified sorted and unique
+    if (start_is_stored) {
+        xlb_rel* sr = store_get(c, fr.atoms[start].rel);
+        start_is_set = sr && sr->canonical;
+    }
     uint64_t limit = c->join_chunk;
     // with several ranks every rank runs the same sequence of exchanges, so the rows are not
     // chunked (chunk counts would differ between ranks)
@@ -608,9 +711,11 @@ static void eval_variant(xlb_ctx* c, const FlatRule& fr_in, size_t start, const 
         Keys part = (at == 0 && hi == start_rows.n) ? start_rows : ops_slice(c, start_rows, at, hi);
         Keys cand;
         DenseSink sink;
+        sink.head = fr.head;
         sink.full = &full;
+        sink.novel = &novel;
         try {
-            cand = run_pipeline(c, fr, start, part, start_part_half, limit, rs, &sink);
+            cand = run_pipeline(c, fr, start, part, start_is_set, start_part_half, limit, rs, &sink);
         } catch (const ChunkTooBig&) {
             chunk = std::max<uint64_t>((hi - at) / 2, 1);
             continue;
@@ -621,6 +726,7 @@ static void eval_variant(xlb_ctx* c, const FlatRule& fr_in, size_t start, const 
             // there were comes back with the count of the new ones
             PhaseTimer t(c, &rs.st.ms_setops);
             Keys fresh = ops_dense_finish(c, sink.set, full);
+            sink.state->rows += fresh.n;
             rs.st.candidate_tuples += sink.set.marked;
             novel = novel.n ? ops_union(c, novel, fresh) : fresh;
             continue;
@@ -633,11 +739,14 @@ static void eval_variant(xlb_ctx* c, const FlatRule& fr_in, size_t start, const 
         if (cand.n == 0) continue;
         Keys fresh;
         int hb = 0, lb = 0;
-        if (!(c->flags & XLB_FLAG_NO_DENSE) && ops_dense_bits(cand, full, &hb, &lb)) {
+        if (!(c->flags & XLB_FLAG_NO_DENSE) && ops_dense_bits(cand, sink.known(), &hb, &lb)) {
             // small dense domain: sort + dedup + difference on a bitmap
             PhaseTimer t(c, &rs.st.ms_setops);
-            fresh = ops_dense_novel(c, cand, full, hb, lb);
+            DenseState* ds = dense_state(c, rs, fr.head, hb, lb, full, novel);
+            fresh = ops_dense_novel(c, cand, full, ds->hi_bits, ds->lo_bits, ds->visited->as<unsigned int>());
+            ds->rows += fresh.n;
         } else {
+            rs.dense[fr.head].valid = false;  // this route does not keep the bitmap: rebuilt when next wanted
             {
                 PhaseTimer t(c, &rs.st.ms_sort);
                 ops_sort(c, cand, /*keep_input=*/cand.buf == start_rows.buf);  // a single-atom body hands over a stored relation

@@ -264,6 +264,54 @@ uint64_t select(xlb_ctx* c, Pred pred, Emit emit, uint64_t n) {
     return h;
 }
 
+// The same selection in one pass for callers that do not need the input order kept (a bag of
+// tuples): every tile reserves its place with one atomic add on the running total, so tiles land
+// in the order they finish; rows keep their order inside a tile.
+template <class Pred, class Emit>
+static __global__ void __launch_bounds__(BLOCK) select_append_k(Pred pred, Emit emit, uint64_t n, unsigned long long* total) {
+    __shared__ uint32_t sm[33];
+    __shared__ unsigned long long base_s;
+    constexpr int ROUNDS = SCAN_TILE / BLOCK;
+    const unsigned lane = lane_id(), warp = threadIdx.x >> 5;
+    const uint64_t wbase = (uint64_t)blockIdx.x * SCAN_TILE + (uint64_t)warp * (32 * ROUNDS);
+    unsigned flags[ROUNDS];
+    uint32_t cnt = 0;
+#pragma unroll
+    for (int r = 0; r < ROUNDS; ++r) {
+        uint64_t i = wbase + r * 32 + lane;
+        bool f = i < n && pred(i);
+        flags[r] = __ballot_sync(FULL, f);
+        cnt += __popc(flags[r]);
+    }
+    uint32_t tot;
+    uint32_t ex = block_exclusive_scan<uint32_t>(lane == 0 ? cnt : 0u, &tot, sm);
+    ex = __shfl_sync(FULL, ex, 0);
+    if (threadIdx.x == 0) base_s = tot ? atomicAdd(total, (unsigned long long)tot) : 0ull;
+    __syncthreads();
+    uint64_t pos = base_s + ex;
+#pragma unroll
+    for (int r = 0; r < ROUNDS; ++r) {
+        unsigned b = flags[r];
+        if ((b >> lane) & 1u) emit(wbase + r * 32 + lane, pos + __popc(b & lanemask_lt()));
+        pos += __popc(b);
+    }
+}
+
+// Returns the number of selected rows (one host read-back); output order unspecified.
+template <class Pred, class Emit>
+uint64_t select_unordered(xlb_ctx* c, Pred pred, Emit emit, uint64_t n) {
+    if (n == 0) return 0;
+    uint64_t ntiles = (n + SCAN_TILE - 1) / SCAN_TILE;
+    Buf total = make_buf(c, 8);
+    CUDA_OK(cudaMemsetAsync(total->p, 0, 8, c->stream));
+    prof_begin(c, "select_append", 0);
+    select_append_k<Pred, Emit><<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(pred, emit, n, total->as<unsigned long long>());
+    check_launch(c, "select_append");
+    unsigned long long h;
+    read_words(c, total->p, 1, &h);
+    return h;
+}
+
 // -------------------------------------------------------------------------------- pack/unpack
 // pack kernels also reduce the OR of the packed rows into *or_out (may be null)
 static __global__ void pack2_k(const uint32_t* __restrict__ c0, const uint32_t* __restrict__ c1, uint64_t* __restrict__ out, uint64_t n, unsigned long long* or_out) {
@@ -878,7 +926,7 @@ __device__ __forceinline__ uint32_t dense_index(uint64_t k, int lo_bits) {
 }
 template <bool SET>
 static __global__ void __launch_bounds__(BLOCK) dense_mark_k(const uint64_t* __restrict__ keys, uint64_t n, int lo_bits, unsigned int* __restrict__ bitmap,
-                                                           uint64_t words, DevStatus* st) {
+                                                           uint64_t words, DevStatus* st, const unsigned int* __restrict__ visited = nullptr) {
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
         uint64_t k = keys[i];
         uint32_t x = dense_index(k, lo_bits);
@@ -888,6 +936,7 @@ static __global__ void __launch_bounds__(BLOCK) dense_mark_k(const uint64_t* __r
             continue;
         }
         unsigned bit = 1u << (x & 31);
+        if (SET && visited && (__ldg(&visited[x >> 5]) & bit)) continue;  // known already (read-only here: cacheable)
         unsigned cur = bitmap[x >> 5];  // most candidates repeat a tuple already seen: skip the atomic then
         if (SET) { if (!(cur & bit)) atomicOr(&bitmap[x >> 5], bit); }
         else     { if (cur & bit) atomicAnd(&bitmap[x >> 5], ~bit); }
@@ -895,23 +944,30 @@ static __global__ void __launch_bounds__(BLOCK) dense_mark_k(const uint64_t* __r
 }
 // The bitmap is counted and emitted in groups of 32 words (1024 tuples): one warp per group, so the
 // prefix sum that places the output runs over domain / 1024 entries only.
-static __global__ void __launch_bounds__(BLOCK) dense_count_k(const unsigned int* __restrict__ bitmap, uint64_t words, uint32_t* __restrict__ group_counts, uint64_t groups) {
+// (with `visited`, bits set there do not count and are not emitted; the emit pass adds what it emits)
+static __global__ void __launch_bounds__(BLOCK) dense_count_k(const unsigned int* __restrict__ bitmap, uint64_t words, uint32_t* __restrict__ group_counts, uint64_t groups,
+                                                            const unsigned int* __restrict__ visited) {
     uint64_t g = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (g >= groups) return;
     uint64_t w = g * 32 + lane_id();
-    unsigned cnt = w < words ? __popc(bitmap[w]) : 0;
+    unsigned cnt = w < words ? __popc(bitmap[w] & ~(visited ? visited[w] : 0u)) : 0;
 #pragma unroll
     for (int d = 16; d; d >>= 1) cnt += __shfl_xor_sync(FULL, cnt, d);
     if (lane_id() == 0) group_counts[g] = cnt;
 }
 static __global__ void __launch_bounds__(BLOCK) dense_emit_k(const unsigned int* __restrict__ bitmap, uint64_t words, const uint64_t* __restrict__ group_offs,
-                                                           uint64_t groups, int lo_bits, uint64_t* __restrict__ out) {
+                                                           uint64_t groups, int lo_bits, uint64_t* __restrict__ out, unsigned int* __restrict__ visited) {
     uint64_t g = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (g >= groups) return;
     const unsigned lane = lane_id();
     const uint64_t lo_mask = (1ull << lo_bits) - 1;
     uint64_t w = g * 32 + lane;
     unsigned m = w < words ? bitmap[w] : 0;
+    if (visited && w < words) {
+        unsigned v = visited[w];
+        m &= ~v;
+        if (m) visited[w] = v | m;  // one thread per word
+    }
     unsigned cnt = __popc(m), incl = cnt;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
@@ -1002,6 +1058,209 @@ static __global__ void __launch_bounds__(BLOCK) hash_probe_k(LoadKey load_key, u
     }
 }
 
+// ------------------------------------------------------- direct (counting) join index
+// For join keys from a small dense domain the build side needs no sort and no hash table: count
+// the rows of every key, prefix-sum the counts, and drop every row's other column at its key's
+// cursor.  After the fill pass cursor[k] is the end of key k's group (= the start of key k+1's),
+// which is all a probe needs.  Rows of one key land in no particular order: the consumers are
+// set-valued (their output is sorted or marked in a bitmap).
+// Skewed inputs (a power-law graph's hub) put tens of thousands of rows on one key, and atomics on
+// one address serialise in the L2 (measured: 16 M rows with a 69 K-row hub took 250 us per pass,
+// the hub's own chain).  So every tile first combines its rows per key in a small shared-memory
+// table (open addressing, a few probes; a row that finds no slot goes to global memory on its
+// own) and touches global memory once per distinct key.
+constexpr int DX_IPT = 8, DX_TILE = BLOCK * DX_IPT, DX_SLOTS = 2048, DX_PROBES = 4;
+constexpr uint32_t DX_EMPTY = 0xFFFFFFFFu, DX_NONE = 0xFFFFFFFFu;
+
+// slot of `key` in the tile's table, or DX_NONE
+__device__ __forceinline__ uint32_t dx_slot(uint32_t* skey, uint32_t key) {
+    uint32_t h = (key * 2654435761u) >> 21;  // 11 bits: DX_SLOTS
+#pragma unroll
+    for (int t = 0; t < DX_PROBES; ++t) {
+        uint32_t old = atomicCAS(&skey[h], DX_EMPTY, key);
+        if (old == DX_EMPTY || old == key) return h;
+        h = (h + 1) & (DX_SLOTS - 1);
+    }
+    return DX_NONE;
+}
+
+static __global__ void __launch_bounds__(BLOCK) direct_count_k(const uint64_t* __restrict__ rows, uint64_t n, int keysel, unsigned int* __restrict__ cnt, uint64_t domain,
+                                                          DevStatus* st) {
+    __shared__ uint32_t skey[DX_SLOTS], scnt[DX_SLOTS];
+    const uint64_t ntiles = (n + DX_TILE - 1) / DX_TILE;
+    for (uint64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        for (int s = threadIdx.x; s < DX_SLOTS; s += BLOCK) {
+            skey[s] = DX_EMPTY;
+            scnt[s] = 0;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < DX_IPT; ++k) {
+            uint64_t i = tile * DX_TILE + (uint64_t)k * BLOCK + threadIdx.x;
+            if (i >= n) break;
+            uint64_t t = rows[i];
+            uint64_t key = keysel == 0 ? (t >> 32) : (t & 0xFFFFFFFFull);
+            if (key >= domain) {
+                set_status(st, XLB_ERR_CAPACITY, 5, key);
+                continue;
+            }
+            uint32_t h = dx_slot(skey, (uint32_t)key);
+            if (h != DX_NONE) atomicAdd(&scnt[h], 1u);
+            else atomicAdd(&cnt[key], 1u);
+        }
+        __syncthreads();
+        for (int s = threadIdx.x; s < DX_SLOTS; s += BLOCK)
+            if (scnt[s]) atomicAdd(&cnt[skey[s]], scnt[s]);
+        __syncthreads();
+    }
+}
+static __global__ void __launch_bounds__(BLOCK) direct_fill_k(const uint64_t* __restrict__ rows, uint64_t n, int keysel, unsigned long long* __restrict__ cursor, uint64_t domain,
+                                                         uint32_t* __restrict__ pay) {
+    __shared__ uint32_t skey[DX_SLOTS], scnt[DX_SLOTS], sbase[DX_SLOTS];
+    const uint64_t ntiles = (n + DX_TILE - 1) / DX_TILE;
+    for (uint64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        for (int s = threadIdx.x; s < DX_SLOTS; s += BLOCK) {
+            skey[s] = DX_EMPTY;
+            scnt[s] = 0;
+        }
+        __syncthreads();
+        uint32_t other[DX_IPT], where[DX_IPT];  // where = (slot << 16) | rank within the slot, or DX_NONE
+#pragma unroll
+        for (int k = 0; k < DX_IPT; ++k) {
+            where[k] = DX_NONE;
+            uint64_t i = tile * DX_TILE + (uint64_t)k * BLOCK + threadIdx.x;
+            if (i >= n) continue;
+            uint64_t t = rows[i];
+            uint64_t key = keysel == 0 ? (t >> 32) : (t & 0xFFFFFFFFull);
+            other[k] = keysel == 0 ? (uint32_t)t : (uint32_t)(t >> 32);
+            if (key >= domain) continue;  // reported by the counting pass
+            uint32_t h = dx_slot(skey, (uint32_t)key);
+            if (h != DX_NONE) {
+                where[k] = (h << 16) | atomicAdd(&scnt[h], 1u);  // rank < DX_TILE = 2^11
+            } else {
+                unsigned long long pos = atomicAdd(&cursor[key], 1ull);
+                if (pos < n) pay[pos] = other[k];
+            }
+        }
+        __syncthreads();
+        for (int s = threadIdx.x; s < DX_SLOTS; s += BLOCK)
+            if (scnt[s]) sbase[s] = (uint32_t)atomicAdd(&cursor[skey[s]], (unsigned long long)scnt[s]);  // positions stay below n < 2^32
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < DX_IPT; ++k) {
+            if (where[k] == DX_NONE) continue;
+            uint64_t pos = (uint64_t)sbase[where[k] >> 16] + (where[k] & 0xFFFFu);
+            if (pos < n) pay[pos] = other[k];
+        }
+        __syncthreads();
+    }
+}
+// match[i] = (start << 32) | len, or 0 when the key has no rows (same form as hash_probe_k)
+template <class LoadKey>
+static __global__ void __launch_bounds__(BLOCK) direct_probe_k(LoadKey load_key, uint64_t n, const unsigned long long* __restrict__ cursor, uint64_t domain,
+                                                          uint64_t* __restrict__ match) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        uint64_t key = load_key(i);
+        uint64_t m = 0;
+        if (key < domain) {
+            uint64_t e = __ldg(&cursor[key]);
+            uint64_t s = key ? __ldg(&cursor[key - 1]) : 0;
+            if (e > s) m = (s << 32) | (e - s);
+        }
+        match[i] = m;
+    }
+}
+
+// ------------------------------------------------------------------ scan join (sides swapped)
+// When the probing bag contributes nothing but the join key to the output and its keys come from
+// a small dense domain, the join can run from the other side without any index on the stored
+// relation: mark the bag's keys in a bitmap, then stream over the relation's rows and keep those
+// whose key is marked.  One sequential read of the relation per use, against a sort of it (or a
+// counting build) for an index.
+static __global__ void __launch_bounds__(BLOCK) keyset_mark_k(const uint64_t* __restrict__ rows, uint64_t n, int keysel, unsigned int* __restrict__ bitmap, uint64_t domain,
+                                                         DevStatus* st) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        uint64_t t = rows[i];
+        uint64_t key = keysel == 0 ? (t >> 32) : (t & 0xFFFFFFFFull);
+        if (key >= domain) {
+            set_status(st, XLB_ERR_CAPACITY, 6, key);
+            continue;
+        }
+        unsigned bit = 1u << (key & 31);
+        if (!(bitmap[key >> 5] & bit)) atomicOr(&bitmap[key >> 5], bit);
+    }
+}
+// output half from a relation row: 0 = its key column, 1 = its other column, 2 = zero
+__device__ __forceinline__ uint32_t sj_pick(int src, uint32_t key, uint32_t other) { return src == 0 ? key : src == 1 ? other : 0u; }
+__device__ __forceinline__ bool sj_in(const unsigned int* __restrict__ keyset, uint64_t domain, uint32_t key) {
+    return key < domain && ((__ldg(&keyset[key >> 5]) >> (key & 31)) & 1u);
+}
+// Rows whose key is in the key set, marked in the head's bitmap; *count += their number.
+// Memory-bound streaming: every thread keeps SJ_VEC 16-byte loads in flight per step (one 8-byte
+// load per thread and step left the kernel at 1.9 TB/s, latency-bound).
+constexpr int SJ_VEC = 4, SJ_TILE = BLOCK * SJ_VEC * 2;
+__device__ __forceinline__ unsigned sj_mark_row(uint64_t t, int keysel, const unsigned int* __restrict__ keyset, uint64_t domain, int hi_src, int lo_src,
+                                                unsigned int* __restrict__ bitmap, uint64_t words, int lo_bits, DevStatus* st,
+                                                const unsigned int* __restrict__ visited) {
+    uint32_t key = keysel == 0 ? (uint32_t)(t >> 32) : (uint32_t)t;
+    uint32_t other = keysel == 0 ? (uint32_t)t : (uint32_t)(t >> 32);
+    if (!sj_in(keyset, domain, key)) return 0;
+    uint64_t out = ((uint64_t)sj_pick(hi_src, key, other) << 32) | sj_pick(lo_src, key, other);
+    uint32_t x = dense_index(out, lo_bits);
+    if ((out & 0xFFFFFFFFull) >> lo_bits || (uint64_t)(x >> 5) >= words) {
+        set_status(st, XLB_ERR_CAPACITY, 7, out);
+        return 1;
+    }
+    unsigned bit = 1u << (x & 31);
+    if (visited && (__ldg(&visited[x >> 5]) & bit)) return 1;  // known already: most of a hub's tuples
+    // (a plain load, served by the L1: reading the hot words of a hub through to the L2 instead
+    // made the kernel three times slower)
+    if (!(bitmap[x >> 5] & bit)) atomicOr(&bitmap[x >> 5], bit);
+    return 1;
+}
+static __global__ void __launch_bounds__(BLOCK) scan_join_mark_k(const uint64_t* __restrict__ rows, uint64_t n, int keysel, const unsigned int* __restrict__ keyset,
+                                                            uint64_t domain, int hi_src, int lo_src, unsigned int* __restrict__ bitmap, uint64_t words, int lo_bits,
+                                                            unsigned long long* __restrict__ count, DevStatus* st, const unsigned int* __restrict__ visited) {
+    unsigned long long mine = 0;
+    const uint64_t ntiles = n / SJ_TILE;  // whole tiles, 16-byte loads (the row array is 16-byte aligned: checked by the host)
+    const ulonglong2* rows2 = reinterpret_cast<const ulonglong2*>(rows);
+    for (uint64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        ulonglong2 v[SJ_VEC];
+#pragma unroll
+        for (int k = 0; k < SJ_VEC; ++k) v[k] = rows2[tile * (SJ_TILE / 2) + (uint64_t)k * BLOCK + threadIdx.x];
+#pragma unroll
+        for (int k = 0; k < SJ_VEC; ++k) {
+            mine += sj_mark_row(v[k].x, keysel, keyset, domain, hi_src, lo_src, bitmap, words, lo_bits, st, visited);
+            mine += sj_mark_row(v[k].y, keysel, keyset, domain, hi_src, lo_src, bitmap, words, lo_bits, st, visited);
+        }
+    }
+    for (uint64_t i = ntiles * SJ_TILE + (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
+        mine += sj_mark_row(rows[i], keysel, keyset, domain, hi_src, lo_src, bitmap, words, lo_bits, st, visited);
+    for (int d = 16; d; d >>= 1) mine += __shfl_down_sync(0xFFFFFFFFu, mine, d);
+    if (lane_id() == 0 && mine) atomicAdd(count, mine);
+}
+struct PredKeyIn {  // the row's key is in the key set
+    const uint64_t* rows;
+    int keysel;
+    const unsigned int* keyset;
+    uint64_t domain;
+    __device__ __forceinline__ bool operator()(uint64_t i) const {
+        uint64_t t = rows[i];
+        return sj_in(keyset, domain, keysel == 0 ? (uint32_t)(t >> 32) : (uint32_t)t);
+    }
+};
+struct EmitScanRow {  // the row in the output layout
+    const uint64_t* rows;
+    int keysel, hi_src, lo_src;
+    uint64_t* out;
+    __device__ __forceinline__ void operator()(uint64_t i, uint64_t pos) const {
+        uint64_t t = rows[i];
+        uint32_t key = keysel == 0 ? (uint32_t)(t >> 32) : (uint32_t)t;
+        uint32_t other = keysel == 0 ? (uint32_t)t : (uint32_t)(t >> 32);
+        out[pos] = ((uint64_t)sj_pick(hi_src, key, other) << 32) | sj_pick(lo_src, key, other);
+    }
+};
+
 struct PredMatched {
     const uint64_t* match;
     __device__ __forceinline__ bool operator()(uint64_t i) const { return match[i] != 0; }
@@ -1036,7 +1295,7 @@ static __global__ void __launch_bounds__(BLOCK) expand_k(const uint64_t* __restr
                                                    uint64_t nrows, uint64_t total, const uint64_t* __restrict__ S,
                                                    const uint32_t* __restrict__ pay, int hi_src, int lo_src, uint64_t* __restrict__ out,
                                                    unsigned int* __restrict__ bitmap, uint64_t words, int lo_bits, DevStatus* st,
-                                                   const uint64_t* __restrict__ total_dev) {
+                                                   const uint64_t* __restrict__ total_dev, const unsigned int* __restrict__ visited) {
     __shared__ uint64_t soff[EX_TILE + 2];
     __shared__ uint64_t row_s[2];
     // With total_dev the output count is still on the device (the host launched a fixed grid
@@ -1092,7 +1351,7 @@ static __global__ void __launch_bounds__(BLOCK) expand_k(const uint64_t* __restr
                 set_status(st, XLB_ERR_CAPACITY, 4, key);
             } else {
                 unsigned bit = 1u << (x & 31);
-                if (!(bitmap[x >> 5] & bit)) atomicOr(&bitmap[x >> 5], bit);
+                if (!(visited && (__ldg(&visited[x >> 5]) & bit)) && !(bitmap[x >> 5] & bit)) atomicOr(&bitmap[x >> 5], bit);
             }
         }
     }

@@ -375,7 +375,7 @@ Keys ops_dense_finish(xlb_ctx* c, DenseSet& d, const Keys& full) {
     Keys o;
     o.bound = d.bound;
     const uint64_t words = d.words;
-    if (full.n) {
+    if (full.n && !d.visited) {
         prof_begin(c, "dense_clear", full.n * 8ull);
         dense_mark_k<false><<<grid_for(c, full.n), BLOCK, 0, c->stream>>>(full.ptr(), full.n, d.lo_bits, d.bitmap->as<unsigned int>(), words, c->d_status);
         check_launch(c, "dense_clear");
@@ -384,7 +384,7 @@ Keys ops_dense_finish(xlb_ctx* c, DenseSet& d, const Keys& full) {
     Buf gcnt = make_buf(c, groups * 4);
     Buf offs = make_buf(c, groups * 8);
     prof_begin(c, "dense_count", words * 4ull);
-    dense_count_k<<<(unsigned)((groups * 32 + BLOCK - 1) / BLOCK), BLOCK, 0, c->stream>>>(d.bitmap->as<unsigned int>(), words, gcnt->as<uint32_t>(), groups);
+    dense_count_k<<<(unsigned)((groups * 32 + BLOCK - 1) / BLOCK), BLOCK, 0, c->stream>>>(d.bitmap->as<unsigned int>(), words, gcnt->as<uint32_t>(), groups, d.visited);
     check_launch(c, "dense_count");
     exclusive_scan<LoadU32, uint64_t>(c, LoadU32{gcnt->as<uint32_t>()}, groups, offs->as<uint64_t>(), d.counts);
     unsigned long long both[2];
@@ -396,18 +396,35 @@ Keys ops_dense_finish(xlb_ctx* c, DenseSet& d, const Keys& full) {
     o.buf = make_buf(c, tot * 8);
     if (tot) {
         prof_begin(c, "dense_emit", words * 4ull + tot * 8ull);
-        dense_emit_k<<<(unsigned)((groups * 32 + BLOCK - 1) / BLOCK), BLOCK, 0, c->stream>>>(d.bitmap->as<unsigned int>(), words, offs->as<uint64_t>(), groups, d.lo_bits, o.buf->as<uint64_t>());
+        dense_emit_k<<<(unsigned)((groups * 32 + BLOCK - 1) / BLOCK), BLOCK, 0, c->stream>>>(d.bitmap->as<unsigned int>(), words, offs->as<uint64_t>(), groups, d.lo_bits, o.buf->as<uint64_t>(), d.visited);
         check_launch(c, "dense_emit");
     }
     return o;
 }
 
-Keys ops_dense_novel(xlb_ctx* c, const Keys& cand, const Keys& full, int hi_bits, int lo_bits) {
+void ops_dense_state_build(xlb_ctx* c, DenseState& s, int hi_bits, int lo_bits, const Keys& full, const Keys& novel) {
+    s.hi_bits = hi_bits;
+    s.lo_bits = lo_bits;
+    s.words = ((1ull << (hi_bits + lo_bits)) + 31) / 32;
+    s.visited = make_buf(c, s.words * 4);
+    CUDA_OK(cudaMemsetAsync(s.visited->p, 0, s.words * 4, c->stream));
+    for (const Keys* k : {&full, &novel}) {
+        if (!k->n) continue;
+        prof_begin(c, "dense_mark", k->n * 8ull);
+        dense_mark_k<true><<<grid_for(c, k->n), BLOCK, 0, c->stream>>>(k->ptr(), k->n, lo_bits, s.visited->as<unsigned int>(), s.words, c->d_status);
+        check_launch(c, "dense_mark");
+    }
+    s.rows = full.n + novel.n;
+    s.valid = true;
+}
+
+Keys ops_dense_novel(xlb_ctx* c, const Keys& cand, const Keys& full, int hi_bits, int lo_bits, unsigned int* visited) {
     DenseSet d = ops_dense_begin(c, hi_bits, lo_bits);
     d.bound = cand.bound;
+    d.visited = visited;
     if (cand.n) {
         prof_begin(c, "dense_mark", cand.n * 8ull);
-        dense_mark_k<true><<<grid_for(c, cand.n), BLOCK, 0, c->stream>>>(cand.ptr(), cand.n, lo_bits, d.bitmap->as<unsigned int>(), d.words, c->d_status);
+        dense_mark_k<true><<<grid_for(c, cand.n), BLOCK, 0, c->stream>>>(cand.ptr(), cand.n, lo_bits, d.bitmap->as<unsigned int>(), d.words, c->d_status, visited);
         check_launch(c, "dense_mark");
     }
     Keys none;
@@ -453,7 +470,7 @@ Keys ops_filter(xlb_ctx* c, const Keys& in, uint32_t cmp, int lhs_src, bool rhs_
     Keys o;
     o.bound = in.bound;
     o.buf = make_buf(c, in.n * 8);
-    o.n = select(c, PredCmp{in.ptr(), cmp, lhs_src, rhs_is_const, rhs}, EmitKey{in.ptr(), o.buf->as<uint64_t>()}, in.n);
+    o.n = select_unordered(c, PredCmp{in.ptr(), cmp, lhs_src, rhs_is_const, rhs}, EmitKey{in.ptr(), o.buf->as<uint64_t>()}, in.n);  // a bag: any order
     return o;
 }
 
@@ -484,15 +501,98 @@ Index ops_index_build(xlb_ctx* c, Buf S, uint64_t n, int key_shift, Buf pay) {
     return ix;
 }
 
+Index ops_index_build_direct(xlb_ctx* c, const Keys& rows, int keysel, int key_bits) {
+    Index ix;
+    ix.n = rows.n;
+    if (rows.n >= 0xFFFFFFFFull) xlb_fail(XLB_ERR_CAPACITY, "join build side of %llu rows exceeds the 2^32 - 1 row limit", (unsigned long long)rows.n);
+    ix.domain = 1ull << key_bits;
+    ix.bound = rows.bound;
+    const uint64_t other = keysel == SRC_HI ? (rows.bound & 0xFFFFFFFFull) : (rows.bound >> 32);
+    ix.pay_bound = rows.bound == ~0ull ? 0xFFFFFFFFull : other;
+    Buf cnt = make_buf(c, ix.domain * 4);
+    CUDA_OK(cudaMemsetAsync(cnt->p, 0, ix.domain * 4, c->stream));
+    ix.cursor = make_buf(c, ix.domain * 8);
+    ix.pay = make_buf(c, rows.n * 4);
+    Buf total = make_buf(c, 8);
+    if (rows.n) {
+        prof_begin(c, "direct_count", rows.n * 8ull);
+        direct_count_k<<<grid_for(c, rows.n, DX_TILE), BLOCK, 0, c->stream>>>(rows.ptr(), rows.n, keysel, cnt->as<unsigned int>(), ix.domain, c->d_status);
+        check_launch(c, "direct_count");
+    }
+    exclusive_scan<LoadU32, uint64_t>(c, LoadU32{cnt->as<uint32_t>()}, ix.domain, ix.cursor->as<uint64_t>(), total->as<uint64_t>());
+    if (rows.n) {
+        prof_begin(c, "direct_fill", rows.n * 12ull);
+        direct_fill_k<<<grid_for(c, rows.n, DX_TILE), BLOCK, 0, c->stream>>>(rows.ptr(), rows.n, keysel, ix.cursor->as<unsigned long long>(), ix.domain, ix.pay->as<uint32_t>());
+        check_launch(c, "direct_fill");
+    }
+    return ix;
+}
+
 Buf ops_probe_match(xlb_ctx* c, const Keys& bag, int keysel, const uint64_t* pkeys, const Index& ix) {
     Buf match = make_buf(c, bag.n * 8);
-    if (bag.n) {
+    if (bag.n && ix.cursor) {
+        prof_begin(c, "direct_probe", bag.n * 32ull);
+        if (pkeys) direct_probe_k<LoadKey64><<<grid_for(c, bag.n), BLOCK, 0, c->stream>>>(LoadKey64{pkeys}, bag.n, ix.cursor->as<unsigned long long>(), ix.domain, match->as<uint64_t>());
+        else direct_probe_k<LoadKeyHalf><<<grid_for(c, bag.n), BLOCK, 0, c->stream>>>(LoadKeyHalf{bag.ptr(), keysel}, bag.n, ix.cursor->as<unsigned long long>(), ix.domain, match->as<uint64_t>());
+        check_launch(c, "direct_probe");
+    } else if (bag.n) {
         prof_begin(c, "hash_probe", bag.n * 32ull);
         if (pkeys) hash_probe_k<LoadKey64><<<grid_for(c, bag.n), BLOCK, 0, c->stream>>>(LoadKey64{pkeys}, bag.n, ix.table->as<ulonglong2>(), ix.mask, match->as<uint64_t>());
         else hash_probe_k<LoadKeyHalf><<<grid_for(c, bag.n), BLOCK, 0, c->stream>>>(LoadKeyHalf{bag.ptr(), keysel}, bag.n, ix.table->as<ulonglong2>(), ix.mask, match->as<uint64_t>());
         check_launch(c, "hash_probe");
     }
     return match;
+}
+
+uint64_t ops_scan_join_bound(const Keys& bag, int keysel, const Keys& rel, int rel_keysel, int rel_hi, int rel_lo) {
+    const uint64_t kb = half_bound(bag.bound, keysel, 0) & half_bound(rel.bound, rel_keysel, 0);  // a produced key is in both
+    const uint64_t ob = half_bound(rel.bound, rel_keysel == SRC_HI ? SRC_LO : SRC_HI, 0);
+    auto pick = [&](int src) { return src == 0 ? kb : src == 1 ? ob : 0ull; };
+    return (pick(rel_hi) << 32) | pick(rel_lo);
+}
+
+static Buf scan_join_keyset(xlb_ctx* c, const Keys& bag, int keysel, int key_bits) {
+    const uint64_t domain = 1ull << key_bits;
+    const uint64_t bytes = std::max<uint64_t>(domain / 8, 4);
+    Buf keyset = make_buf(c, bytes);
+    CUDA_OK(cudaMemsetAsync(keyset->p, 0, bytes, c->stream));
+    if (bag.n) {
+        prof_begin(c, "keyset_mark", bag.n * 8ull);
+        keyset_mark_k<<<grid_for(c, bag.n), BLOCK, 0, c->stream>>>(bag.ptr(), bag.n, keysel, keyset->as<unsigned int>(), domain, c->d_status);
+        check_launch(c, "keyset_mark");
+    }
+    return keyset;
+}
+
+Keys ops_scan_join(xlb_ctx* c, const Keys& bag, int keysel, int key_bits, const Keys& rel, int rel_keysel, int rel_hi, int rel_lo) {
+    Keys o;
+    o.bound = ops_scan_join_bound(bag, keysel, rel, rel_keysel, rel_hi, rel_lo);
+    if (bag.n == 0 || rel.n == 0) {
+        o.buf = make_buf(c, 0);
+        return o;
+    }
+    Buf keyset = scan_join_keyset(c, bag, keysel, key_bits);
+    // the output is at most the relation
+    Buf out = make_buf(c, rel.n * 8);
+    o.n = select_unordered(c, PredKeyIn{rel.ptr(), rel_keysel, keyset->as<unsigned int>(), 1ull << key_bits}, EmitScanRow{rel.ptr(), rel_keysel, rel_hi, rel_lo, out->as<uint64_t>()}, rel.n);
+    if (o.n * 2 < rel.n) {  // give the large buffer back
+        Keys full;
+        full.buf = out;
+        full.n = o.n;
+        o.buf = ops_slice(c, full, 0, o.n).buf;
+    } else o.buf = out;
+    return o;
+}
+
+void ops_scan_join_mark(xlb_ctx* c, const Keys& bag, int keysel, int key_bits, const Keys& rel, int rel_keysel, int rel_hi, int rel_lo, DenseSet& d) {
+    d.bound |= ops_scan_join_bound(bag, keysel, rel, rel_keysel, rel_hi, rel_lo);
+    if (bag.n == 0 || rel.n == 0) return;
+    Buf keyset = scan_join_keyset(c, bag, keysel, key_bits);
+    prof_begin(c, "scan_join_mark", rel.n * 8ull);
+    if ((uintptr_t)rel.ptr() & 15) xlb_fail(XLB_ERR_INVALID, "internal: scan join over a row array that is not 16-byte aligned");
+    scan_join_mark_k<<<grid_for(c, rel.n, SJ_TILE), BLOCK, 0, c->stream>>>(rel.ptr(), rel.n, rel_keysel, keyset->as<unsigned int>(), 1ull << key_bits, rel_hi, rel_lo,
+                                                                  d.bitmap->as<unsigned int>(), d.words, d.lo_bits, (unsigned long long*)(d.counts + 1), c->d_status, d.visited);
+    check_launch(c, "scan_join_mark");
 }
 
 Keys ops_semi_filter(xlb_ctx* c, const Keys& bag, int keysel, const Index& ix, bool anti, const uint64_t* pkeys) {
@@ -507,7 +607,7 @@ Keys ops_semi_filter(xlb_ctx* c, const Keys& bag, int keysel, const Index& ix, b
 }
 
 uint64_t ops_expand_bound(const Keys& bag, const Index& ix, int hi_src, int lo_src) {
-    uint64_t other_bound = ix.pay ? 0xFFFFFFFFull : (ix.bound == ~0ull ? 0xFFFFFFFFull : (ix.bound & 0xFFFFFFFFull));
+    uint64_t other_bound = ix.pay ? ix.pay_bound : (ix.bound == ~0ull ? 0xFFFFFFFFull : (ix.bound & 0xFFFFFFFFull));
     return (half_bound(bag.bound, hi_src, other_bound) << 32) | half_bound(bag.bound, lo_src, other_bound);
 }
 
@@ -528,8 +628,8 @@ static Keys join_expand(xlb_ctx* c, const Keys& bag, int keysel, const uint64_t*
         exclusive_scan<LoadLow32, uint64_t>(c, LoadLow32{match->as<uint64_t>()}, bag.n, off->as<uint64_t>(), dense->counts + 1);
         const unsigned grid = (unsigned)c->sm_count * 8;
         prof_begin(c, "expand_mark", bag.n * 24ull);
-        expand_k<true><<<grid, BLOCK, 0, c->stream>>>(bag.ptr(), match->as<uint64_t>(), off->as<uint64_t>(), bag.n, 0, ix.S->as<uint64_t>(), pay, hi_src, lo_src,
-                                                       nullptr, dense->bitmap->as<unsigned int>(), dense->words, dense->lo_bits, c->d_status, dense->counts + 1);
+        expand_k<true><<<grid, BLOCK, 0, c->stream>>>(bag.ptr(), match->as<uint64_t>(), off->as<uint64_t>(), bag.n, 0, ix.S ? ix.S->as<uint64_t>() : nullptr, pay, hi_src, lo_src,
+                                                       nullptr, dense->bitmap->as<unsigned int>(), dense->words, dense->lo_bits, c->d_status, dense->counts + 1, dense->visited);
         check_launch(c, "expand_mark");
         dense->bound |= out.bound;
         return out;
@@ -543,8 +643,8 @@ static Keys join_expand(xlb_ctx* c, const Keys& bag, int keysel, const uint64_t*
     if (tot == 0) return out;
     uint64_t ntiles = (tot + EX_TILE - 1) / EX_TILE;
     prof_begin(c, "expand", tot * 12ull + bag.n * 24ull);
-    expand_k<false><<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(bag.ptr(), match->as<uint64_t>(), off->as<uint64_t>(), bag.n, tot, ix.S->as<uint64_t>(), pay, hi_src, lo_src,
-                                                                out.buf->as<uint64_t>(), nullptr, 0, 0, c->d_status, nullptr);
+    expand_k<false><<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(bag.ptr(), match->as<uint64_t>(), off->as<uint64_t>(), bag.n, tot, ix.S ? ix.S->as<uint64_t>() : nullptr, pay, hi_src, lo_src,
+                                                                out.buf->as<uint64_t>(), nullptr, 0, 0, c->d_status, nullptr, nullptr);
     check_launch(c, "expand");
     return out;
 }

@@ -26,6 +26,12 @@ struct Index {
     uint64_t mask = 0; // capacity - 1
     uint64_t nkeys = 0;
     uint64_t bound = ~0ull;  // OR bound of the rows of S
+    // Direct form (ops_index_build_direct): no S and no table; cursor[k] = end of key k's group in
+    // `pay` for every key below `domain`.
+    Buf cursor;
+    uint64_t domain = 0;
+    uint64_t pay_bound = 0xFFFFFFFFull;  // OR bound of the payload column
+    bool built() const { return S || cursor; }
 };
 
 Keys ops_rel_packed(xlb_ctx* c, const xlb_rel* r);             // packed view (cached on the relation)
@@ -46,7 +52,7 @@ Keys ops_dedup_diff(xlb_ctx* c, const Keys& a, const Keys& b);   // distinct row
 // The same result through a bitmap over a dense domain; `ops_dense_bits` says whether the rows of
 // both arrays fit one (returns false otherwise) and how many low-half bits to keep.
 bool ops_dense_bits(const Keys& a, const Keys& b, int* hi_bits, int* lo_bits);
-Keys ops_dense_novel(xlb_ctx* c, const Keys& cand, const Keys& full, int hi_bits, int lo_bits);
+Keys ops_dense_novel(xlb_ctx* c, const Keys& cand, const Keys& full, int hi_bits, int lo_bits, unsigned int* visited = nullptr);
 // The same in pieces, so that a join can mark its output tuples straight into the bitmap:
 struct DenseSet {
     Buf bitmap;
@@ -57,9 +63,24 @@ struct DenseSet {
     // the marking joins, which stay on the device until ops_dense_finish reads both at once
     uint64_t* counts = nullptr;
     uint64_t marked = 0;  // host copy of counts[1], valid after ops_dense_finish
+    // Optional bitmap (same domain) of the tuples known already: marking skips them, and
+    // ops_dense_finish emits only what it lacks and adds that to it.
+    unsigned int* visited = nullptr;
 };
+// The tuples of one relation as a bitmap that lives across the iterations of a fixpoint, so that
+// no iteration has to subtract the whole relation from its candidates again.
+struct DenseState {
+    Buf visited;
+    uint64_t words = 0;
+    int hi_bits = 0, lo_bits = 0;
+    uint64_t rows = 0;  // tuples marked (the relation's rows plus what the running iteration found)
+    bool valid = false;
+};
+void ops_dense_state_build(xlb_ctx* c, DenseState& s, int hi_bits, int lo_bits, const Keys& full, const Keys& novel);
 DenseSet ops_dense_begin(xlb_ctx* c, int hi_bits, int lo_bits);
-Keys ops_dense_finish(xlb_ctx* c, DenseSet& d, const Keys& full);  // clear `full`, emit the rest in order
+// Emit, in order, the marked tuples that are new: with d.visited those it lacks (which it then
+// gains; `full` is not read), else those not in `full` (cleared from the bitmap first).
+Keys ops_dense_finish(xlb_ctx* c, DenseSet& d, const Keys& full);
 // OR bound of the rows ops_join_expand would produce
 uint64_t ops_expand_bound(const Keys& bag, const Index& ix, int hi_src, int lo_src);
 // ops_join_expand that marks instead of materialising.  No count comes back to the host here:
@@ -72,9 +93,21 @@ Keys ops_remap(xlb_ctx* c, const Keys& in, int hi_src, int lo_src);
 Keys ops_filter(xlb_ctx* c, const Keys& in, uint32_t cmp, int lhs_src, bool rhs_is_const, uint64_t rhs);
 
 Index ops_index_build(xlb_ctx* c, Buf S, uint64_t n, int key_shift, Buf pay);
+// Counting build for keys of at most key_bits bits: rows = packed two-column rows in any order,
+// key = the half named by keysel (SRC_HI / SRC_LO), payload = the other half.
+Index ops_index_build_direct(xlb_ctx* c, const Keys& rows, int keysel, int key_bits);
 // Probe `bag` (key = the half named by keysel, or pkeys[i] when given) and expand every match:
 // out row = (pick(hi_src) << 32) | pick(lo_src) with SRC_OTHER = the build row's payload.
 Keys ops_join_expand(xlb_ctx* c, const Keys& bag, int keysel, const uint64_t* pkeys, const Index& ix, int hi_src, int lo_src);
+// Scan join: the join of `bag` (key = its half keysel) with the stored rows `rel` (key = its half
+// rel_keysel), run from the relation's side.  Only for outputs that take nothing from the bag but
+// the key: rel_hi / rel_lo say what lands in each output half (0 key, 1 the relation's other
+// column, 2 zero).  key_bits = bit length of the bag's keys (at most 27).  Every relation row
+// with a key in the bag is produced once, however often the bag repeats the key.
+uint64_t ops_scan_join_bound(const Keys& bag, int keysel, const Keys& rel, int rel_keysel, int rel_hi, int rel_lo);
+Keys ops_scan_join(xlb_ctx* c, const Keys& bag, int keysel, int key_bits, const Keys& rel, int rel_keysel, int rel_hi, int rel_lo);
+// the same, marking into d (one marking step per DenseSet; count in d.marked after ops_dense_finish)
+void ops_scan_join_mark(xlb_ctx* c, const Keys& bag, int keysel, int key_bits, const Keys& rel, int rel_keysel, int rel_hi, int rel_lo, DenseSet& d);
 // rows of `bag` whose key has (semi) or lacks (anti) a match in the index, in bag order
 // (pkeys, when given, holds the key word of every bag row instead of a half named by keysel)
 Keys ops_semi_filter(xlb_ctx* c, const Keys& bag, int keysel, const Index& ix, bool anti, const uint64_t* pkeys = nullptr);
