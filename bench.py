@@ -151,10 +151,12 @@ def main():
     ap.add_argument("--impl", default="xlb", choices=["xlb", "reference"])
     ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c5"])
     ap.add_argument("--scale", type=int, default=20)
-    ap.add_argument("--kernel", default="radix_scatter", help="kernel whose launches are timed for the roofline object")
+    ap.add_argument("--kernel", default="auto",
+                    help="kernel whose launches are timed for the roofline object (auto: the one with the most device time in the last warm-up step)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (large results)")
     ap.add_argument("--no-clocks", action="store_true", help="do not run nvidia-smi beside the timed region")
+    ap.add_argument("--phases", action="store_true", help="time the executor's phases with events (fills phases_last_step; adds event records to the timed steps)")
     ap.add_argument("--breakdown", action="store_true", help="extra untimed pass with every kernel timed, to stderr")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
@@ -168,6 +170,7 @@ def main():
 
     from xlog_b200.executor import Executor
     from xlog_b200.provider import KernelProvider
+    from xlog_b200 import _abi as A
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -194,7 +197,7 @@ def main():
         a[:] = c[lo:hi]
         host_cols.append(a)
 
-    prov = KernelProvider(device=local)
+    prov = KernelProvider(device=local, flags=A.FLAG_PROFILE if args.phases else 0)
     if world > 1:
         from xlog_b200 import dist as D
         D.init_comm(prov, rank, world, device="cuda")
@@ -231,8 +234,14 @@ def main():
     sampler = ClockSampler(local) if rank == 0 and not args.no_clocks else None
     if sampler:
         time.sleep(1.0)  # let nvidia-smi finish starting up: its first query stalls CUDA calls for milliseconds
-    for _ in range(args.warmup):
+    for w in range(args.warmup):
+        if args.kernel == "auto" and w == args.warmup - 1:
+            prov.profile_enable("*")  # untimed step: find the kernel that dominates this workload
         device_step()
+    if args.kernel == "auto":
+        seen = {k: v for k, v in prov.profile_read().items() if v["bytes"]}
+        prov.profile_enable(None)
+        args.kernel = max(seen, key=lambda k: seen[k]["ms"]) if seen else "radix_scatter"
     prov.profile_enable(args.kernel)
     ms_steps, host_steps, stats = [], [], None
     launches = 0
@@ -301,7 +310,9 @@ def main():
         # DRAM bytes per key of this kernel from the ncu capture summarised in
         # profiles/radix_scatter_sort_16M_keys.md (13.2 B/key against 16 algorithmic), scaled to the
         # keys an average launch of this run processed
-        traffic = (k["bytes"] / k["launches"]) / 16.0 * 13.2 if args.kernel == "radix_scatter" else None
+        # (scan_join_mark: 1.0 of its algorithmic bytes, profiles/scan_join_mark_c2.md)
+        per_alg = {"radix_scatter": 13.2 / 16.0, "scan_join_mark": 1.0}.get(args.kernel)
+        traffic = (k["bytes"] / k["launches"]) * per_alg if per_alg else None
         roof = {"bound": "hbm", "kernel": args.kernel, "achieved": achieved, "peak": peak, "peak_kind": peak_kind,
                 "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
                 "launches": k["launches"], "avg_launch_us": 1e3 * k["ms"] / k["launches"],
@@ -332,6 +343,9 @@ def main():
         "roofline": roof,
         "cpu_baseline": cpu,
         "host_last_step": {k: stats[k] for k in ("host_syncs", "ms_host_wait", "ms_host_total")},
+        # device time per phase in the last step (rank 0; only with XLB_FLAG_PROFILE, else zeros) and exchanged bytes
+        "phases_last_step": {k: round(stats[k], 4) if isinstance(stats[k], float) else stats[k]
+                             for k in ("ms_join", "ms_sort", "ms_setops", "ms_exchange", "exchange_bytes")},
         "host_ms_total_wait_alloc_per_step": host_steps,
     }
     emit(line)

@@ -241,7 +241,11 @@ Keys ops_rel_packed(xlb_ctx* c, const xlb_rel* r) {
         Buf oa = make_buf(c, 8);
         CUDA_OK(cudaMemsetAsync(oa->p, 0, 8, c->stream));
         prof_begin(c, "pack", r->rows * 16ull);
-        if (r->schema.arity == 2) pack2_k<<<grid_for(c, r->rows), BLOCK, 0, c->stream>>>(r->cols[0]->as<uint32_t>(), r->cols[1]->as<uint32_t>(), b->as<uint64_t>(), r->rows, oa->as<unsigned long long>());
+        if (r->schema.arity == 2) {
+            const bool vec = (((uintptr_t)r->cols[0]->p | (uintptr_t)r->cols[1]->p | (uintptr_t)b->p) & 15) == 0;
+            pack2_k<<<grid_for(c, r->rows, BLOCK * 4), BLOCK, 0, c->stream>>>(r->cols[0]->as<uint32_t>(), r->cols[1]->as<uint32_t>(), b->as<uint64_t>(), r->rows,
+                                                                              oa->as<unsigned long long>(), vec);
+        }
         else pack1_k<<<grid_for(c, r->rows), BLOCK, 0, c->stream>>>(r->cols[0]->as<uint32_t>(), b->as<uint64_t>(), r->rows, oa->as<unsigned long long>());
         check_launch(c, "pack");
         unsigned long long h[1];
