@@ -1,0 +1,113 @@
+"""The plan importer (serialized xlog_ir::ExecutionPlan -> plan descriptor) without a GPU: the
+imported plans are evaluated by the CPU oracle and compared with the hand-built ones."""
+import json
+
+import numpy as np
+import pytest
+
+from xlog_b200 import _abi as A
+from xlog_b200 import plan_json as PJ
+from xlog_b200 import programs, workloads
+from xlog_b200.lib import XlbError
+from xlog_b200.plan import Filter, Join, Project, Scan
+
+# reach(X,Y) :- edge(X,Y).  reach(X,Z) :- reach(X,Y), edge(Y,Z).   as serde would print it: the
+# recursive body promoted to a ChainJoin whose fallback is the plain Join/Project tree, RirMeta
+# carried along, strata given
+TC_JSON = """
+{"sccs": [{"id": 0, "predicates": ["reach"], "is_recursive": true}],
+ "strata": [{"id": 0, "sccs": [0]}],
+ "rules_by_scc": [[
+   {"head": "reach", "body": {"Scan": {"rel": 0}}, "meta": {"est_rows": 3, "est_bytes": 24}},
+   {"head": "reach",
+    "body": {"ChainJoin": {"left": {"Scan": {"rel": 1}}, "right": {"Scan": {"rel": 0}}, "left_key": 1, "right_key": 0,
+                           "output_columns": [{"Column": 0}, {"Column": 3}],
+                           "fallback": {"Project": {"input": {"Join": {"left": {"Scan": {"rel": 1}}, "right": {"Scan": {"rel": 0}},
+                                                                        "left_keys": [1], "right_keys": [0], "join_type": "Inner"}},
+                                                    "columns": [{"Column": 0}, {"Column": 3}]}}}},
+    "meta": {"est_rows": 9, "est_bytes": 72}}]],
+ "generated_query_rules": [], "est_memory_peak": 0,
+ "rel_arities": {"0": 2, "1": 2}}
+"""
+
+
+def test_transitive_closure_known_answer(oracle):
+    plan = PJ.plan_from_json(TC_JSON, rel_names={0: "edge", 1: "reach"})
+    edge = [np.array([1, 2, 3], np.uint32), np.array([2, 3, 4], np.uint32)]
+    out, _ = oracle.run_program(plan, {"edge": edge}, ["reach"])
+    assert list(zip(*[c.tolist() for c in out["reach"]])) == [(1, 2), (1, 3), (1, 4), (2, 3), (2, 4), (3, 4)]
+    assert plan.sccs[0].is_recursive and plan.rel_ids == {"edge": 0, "reach": 1}
+    assert isinstance(plan.sccs[0].rules[1].body, Project)      # the ChainJoin's fallback tree
+
+
+@pytest.mark.parametrize("builder", [programs.transitive_closure, programs.transitive_closure_left_linear,
+                                     programs.transitive_closure_nonlinear, programs.transitive_closure_swapped_head,
+                                     programs.reach_from_source, programs.same_generation, programs.andersen,
+                                     programs.points_to_copy, programs.unreachable_nodes])
+def test_every_program_round_trips(builder):
+    plan = builder()
+    back = PJ.plan_from_json(PJ.plan_to_json(plan))
+    assert back.rel_ids == plan.rel_ids and len(back.sccs) == len(plan.sccs)
+    for a, b in zip(back.sccs, plan.sccs):
+        assert (a.id, bool(a.is_recursive)) == (b.id, bool(b.is_recursive))
+        assert [(r.head, r.body, tuple(r.head_types)) for r in a.rules] == [(r.head, r.body, tuple(r.head_types)) for r in b.rules]
+
+
+def test_imported_program_gives_the_same_fixpoint(oracle):
+    c0, c1, _ = workloads.tree_dag(300, 0.05, 5)
+    plan = programs.same_generation()
+    want, _ = oracle.run_program(plan, {"edge": [c0, c1]}, ["sg"])
+    got, _ = oracle.run_program(PJ.plan_from_json(PJ.plan_to_json(plan)), {"edge": [c0, c1]}, ["sg"])
+    assert all(np.array_equal(g, w) for g, w in zip(got["sg"], want["sg"]))
+
+
+def test_filters_constants_and_conjunctions():
+    pred = {"And": [{"Compare": {"left": {"Const": {"U32": 5}}, "op": "Lt", "right": {"Column": 1}}},
+                    {"Compare": {"left": {"Column": 0}, "op": "Ne", "right": {"Column": 1}}}]}
+    node = PJ.node_from_json({"Filter": {"input": {"Scan": {"rel": 3}}, "predicate": pred}})
+    # 5 < c1  is  c1 > 5; the conjunction nests
+    assert node == Filter(Filter(Scan(3), A.GT, 1, 5, True), A.NE, 0, 1, False)
+    semi = PJ.node_from_json({"Join": {"left": {"Scan": {"rel": 0}}, "right": {"Scan": {"rel": 1}}, "left_keys": [0],
+                                      "right_keys": [0], "join_type": "Anti"}})
+    assert semi == Join(Scan(0), Scan(1), [0], [0], A.JOIN_ANTI)
+
+
+def test_strata_order_is_the_evaluation_order():
+    doc = json.loads(PJ.plan_to_json(programs.unreachable_nodes()))
+    ids = [s["id"] for s in doc["sccs"]]
+    assert len(ids) >= 2
+    # list the SCCs in reverse, keep the strata: the importer follows the strata
+    doc["sccs"].reverse()
+    doc["rules_by_scc"].reverse()
+    plan = PJ.plan_from_json(doc)
+    assert [s.id for s in plan.sccs] == ids
+
+
+@pytest.mark.parametrize("body,what", [
+    ({"GroupBy": {"input": {"Scan": {"rel": 0}}, "key_cols": [0], "aggs": []}}, "RirNode::GroupBy"),
+    ({"Project": {"input": {"Scan": {"rel": 0}}, "columns": [{"Computed": [{"Column": 0}, "U32"]}]}}, "ProjectExpr::Computed"),
+    ({"Filter": {"input": {"Scan": {"rel": 0}}, "predicate": {"Not": {"Column": 0}}}}, "Expr::Not"),
+    ({"Join": {"left": {"Scan": {"rel": 0}}, "right": {"Scan": {"rel": 0}}, "left_keys": [0], "right_keys": [0],
+               "join_type": "LeftOuter"}}, "JoinType::LeftOuter"),
+    ({"Filter": {"input": {"Scan": {"rel": 0}}, "predicate": {"Compare": {"left": {"Column": 0}, "op": "Eq",
+                                                                       "right": {"Const": {"Symbol": "a"}}}}}}, "Symbol constant"),
+])
+def test_constructs_outside_the_subset_are_named(body, what):
+    with pytest.raises(XlbError, match=what.replace("::", "::")) as e:
+        PJ.node_from_json(body)
+    assert e.value.status == A.ERR_UNSUPPORTED
+
+
+def test_malformed_documents_are_errors():
+    with pytest.raises(XlbError, match="rel_names"):
+        PJ.plan_from_json(TC_JSON)
+    with pytest.raises(XlbError, match="same length"):
+        PJ.plan_from_json({"sccs": [], "rules_by_scc": [[]]}, rel_names={0: "e"})
+    bad = json.loads(TC_JSON)
+    bad["strata"] = [{"id": 0, "sccs": [7]}]
+    with pytest.raises(XlbError, match="unknown SCC 7"):
+        PJ.plan_from_json(bad, rel_names={0: "edge", 1: "reach"})
+    bad = json.loads(TC_JSON)
+    bad["rules_by_scc"][0][0]["head"] = "nobody"
+    with pytest.raises(XlbError, match="no RelId"):
+        PJ.plan_from_json(bad, rel_names={0: "edge", 1: "reach"})
