@@ -155,6 +155,17 @@ xlb_status xlb_union(xlb_ctx* ctx, const xlb_rel* const* ins, uint32_t n, xlb_re
 /* diff_gpu (relational.rs:1102): a \ b with set semantics on full rows; sorted, unique. */
 xlb_status xlb_diff(xlb_ctx* ctx, const xlb_rel* a, const xlb_rel* b, xlb_rel** out);
 
+/* AggOp (crates/xlog-ir/src/rir.rs).  Built here: count, sum, min, max. */
+typedef enum xlb_agg_op { XLB_AGG_COUNT = 0, XLB_AGG_SUM = 1, XLB_AGG_MIN = 2, XLB_AGG_MAX = 3 } xlb_agg_op;
+
+/* groupby_multi_agg (crates/xlog-cuda/src/provider/groupby.rs:66): one row per distinct value of
+ * the key columns (u32, symbol or u64; ascending), the key columns first, then one column per
+ * (agg_cols[i], agg_ops[i]) in the order given.  Count and sum columns are u64; min and max keep
+ * the width of their value column (u32 or u64 values).  An empty input gives an empty relation of
+ * the output schema; no key column or no aggregation is XLB_ERR_INVALID. */
+xlb_status xlb_groupby(xlb_ctx* ctx, const xlb_rel* in, const uint32_t* key_cols, uint32_t n_keys,
+                       const uint32_t* agg_cols, const uint32_t* agg_ops, uint32_t n_aggs, xlb_rel** out);
+
 /* ---- plans: the subset of RirNode the fixpoint path uses (crates/xlog-ir/src/rir.rs:339-541) - */
 
 typedef enum xlb_node_kind {

@@ -185,6 +185,38 @@ def diff(a, b):
     return a._like(lib().xo_diff(a._h, b._h))
 
 
+def groupby_columns(cols, key_cols, aggs):
+    """groupby_multi_agg on host columns (crates/xlog-cuda/src/provider/groupby.rs:66-819): one row
+    per distinct key, ascending by key; key columns, then per (value column, op) with op 0 count,
+    1 sum, 2 min, 3 max: count and sum as u64, min and max in the width of the value column.
+    Plain numpy: lexicographic sort of the key columns, boundaries, ``reduceat``."""
+    cols = [np.asarray(c) for c in cols]
+    n = len(cols[0]) if cols else 0
+    out_types = [cols[k].dtype for k in key_cols] + [np.dtype(np.uint64) if op in (0, 1) else (np.dtype(np.uint64) if cols[v].dtype == np.uint64 else np.dtype(np.uint32)) for v, op in aggs]
+    if n == 0:
+        return [np.zeros(0, dtype=t) for t in out_types]
+    order = np.lexsort([cols[k] for k in reversed(list(key_cols))])
+    keys = [cols[k][order] for k in key_cols]
+    head = np.ones(n, dtype=bool)
+    head[1:] = np.zeros(n - 1, dtype=bool)
+    for k in keys:
+        head[1:] |= k[1:] != k[:-1]
+    starts = np.flatnonzero(head)
+    out = [k[starts] for k in keys]
+    for (v, op), t in zip(aggs, out_types[len(key_cols):]):
+        vals = cols[v][order].astype(np.uint64)
+        if op == 0:
+            r = np.diff(np.append(starts, n)).astype(np.uint64)
+        elif op == 1:
+            r = np.add.reduceat(vals, starts)          # wraps modulo 2^64 like the device sum
+        elif op == 2:
+            r = np.minimum.reduceat(vals, starts)
+        else:
+            r = np.maximum.reduceat(vals, starts)
+        out.append(r.astype(t))
+    return out
+
+
 def hash_join(l, r, lk, rk, join_type=0):
     dt = (l.dtypes or []) + (r.dtypes or []) if join_type == 0 else l.dtypes
     return OracleRel(lib().xo_hash_join(l._h, r._h, _u32s(lk), _u32s(rk), len(lk), join_type), dt)

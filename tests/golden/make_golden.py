@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Writes tests/golden/operators.json and tests/golden/programs.json.
+"""Writes tests/golden/operators.json, tests/golden/programs.json and tests/golden/groupby.json.
 
 Every case is a known-answer test transcribed from the reference's own test suite (cited per
 case by path inside the reference project).  Operator cases carry the literal inputs and the
@@ -22,6 +22,7 @@ FR = "crates/xlog-cuda/tests/test_full_row_set_algebra.rs"
 JV = "crates/xlog-cuda/tests/join_v2_tests.rs"
 JC = "crates/xlog-cuda/tests/join_collision_test.rs"
 ST = "crates/xlog-cuda/tests/sort_tests.rs"
+GB = "crates/xlog-cuda/tests/groupby_tests.rs"
 
 
 def rows1(xs):
@@ -261,9 +262,34 @@ def novel_step():
             "expected_source": "set comprehension restating oracle_novel_step (" + SPIKE + ":159-180)"}
 
 
+def groupby():
+    """Literal inputs and asserted outputs of the reference's group-by tests.  `aggs`: (value
+    column, op) with op in count / sum / min / max; expected columns = keys, then aggregates."""
+    c = []
+
+    def add(cite, cols, keys, aggs, expected, types=None):
+        c.append({"cite": cite, "types": types or ["u32"] * len(cols), "cols": cols, "keys": keys, "aggs": aggs, "expected": expected})
+
+    kv = [[1, 1, 2, 2, 2], [10, 20, 5, 15, 25]]
+    add(GB + ":19-53", kv, [0], [[1, "count"]], [[1, 2], [2, 3]])
+    add(GB + ":56-89", kv, [0], [[1, "sum"]], [[1, 2], [30, 45]])
+    add(GB + ":92-123", kv, [0], [[1, "min"]], [[1, 2], [10, 5]])
+    add(GB + ":124-135", kv, [0], [[1, "max"]], [[1, 2], [20, 25]])
+    add(GB + ":138-188", kv, [0], [[1, "sum"], [1, "count"], [1, "min"], [1, "max"]], [[1, 2], [30, 45], [2, 3], [10, 5], [20, 25]])
+    add(GB + ":191-209", [[], []], [0], [[1, "sum"]], [[], []])
+    add(GB + ":212-244", [[5, 5, 5, 5], [10, 20, 30, 40]], [0], [[1, "sum"], [1, "count"]], [[5], [100], [4]])
+    add(GB + ":247-281", [[2, 1, 2, 1, 2], [5, 10, 15, 20, 25]], [0], [[1, "sum"]], [[1, 2], [30, 45]])
+    add(GB + ":284-317", [[1, 1, 2, 2], [10, 10, 20, 20], [5, 7, 11, 13]], [0, 1], [[2, "sum"]], [[1, 2], [10, 20], [12, 24]])
+    add(GB + ":331-367", [[5, 3, 1, 4, 2], [50, 30, 10, 40, 20]], [0], [[1, "sum"], [1, "count"]],
+        [[1, 2, 3, 4, 5], [10, 20, 30, 40, 50], [1, 1, 1, 1, 1]])
+    return c
+
+
 if __name__ == "__main__":
+    with open(os.path.join(HERE, "groupby.json"), "w") as f:
+        json.dump(groupby(), f, separators=(",", ":"))
     with open(os.path.join(HERE, "operators.json"), "w") as f:
         json.dump(operators(), f, separators=(",", ":"))
     with open(os.path.join(HERE, "programs.json"), "w") as f:
         json.dump({"programs": programs(), "novel_step": novel_step()}, f, separators=(",", ":"))
-    print("wrote operators.json, programs.json")
+    print("wrote operators.json, programs.json, groupby.json")

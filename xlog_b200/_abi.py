@@ -17,6 +17,8 @@ STATUS_NAMES = ["OK", "INVALID", "TYPE", "RESOURCE_EXHAUSTED", "CAPACITY", "ITER
 U32, U64, I32, I64, F32, F64, BOOL, SYMBOL = range(8)
 # xlb_join_type
 JOIN_INNER, JOIN_SEMI, JOIN_ANTI = range(3)
+# xlb_agg_op (AggOp, crates/xlog-ir/src/rir.rs)
+AGG_COUNT, AGG_SUM, AGG_MIN, AGG_MAX = range(4)
 # xlb_node_kind
 NODE_SCAN, NODE_FILTER, NODE_PROJECT, NODE_JOIN, NODE_UNION = 1, 2, 3, 4, 5
 # xlb_cmp

@@ -55,6 +55,55 @@ __device__ __forceinline__ bool rows_equal(const ColSet& cs, uint64_t a, uint64_
     }
     return true;
 }
+// Segmented reduction for group-by over rows sorted by key.  heads[g] = first row of group g.
+// A thread walks GB_ITEMS consecutive rows and hands a group's partial result over with one atomic
+// when the group changes, so a group of any size costs at most one atomic per GB_ITEMS of its
+// rows.  vals: the value column in sorted order (null for a count); out: one u64 per group, set to
+// the operator's identity beforehand.
+constexpr int GB_ITEMS = 8;
+template <class V>
+__global__ void groupby_reduce_k(const V* __restrict__ vals, const uint32_t* __restrict__ heads, uint64_t m, uint64_t n, int op,
+                                 unsigned long long* __restrict__ out) {
+    const unsigned long long ident = op == XLB_AGG_MIN ? ~0ull : 0ull;
+    auto flush = [&](uint64_t g, unsigned long long acc) {
+        if (op == XLB_AGG_MIN) atomicMin(&out[g], acc);
+        else if (op == XLB_AGG_MAX) atomicMax(&out[g], acc);
+        else if (acc) atomicAdd(&out[g], acc);
+    };
+    for (uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; t * GB_ITEMS < n; t += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t first = t * GB_ITEMS, last = first + GB_ITEMS < n ? first + GB_ITEMS : n;
+        // group of the first row: the last head at or before it
+        uint64_t lo = 0, hi = m;
+        while (lo < hi) {
+            uint64_t mid = (lo + hi) >> 1;
+            if (heads[mid] <= first) lo = mid + 1;
+            else hi = mid;
+        }
+        uint64_t g = lo - 1;
+        uint64_t next = g + 1 < m ? heads[g + 1] : n;
+        unsigned long long acc = ident;
+        for (uint64_t i = first; i < last; ++i) {
+            if (i == next) {
+                flush(g, acc);
+                acc = ident;
+                ++g;
+                next = g + 1 < m ? heads[g + 1] : n;
+            }
+            unsigned long long v = op == XLB_AGG_COUNT ? 1ull : (unsigned long long)vals[i];
+            if (op == XLB_AGG_MIN) acc = v < acc ? v : acc;
+            else if (op == XLB_AGG_MAX) acc = v > acc ? v : acc;
+            else acc += v;
+        }
+        flush(g, acc);
+    }
+}
+__global__ void fill_u64_k(unsigned long long* out, uint64_t n, unsigned long long v) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) out[i] = v;
+}
+__global__ void narrow_u64_k(const unsigned long long* in, uint32_t* out, uint64_t n) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) out[i] = (uint32_t)in[i];
+}
+
 struct PredRowHead {
     ColSet cs;
     __device__ __forceinline__ bool operator()(uint64_t i) const { return i == 0 || !rows_equal(cs, i, i - 1); }
@@ -1257,6 +1306,90 @@ extern "C" xlb_status xlb_diff(xlb_ctx* c, const xlb_rel* a, const xlb_rel* b, x
     if (!c || !a || !b || !out) return XLB_ERR_INVALID;
     const xlb_rel* both[2] = {a, b};
     return with_typed(c, both, 2, out, [&](const xlb_rel* const* v, xlb_rel** o) { return diff_unsigned(c, v[0], v[1], o); });
+}
+
+// groupby_multi_agg (crates/xlog-cuda/src/provider/groupby.rs:66-770): sort by the key columns,
+// find the group boundaries, reduce every aggregate per group.  Output: key columns, then one
+// column per aggregate in the order given; one row per group, ascending by key.
+extern "C" xlb_status xlb_groupby(xlb_ctx* c, const xlb_rel* in, const uint32_t* key_cols, uint32_t nk, const uint32_t* agg_cols, const uint32_t* agg_ops,
+                                  uint32_t na, xlb_rel** out) {
+    if (!c || !in || !out) return XLB_ERR_INVALID;
+    API_BEGIN(c)
+    if (nk == 0 || !key_cols) xlb_fail(XLB_ERR_INVALID, "GroupBy requires at least one key column");
+    if (na == 0 || !agg_cols || !agg_ops) xlb_fail(XLB_ERR_INVALID, "GroupBy requires at least one aggregation");
+    if (nk + na > XLB_MAX_ARITY) xlb_fail(XLB_ERR_UNSUPPORTED, "GroupBy output arity above %u", XLB_MAX_ARITY);
+    xlb_schema os{};
+    for (uint32_t i = 0; i < nk; ++i) {
+        if (key_cols[i] >= in->schema.arity) xlb_fail(XLB_ERR_INVALID, "Key column %u out of bounds (arity %u)", key_cols[i], in->schema.arity);
+        uint8_t t = in->schema.types[key_cols[i]];
+        if (!type_unsigned(t)) xlb_fail(XLB_ERR_TYPE, "GroupBy keys must be u32, symbol or u64 columns");
+        os.types[os.arity++] = t;
+    }
+    for (uint32_t i = 0; i < na; ++i) {
+        if (agg_cols[i] >= in->schema.arity) xlb_fail(XLB_ERR_INVALID, "Value column %u out of bounds (arity %u)", agg_cols[i], in->schema.arity);
+        if (agg_ops[i] > XLB_AGG_MAX) xlb_fail(XLB_ERR_UNSUPPORTED, "aggregation %u is not built (count, sum, min, max are)", agg_ops[i]);
+        uint8_t vt = in->schema.types[agg_cols[i]];
+        if (agg_ops[i] != XLB_AGG_COUNT && vt != XLB_U32 && vt != XLB_U64)
+            xlb_fail(XLB_ERR_TYPE, "%s currently requires U32 or U64 values", agg_ops[i] == XLB_AGG_SUM ? "Sum" : agg_ops[i] == XLB_AGG_MIN ? "Min" : "Max");
+        // count and sum are u64; min and max keep the width of the value column (groupby.rs:799-811)
+        os.types[os.arity++] = (agg_ops[i] == XLB_AGG_COUNT || agg_ops[i] == XLB_AGG_SUM) ? XLB_U64 : (vt == XLB_U64 ? XLB_U64 : XLB_U32);
+    }
+    if (in->rows == 0) {
+        *out = rel_empty(c, os);
+        (*out)->canonical = false;
+    } else {
+        if (in->rows > 0xFFFFFFFFull) xlb_fail(XLB_ERR_CAPACITY, "GroupBy supports at most %u rows, got %llu", 0xFFFFFFFFu, (unsigned long long)in->rows);
+        ops_rel_columns(c, in);
+        const uint64_t n = in->rows;
+        Buf idx = sort_permutation(c, in, key_cols, nk);
+        // the key columns in sorted order, then the first row of every group
+        xlb_rel keys_only;
+        keys_only.ctx = c;
+        keys_only.rows = n;
+        for (uint32_t i = 0; i < nk; ++i) {
+            keys_only.schema.types[i] = in->schema.types[key_cols[i]];
+            keys_only.cols[i] = in->cols[key_cols[i]];
+        }
+        keys_only.schema.arity = nk;
+        std::unique_ptr<xlb_rel> ksorted(gather_rel(c, &keys_only, idx->as<uint32_t>(), n));
+        Buf heads = make_buf(c, n * 4);
+        const uint64_t m = select(c, PredRowHead{colset_of(ksorted.get())}, EmitIndex{heads->as<uint32_t>()}, n);
+        std::unique_ptr<xlb_rel> o(gather_rel(c, ksorted.get(), heads->as<uint32_t>(), m));
+        o->schema = os;
+        for (uint32_t a = 0; a < na; ++a) {
+            const uint32_t vc = agg_cols[a], op = agg_ops[a];
+            const uint32_t vw = type_width(in->schema.types[vc]);
+            Buf acc = make_buf(c, m * 8);
+            fill_u64_k<<<grid_for(c, m), BLOCK, 0, c->stream>>>(acc->as<unsigned long long>(), m, op == XLB_AGG_MIN ? ~0ull : 0ull);
+            check_launch(c, "groupby_fill");
+            const unsigned grid = grid_for(c, (n + GB_ITEMS - 1) / GB_ITEMS);
+            prof_begin(c, "groupby_reduce", n * (op == XLB_AGG_COUNT ? 0ull : vw) + m * 12ull);
+            if (op == XLB_AGG_COUNT) {
+                groupby_reduce_k<uint32_t><<<grid, BLOCK, 0, c->stream>>>(nullptr, heads->as<uint32_t>(), m, n, (int)op, acc->as<unsigned long long>());
+            } else if (vw == 4) {
+                Buf vs = make_buf(c, n * 4);
+                gather_k<uint32_t><<<grid_for(c, n), BLOCK, 0, c->stream>>>(in->cols[vc]->as<uint32_t>(), idx->as<uint32_t>(), vs->as<uint32_t>(), n);
+                groupby_reduce_k<uint32_t><<<grid, BLOCK, 0, c->stream>>>(vs->as<uint32_t>(), heads->as<uint32_t>(), m, n, (int)op, acc->as<unsigned long long>());
+            } else {
+                Buf vs = make_buf(c, n * 8);
+                gather_k<uint64_t><<<grid_for(c, n), BLOCK, 0, c->stream>>>(in->cols[vc]->as<uint64_t>(), idx->as<uint32_t>(), vs->as<uint64_t>(), n);
+                groupby_reduce_k<uint64_t><<<grid, BLOCK, 0, c->stream>>>(vs->as<uint64_t>(), heads->as<uint32_t>(), m, n, (int)op, acc->as<unsigned long long>());
+            }
+            check_launch(c, "groupby_reduce");
+            if (os.types[nk + a] == XLB_U64) {
+                o->cols[nk + a] = acc;
+            } else {
+                Buf narrow = make_buf(c, m * 4);
+                narrow_u64_k<<<grid_for(c, m), BLOCK, 0, c->stream>>>(acc->as<unsigned long long>(), narrow->as<uint32_t>(), m);
+                check_launch(c, "groupby_narrow");
+                o->cols[nk + a] = narrow;
+            }
+        }
+        o->canonical = false;
+        *out = o.release();
+        CUDA_OK(cudaStreamSynchronize(c->stream));
+    }
+    API_END()
 }
 
 // key word per row for a join side; two 32-bit key columns fuse into one word

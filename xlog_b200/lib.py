@@ -36,6 +36,8 @@ PROTOTYPES = {
     "xlb_dedup": (C.c_int, [P, P, U32P, C.c_uint32, C.POINTER(P)]),
     "xlb_union": (C.c_int, [P, C.POINTER(P), C.c_uint32, C.POINTER(P)]),
     "xlb_diff": (C.c_int, [P, P, P, C.POINTER(P)]),
+    "xlb_groupby": (C.c_int, [P, P, C.POINTER(C.c_uint32), C.c_uint32, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32), C.c_uint32,
+                              C.POINTER(P)]),
     "xlb_register_relation": (C.c_int, [P, C.c_uint32, C.c_char_p]),
     "xlb_store_put": (C.c_int, [P, C.c_char_p, P]),
     "xlb_store_get": (C.c_int, [P, C.c_char_p, C.POINTER(P)]),

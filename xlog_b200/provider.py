@@ -169,6 +169,16 @@ class KernelProvider:
 
     diff_full_row = diff_gpu
 
+    def groupby_multi_agg(self, buf: Buffer, key_cols, aggs) -> Buffer:
+        """``aggs``: (value column, A.AGG_*) pairs.  Key columns, then one column per aggregate;
+        one row per group, ascending by key (provider/groupby.rs:66)."""
+        aggs = list(aggs)
+        return self._out(self._lib.xlb_groupby, buf._h, _u32s(key_cols), len(key_cols), _u32s([a[0] for a in aggs]),
+                         _u32s([a[1] for a in aggs]), len(aggs))
+
+    def groupby_agg(self, buf: Buffer, key_cols, agg: int, value_col: int) -> Buffer:
+        return self.groupby_multi_agg(buf, key_cols, [(value_col, agg)])
+
     def memory_stats(self) -> tuple[int, int]:
         a, p = C.c_uint64(), C.c_uint64()
         self._check(self._lib.xlb_memory_stats(self._ctx, C.byref(a), C.byref(p)))
