@@ -307,10 +307,10 @@ def main():
     k = prof.get(args.kernel)
     if k and k["ms"] > 0 and k["launches"]:
         achieved = k["bytes"] / (k["ms"] / 1e3) / 1e9
-        # DRAM bytes per key of this kernel from the ncu capture summarised in
-        # profiles/radix_scatter_sort_16M_keys.md (13.2 B/key against 16 algorithmic), scaled to the
-        # keys an average launch of this run processed
-        # (scan_join_mark: 1.0 of its algorithmic bytes, profiles/scan_join_mark_c2.md)
+        # DRAM bytes per launch: ncu captures of these kernels measured 13.2 B per key against 16
+        # algorithmic for one radix pass over 16 M keys, and 1.0 x the algorithmic bytes for the
+        # scan join over the 16 M edge rows; both grow with the rows of a launch, so they are
+        # scaled to the rows an average launch of this run processed
         per_alg = {"radix_scatter": 13.2 / 16.0, "scan_join_mark": 1.0}.get(args.kernel)
         traffic = (k["bytes"] / k["launches"]) * per_alg if per_alg else None
         roof = {"bound": "hbm", "kernel": args.kernel, "achieved": achieved, "peak": peak, "peak_kind": peak_kind,

@@ -5,7 +5,7 @@ CUDA events (xlb_profile_enable) and reported against its algorithmic bytes.
   python -m xlog_b200.microbench setops --rows 32000000 --bits 24
   python -m xlog_b200.microbench join  --rows 16000000 --bits 20 --probe 4000000
 
-These are the small cases the ncu captures under profiles/ run; the figures the benchmark
+These are the small cases that ncu captures of single kernels run; the figures the benchmark
 reports come from bench.py.
 """
 from __future__ import annotations
