@@ -87,6 +87,11 @@ typedef struct xlb_config {
 #define XLB_FLAG_NO_DENSE 2u       /* never take the bitmap route for small dense domains (the kill
                                       switch the reference gives its factorized routes,
                                       XLOG_DISABLE_FACTORIZED_DELTA)                                 */
+#define XLB_FLAG_KEEP_DELTAS 4u    /* when a recursive SCC stops at the iteration limit, leave its
+                                      delta relations in the store under "__delta_<head>" so that
+                                      the state (full, delta) can be saved; a later
+                                      xlb_execute_plan that finds the delta of every head of an SCC
+                                      in the store resumes that SCC from them instead of seeding it */
 
 
 /* ---- context ------------------------------------------------------------------------------ */

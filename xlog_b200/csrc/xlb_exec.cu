@@ -893,7 +893,27 @@ static void run_scc(xlb_ctx* c, const xlb_scc& scc, RunState& rs) {
         }
     }
 
-    seed_pass(c, rules, preds, rec, schema, home, scc.is_recursive != 0, rs);
+    // Resume: the caller restored (full, delta) of every head of this SCC, as left behind by a run
+    // that stopped at the iteration limit with XLB_FLAG_KEEP_DELTAS.  The seed pass is then
+    // skipped: its tuples are in `full` already, and the deltas say where the loop stood.
+    bool resume = scc.is_recursive != 0;
+    for (auto& p : preds) {
+        xlb_rel* d = store_get(c, "__delta_" + p);
+        if (!d || !rel_packable(d->schema) || d->schema.arity != schema[p].arity) resume = false;
+    }
+    if (resume) {
+        for (auto& p : preds) {
+            // both are handed to the loop as it keeps them: sorted and unique
+            for (const std::string& name : {p, "__delta_" + p}) {
+                xlb_rel* r = store_get(c, name);
+                if (r->canonical) continue;
+                Keys k = canonical_keys(c, r, rs);
+                store_put(c, name, ops_rel_from_keys(c, schema[p], k, true));
+            }
+        }
+    } else {
+        seed_pass(c, rules, preds, rec, schema, home, scc.is_recursive != 0, rs);
+    }
     if (!scc.is_recursive) return;
 
     bool fix = false;
@@ -939,6 +959,7 @@ static void run_scc(xlb_ctx* c, const xlb_scc& scc, RunState& rs) {
         }
     }
     for (auto& p : preds) {  // :940-945
+        if (!fix && (c->flags & XLB_FLAG_KEEP_DELTAS)) break;  // left for a checkpoint
         auto it = c->store.find("__delta_" + p);
         if (it != c->store.end()) {
             delete it->second;
