@@ -52,3 +52,19 @@ def test_fixpoint_from_arrow_inputs_to_arrow_output(provider, oracle, tmp_path):
 def test_missing_file_is_reported(provider, tmp_path):
     with pytest.raises(XlbError, match="Failed to read Arrow IPC stream from"):
         AIO.read_arrow_ipc_stream_file(provider, tmp_path / "nothing.arrow")
+
+
+def test_imported_plan_runs_on_the_gpu(oracle):
+    # the caller side: a serialized plan (as the reference's planner would print it) drives the executor
+    from test_plan_json_cpu import TC_JSON
+    from xlog_b200 import plan_json as PJ
+    from xlog_b200.executor import run_program
+    from xlog_b200.provider import KernelProvider
+    plan = PJ.plan_from_json(TC_JSON, rel_names={0: "edge", 1: "reach"})
+    c0, c1 = workloads.uniform_digraph(150, 400, 9)
+    fresh = KernelProvider(device=0)      # its own store: `reach` must start empty
+    got, stats = run_program(fresh, plan, {"edge": [c0, c1]}, ["reach"])
+    fresh.close()
+    want, ex = oracle.run_program(programs.transitive_closure(), {"edge": [c0, c1]}, ["reach"])
+    assert all(np.array_equal(g, w) for g, w in zip(got["reach"], want["reach"]))
+    assert stats["candidate_tuples"] == ex.candidates

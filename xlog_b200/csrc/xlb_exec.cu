@@ -242,6 +242,14 @@ struct Flattener {
 struct RunState {
     xlb_run_stats st{};
     std::map<std::string, DenseState> dense;  // per head relation: its tuples as a bitmap, while they fit one
+    // Deltas of a head whose merge into the stored sorted list is put off: while the bitmap serves
+    // the set difference and no rule reads the list, merging it every iteration is wasted work.
+    struct Pending {
+        std::vector<Keys> deltas;
+        uint64_t rows = 0, bound = 0;
+    };
+    std::map<std::string, Pending> pending;
+    std::map<std::string, xlb_schema> head_schema;
     std::map<std::pair<std::string, int>, int> scans;  // scan joins run so far per (relation, key column)
 };
 
@@ -438,6 +446,46 @@ struct DenseSink {
     }
 };
 
+static void install_full(xlb_ctx* c, const std::string& pred, const xlb_schema& hs, const Keys& full_new, const Keys* delta, RunState& rs);
+
+// Row count and OR bound of a head relation with the deltas whose merge is put off; the buffer is
+// the stored list, which lacks them: read it only through real_full.
+static Keys full_view(xlb_ctx* c, RunState& rs, const std::string& head) {
+    Keys k = ops_rel_packed(c, store_get(c, head));
+    auto it = rs.pending.find(head);
+    if (it != rs.pending.end() && it->second.rows) {
+        k.bound = (k.n ? k.bound : 0) | it->second.bound;
+        k.n += it->second.rows;
+    }
+    return k;
+}
+
+// Bring the stored list of `head` up to date: read it off the bitmap when that holds exactly the
+// relation, else merge the deltas in.
+static void materialize_full(xlb_ctx* c, RunState& rs, const std::string& head) {
+    auto it = rs.pending.find(head);
+    if (it == rs.pending.end() || it->second.rows == 0) return;
+    RunState::Pending pd = std::move(it->second);
+    rs.pending.erase(it);
+    PhaseTimer t(c, &rs.st.ms_setops);
+    Keys full = ops_rel_packed(c, store_get(c, head));
+    const DenseState& ds = rs.dense[head];
+    Keys merged;
+    if (ds.valid && ds.rows == full.n + pd.rows) {
+        merged = ops_dense_state_rows(c, ds, (full.n ? full.bound : 0) | pd.bound);
+    } else {
+        Keys acc = pd.deltas[0];
+        for (size_t i = 1; i < pd.deltas.size(); ++i) acc = ops_merge_disjoint(c, acc, pd.deltas[i]);
+        merged = full.n ? ops_merge_disjoint(c, full, acc) : acc;
+    }
+    install_full(c, head, rs.head_schema[head], merged, nullptr, rs);
+}
+
+static Keys real_full(xlb_ctx* c, RunState& rs, const std::string& head) {
+    materialize_full(c, rs, head);
+    return ops_rel_packed(c, store_get(c, head));
+}
+
 // The bitmap of `head` = full + novel over a domain of at least (hb, lb) bits, built or rebuilt
 // when it is missing, too narrow, or out of step with the rows (a route that does not keep it up
 // to date has added tuples).
@@ -449,7 +497,7 @@ static DenseState* dense_state(xlb_ctx* c, RunState& rs, const std::string& head
         nh = std::max(hb, ds.hi_bits);
         nl = std::max(lb, ds.lo_bits);
     }
-    ops_dense_state_build(c, ds, nh, nl, full, novel);
+    ops_dense_state_build(c, ds, nh, nl, real_full(c, rs, head), novel);  // (`full` may be a view: its list is read here)
     return &ds;
 }
 
@@ -752,7 +800,7 @@ static void eval_variant(xlb_ctx* c, const FlatRule& fr_in, size_t start, const 
                 ops_sort(c, cand, /*keep_input=*/cand.buf == start_rows.buf);  // a single-atom body hands over a stored relation
             }
             PhaseTimer t(c, &rs.st.ms_setops);
-            fresh = ops_dedup_diff(c, cand, full);  // duplicates dropped and `full` subtracted in one merge pass
+            fresh = ops_dedup_diff(c, cand, real_full(c, rs, fr.head));  // duplicates dropped and `full` subtracted in one merge pass
         }
         PhaseTimer t2(c, &rs.st.ms_setops);
         novel = novel.n ? ops_union(c, novel, fresh) : fresh;
@@ -882,6 +930,18 @@ static void run_scc(xlb_ctx* c, const xlb_scc& scc, RunState& rs) {
     }
     std::map<std::string, int> home;
     for (auto& p : preds) home[p] = home_half(rules, p, rec, schema[p].arity);
+    // Heads whose sorted list some rule reads during the loop: the other recursive atoms of a rule
+    // with several (a variant reads their full relations), and relations tested by a semi / anti
+    // join.  For every other head the merge of an iteration's delta can wait.
+    std::set<std::string> list_read;
+    for (auto& fr : rules) {
+        int nrec = 0;
+        for (auto& a : fr.atoms) nrec += rec.count(a.rel) ? 1 : 0;
+        for (auto& a : fr.atoms)
+            if (nrec >= 2 && rec.count(a.rel)) list_read.insert(a.rel);
+        for (auto& k : fr.checks) list_read.insert(k.rel);
+    }
+    for (auto& p : preds) rs.head_schema[p] = schema[p];
     if (c->world > 1) {
         // a head relation that already holds rows is re-homed so that equal tuples meet on one rank
         for (auto& p : preds) {
@@ -930,7 +990,7 @@ static void run_scc(xlb_ctx* c, const xlb_scc& scc, RunState& rs) {
                 for (size_t j = 0; j < fr.atoms.size(); ++j)
                     if (j != i && store_get(c, fr.atoms[j].rel)->rows == 0 && c->world == 1) any_empty = true;
                 if (any_empty) continue;
-                Keys full = ops_rel_packed(c, store_get(c, fr.head));
+                Keys full = full_view(c, rs, fr.head);
                 eval_variant(c, fr, i, ops_rel_packed(c, d), false, home[fr.atoms[i].rel], full, home[fr.head], novel[fr.head], rs);
             }
         }
@@ -949,6 +1009,19 @@ static void run_scc(xlb_ctx* c, const xlb_scc& scc, RunState& rs) {
         for (auto& p : preds) {                    // :868-937
             Keys& d = novel[p];
             if (d.n == 0 && c->world == 1) continue;
+            {
+                // nobody reads the list and the bitmap is in step with full + delta: put the merge off
+                const DenseState& ds = rs.dense[p];
+                const Keys view = full_view(c, rs, p);
+                if (c->world == 1 && !(c->flags & XLB_FLAG_NO_DENSE) && !list_read.count(p) && ds.valid && ds.rows == view.n + d.n) {
+                    RunState::Pending& pd = rs.pending[p];
+                    pd.deltas.push_back(d);
+                    pd.rows += d.n;
+                    pd.bound |= d.bound;
+                    continue;
+                }
+            }
+            materialize_full(c, rs, p);
             Keys full = ops_rel_packed(c, store_get(c, p));
             Keys merged;
             {
@@ -958,6 +1031,7 @@ static void run_scc(xlb_ctx* c, const xlb_scc& scc, RunState& rs) {
             install_full(c, p, schema[p], merged, &d, rs);
         }
     }
+    for (auto& p : preds) materialize_full(c, rs, p);
     for (auto& p : preds) {  // :940-945
         if (!fix && (c->flags & XLB_FLAG_KEEP_DELTAS)) break;  // left for a checkpoint
         auto it = c->store.find("__delta_" + p);

@@ -985,7 +985,8 @@ static __global__ void __launch_bounds__(BLOCK) dense_count_k(const unsigned int
     if (lane_id() == 0) group_counts[g] = cnt;
 }
 static __global__ void __launch_bounds__(BLOCK) dense_emit_k(const unsigned int* __restrict__ bitmap, uint64_t words, const uint64_t* __restrict__ group_offs,
-                                                           uint64_t groups, int lo_bits, uint64_t* __restrict__ out, unsigned int* __restrict__ visited) {
+                                                           uint64_t groups, int lo_bits, uint64_t* __restrict__ out, unsigned int* __restrict__ visited,
+                                                           uint64_t cap, DevStatus* st) {
     uint64_t g = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (g >= groups) return;
     const unsigned lane = lane_id();
@@ -1008,6 +1009,10 @@ static __global__ void __launch_bounds__(BLOCK) dense_emit_k(const unsigned int*
         unsigned b = __ffs(m) - 1;
         m &= m - 1;
         uint64_t x = (w << 5) | b;
+        if (pos >= cap) {  // more bits than the rows the host sized the output for: report, never write past it
+            set_status(st, XLB_ERR_CAPACITY, 8, pos);
+            break;
+        }
         out[pos++] = ((x >> lo_bits) << 32) | (x & lo_mask);
     }
 }
@@ -1085,6 +1090,11 @@ static __global__ void __launch_bounds__(BLOCK) hash_probe_k(LoadKey load_key, u
         }
         match[i] = m;
     }
+}
+
+// The host sized an output from a count it kept itself: the device's own count must agree.
+static __global__ void verify_count_k(const uint64_t* device_count, uint64_t host_count, DevStatus* st) {
+    if (*device_count != host_count) set_status(st, XLB_ERR_CAPACITY, 9, *device_count);
 }
 
 // ------------------------------------------------------- direct (counting) join index

@@ -424,7 +424,11 @@ DenseSet ops_dense_begin(xlb_ctx* c, int hi_bits, int lo_bits) {
     return d;
 }
 
-Keys ops_dense_finish(xlb_ctx* c, DenseSet& d, const Keys& full) {
+static Keys dense_finish(xlb_ctx* c, DenseSet& d, const Keys& full, const uint64_t* known_total);
+Keys ops_dense_finish(xlb_ctx* c, DenseSet& d, const Keys& full) { return dense_finish(c, d, full, nullptr); }
+
+// known_total: the number of rows that will come out, when the host knows it already (no read-back)
+static Keys dense_finish(xlb_ctx* c, DenseSet& d, const Keys& full, const uint64_t* known_total) {
     Keys o;
     o.bound = d.bound;
     const uint64_t words = d.words;
@@ -440,8 +444,12 @@ Keys ops_dense_finish(xlb_ctx* c, DenseSet& d, const Keys& full) {
     dense_count_k<<<(unsigned)((groups * 32 + BLOCK - 1) / BLOCK), BLOCK, 0, c->stream>>>(d.bitmap->as<unsigned int>(), words, gcnt->as<uint32_t>(), groups, d.visited);
     check_launch(c, "dense_count");
     exclusive_scan<LoadU32, uint64_t>(c, LoadU32{gcnt->as<uint32_t>()}, groups, offs->as<uint64_t>(), d.counts);
-    unsigned long long both[2];
-    read_words(c, d.counts, 2, both);
+    unsigned long long both[2] = {known_total ? *known_total : 0ull, 0ull};
+    if (!known_total) read_words(c, d.counts, 2, both);
+    else {
+        verify_count_k<<<1, 1, 0, c->stream>>>(d.counts, *known_total, c->d_status);  // a mismatch surfaces as an error at the next status check
+        check_launch(c, "verify_count");
+    }
     const uint64_t tot = both[0];
     d.marked = both[1];
     prof_add_bytes(c, "expand_mark", d.marked * 4ull);
@@ -449,7 +457,7 @@ Keys ops_dense_finish(xlb_ctx* c, DenseSet& d, const Keys& full) {
     o.buf = make_buf(c, tot * 8);
     if (tot) {
         prof_begin(c, "dense_emit", words * 4ull + tot * 8ull);
-        dense_emit_k<<<(unsigned)((groups * 32 + BLOCK - 1) / BLOCK), BLOCK, 0, c->stream>>>(d.bitmap->as<unsigned int>(), words, offs->as<uint64_t>(), groups, d.lo_bits, o.buf->as<uint64_t>(), d.visited);
+        dense_emit_k<<<(unsigned)((groups * 32 + BLOCK - 1) / BLOCK), BLOCK, 0, c->stream>>>(d.bitmap->as<unsigned int>(), words, offs->as<uint64_t>(), groups, d.lo_bits, o.buf->as<uint64_t>(), d.visited, tot, c->d_status);
         check_launch(c, "dense_emit");
     }
     return o;
@@ -469,6 +477,20 @@ void ops_dense_state_build(xlb_ctx* c, DenseState& s, int hi_bits, int lo_bits, 
     }
     s.rows = full.n + novel.n;
     s.valid = true;
+}
+
+Keys ops_dense_state_rows(xlb_ctx* c, const DenseState& s, uint64_t bound) {
+    DenseSet d;
+    d.hi_bits = s.hi_bits;
+    d.lo_bits = s.lo_bits;
+    d.words = s.words;
+    d.bitmap = s.visited;
+    d.bound = bound;
+    Buf counts = make_buf(c, 16);
+    CUDA_OK(cudaMemsetAsync(counts->p, 0, 16, c->stream));
+    d.counts = counts->as<uint64_t>();
+    Keys none;
+    return dense_finish(c, d, none, &s.rows);  // nothing to subtract, no second bitmap: every set bit comes out, s.rows of them
 }
 
 Keys ops_dense_novel(xlb_ctx* c, const Keys& cand, const Keys& full, int hi_bits, int lo_bits, unsigned int* visited) {

@@ -77,6 +77,7 @@ struct DenseState {
     bool valid = false;
 };
 void ops_dense_state_build(xlb_ctx* c, DenseState& s, int hi_bits, int lo_bits, const Keys& full, const Keys& novel);
+Keys ops_dense_state_rows(xlb_ctx* c, const DenseState& s, uint64_t bound);  // all its tuples, in order
 DenseSet ops_dense_begin(xlb_ctx* c, int hi_bits, int lo_bits);
 // Emit, in order, the marked tuples that are new: with d.visited those it lacks (which it then
 // gains; `full` is not read), else those not in `full` (cleared from the bitmap first).
