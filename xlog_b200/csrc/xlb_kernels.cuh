@@ -154,6 +154,31 @@ static __global__ void __launch_bounds__(BLOCK) scan_apply_k(Load load, uint64_t
     if (!tile_offsets && total && threadIdx.x == 0) *total = tot;
 }
 
+// The same for one block of 1024 threads: up to 8192 entries in one launch instead of three.
+constexpr int SCAN_BLOCK_MAX = 1024 * SCAN_IPT;
+template <class Load, class Tout>
+static __global__ void __launch_bounds__(1024) scan_block_k(Load load, uint64_t n, Tout* out, Tout* total) {
+    __shared__ Tout sm[33];
+    uint64_t base = (uint64_t)threadIdx.x * SCAN_IPT;
+    Tout v[SCAN_IPT];
+    Tout s = 0;
+#pragma unroll
+    for (int k = 0; k < SCAN_IPT; ++k) {
+        uint64_t i = base + k;
+        v[k] = i < n ? (Tout)load(i) : Tout(0);
+        s += v[k];
+    }
+    Tout tot;
+    Tout run = block_exclusive_scan<Tout>(s, &tot, sm);
+#pragma unroll
+    for (int k = 0; k < SCAN_IPT; ++k) {
+        uint64_t i = base + k;
+        if (i < n) out[i] = run;
+        run += v[k];
+    }
+    if (total && threadIdx.x == 0) *total = tot;
+}
+
 struct LoadU32 {
     const uint32_t* p;
     __device__ __forceinline__ uint32_t operator()(uint64_t i) const { return p[i]; }
@@ -175,6 +200,12 @@ void exclusive_scan(xlb_ctx* c, Load load, uint64_t n, Tout* out, Tout* d_total)
         prof_begin(c, "scan_apply", 0);
         scan_apply_k<Load, Tout><<<1, BLOCK, 0, c->stream>>>(load, n, nullptr, out, d_total);
         check_launch(c, "scan_apply");
+        return;
+    }
+    if (n <= (uint64_t)SCAN_BLOCK_MAX) {
+        prof_begin(c, "scan_block", 0);
+        scan_block_k<Load, Tout><<<1, 1024, 0, c->stream>>>(load, n, out, d_total);
+        check_launch(c, "scan_block");
         return;
     }
     Buf sums = make_buf(c, ntiles * sizeof(Tout));
