@@ -154,6 +154,36 @@ static __global__ void __launch_bounds__(BLOCK) scan_apply_k(Load load, uint64_t
     if (!tile_offsets && total && threadIdx.x == 0) *total = tot;
 }
 
+// scan_apply_k without the spine pass, for up to SCAN_SUMS_MAX tiles: every block adds up the sums
+// of the tiles before it by itself (a few KB out of the L2), the last one also writes the total.
+constexpr int SCAN_SUMS_MAX = 1024;
+template <class Load, class Tout>
+static __global__ void __launch_bounds__(BLOCK) scan_apply_sums_k(Load load, uint64_t n, const Tout* __restrict__ tile_sums, Tout* out, Tout* total) {
+    __shared__ Tout sm[33];
+    Tout part = 0;
+    for (unsigned t = threadIdx.x; t < blockIdx.x; t += BLOCK) part += tile_sums[t];
+    Tout offset;
+    block_exclusive_scan<Tout>(part, &offset, sm);
+    uint64_t base = (uint64_t)blockIdx.x * SCAN_TILE + (uint64_t)threadIdx.x * SCAN_IPT;
+    Tout v[SCAN_IPT];
+    Tout s = 0;
+#pragma unroll
+    for (int k = 0; k < SCAN_IPT; ++k) {
+        uint64_t i = base + k;
+        v[k] = i < n ? (Tout)load(i) : Tout(0);
+        s += v[k];
+    }
+    Tout tot;
+    Tout run = block_exclusive_scan<Tout>(s, &tot, sm) + offset;
+#pragma unroll
+    for (int k = 0; k < SCAN_IPT; ++k) {
+        uint64_t i = base + k;
+        if (i < n) out[i] = run;
+        run += v[k];
+    }
+    if (total && blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) *total = offset + tot;
+}
+
 // The same for one block of 1024 threads: up to 8192 entries in one launch instead of three.
 constexpr int SCAN_BLOCK_MAX = 1024 * SCAN_IPT;
 template <class Load, class Tout>
@@ -212,6 +242,12 @@ void exclusive_scan(xlb_ctx* c, Load load, uint64_t n, Tout* out, Tout* d_total)
     prof_begin(c, "scan_reduce", 0);
     scan_reduce_k<Load, Tout><<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(load, n, sums->as<Tout>());
     check_launch(c, "scan_reduce");
+    if (ntiles <= (uint64_t)SCAN_SUMS_MAX) {
+        prof_begin(c, "scan_apply", 0);
+        scan_apply_sums_k<Load, Tout><<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(load, n, sums->as<Tout>(), out, d_total);
+        check_launch(c, "scan_apply");
+        return;
+    }
     prof_begin(c, "scan_spine", 0);
     scan_spine_k<Tout><<<1, 1024, 0, c->stream>>>(sums->as<Tout>(), ntiles, d_total);
     check_launch(c, "scan_spine");
