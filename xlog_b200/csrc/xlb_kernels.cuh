@@ -1051,6 +1051,45 @@ static __global__ void __launch_bounds__(BLOCK) dense_count_k(const unsigned int
     for (int d = 16; d; d >>= 1) cnt += __shfl_xor_sync(FULL, cnt, d);
     if (lane_id() == 0) group_counts[g] = cnt;
 }
+// dense_count_k and the prefix sum over its group counts in one launch, for up to
+// DENSE_FUSED_GROUPS groups: the block that finishes last (an atomic ticket after a fence, the
+// pattern of a single-pass reduction) scans the counts.  `ticket` must be zero on entry and is
+// zero again on exit.
+constexpr int DENSE_FUSED_GROUPS = 8192;
+static __global__ void __launch_bounds__(BLOCK) dense_count_scan_k(const unsigned int* __restrict__ bitmap, uint64_t words, uint32_t* group_counts, uint64_t groups,
+                                                              const unsigned int* __restrict__ visited, uint64_t* __restrict__ group_offs, uint64_t* total,
+                                                              unsigned int* ticket) {
+    __shared__ uint64_t sm[33];
+    __shared__ bool last_s;
+    uint64_t g = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (g < groups) {
+        uint64_t w = g * 32 + lane_id();
+        unsigned cnt = w < words ? __popc(bitmap[w] & ~(visited ? visited[w] : 0u)) : 0;
+#pragma unroll
+        for (int d = 16; d; d >>= 1) cnt += __shfl_xor_sync(FULL, cnt, d);
+        if (lane_id() == 0) group_counts[g] = cnt;
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) last_s = atomicAdd(ticket, 1u) == gridDim.x - 1;
+    __syncthreads();
+    if (!last_s) return;
+    __threadfence();
+    const uint64_t per = (groups + BLOCK - 1) / BLOCK;  // at most 32
+    const uint64_t lo = (uint64_t)threadIdx.x * per, hi = lo + per < groups ? lo + per : groups;
+    uint64_t s = 0;
+    for (uint64_t i = lo; i < hi; ++i) s += __ldcg(&group_counts[i]);
+    uint64_t tot;
+    uint64_t run = block_exclusive_scan<uint64_t>(s, &tot, sm);
+    for (uint64_t i = lo; i < hi; ++i) {
+        group_offs[i] = run;
+        run += __ldcg(&group_counts[i]);
+    }
+    if (threadIdx.x == 0) {
+        *total = tot;
+        *ticket = 0;
+    }
+}
 static __global__ void __launch_bounds__(BLOCK) dense_emit_k(const unsigned int* __restrict__ bitmap, uint64_t words, const uint64_t* __restrict__ group_offs,
                                                            uint64_t groups, int lo_bits, uint64_t* __restrict__ out, unsigned int* __restrict__ visited,
                                                            uint64_t cap, DevStatus* st) {

@@ -418,9 +418,9 @@ DenseSet ops_dense_begin(xlb_ctx* c, int hi_bits, int lo_bits) {
     d.lo_bits = lo_bits;
     d.words = ((1ull << (hi_bits + lo_bits)) + 31) / 32;
     const uint64_t bitmap_bytes = (d.words * 4 + 7) & ~7ull;
-    d.bitmap = make_buf(c, bitmap_bytes + 16);
+    d.bitmap = make_buf(c, bitmap_bytes + 24);
     d.counts = (uint64_t*)((char*)d.bitmap->p + bitmap_bytes);
-    CUDA_OK(cudaMemsetAsync(d.bitmap->p, 0, bitmap_bytes + 16, c->stream));
+    CUDA_OK(cudaMemsetAsync(d.bitmap->p, 0, bitmap_bytes + 24, c->stream));
     return d;
 }
 
@@ -441,9 +441,15 @@ static Keys dense_finish(xlb_ctx* c, DenseSet& d, const Keys& full, const uint64
     Buf gcnt = make_buf(c, groups * 4);
     Buf offs = make_buf(c, groups * 8);
     prof_begin(c, "dense_count", words * 4ull);
-    dense_count_k<<<(unsigned)((groups * 32 + BLOCK - 1) / BLOCK), BLOCK, 0, c->stream>>>(d.bitmap->as<unsigned int>(), words, gcnt->as<uint32_t>(), groups, d.visited);
-    check_launch(c, "dense_count");
-    exclusive_scan<LoadU32, uint64_t>(c, LoadU32{gcnt->as<uint32_t>()}, groups, offs->as<uint64_t>(), d.counts);
+    if (groups <= (uint64_t)DENSE_FUSED_GROUPS) {
+        dense_count_scan_k<<<(unsigned)((groups * 32 + BLOCK - 1) / BLOCK), BLOCK, 0, c->stream>>>(d.bitmap->as<unsigned int>(), words, gcnt->as<uint32_t>(), groups, d.visited,
+                                                                                                  offs->as<uint64_t>(), d.counts, (unsigned int*)(d.counts + 2));
+        check_launch(c, "dense_count");
+    } else {
+        dense_count_k<<<(unsigned)((groups * 32 + BLOCK - 1) / BLOCK), BLOCK, 0, c->stream>>>(d.bitmap->as<unsigned int>(), words, gcnt->as<uint32_t>(), groups, d.visited);
+        check_launch(c, "dense_count");
+        exclusive_scan<LoadU32, uint64_t>(c, LoadU32{gcnt->as<uint32_t>()}, groups, offs->as<uint64_t>(), d.counts);
+    }
     unsigned long long both[2] = {known_total ? *known_total : 0ull, 0ull};
     if (!known_total) read_words(c, d.counts, 2, both);
     else {
@@ -486,8 +492,8 @@ Keys ops_dense_state_rows(xlb_ctx* c, const DenseState& s, uint64_t bound) {
     d.words = s.words;
     d.bitmap = s.visited;
     d.bound = bound;
-    Buf counts = make_buf(c, 16);
-    CUDA_OK(cudaMemsetAsync(counts->p, 0, 16, c->stream));
+    Buf counts = make_buf(c, 24);
+    CUDA_OK(cudaMemsetAsync(counts->p, 0, 24, c->stream));
     d.counts = counts->as<uint64_t>();
     Keys none;
     return dense_finish(c, d, none, &s.rows);  // nothing to subtract, no second bitmap: every set bit comes out, s.rows of them

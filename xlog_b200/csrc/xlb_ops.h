@@ -59,8 +59,9 @@ struct DenseSet {
     uint64_t words = 0;
     int hi_bits = 0, lo_bits = 0;
     uint64_t bound = 0;  // OR bound of what was marked
-    // two words behind the bitmap: [0] rows ops_dense_finish emits, [1] sum of the tuple counts of
-    // the marking joins, which stay on the device until ops_dense_finish reads both at once
+    // three words behind the bitmap: [0] rows ops_dense_finish emits, [1] sum of the tuple counts of
+    // the marking joins, which stay on the device until ops_dense_finish reads both at once,
+    // [2] the ticket of the fused count-and-scan kernel
     uint64_t* counts = nullptr;
     uint64_t marked = 0;  // host copy of counts[1], valid after ops_dense_finish
     // Optional bitmap (same domain) of the tuples known already: marking skips them, and
