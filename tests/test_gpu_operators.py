@@ -215,3 +215,16 @@ def test_typed_columns_against_oracle(provider, oracle):
         provider.union_gpu(provider.create_buffer_from_slices([i32.astype(np.int32)]),
                            provider.create_buffer_from_slices([raw]))
     assert e.value.status == A.ERR_TYPE
+
+
+@pytest.mark.parametrize("nl", [2048, 2049, 8192, 8193, 2_097_152, 2_097_153])
+def test_join_at_the_size_edges_of_the_prefix_sum(provider, nl):
+    # the join scans one match length per left row: a single tile up to 2048 entries, one block up
+    # to 8192, two launches up to 1024 tiles (2 097 152 entries), three beyond
+    lk = (np.arange(nl, dtype=np.uint64) * np.uint64(2654435761) % np.uint64(1000)).astype(np.uint32)
+    l = [lk, np.arange(nl, dtype=np.uint32)]
+    r = [np.arange(0, 1000, 2, dtype=np.uint32), np.arange(0, 1000, 2, dtype=np.uint32) + 5]   # even keys only, once each
+    out = provider.download(provider.hash_join_v2(provider.create_buffer_from_slices(l), provider.create_buffer_from_slices(r), [0], [0]))
+    keep = lk % 2 == 0
+    assert np.array_equal(out[0], lk[keep]) and np.array_equal(out[1], l[1][keep])     # left row order kept
+    assert np.array_equal(out[2], lk[keep]) and np.array_equal(out[3], lk[keep] + 5)
