@@ -98,8 +98,9 @@ def _from_ordered(u: np.ndarray, dtype) -> np.ndarray:
 
 
 class OracleRel:
-    """Host relation: equal-length numpy columns of one width class (4 or 8 bytes).  Signed and
-    floating columns are held as their order-preserving unsigned images."""
+    """Host relation: equal-length numpy columns, held in one width class (4 or 8 bytes; mixed
+    widths are widened to 8).  Signed and floating columns are held as their order-preserving
+    unsigned images."""
 
     def __init__(self, handle, dtypes=None):
         if not handle:
@@ -116,9 +117,12 @@ class OracleRel:
             cols = [c if c.dtype.itemsize in (4, 8) and c.dtype.kind in "uif" else c.astype(np.uint32) for c in cols]
         dtypes = [c.dtype for c in cols]
         width = dtypes[0].itemsize if dtypes else (np.dtype(dtype).itemsize if dtype is not None else 4)
-        if any(d.itemsize != width for d in dtypes):
-            raise ValueError("the oracle takes columns of one width class")
         ucols = [np.ascontiguousarray(_to_ordered(c)) for c in cols]
+        if any(d.itemsize != width for d in dtypes):
+            # 4- and 8-byte columns together: the unsigned images of the narrow ones are widened
+            # (same order, same equality); `columns` narrows them again
+            width = 8
+            ucols = [np.ascontiguousarray(u.astype(np.uint64)) for u in ucols]
         arity = len(cols) if arity is None else arity
         rows = len(cols[0]) if cols else 0
         ptrs = (C.c_void_p * max(arity, 1))(*[c.ctypes.data for c in ucols])
@@ -145,7 +149,8 @@ class OracleRel:
         ptrs = (C.c_void_p * max(self.arity, 1))(*[c.ctypes.data for c in cols])
         lib().xo_rel_to_cols(self._h, ptrs)
         if self.dtypes and len(self.dtypes) == len(cols):
-            cols = [_from_ordered(c, d) for c, d in zip(cols, self.dtypes)]
+            cols = [_from_ordered(c.astype(np.uint32) if np.dtype(d).itemsize == 4 and c.dtype.itemsize == 8 else c, d)
+                    for c, d in zip(cols, self.dtypes)]
         return cols
 
     def tuples(self):

@@ -23,6 +23,8 @@ JV = "crates/xlog-cuda/tests/join_v2_tests.rs"
 JC = "crates/xlog-cuda/tests/join_collision_test.rs"
 ST = "crates/xlog-cuda/tests/sort_tests.rs"
 GB = "crates/xlog-cuda/tests/groupby_tests.rs"
+SD = "crates/xlog-cuda/tests/test_sort_dedup_u64.rs"
+TCOV = "crates/xlog-cuda/tests/type_coverage_tests.rs"
 
 
 def rows1(xs):
@@ -139,6 +141,29 @@ def operators():
         a=[[1, 2, 100]], b=[[1, 3, 200]], lk=[0, 1], rk=[0, 1], join="inner")
     add("join", JC + ":132-162", [], types=u1, rtypes=u1, a=rows1([100, 200]), b=rows1([300, 400]), lk=[0], rk=[0], join="semi")
     add("join", JC + ":165-194", rows1([100, 200]), types=u1, rtypes=u1, a=rows1([100, 200]), b=rows1([300, 400]), lk=[0], rk=[0], join="anti")
+    # ---- u64 keys: both halves of the key take part in the order ---------------------------------
+    big = (1 << 32)
+    add("sort", SD + ":253-270", rows1(list(range(1, 10))), types=["u64"], a=rows1([5, 2, 8, 1, 9, 3, 7, 4, 6]), keys=[0])
+    add("sort", SD + ":273-287", [[10, 100], [20, 200], [30, 300], [40, 400]], types=["u64", "u32"],
+        a=[[30, 300], [10, 100], [20, 200], [40, 400]], keys=[0])
+    add("sort", SD + ":290-302", [], types=["u64"], a=[], keys=[0])
+    add("sort", SD + ":305-318", rows1([1, 2, 3, 5, 8, 13, 21]), types=["u64"], a=rows1([1, 2, 3, 5, 8, 13, 21]), keys=[0])
+    above = [big + 7, 2, big, big + 2, 7, (1 << 64) - 1, big - 1]
+    add("sort", SD + ":321-356 (keys above u32::MAX)", rows1(sorted(above)), types=["u64"], a=rows1(above), keys=[0])
+    d64 = [[big, 5], [1, 2], [1, 2], [big, 5], [big, 4], [1, 3]]
+    add("dedup", SD + ":363-387", [list(t) for t in sorted({tuple(r) for r in d64})], types=["u64", "u64"], a=d64)
+    add("dedup", SD + ":390-407", [[1, 2], [1, 3], [big, 1], [big, 2]], types=["u64", "u64"], a=[[1, 2], [1, 3], [big, 1], [big, 2]])
+    # ---- the u32 matrix of the type-coverage suite -----------------------------------------------
+    add("sort", TCOV + ":128-149", [[1, 10], [2, 20], [3, 30], [5, 50], [8, 80], [9, 90]], types=t2,
+        a=[[5, 50], [2, 20], [8, 80], [1, 10], [9, 90], [3, 30]], keys=[0])
+    add("sort", TCOV + ":153-170", rows1([1, 1, 2, 2, 3, 3]), types=u1, a=rows1([3, 1, 2, 1, 3, 2]), keys=[0])
+    add("join", TCOV + ":209-237", rows1([2, 4]), types=u1, rtypes=u1, a=rows1([1, 2, 3, 4]), b=rows1([2, 4]), lk=[0], rk=[0], join="semi")
+    add("join", TCOV + ":240-268", rows1([1, 3]), types=u1, rtypes=u1, a=rows1([1, 2, 3, 4]), b=rows1([2, 4]), lk=[0], rk=[0], join="anti")
+    add("union", TCOV + ":368-390", rows1([1, 2, 3, 4, 5]), types=u1, ins=[rows1([1, 2, 3]), rows1([3, 4, 5])])
+    add("union", TCOV + ":394-415", rows1([1, 2, 3, 4]), types=u1, ins=[rows1([1, 2]), rows1([3, 4])])
+    add("diff", TCOV + ":421-443", rows1([1, 3]), types=u1, a=rows1([1, 2, 3, 4]), b=rows1([2, 4]))
+    add("diff", TCOV + ":447-468", rows1([1, 2, 3]), types=u1, a=rows1([1, 2, 3]), b=rows1([4, 5, 6]))
+    add("sort", TCOV + ":707-724", rows1([42]), types=u1, a=rows1([42]), keys=[0])
     return c
 
 
@@ -282,6 +307,9 @@ def groupby():
     add(GB + ":284-317", [[1, 1, 2, 2], [10, 10, 20, 20], [5, 7, 11, 13]], [0, 1], [[2, "sum"]], [[1, 2], [10, 20], [12, 24]])
     add(GB + ":331-367", [[5, 3, 1, 4, 2], [50, 30, 10, 40, 20]], [0], [[1, "sum"], [1, "count"]],
         [[1, 2, 3, 4, 5], [10, 20, 30, 40, 50], [1, 1, 1, 1, 1]])
+    add(TCOV + ":301-326", [[1, 1, 2, 2, 2, 3], [10, 20, 30, 40, 50, 60]], [0], [[1, "count"]], [[1, 2, 3], [2, 3, 1]])
+    add(TCOV + ":542-585", [[1, 1, 2, 2, 2, 3], [10, 20, 5, 15, 25, 100]], [0], [[1, "count"], [1, "sum"], [1, "min"], [1, "max"]],
+        [[1, 2, 3], [2, 3, 1], [30, 45, 100], [10, 5, 100], [20, 25, 100]])
     return c
 
 
