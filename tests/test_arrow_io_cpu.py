@@ -93,3 +93,22 @@ def test_symbol_table():
         st.resolve(2)
     st.clear()
     assert len(st) == 0 and st.intern("b") == 0
+
+
+def test_reference_export_case():
+    # crates/xlog-cuda/tests/arrow_tests.rs:12-64 and :108-140: (id u32, value i64), names kept
+    data = AIO.columns_to_ipc_stream([np.array([1, 2, 3, 4, 5], np.uint32), np.array([100, 200, 300, 400, 500], np.int64)],
+                                     [A.U32, A.I64], ["id", "value"])
+    batch, = list(pa.ipc.open_stream(pa.BufferReader(data)))
+    assert (batch.num_rows, batch.num_columns) == (5, 2) and batch.schema.names == ["id", "value"]
+    assert batch.schema.field(0).type == pa.uint32() and batch.schema.field(1).type == pa.int64()
+    assert batch.column(0).to_pylist() == [1, 2, 3, 4, 5] and batch.column(1).to_pylist() == [100, 200, 300, 400, 500]
+
+
+def test_reference_import_case():
+    # crates/xlog-cuda/tests/arrow_tests.rs:210-245: a batch built by another Arrow writer
+    schema = pa.schema([pa.field("x", pa.uint32(), nullable=False), pa.field("y", pa.float64(), nullable=False)])
+    batch = pa.record_batch([pa.array([10, 20, 30], pa.uint32()), pa.array([1.5, 2.5, 3.5], pa.float64())], schema=schema)
+    cols, types, names = AIO.ipc_stream_to_columns(_stream([batch], schema))
+    assert types == [A.U32, A.F64] and names == ["x", "y"]
+    assert cols[0].tolist() == [10, 20, 30] and cols[1].tolist() == [1.5, 2.5, 3.5]

@@ -977,6 +977,27 @@ static void run_scc(xlb_ctx* c, const xlb_scc& scc, RunState& rs) {
     if (!scc.is_recursive) return;
 
     bool fix = false;
+    // A failure inside the loop (memory budget, a device status) must not leave deltas behind: a
+    // later call would take them for a saved state and resume from them, over a full relation
+    // that may lack merges still put off.  Without them the next call seeds again from the stored
+    // relations, which are a valid earlier state.
+    struct DropDeltasOnFailure {
+        xlb_ctx* c;
+        RunState& rs;
+        const std::vector<std::string>& preds;
+        bool armed = true;
+        ~DropDeltasOnFailure() {
+            if (!armed) return;
+            rs.pending.clear();
+            for (auto& p : preds) {
+                auto it = c->store.find("__delta_" + p);
+                if (it == c->store.end()) continue;
+                delete it->second;
+                c->store.erase(it);
+                c->versions["__delta_" + p]++;
+            }
+        }
+    } guard{c, rs, preds};
     for (uint64_t it = 0; it < c->max_iterations; ++it) {  // recursive.rs:619-937
         rs.st.iterations++;
         std::map<std::string, Keys> novel;
@@ -1032,6 +1053,7 @@ static void run_scc(xlb_ctx* c, const xlb_scc& scc, RunState& rs) {
         }
     }
     for (auto& p : preds) materialize_full(c, rs, p);
+    guard.armed = false;  // the loop ended by itself: what follows decides about the deltas
     for (auto& p : preds) {  // :940-945
         if (!fix && (c->flags & XLB_FLAG_KEEP_DELTAS)) break;  // left for a checkpoint
         auto it = c->store.find("__delta_" + p);
