@@ -84,3 +84,27 @@ def test_join_against_a_dictionary(oracle, jt):
         assert got == [lt for lt in _tuples(l) if lt[0] in by_key]
     else:
         assert got == [lt for lt in _tuples(l) if lt[0] not in by_key]
+
+
+@pytest.mark.parametrize("nodes,edges,seed", [(12, 20, 1), (60, 150, 2), (200, 380, 3)])
+def test_fixpoints_against_boolean_matrix_closure(oracle, nodes, edges, seed):
+    from xlog_b200 import programs
+    rng = np.random.default_rng(seed)
+    c0, c1 = rng.integers(0, nodes, edges).astype(np.uint32), rng.integers(0, nodes, edges).astype(np.uint32)
+    adj = np.zeros((nodes, nodes), dtype=bool)
+    adj[c0, c1] = True
+    reach = adj.copy()
+    while True:                                   # paths of length >= 1, by repeated squaring-free closure
+        nxt = reach | (reach.astype(np.uint8) @ adj.astype(np.uint8) > 0)
+        if np.array_equal(nxt, reach):
+            break
+        reach = nxt
+    xs, ys = np.nonzero(reach)
+    out, _ = oracle.run_program(programs.transitive_closure(), {"edge": [c0, c1]}, ["reach"])
+    assert np.array_equal(out["reach"][0], xs.astype(np.uint32)) and np.array_equal(out["reach"][1], ys.astype(np.uint32))
+    for builder in (programs.transitive_closure_left_linear, programs.transitive_closure_nonlinear):
+        alt, _ = oracle.run_program(builder(), {"edge": [c0, c1]}, ["reach"])
+        assert all(np.array_equal(a, b) for a, b in zip(alt["reach"], out["reach"]))
+    src = int(c0[0])
+    r, _ = oracle.run_program(programs.reach_from_source(src), {"edge": [c0, c1]}, ["r"])
+    assert np.array_equal(r["r"][0], np.nonzero(reach[src])[0].astype(np.uint32))
