@@ -272,4 +272,17 @@ def run_program(plan, inputs, outputs, max_iterations=0):
         ex.put_relation(name, OracleRel.from_columns(cols))
     cp = plan.compile()
     ex.execute_plan(cp)
-    return {o: ex.get(o).columns() for o in outputs}, ex
+    # typed columns are held as order-preserving unsigned images: decode the outputs with the column
+    # types the plan declares for its heads (inputs keep the types they came with)
+    np_of = {0: np.uint32, 1: np.uint64, 2: np.int32, 3: np.int64, 4: np.float32, 5: np.float64, 7: np.uint32}
+    types = {name: [np.asarray(c).dtype for c in cols] for name, cols in inputs.items()}
+    for s in plan.sccs:
+        for r in s.rules:
+            types.setdefault(r.head, [np.dtype(np_of[t]) for t in r.head_types])
+    out = {}
+    for o in outputs:
+        rel = ex.get(o)
+        if o in types and len(types[o]) == rel.arity:
+            rel.dtypes = types[o]
+        out[o] = rel.columns()
+    return out, ex

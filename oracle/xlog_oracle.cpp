@@ -407,7 +407,7 @@ void collect_scans(const xlb_node* n, std::vector<const xlb_node*>& out) {
 Rel empty_like(const xlb_schema& s) {
     Rel r;
     r.arity = s.arity;
-    r.width = (s.arity && (s.types[0] == XLB_U64 || s.types[0] == XLB_I64)) ? 8 : 4;
+    r.width = (s.arity && (s.types[0] == XLB_U64 || s.types[0] == XLB_I64 || s.types[0] == XLB_F64)) ? 8 : 4;
     r.canonical = true;
     return r;
 }

@@ -12,6 +12,7 @@
 //     merges, never a re-sort of the full relation (relational.rs:976-999 re-sorts).
 #include <algorithm>
 #include <cstring>
+#include <deque>
 #include <functional>
 #include <set>
 
@@ -1065,9 +1066,199 @@ static void run_scc(xlb_ctx* c, const xlb_scc& scc, RunState& rs) {
     if (!fix) xlb_fail(XLB_ERR_ITER_LIMIT, "Recursive SCC iteration limit (%llu) exceeded", (unsigned long long)c->max_iterations);
 }
 
+// ---- plans over wide or typed columns ------------------------------------------------------------
+// The pipelines carry two 32-bit columns per tuple.  Relations with u64, signed or floating columns
+// (the reference runs them on its general path, e.g. the u64 closure of
+// crates/xlog-integration/tests/test_factorized_delta_e2e.rs:385-411) are therefore run as relations
+// of dictionary ranks: one sorted dictionary over the order-preserving images of all values of all
+// relations the plan touches, every column replaced by 32-bit ranks, the same engine, and the heads
+// decoded at the end.  Ranks order and compare as the values do, so joins, comparisons between
+// columns and the sorted result are unchanged; constants of filters are translated to rank bounds.
+static bool rank32(uint8_t t) { return t == XLB_U32 || t == XLB_SYMBOL; }
+
+struct EncodedRun {
+    xlb_ctx* c = nullptr;
+    Keys dict;
+    std::deque<xlb_node> nodes;
+    std::deque<std::vector<const xlb_node*>> lists;
+    std::deque<std::vector<xlb_rule>> rules;
+    std::vector<xlb_scc> sccs;
+    xlb_plan plan{};
+    std::map<std::string, xlb_rel*> originals;      // taken out of the store while the ranks stand in
+    std::map<std::string, xlb_schema> head_types;   // as the plan declares them
+    std::vector<const xlb_node*> const_filters;
+    std::vector<uint64_t> below, not_above;
+    bool active = false;
+
+    static void walk(xlb_ctx* c, const xlb_node* n, std::set<std::string>& scanned, std::vector<const xlb_node*>& consts) {
+        if (!n) return;
+        if (n->kind == XLB_NODE_SCAN) {
+            auto nm = c->rel_names.find(n->rel_id);
+            if (nm != c->rel_names.end()) scanned.insert(nm->second);
+        }
+        if (n->kind == XLB_NODE_FILTER && n->cmp_rhs_is_const) consts.push_back(n);
+        walk(c, n->input, scanned, consts);
+        walk(c, n->left, scanned, consts);
+        walk(c, n->right, scanned, consts);
+        if (n->kind == XLB_NODE_UNION && n->inputs)
+            for (uint32_t i = 0; i < n->n_inputs; ++i) walk(c, n->inputs[i], scanned, consts);
+    }
+
+    const xlb_node* clone(const xlb_node* n) {
+        if (!n) return nullptr;
+        nodes.push_back(*n);
+        xlb_node& m = nodes.back();  // a deque keeps this reference through the pushes below
+        m.input = clone(n->input);
+        m.left = clone(n->left);
+        m.right = clone(n->right);
+        if (n->kind == XLB_NODE_UNION && n->inputs) {
+            std::vector<const xlb_node*> list;
+            for (uint32_t i = 0; i < n->n_inputs; ++i) list.push_back(clone(n->inputs[i]));
+            lists.push_back(std::move(list));
+            m.inputs = lists.back().data();
+        }
+        if (n->kind == XLB_NODE_FILTER && n->cmp_rhs_is_const) {
+            size_t k = std::find(const_filters.begin(), const_filters.end(), n) - const_filters.begin();
+            const uint64_t lo = below[k], hi = not_above[k];  // ranks of values below c; of values not above c
+            switch (n->cmp) {
+                case XLB_EQ: case XLB_NE: m.cmp_rhs = hi > lo ? lo : 0xFFFFFFFFull; break;  // absent: a rank no value has
+                case XLB_LT: case XLB_GE: m.cmp_rhs = lo; break;                             // x < c  <=>  rank(x) < lo
+                case XLB_LE: m.cmp = XLB_LT; m.cmp_rhs = hi; break;                          // x <= c <=>  rank(x) < hi
+                default: m.cmp = XLB_GE; m.cmp_rhs = hi; break;                              // x > c  <=>  rank(x) >= hi
+            }
+        }
+        return &m;
+    }
+
+    // Decide, and if the plan needs it swap the ranks in.  Returns the plan to run.
+    const xlb_plan* begin(xlb_ctx* ctx, const xlb_plan* in) {
+        c = ctx;
+        std::set<std::string> names;
+        bool wide = false;
+        for (uint32_t s = 0; s < in->n_sccs; ++s) {
+            const xlb_scc& scc = in->sccs[s];
+            if (!scc.rules) continue;
+            for (uint32_t i = 0; i < scc.n_rules; ++i) {
+                const xlb_rule& r = scc.rules[i];
+                if (!r.head || !r.body) continue;
+                walk(c, r.body, names, const_filters);
+                names.insert(r.head);
+                if (!head_types.count(r.head)) head_types[r.head] = r.head_schema;
+                for (uint32_t k = 0; k < r.head_schema.arity && k < XLB_MAX_ARITY; ++k) wide |= !rank32(r.head_schema.types[k]);
+            }
+        }
+        std::vector<const xlb_rel*> rels;
+        for (auto& n : names) {
+            xlb_rel* r = store_get(c, n);
+            if (!r) continue;
+            rels.push_back(r);
+            for (uint32_t k = 0; k < r->schema.arity; ++k) wide |= !rank32(r->schema.types[k]);
+        }
+        if (!wide) return in;
+        if (c->world > 1) xlb_fail(XLB_ERR_UNSUPPORTED, "plans over u64, signed or floating columns run on one GPU");
+        if (c->flags & XLB_FLAG_KEEP_DELTAS) xlb_fail(XLB_ERR_UNSUPPORTED, "XLB_FLAG_KEEP_DELTAS with u64, signed or floating columns is not built");
+        for (const xlb_rel* r : rels) {
+            if (r->schema.arity < 1 || r->schema.arity > 2) xlb_fail(XLB_ERR_UNSUPPORTED, "plans take relations of one or two columns");
+            for (uint32_t k = 0; k < r->schema.arity; ++k)
+                if (!type_built(r->schema.types[k])) xlb_fail(XLB_ERR_UNSUPPORTED, "bool columns are not built");
+        }
+        for (auto& h : head_types) {
+            if (h.second.arity < 1 || h.second.arity > 2) xlb_fail(XLB_ERR_UNSUPPORTED, "head %s: derived relations of one or two columns are built", h.first.c_str());
+            for (uint32_t k = 0; k < h.second.arity; ++k)
+                if (!type_built(h.second.types[k])) xlb_fail(XLB_ERR_UNSUPPORTED, "bool columns are not built");
+            if (store_get(c, "__delta_" + h.first)) xlb_fail(XLB_ERR_UNSUPPORTED, "resuming a fixpoint over u64, signed or floating columns is not built");
+        }
+        if (!const_filters.empty()) {
+            // a filter constant is an unsigned value: its place among signed or floating values is not defined here
+            auto ordered = [](uint8_t t) { return t == XLB_I32 || t == XLB_I64 || t == XLB_F32 || t == XLB_F64; };
+            bool typed = false;
+            for (const xlb_rel* r : rels)
+                for (uint32_t k = 0; k < r->schema.arity; ++k) typed |= ordered(r->schema.types[k]);
+            for (auto& h : head_types)
+                for (uint32_t k = 0; k < h.second.arity; ++k) typed |= ordered(h.second.types[k]);
+            if (typed) xlb_fail(XLB_ERR_UNSUPPORTED, "filters with constants over signed or floating columns are not built");
+        }
+        dict = ops_dict_build(c, rels);
+        std::vector<uint64_t> consts;
+        for (const xlb_node* f : const_filters) consts.push_back(f->cmp_rhs);
+        ops_dict_bounds(c, dict, consts, below, not_above);
+        // the plan, with rank constants and 32-bit heads
+        for (uint32_t s = 0; s < in->n_sccs; ++s) {
+            xlb_scc scc = in->sccs[s];
+            std::vector<xlb_rule> rr;
+            for (uint32_t i = 0; scc.rules && i < scc.n_rules; ++i) {
+                xlb_rule r = scc.rules[i];
+                r.body = clone(r.body);
+                for (uint32_t k = 0; k < r.head_schema.arity && k < XLB_MAX_ARITY; ++k) r.head_schema.types[k] = XLB_U32;
+                rr.push_back(r);
+            }
+            rules.push_back(std::move(rr));
+            scc.rules = rules.back().data();
+            sccs.push_back(scc);
+        }
+        plan.sccs = sccs.data();
+        plan.n_sccs = (uint32_t)sccs.size();
+        // the ranks stand in for the relations
+        active = true;
+        for (auto& n : names) {
+            auto it = c->store.find(n);
+            if (it == c->store.end()) continue;
+            xlb_rel* enc = ops_dict_encode(c, it->second, dict);
+            originals[n] = it->second;
+            it->second = enc;
+            c->versions[n]++;
+        }
+        return &plan;
+    }
+
+    // After a successful run: decode the heads, put the inputs back.
+    void finish() {
+        if (!active) return;
+        for (auto& h : head_types) {
+            xlb_rel* ranks = store_get(c, h.first);
+            if (!ranks) continue;
+            xlb_rel* decoded = ops_dict_decode(c, ranks, h.second, dict);
+            store_put(c, h.first, decoded);  // frees the rank relation
+            auto o = originals.find(h.first);
+            if (o != originals.end()) {      // a head that held rows before: superseded by the result
+                delete o->second;
+                originals.erase(o);
+            }
+        }
+        restore_inputs();
+        active = false;
+    }
+
+    // After a failure: nothing in rank space may stay behind.
+    void rollback() {
+        if (!active) return;
+        for (auto& h : head_types) {
+            if (originals.count(h.first)) continue;  // put back below
+            auto it = c->store.find(h.first);
+            if (it == c->store.end()) continue;
+            delete it->second;
+            c->store.erase(it);
+            c->versions[h.first]++;
+        }
+        restore_inputs();
+        active = false;
+    }
+
+    void restore_inputs() {
+        for (auto& o : originals) {
+            auto it = c->store.find(o.first);
+            if (it != c->store.end()) delete it->second;
+            c->store[o.first] = o.second;
+            c->versions[o.first]++;
+        }
+        originals.clear();
+    }
+};
+
 extern "C" xlb_status xlb_execute_plan(xlb_ctx* c, const xlb_plan* plan, xlb_run_stats* stats) {
     if (!c || !plan) return XLB_ERR_INVALID;
     RunState rs;
+    EncodedRun enc;
     cudaEvent_t e0 = nullptr, e1 = nullptr;
     uint64_t launches0 = c->launches, syncs0 = c->syncs;
     double wait0 = c->ms_sync_wait, alloc0 = c->ms_alloc;
@@ -1081,10 +1272,12 @@ extern "C" xlb_status xlb_execute_plan(xlb_ctx* c, const xlb_plan* plan, xlb_run
         CUDA_OK(cudaEventRecord(e0, c->stream));
         if (!plan->sccs && plan->n_sccs) xlb_fail(XLB_ERR_INVALID, "plan has no SCC array");
         std::set<std::string> heads;
-        for (uint32_t s = 0; s < plan->n_sccs; ++s) {
-            run_scc(c, plan->sccs[s], rs);
-            for (uint32_t i = 0; i < plan->sccs[s].n_rules; ++i) heads.insert(plan->sccs[s].rules[i].head);
+        const xlb_plan* run = enc.begin(c, plan);
+        for (uint32_t s = 0; s < run->n_sccs; ++s) {
+            run_scc(c, run->sccs[s], rs);
+            for (uint32_t i = 0; i < run->sccs[s].n_rules; ++i) heads.insert(run->sccs[s].rules[i].head);
         }
+        enc.finish();
         check_dev_status(c);
         CUDA_OK(cudaEventRecord(e1, c->stream));
         CUDA_OK(cudaStreamSynchronize(c->stream));  // executor/mod.rs:1463
@@ -1103,6 +1296,12 @@ extern "C" xlb_status xlb_execute_plan(xlb_ctx* c, const xlb_plan* plan, xlb_run
     } catch (const std::bad_alloc&) {
         c->last_error = "host allocation failed";
         result = XLB_ERR_RESOURCE_EXHAUSTED;
+    }
+    if (result != XLB_OK) {
+        try {
+            enc.rollback();
+        } catch (...) {
+        }
     }
     xlb_resolve_phase_timers(c);
     if (e0) cudaEventDestroy(e0);

@@ -1256,6 +1256,163 @@ static bool schema_typed(const xlb_schema& s) {
     return false;
 }
 
+// ---- dictionary encoding -----------------------------------------------------------------------
+namespace {
+// order-preserving unsigned image of one value, widened to 64 bits (kind as in order_map_k)
+__device__ __forceinline__ uint64_t dict_image(const void* col, int width, int kind, uint64_t i) {
+    if (width == 4) {
+        uint32_t x = ((const uint32_t*)col)[i];
+        const uint32_t sign = 0x80000000u;
+        if (kind == 1) x ^= sign;
+        else if (kind == 2) x = (x & sign) ? ~x : (x | sign);
+        return x;
+    }
+    uint64_t x = ((const uint64_t*)col)[i];
+    const uint64_t sign = 1ull << 63;
+    if (kind == 1) x ^= sign;
+    else if (kind == 2) x = (x & sign) ? ~x : (x | sign);
+    return x;
+}
+__global__ void dict_image_k(const void* col, int width, int kind, uint64_t* __restrict__ out, uint64_t n) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) out[i] = dict_image(col, width, kind, i);
+}
+// number of dictionary entries below v
+__device__ __forceinline__ uint64_t dict_below(const uint64_t* __restrict__ dict, uint64_t m, uint64_t v) {
+    uint64_t lo = 0, hi = m;
+    while (lo < hi) {
+        uint64_t mid = (lo + hi) >> 1;
+        if (dict[mid] < v) lo = mid + 1;
+        else hi = mid;
+    }
+    return lo;
+}
+__global__ void dict_rank_k(const void* col, int width, int kind, const uint64_t* __restrict__ dict, uint64_t m, uint32_t* __restrict__ out, uint64_t n,
+                            DevStatus* st) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t v = dict_image(col, width, kind, i);
+        const uint64_t r = dict_below(dict, m, v);
+        if (r >= m || dict[r] != v) {  // every value was put into the dictionary: a miss means it is not the right one
+            set_status(st, XLB_ERR_CAPACITY, 10, v);
+            out[i] = 0;
+        } else out[i] = (uint32_t)r;
+    }
+}
+__global__ void dict_decode_k(const uint32_t* __restrict__ ranks, const uint64_t* __restrict__ dict, uint64_t m, int width, int kind, void* out, uint64_t n,
+                              DevStatus* st) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t r = ranks[i];
+        if (r >= m) {
+            set_status(st, XLB_ERR_CAPACITY, 11, r);
+            continue;
+        }
+        uint64_t x = dict[r];
+        if (width == 4) {
+            uint32_t y = (uint32_t)x;
+            const uint32_t sign = 0x80000000u;
+            if (kind == 1) y ^= sign;
+            else if (kind == 2) y = (y & sign) ? (y ^ sign) : ~y;
+            ((uint32_t*)out)[i] = y;
+        } else {
+            const uint64_t sign = 1ull << 63;
+            if (kind == 1) x ^= sign;
+            else if (kind == 2) x = (x & sign) ? (x ^ sign) : ~x;
+            ((uint64_t*)out)[i] = x;
+        }
+    }
+}
+__global__ void dict_bounds_k(const uint64_t* __restrict__ dict, uint64_t m, const uint64_t* __restrict__ consts, uint32_t k, uint64_t* __restrict__ out) {
+    uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= k) return;
+    const uint64_t v = consts[i];
+    const uint64_t below = dict_below(dict, m, v);
+    out[2 * i] = below;
+    out[2 * i + 1] = below + ((below < m && dict[below] == v) ? 1 : 0);
+}
+}  // namespace
+
+static int order_kind(uint8_t t);
+
+Keys ops_dict_build(xlb_ctx* c, const std::vector<const xlb_rel*>& rels) {
+    uint64_t total = 0;
+    for (const xlb_rel* r : rels) total += r->rows * r->schema.arity;
+    Keys k;
+    k.n = total;
+    k.buf = make_buf(c, total * 8);
+    uint64_t at = 0;
+    for (const xlb_rel* r : rels) {
+        if (!r->rows) continue;
+        ops_rel_columns(c, r);
+        for (uint32_t i = 0; i < r->schema.arity; ++i) {
+            prof_begin(c, "dict_image", r->rows * 12ull);
+            dict_image_k<<<grid_for(c, r->rows), BLOCK, 0, c->stream>>>(r->cols[i]->p, (int)type_width(r->schema.types[i]), order_kind(r->schema.types[i]),
+                                                                       k.buf->as<uint64_t>() + at, r->rows);
+            check_launch(c, "dict_image");
+            at += r->rows;
+        }
+    }
+    ops_sort(c, k);
+    ops_dedup_sorted(c, k);
+    if (k.n >= 0xFFFFFFFFull) xlb_fail(XLB_ERR_CAPACITY, "%llu distinct values exceed the 2^32 - 1 a plan over wide columns can hold", (unsigned long long)k.n);
+    return k;
+}
+
+xlb_rel* ops_dict_encode(xlb_ctx* c, const xlb_rel* r, const Keys& dict) {
+    ops_rel_columns(c, r);
+    std::unique_ptr<xlb_rel> o(new xlb_rel);
+    o->ctx = c;
+    o->rows = r->rows;
+    o->schema.arity = r->schema.arity;
+    o->canonical = r->canonical;  // ranks order as the values do
+    for (uint32_t i = 0; i < r->schema.arity; ++i) {
+        o->schema.types[i] = XLB_U32;
+        o->cols[i] = make_buf(c, r->rows * 4);
+        if (!r->rows) continue;
+        prof_begin(c, "dict_rank", r->rows * 12ull);
+        dict_rank_k<<<grid_for(c, r->rows), BLOCK, 0, c->stream>>>(r->cols[i]->p, (int)type_width(r->schema.types[i]), order_kind(r->schema.types[i]), dict.ptr(), dict.n,
+                                                                  o->cols[i]->as<uint32_t>(), r->rows, c->d_status);
+        check_launch(c, "dict_rank");
+    }
+    return o.release();
+}
+
+xlb_rel* ops_dict_decode(xlb_ctx* c, const xlb_rel* ranks, const xlb_schema& types, const Keys& dict) {
+    if (ranks->schema.arity != types.arity) xlb_fail(XLB_ERR_INVALID, "internal: decoding %u columns into %u", ranks->schema.arity, types.arity);
+    ops_rel_columns(c, ranks);
+    std::unique_ptr<xlb_rel> o(new xlb_rel);
+    o->ctx = c;
+    o->rows = ranks->rows;
+    o->schema = types;
+    o->canonical = ranks->canonical;
+    for (uint32_t i = 0; i < types.arity; ++i) {
+        const uint32_t w = type_width(types.types[i]);
+        o->cols[i] = make_buf(c, ranks->rows * w);
+        if (!ranks->rows) continue;
+        prof_begin(c, "dict_decode", ranks->rows * (4ull + w));
+        dict_decode_k<<<grid_for(c, ranks->rows), BLOCK, 0, c->stream>>>(ranks->cols[i]->as<uint32_t>(), dict.ptr(), dict.n, (int)w, order_kind(types.types[i]), o->cols[i]->p,
+                                                                        ranks->rows, c->d_status);
+        check_launch(c, "dict_decode");
+    }
+    return o.release();
+}
+
+void ops_dict_bounds(xlb_ctx* c, const Keys& dict, const std::vector<uint64_t>& consts, std::vector<uint64_t>& below, std::vector<uint64_t>& not_above) {
+    below.assign(consts.size(), 0);
+    not_above.assign(consts.size(), 0);
+    for (size_t base = 0; base < consts.size(); base += 8) {  // the pinned staging area holds a few words at a time
+        const uint32_t k = (uint32_t)std::min<size_t>(8, consts.size() - base);
+        Keys cs = ops_from_host(c, consts.data() + base, k);
+        Buf out = make_buf(c, 2 * k * 8);
+        dict_bounds_k<<<1, 32, 0, c->stream>>>(dict.ptr(), dict.n, cs.ptr(), k, out->as<uint64_t>());
+        check_launch(c, "dict_bounds");
+        unsigned long long h[16];
+        read_words(c, out->p, 2 * (int)k, h);
+        for (uint32_t i = 0; i < k; ++i) {
+            below[base + i] = h[2 * i];
+            not_above[base + i] = h[2 * i + 1];
+        }
+    }
+}
+
 // forward: a view of `r` whose typed columns are mapped to unsigned words (schema becomes
 // unsigned); inverse: `r` is an unsigned result, `types` the schema to restore.
 static xlb_rel* map_rel(xlb_ctx* c, const xlb_rel* r, const xlb_schema& types, bool inverse) {

@@ -116,6 +116,18 @@ Keys ops_semi_filter(xlb_ctx* c, const Keys& bag, int keysel, const Index& ix, b
 // match[i] != 0 flags for semi / anti joins (device array of bag.n words)
 Buf ops_probe_match(xlb_ctx* c, const Keys& bag, int keysel, const uint64_t* pkeys, const Index& ix);
 
+// Dictionary encoding for the executor: relations whose columns are not all 32-bit unsigned
+// (u64, signed, floating) run through the fixpoint as relations of dense 32-bit ranks.  The
+// dictionary holds the order-preserving unsigned images (widened to 64 bits) of every value of
+// every column, sorted and unique, so ranks compare as the values do and results come out in the
+// values' order.
+Keys ops_dict_build(xlb_ctx* c, const std::vector<const xlb_rel*>& rels);
+xlb_rel* ops_dict_encode(xlb_ctx* c, const xlb_rel* r, const Keys& dict);                            // same arity, u32 rank columns
+xlb_rel* ops_dict_decode(xlb_ctx* c, const xlb_rel* ranks, const xlb_schema& types, const Keys& dict);  // ranks back to values
+// For every constant (as an unsigned value): the number of dictionary entries below it and the
+// number not above it (equal: the constant is absent).
+void ops_dict_bounds(xlb_ctx* c, const Keys& dict, const std::vector<uint64_t>& consts, std::vector<uint64_t>& below, std::vector<uint64_t>& not_above);
+
 // owner rank of every row by the half `keysel`; stable partition into `world` runs.
 // counts_out[world] (host) receives the run lengths; returns the partitioned copy.
 Keys ops_partition_by_owner(xlb_ctx* c, const Keys& in, int keysel, uint32_t world, std::vector<uint64_t>& counts_out);
