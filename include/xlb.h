@@ -261,7 +261,11 @@ xlb_status xlb_store_put(xlb_ctx* ctx, const char* name, xlb_rel* rel);
 xlb_status xlb_store_get(xlb_ctx* ctx, const char* name, const xlb_rel** rel);
 xlb_status xlb_store_remove(xlb_ctx* ctx, const char* name);
 /* execute_plan(&ExecutionPlan) (executor/mod.rs:1404-1469); recursive SCCs run the semi-naive
- * loop of execute_recursive_scc (executor/recursive.rs:447-957).  `stats` may be NULL. */
+ * loop of execute_recursive_scc (executor/recursive.rs:447-957).  `stats` may be NULL.
+ * Relations of one or two columns.  u32 / symbol columns run as they are; when a relation or a
+ * declared head has u64, signed or floating columns, the plan runs on 32-bit ranks of one sorted
+ * dictionary of all values and the heads are decoded into their declared types (one GPU; at most
+ * 2^32 - 1 distinct values; no constant filters over signed or floating columns). */
 xlb_status xlb_execute_plan(xlb_ctx* ctx, const xlb_plan* plan, xlb_run_stats* stats);
 
 /* ---- allocation-free entry point ---------------------------------------------------------- */
