@@ -1301,6 +1301,7 @@ extern "C" xlb_status xlb_execute_plan(xlb_ctx* c, const xlb_plan* plan, xlb_run
         try {
             enc.rollback();
         } catch (...) {
+            // the error already being reported is the one the caller sees
         }
     }
     xlb_resolve_phase_timers(c);

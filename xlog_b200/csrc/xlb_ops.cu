@@ -761,17 +761,6 @@ Keys ops_partition_by_owner_dev(xlb_ctx* c, const Keys& in, int keysel, uint32_t
     return out;
 }
 
-Keys ops_partition_by_owner(xlb_ctx* c, const Keys& in, int keysel, uint32_t world, std::vector<uint64_t>& counts_out) {
-    counts_out.assign(world, 0);
-    Buf cnt = make_buf(c, 64 * 8);
-    Keys out = ops_partition_by_owner_dev(c, in, keysel, world, cnt->as<unsigned long long>());
-    if (in.n == 0) return out;
-    unsigned long long h[64];
-    read_words(c, cnt->p, (int)world, h);
-    for (uint32_t r = 0; r < world; ++r) counts_out[r] = h[r];
-    return out;
-}
-
 // ------------------------------------------------------------------------------ C ABI: context
 #define API_BEGIN(ctxp) \
     xlb_ctx* ctx__ = (ctxp); \

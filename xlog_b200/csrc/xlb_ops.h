@@ -128,10 +128,8 @@ xlb_rel* ops_dict_decode(xlb_ctx* c, const xlb_rel* ranks, const xlb_schema& typ
 // number not above it (equal: the constant is absent).
 void ops_dict_bounds(xlb_ctx* c, const Keys& dict, const std::vector<uint64_t>& consts, std::vector<uint64_t>& below, std::vector<uint64_t>& not_above);
 
-// owner rank of every row by the half `keysel`; stable partition into `world` runs.
-// counts_out[world] (host) receives the run lengths; returns the partitioned copy.
-Keys ops_partition_by_owner(xlb_ctx* c, const Keys& in, int keysel, uint32_t world, std::vector<uint64_t>& counts_out);
-// The same without the read-back: the `world` run lengths are left in device memory at `counts_dev`.
+// owner rank of every row by the half `keysel`; stable partition into `world` runs, whose lengths
+// are left in device memory at `counts_dev` (no read-back); returns the partitioned copy.
 Keys ops_partition_by_owner_dev(xlb_ctx* c, const Keys& in, int keysel, uint32_t world, unsigned long long* counts_dev);
 
 // Per-phase event timing (XLB_FLAG_PROFILE): bracket with phase_begin / phase_end.
