@@ -92,7 +92,10 @@ typedef struct xlb_config {
                                       the state (full, delta) can be saved; a later
                                       xlb_execute_plan that finds the delta of every head of an SCC
                                       in the store resumes that SCC from them instead of seeding it */
-
+#define XLB_FLAG_SHUFFLE_ONLY 8u   /* several ranks: never give every rank a full copy of a relation
+                                      (no replicated evaluation of small-domain components, no
+                                      broadcast of small stored relations): every join runs on hash
+                                      partitions with an all-to-all exchange                          */
 
 /* ---- context ------------------------------------------------------------------------------ */
 
@@ -280,13 +283,17 @@ xlb_status xlb_execute_plan(xlb_ctx* ctx, const xlb_plan* plan, xlb_run_stats* s
  *     (tile counts, tile offsets, scan partials) is a fixed array of about 385 KiB inside the
  *     library image, held by every GPU that loads the library until the process exits;
  *   - n above xlb_dedup_sorted_u64_static_max() (2^26 keys) is refused with XLB_ERR_CAPACITY;
+ *   - `d_unique` must not overlap `d_sorted` (blocks write output while others still read
+ *     input): overlapping ranges are refused with XLB_ERR_INVALID before anything is launched;
+ *     so is a call made while an earlier CUDA error of the caller is still pending
+ *     (XLB_ERR_CUDA; the pending error is left for the caller to read);
  *   - the first call on each device looks up the array's device address
- *     (cudaGetSymbolAddress); make that first call before starting any stream capture;
+ *     (cudaGetSymbolAddress); make that first call before starting any stream capture.  Every
+ *     call waits for the stream before it returns;
  *   - every call shares the one array: calls that may overlap on the GPU (different streams,
  *     different host threads) race on it and must be serialised by the caller.  The array
  *     keeps the last call's contents; each call overwrites every word it later reads;
- *   - returns after the stream has been synchronised.  xlb_static_last_error() gives the
- *     message of the calling thread's last failing call. */
+ *   - xlb_static_last_error() gives the message of the calling thread's last failing call. */
 xlb_status xlb_dedup_sorted_u64_static(const uint64_t* d_sorted, uint64_t n, uint64_t* d_unique,
                                        uint64_t* d_count, void* cuda_stream);
 uint64_t xlb_dedup_sorted_u64_static_max(void);
@@ -318,6 +325,19 @@ xlb_status xlb_comm_init(xlb_ctx* ctx, const uint8_t id[XLB_UNIQUE_ID_BYTES], ui
                          uint32_t world);
 /* Owner rank of a join-key value: identical on host and device. */
 uint32_t xlb_owner_of(uint64_t key, uint32_t world);
+/* Test support, no counterpart in the reference: puts the context into the state that an exchange
+ * which timed out or failed leaves behind (communicator aborted), without any device work.  Every
+ * later call that needs the other ranks then fails at once with XLB_ERR_NCCL.  On a context that
+ * never joined a communicator it first records a world of two ranks. */
+xlb_status xlb_comm_mark_aborted_for_test(xlb_ctx* ctx);
+/* Test support, no counterpart in the reference.  Every wait inside a kernel is bounded: a tile of
+ * the one-sweep radix sort polls at most `spin_limit` times (0 = the default, 2^22) for the tiles
+ * before it, then reports XLB_ERR_TIMEOUT through the device status word and returns.  With
+ * `first_tile` = 1 the tiles take their numbers from 1, so tile 0 never runs and never publishes
+ * its counts: every other tile's wait runs out, which is how a test sees the limit work without
+ * hanging the device (0 = normal numbering).  The result of such a sort is garbage, the call fails
+ * with XLB_ERR_TIMEOUT, and the context stays usable. */
+xlb_status xlb_test_set_lookback(xlb_ctx* ctx, uint32_t spin_limit, uint32_t first_tile);
 
 #ifdef __cplusplus
 }

@@ -3,6 +3,15 @@
 Runs only where at least two GPUs are visible.  Every rank loads a slice of each input, all
 ranks run the same plan, and the gathered shards must equal the CPU oracle's single-rank result
 bit for bit; shards must be disjoint and the derived-tuple count must be the global one.
+
+Every program runs in each way the library evaluates a component on several ranks:
+  replicated   heads of a small dense domain live on every rank as bitmaps; one OR of the ranks'
+               candidate bitmaps per iteration (the default for these small inputs);
+  sliced       the same with the large stored relation left in slices (forced here by lowering
+               the size from which a relation counts as large);
+  broadcast    hash-partitioned heads, stored relations copied to every rank (XLB_FLAG_NO_DENSE
+               switches the bitmaps off);
+  shuffle      everything hash-partitioned, an all-to-all per join step (XLB_FLAG_SHUFFLE_ONLY).
 """
 import os
 import socket
@@ -46,6 +55,12 @@ def _cases():
     ]
 
 
+def _modes():
+    from xlog_b200 import _abi as A
+    return [("replicated", 0, None), ("sliced", 0, "64"), ("broadcast", A.FLAG_NO_DENSE, None),
+            ("shuffle", A.FLAG_SHUFFLE_ONLY, None), ("shuffle_sorted", A.FLAG_SHUFFLE_ONLY | A.FLAG_NO_DENSE, None)]
+
+
 def _rank_main(rank, world, port, out_dir):
     import sys
     sys.path.insert(0, ROOT)
@@ -63,8 +78,14 @@ def _rank_main(rank, world, port, out_dir):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         results = {}
-        for name, plan, inputs, out in _cases():
-            prov = KernelProvider(device=rank)
+        for mode, flags, slice_min in _modes():
+          if slice_min is None:
+              os.environ.pop("XLB_REPL_SLICE_MIN", None)
+          else:
+              os.environ["XLB_REPL_SLICE_MIN"] = slice_min
+          for case, plan, inputs, out in _cases():
+            name = f"{mode}/{case}"
+            prov = KernelProvider(device=rank, flags=flags)
             D.init_comm(prov, rank, world)
             ex = Executor(prov)
             for rel, rid in plan.rel_ids.items():
@@ -96,13 +117,19 @@ def test_sharded_fixpoints_match_the_oracle(oracle, tmp_path):
     world = 2 if n < 4 else 4
     mp.spawn(_rank_main, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     results = np.load(tmp_path / "results.npy", allow_pickle=True).item()
-    for name, plan, inputs, out in _cases():
-        want, ex = oracle.run_program(plan, inputs, [out])
+    for case, plan, inputs, out in _cases():
+      want, ex = oracle.run_program(plan, inputs, [out])
+      for mode, _, _ in _modes():
+        name = f"{mode}/{case}"
+        if name not in results:
+            continue
         got = results[name]
         assert len(got["cols"]) == len(want[out])
         for g, w in zip(got["cols"], want[out]):
             assert np.array_equal(g, w), f"{name}: gathered shards differ from the oracle"
         assert sum(got["sizes"]) == len(want[out][0]), f"{name}: shards overlap"
-        if name != "negation":      # derived_tuples counts every head of the plan; that plan has three
-            assert got["derived"] == len(want[out][0])
-        assert got["exchange_bytes"] > 0
+        if case != "negation":      # derived_tuples counts every head of the plan; that plan has three
+            assert got["derived"] == len(want[out][0]), name
+        if case not in ("negation", "triangle"):
+            assert got["iterations"] == ex.iterations, f"{name}: the ranks stopped in another round than one rank does"
+        assert got["exchange_bytes"] > 0, name

@@ -27,6 +27,7 @@ EQ, NE, LT, LE, GT, GE = range(6)
 FLAG_PROFILE = 1
 FLAG_NO_DENSE = 2
 FLAG_KEEP_DELTAS = 4
+FLAG_SHUFFLE_ONLY = 8
 
 
 class Schema(C.Structure):

@@ -360,7 +360,15 @@ struct xlb_ctx {
     std::map<std::string, uint64_t> versions;
     struct IndexCache* indexes = nullptr;
     Comm* comm = nullptr;
+    // `world` / `rank` are what the executor plans by; while a strongly connected component runs
+    // on replicated relations they read 1 / 0 although the communicator has comm_world ranks.
     uint32_t rank = 0, world = 1;
+    uint32_t comm_rank = 0, comm_world = 1;
+    void (*wait_hook)(xlb_ctx*) = nullptr;  // set with a communicator: host waits then watch it as well
+    // bounded look-back of the one-sweep sort: polls before a tile gives up (XLB_ERR_TIMEOUT), and
+    // the number the first tile takes (0; a test makes tile 0 never run so that the wait runs out)
+    unsigned lb_spin_limit = 1u << 22, lb_first_tile = 0;
+    bool sort_attr_set = false;  // the scatter kernels' shared-memory opt-in was made on this context's device
     // per-kernel event timing (xlb_profile_enable)
     struct ProfEntry {
         uint64_t launches = 0, bytes = 0;
@@ -441,6 +449,10 @@ inline void check_launch(xlb_ctx* c, const char* what) {
 
 // Read `n` 64-bit words from device memory (one stream synchronisation).
 inline void stream_wait(xlb_ctx* c) {
+    if (c->wait_hook) {  // several ranks: never block for good on a stream a late peer may be holding up
+        c->wait_hook(c);
+        return;
+    }
     auto t0 = std::chrono::steady_clock::now();
     static const bool spin = getenv("XLB_BLOCKING_WAIT") == nullptr;
     if (spin) {  // poll first: a fixpoint waits for a row count many times, and a blocked thread's wake-up

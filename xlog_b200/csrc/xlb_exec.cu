@@ -26,6 +26,7 @@ struct CachedIndex {
     Index ix;
     uint64_t version = 0;   // store version of the relation the rows came from
     bool table_ok = false;  // hash table matches ix.S
+    bool local = false;     // several ranks: built over the rows this rank holds, not over its hash partition
 };
 struct IndexCache {
     std::map<std::pair<std::string, int>, CachedIndex> m;
@@ -252,7 +253,30 @@ struct RunState {
     std::map<std::string, Pending> pending;
     std::map<std::string, xlb_schema> head_schema;
     std::map<std::pair<std::string, int>, int> scans;  // scan joins run so far per (relation, key column)
+    // Several ranks.  Relations whose rows every rank holds in full while the running component is
+    // evaluated: full copies of small stored relations (kept in the store under an alias name) and,
+    // in replicated mode, the component's own heads.  A join against one of them needs no exchange.
+    std::set<std::string> replicated;
+    std::vector<std::string> aliases;  // alias names to remove from the store when the component is done
+    // Replicated mode: the component's heads fit a small dense domain, so every rank keeps all of
+    // their tuples (a bitmap and the sorted list), evaluates its share of every rule variant into a
+    // candidate bitmap, and one OR over the ranks' bitmaps per head and iteration replaces the
+    // counted all-to-all, the per-rank sort and the termination vote.
+    struct Repl {
+        bool on = false;
+        uint32_t rank = 0, world = 1;
+        int vb = 1;                             // bit length of the largest value any column holds, agreed by all ranks
+        std::map<std::string, DenseSet> cand;   // per head: this iteration's candidate bitmap, shared by its rule variants
+        std::set<std::string> sliced;           // stored relations of which every rank joins only its own rows
+    } repl;
+    // Partitioned mode: join chunks per rule variant, agreed by all ranks with the termination vote
+    // of the iteration before (every rank runs the same number of exchanges).
+    uint64_t agreed_chunks = 1, max_cand_local = 0;
 };
+
+static bool local_build(xlb_ctx* c, const RunState& rs, const std::string& name) {
+    return c->comm_world > 1 && (c->world == 1 || rs.replicated.count(name));
+}
 
 // Rows of relation `name` arranged for a join on column kc: (key << 32) | other, sorted.
 // kc 0 / 1: join index on that column.  kc == ROW_INDEX: the whole row is the key (membership of a
@@ -285,9 +309,9 @@ static Keys index_rows(xlb_ctx* c, const xlb_rel* r, int kc) {
 }
 
 // Is a current index of `name` on column kc in the cache?
-static bool index_ready(xlb_ctx* c, const std::string& name, int kc) {
+static bool index_ready(xlb_ctx* c, const std::string& name, int kc, const RunState& rs) {
     auto it = cache(c).m.find({name, kc});
-    return it != cache(c).m.end() && it->second.version == c->versions[name] && it->second.ix.built();
+    return it != cache(c).m.end() && it->second.version == c->versions[name] && it->second.ix.built() && it->second.local == local_build(c, rs, name);
 }
 
 static const Index& get_index(xlb_ctx* c, const std::string& name, int kc, RunState& rs) {
@@ -296,7 +320,16 @@ static const Index& get_index(xlb_ctx* c, const std::string& name, int kc, RunSt
     CachedIndex& ci = cache(c).m[{name, kc}];
     uint64_t ver = c->versions[name];
     PhaseTimer t(c, &rs.st.ms_join);
-    if ((ci.version != ver || !ci.ix.built()) && (kc == 0 || kc == 1) && r->schema.arity == 2 && !r->canonical && c->world == 1 && !(c->flags & XLB_FLAG_NO_DENSE)) {
+    // With several ranks an index is either over this rank's hash partition of the relation (rows
+    // exchanged by their key first) or over the rows this rank holds (replicated relations, and
+    // everything while a component runs in replicated mode): one kind never stands in for the other.
+    const bool local = local_build(c, rs, name);
+    const bool exchange = c->world > 1 && !local;
+    if (ci.local != local) {
+        ci = CachedIndex();
+        ci.local = local;
+    }
+    if ((ci.version != ver || !ci.ix.built()) && (kc == 0 || kc == 1) && r->schema.arity == 2 && !r->canonical && !exchange && !(c->flags & XLB_FLAG_NO_DENSE)) {
         // A stored relation in no particular order whose join keys come from a small dense domain:
         // group its rows by counting instead of sorting them, and address the groups directly.
         Keys rows = ops_rel_packed(c, r);
@@ -311,12 +344,12 @@ static const Index& get_index(xlb_ctx* c, const std::string& name, int kc, RunSt
         }
     }
     if (ci.version != ver || !ci.ix.built()) {
-        Keys local = index_rows(c, r, kc);
-        if (c->world > 1) local = comm_repartition(c, local, SRC_HI, /*sorted_unique_result=*/true, rs.st);
+        Keys part = index_rows(c, r, kc);
+        if (exchange) part = comm_repartition(c, part, SRC_HI, /*sorted_unique_result=*/true, rs.st);
         ci.ix = Index();
-        ci.ix.S = local.buf;
-        ci.ix.n = local.n;
-        ci.ix.bound = local.bound;
+        ci.ix.S = part.buf;
+        ci.ix.n = part.n;
+        ci.ix.bound = part.bound;
         ci.version = ver;
         ci.table_ok = false;
     }
@@ -393,7 +426,7 @@ static void apply_ready_filters(xlb_ctx* c, FlatRule& fr, Bag& b, RunState& rs) 
         if (k.applied || (k.var != b.hi && k.var != b.lo)) continue;
         const Index& ix = get_index(c, k.rel, k.kc, rs);
         int keysel = src_of(b, k.var);
-        if (c->world > 1 && b.part != k.var) {  // the index is partitioned by its key: take the rows there
+        if (c->world > 1 && b.part != k.var && !rs.replicated.count(k.rel)) {  // the index is partitioned by its key: take the rows there
             b.k = comm_repartition(c, b.k, keysel, false, rs.st);
             b.part = k.var;
         }
@@ -502,16 +535,69 @@ static DenseState* dense_state(xlb_ctx* c, RunState& rs, const std::string& head
     return &ds;
 }
 
+// Replicated mode: the fixed domain of a head (every column holds values of at most vb bits).
+static void repl_bits(const RunState& rs, uint32_t arity, int* hb, int* lb) {
+    *lb = rs.repl.vb;
+    *hb = arity == 2 ? rs.repl.vb : 0;
+}
+
+// Replicated mode: the candidate bitmap of `head` for the running iteration (created on first use),
+// with the head's own bitmap attached so that marking skips what the head holds.
+static DenseSet& repl_cand(xlb_ctx* c, RunState& rs, const std::string& head, const Keys& full, const Keys& novel) {
+    int hb, lb;
+    repl_bits(rs, rs.head_schema[head].arity, &hb, &lb);
+    DenseState* state = dense_state(c, rs, head, hb, lb, full, novel);
+    auto it = rs.repl.cand.find(head);
+    if (it == rs.repl.cand.end()) {
+        DenseSet d = ops_dense_begin(c, state->hi_bits, state->lo_bits);
+        d.shared = true;
+        it = rs.repl.cand.emplace(head, d).first;
+    }
+    it->second.visited = state->visited->as<unsigned int>();
+    return it->second;
+}
+
+// Replicated mode, once per head and iteration: OR the ranks' candidate bitmaps, then count, emit
+// and record what the head lacks.  Every rank ends up with the same new tuples, so the emptiness
+// of an iteration needs no vote.
+static Keys repl_finish(xlb_ctx* c, RunState& rs, const std::string& head, const Keys& full) {
+    Keys none;
+    DenseSet& d = repl_cand(c, rs, head, full, none);
+    {
+        PhaseTimer t(c, &rs.st.ms_exchange);
+        comm_or_bitmaps(c, d.bitmap->as<unsigned int>(), d.words);
+        rs.st.exchange_bytes += d.words * 4 * (uint64_t)(rs.repl.world - 1);
+    }
+    // what other ranks marked is not in this rank's OR bound: the domain's is
+    d.bound = (((1ull << d.hi_bits) - 1) << 32) | ((1ull << d.lo_bits) - 1);
+    PhaseTimer t(c, &rs.st.ms_setops);
+    Keys fresh = ops_dense_finish(c, d, full);
+    rs.dense[head].rows += fresh.n;
+    rs.st.candidate_tuples += d.marked;
+    rs.repl.cand.erase(head);
+    return fresh;
+}
+
 static void dense_sink_begin(xlb_ctx* c, RunState& rs, DenseSink* sink, int hb, int lb) {
+    if (rs.repl.on) {
+        DenseSet& shared = repl_cand(c, rs, sink->head, *sink->full, *sink->novel);
+        sink->state = &rs.dense[sink->head];
+        sink->set = shared;  // shares the bitmap and the count words
+        sink->used = true;
+        return;
+    }
     sink->state = dense_state(c, rs, sink->head, hb, lb, *sink->full, *sink->novel);
     sink->set = ops_dense_begin(c, sink->state->hi_bits, sink->state->lo_bits);
     sink->set.visited = sink->state->visited->as<unsigned int>();
     sink->used = true;
 }
 
+// `out_part`: which half of the returned head tuples decides the rank they already sit on
+// (SRC_HI / SRC_LO), or -1 when they are placed by nothing the head keeps.
 static Keys run_pipeline(xlb_ctx* c, FlatRule fr /*by value: filter flags*/, size_t start, const Keys& start_rows, bool start_is_set, int start_part_half, uint64_t limit,
-                         RunState& rs, DenseSink* sink = nullptr) {
+                         RunState& rs, DenseSink* sink = nullptr, int* out_part = nullptr) {
     std::vector<bool> done(fr.atoms.size(), false);
+    if (out_part) *out_part = -1;
     Bag bag;
     const Atom& sa = fr.atoms[start];
     // every key of the bag occurs once: rows of a one-column set (a join output may repeat keys)
@@ -541,7 +627,7 @@ static Keys run_pipeline(xlb_ctx* c, FlatRule fr /*by value: filter flags*/, siz
             if (!b0 || !b1) continue;
             const Index& ix = get_index(c, a.rel, ROW_INDEX, rs);
             Keys probe = bag.k;
-            if (c->world > 1 && bag.part != a.var[0]) {  // the row index is partitioned by its first column
+            if (c->world > 1 && bag.part != a.var[0] && !rs.replicated.count(a.rel)) {  // the row index is partitioned by its first column
                 PhaseTimer t(c, &rs.st.ms_exchange);
                 probe = comm_repartition(c, probe, src_of(bag, a.var[0]), false, rs.st);
                 bag.part = a.var[0];
@@ -616,7 +702,12 @@ static Keys run_pipeline(xlb_ctx* c, FlatRule fr /*by value: filter flags*/, siz
         Bag nb;
         Keys probe = bag.k;
         int keysel = src_of(bag, keyvar);
-        if (c->world > 1 && bag.part != keyvar) {
+        // a relation every rank holds in full is joined where the bag's rows are; any other sits on
+        // the owners of its join keys, and the bag goes there first
+        const bool rel_everywhere = c->world > 1 && rs.replicated.count(a.rel);
+        int part_after = keyvar;
+        if (rel_everywhere) part_after = bag.part;
+        else if (c->world > 1 && bag.part != keyvar) {
             PhaseTimer t(c, &rs.st.ms_exchange);
             probe = comm_repartition(c, probe, keysel, false, rs.st);
         }
@@ -632,7 +723,7 @@ static Keys run_pipeline(xlb_ctx* c, FlatRule fr /*by value: filter flags*/, siz
             const uint64_t kb = keysel == SRC_HI ? probe.bound >> 32 : probe.bound & 0xFFFFFFFFull;
             int key_bits = 0;
             while (key_bits < 32 && (kb >> key_bits)) ++key_bits;
-            const bool indexed = index_ready(c, a.rel, kc);
+            const bool indexed = index_ready(c, a.rel, kc, rs);
             int& scans = rs.scans[{a.rel, kc}];
             if (r && !indexed && key_bits <= 27 && scans < (r->canonical && kc == 0 ? 3 : 12)) {
                 ++scans;
@@ -643,7 +734,7 @@ static Keys run_pipeline(xlb_ctx* c, FlatRule fr /*by value: filter flags*/, siz
                 Keys shape;
                 shape.n = 1;
                 shape.bound = ops_scan_join_bound(probe, keysel, rows, rel_keysel, rel_src(hs), rel_src(ls));
-                if (sink && last && !pending && ops_dense_bits(shape, sink->known(), &hb, &lb)) {
+                if (sink && last && !pending && (rs.repl.on || ops_dense_bits(shape, sink->known(), &hb, &lb))) {
                     dense_sink_begin(c, rs, sink, hb, lb);
                     ops_scan_join_mark(c, probe, keysel, key_bits, rows, rel_keysel, rel_src(hs), rel_src(ls), sink->set);
                     Keys marked;  // no rows and no count: both are in the sink
@@ -651,10 +742,11 @@ static Keys run_pipeline(xlb_ctx* c, FlatRule fr /*by value: filter flags*/, siz
                     return marked;
                 }
                 nb.k = ops_scan_join(c, probe, keysel, key_bits, rows, rel_keysel, rel_src(hs), rel_src(ls));
-                nb.part = keyvar;
+                nb.part = part_after;
                 if (limit && nb.k.n > limit && start_rows.n > 1) throw ChunkTooBig{};
                 nb.hi = out_hi;
                 nb.lo = out_lo;
+                if (nb.part != nb.hi && nb.part != nb.lo) nb.part = -1;  // the step dropped the variable the rows were placed by
                 bag = nb;
                 bag_keys_unique = false;
                 apply_ready_filters(c, fr, bag, rs);
@@ -668,7 +760,7 @@ static Keys run_pipeline(xlb_ctx* c, FlatRule fr /*by value: filter flags*/, siz
             Keys shape;  // stands for the rows this step would produce: only their OR bound matters here
             shape.n = 1;
             shape.bound = ops_expand_bound(probe, ix, hs, ls);
-            if (sink && last && !pending && c->world == 1 && !(c->flags & XLB_FLAG_NO_DENSE) && ops_dense_bits(shape, sink->known(), &hb, &lb)) {
+            if (sink && last && !pending && c->world == 1 && !(c->flags & XLB_FLAG_NO_DENSE) && (rs.repl.on || ops_dense_bits(shape, sink->known(), &hb, &lb))) {
                 dense_sink_begin(c, rs, sink, hb, lb);
                 ops_join_expand_mark(c, probe, keysel, ix, hs, ls, sink->set);
                 Keys marked;  // no rows and no count: both are in the sink
@@ -676,10 +768,11 @@ static Keys run_pipeline(xlb_ctx* c, FlatRule fr /*by value: filter flags*/, siz
                 return marked;
             }
             nb.k = ops_join_expand(c, probe, keysel, nullptr, ix, hs, ls);
-            nb.part = keyvar;
+            nb.part = part_after;
             if (limit && nb.k.n > limit && start_rows.n > 1) throw ChunkTooBig{};
             nb.hi = out_hi;
             nb.lo = out_lo;
+            if (nb.part != nb.hi && nb.part != nb.lo) nb.part = -1;  // the step dropped the variable the rows were placed by
             bag = nb;
             bag_keys_unique = false;
             apply_ready_filters(c, fr, bag, rs);
@@ -702,6 +795,7 @@ static Keys run_pipeline(xlb_ctx* c, FlatRule fr /*by value: filter flags*/, siz
         PhaseTimer t(c, &rs.st.ms_join);
         bag.k = ops_remap(c, bag.k, sel(want_hi), sel(want_lo));
     }
+    if (out_part) *out_part = bag.part < 0 ? -1 : bag.part == want_hi ? SRC_HI : bag.part == want_lo ? SRC_LO : -1;
     return bag.k;
 }
 
@@ -722,7 +816,7 @@ static void eval_variant(xlb_ctx* c, const FlatRule& fr_in, size_t start, const 
                 if (sa.var[j] == f.lhs) kc = (int)j;
             if (kc < 0 || (sa.arity == 2 && sa.var[0] == sa.var[1])) continue;
             // one filtering pass over the relation costs far less than building its index
-            if (c->world == 1 && !index_ready(c, sa.rel, kc)) continue;
+            if (c->world == 1 && !index_ready(c, sa.rel, kc, rs)) continue;
             const Index& ix = get_index(c, sa.rel, kc, rs);
             uint64_t key = f.rhs;
             Keys probe = ops_from_host(c, &key, 1);
@@ -738,6 +832,21 @@ static void eval_variant(xlb_ctx* c, const FlatRule& fr_in, size_t start, const 
             break;
         }
     }
+    // Several ranks, start rows that every rank holds in full (a replicated relation; in replicated
+    // mode also a delta): each rank takes its slice of them, unless the rule joins a relation of
+    // which every rank holds only its own rows, which splits the work already.
+    {
+        const std::string& srel = fr.atoms[start].rel;
+        const bool everywhere = c->comm_world > 1 && (rs.repl.on ? !rs.repl.sliced.count(srel) : (start_is_stored && rs.replicated.count(srel) > 0));
+        bool split_by_rule = false;
+        if (rs.repl.on)
+            for (auto& a : fr.atoms) split_by_rule |= rs.repl.sliced.count(a.rel) > 0;
+        if (everywhere && !split_by_rule) {
+            const uint64_t n = start_rows.n, lo = n * c->comm_rank / c->comm_world, hi = n * (c->comm_rank + 1) / c->comm_world;
+            if (lo != 0 || hi != n) start_rows = ops_slice(c, start_rows, lo, hi);
+            start_part_half = -1;  // a slice by position: its rows are placed by no column
+        }
+    }
     if (start_rows.n == 0 && c->world == 1) return;
     bool start_is_set = true;  // a delta is; a stored relation when it is certified sorted and unique
     if (start_is_stored) {
@@ -745,17 +854,22 @@ static void eval_variant(xlb_ctx* c, const FlatRule& fr_in, size_t start, const 
         start_is_set = sr && sr->canonical;
     }
     uint64_t limit = c->join_chunk;
-    // with several ranks every rank runs the same sequence of exchanges, so the rows are not
-    // chunked (chunk counts would differ between ranks)
-    if (c->world > 1) limit = 0;
-    else if (!limit) {
+    if (!limit) {
         uint64_t room = c->budget > c->allocated ? c->budget - c->allocated : 0;
         limit = std::max<uint64_t>(room / (8 * 8), 1u << 20);  // a chunk is held, sorted and merged: ~8 copies
     }
+    // With several ranks on hash partitions every rank runs the same sequence of exchanges, so the
+    // number of chunks is the one all ranks agreed on with the last vote, and no chunk is split.
+    const bool fixed_chunks = c->world > 1;
     uint64_t chunk = std::max<uint64_t>(start_rows.n, 1), at = 0;
-    bool first = true;
-    while (at < start_rows.n || (first && c->world > 1)) {
-        first = false;
+    uint64_t rounds_left = 1;
+    if (fixed_chunks) {
+        rounds_left = std::max<uint64_t>(rs.agreed_chunks, 1);
+        chunk = std::max<uint64_t>((start_rows.n + rounds_left - 1) / rounds_left, 1);
+        limit = 0;
+    }
+    while (fixed_chunks ? rounds_left > 0 : at < start_rows.n) {
+        if (fixed_chunks) --rounds_left;
         uint64_t hi = std::min(start_rows.n, at + chunk);
         Keys part = (at == 0 && hi == start_rows.n) ? start_rows : ops_slice(c, start_rows, at, hi);
         Keys cand;
@@ -763,13 +877,19 @@ static void eval_variant(xlb_ctx* c, const FlatRule& fr_in, size_t start, const 
         sink.head = fr.head;
         sink.full = &full;
         sink.novel = &novel;
+        int placed = -1;
         try {
-            cand = run_pipeline(c, fr, start, part, start_is_set, start_part_half, limit, rs, &sink);
+            cand = run_pipeline(c, fr, start, part, start_is_set, start_part_half, limit, rs, &sink, &placed);
         } catch (const ChunkTooBig&) {
             chunk = std::max<uint64_t>((hi - at) / 2, 1);
             continue;
         }
         at = hi;
+        if (sink.used && rs.repl.on) {
+            // marked into the head's shared candidate bitmap: counted and emitted once per iteration
+            rs.repl.cand[fr.head].bound |= sink.set.bound;
+            continue;
+        }
         if (sink.used) {
             // the last join marked its tuples in the bitmap already (single rank only); how many
             // there were comes back with the count of the new ones
@@ -781,7 +901,13 @@ static void eval_variant(xlb_ctx* c, const FlatRule& fr_in, size_t start, const 
             continue;
         }
         rs.st.candidate_tuples += cand.n;
-        if (c->world > 1) {
+        rs.max_cand_local = std::max(rs.max_cand_local, cand.n);
+        if (rs.repl.on) {
+            PhaseTimer t(c, &rs.st.ms_setops);
+            ops_dense_mark_into(c, repl_cand(c, rs, fr.head, full, novel), cand);
+            continue;
+        }
+        if (c->world > 1 && placed != home_sel) {
             PhaseTimer t(c, &rs.st.ms_exchange);
             cand = comm_repartition(c, cand, home_sel, false, rs.st);
         }
@@ -883,6 +1009,7 @@ static void seed_pass(xlb_ctx* c, const std::vector<FlatRule>& rules, const std:
     }
     for (auto& p : preds) {
         Keys full_old = canonical_keys(c, store_get(c, p), rs);
+        if (rs.repl.on) novel[p] = repl_finish(c, rs, p, full_old);
         Keys& d = novel[p];
         if (!d.buf) d.buf = make_buf(c, 0);
         Keys full_new;
@@ -893,6 +1020,213 @@ static void seed_pass(xlb_ctx* c, const std::vector<FlatRule>& rules, const std:
         if (make_delta) store_put(c, "__delta_" + p, ops_rel_from_keys(c, schema[p], d, true));
         install_full(c, p, schema[p], full_new, nullptr, rs);
     }
+}
+
+// ------------------------------------------------------------------------------ several ranks
+// rows: a smaller stored relation is copied to every rank rather than joined slice by slice
+// (XLB_REPL_SLICE_MIN overrides it, so that a test can run the sliced route on a small input)
+static uint64_t repl_slice_min() {
+    const char* v = getenv("XLB_REPL_SLICE_MIN");
+    return v ? strtoull(v, nullptr, 10) : (1ull << 20);
+}
+constexpr uint64_t REPL_COPY_MAX = 1ull << 27;         // rows: the largest relation replicated mode copies to every rank (1 GiB)
+constexpr uint64_t BROADCAST_MAX = 1ull << 25;         // rows: the largest stored relation a partitioned component copies to every rank
+
+static int bit_len(uint64_t v) { return v ? 64 - __builtin_clzll(v) : 0; }
+
+static uint64_t chunk_limit(xlb_ctx* c) {
+    if (c->join_chunk) return c->join_chunk;
+    uint64_t room = c->budget > c->allocated ? c->budget - c->allocated : 0;
+    return std::max<uint64_t>(room / (8 * 8), 1u << 20);  // a chunk is held, sorted and merged: ~8 copies
+}
+
+// Restores the context's planning view when a component that ran on replicated relations is done.
+struct PlanAsOneRank {
+    xlb_ctx* c = nullptr;
+    uint32_t world = 1;
+    bool on = false;
+    void begin(xlb_ctx* ctx) {
+        c = ctx;
+        world = c->world;
+        c->world = 1;
+        on = true;
+    }
+    void end() {
+        if (on) c->world = world;
+        on = false;
+    }
+    ~PlanAsOneRank() { end(); }
+};
+
+// Several ranks: agree (one small all-gather) on how the component runs, and give every rank a full
+// copy of the stored relations that are cheaper to copy than to join partition by partition.
+//   replicated mode (rs.repl.on): every head fits a dense domain of at most 2^27 tuples; heads and
+//     deltas live on every rank, at most one large stored relation per rule stays in slices;
+//   partitioned mode: heads are hash-partitioned; small stored relations are copied everywhere, so
+//     a join with one needs no exchange and keeps the placement of the rows.
+// Every decision depends only on the plan, the flags and the gathered numbers, so all ranks agree.
+static void setup_ranks(xlb_ctx* c, const xlb_scc& scc, std::vector<FlatRule>& rules, const std::vector<std::string>& preds, const std::set<std::string>& rec,
+                        std::map<std::string, xlb_schema>& schema, RunState& rs) {
+    if (c->world <= 1 || (c->flags & XLB_FLAG_SHUFFLE_ONLY)) return;
+    std::set<std::string> stored, checked;
+    for (auto& fr : rules) {
+        for (auto& a : fr.atoms)
+            if (!rec.count(a.rel)) stored.insert(a.rel);
+        for (auto& k : fr.checks) {
+            if (!rec.count(k.rel)) stored.insert(k.rel);
+            checked.insert(k.rel);
+        }
+    }
+    std::vector<std::string> names(stored.begin(), stored.end());
+    if (names.size() + preds.size() + 2 > COMM_WORDS_MAX) return;  // no agreement vector that long: plain partitioned evaluation
+    bool resume = scc.is_recursive != 0;
+    for (auto& p : preds) resume = resume && store_get(c, "__delta_" + p) != nullptr;
+    // this rank's numbers: rows per relation, the widest value it holds, whether it would resume
+    std::vector<uint64_t> mine;
+    uint64_t values = 0;
+    bool unknown = false;
+    auto look = [&](const std::string& name) {
+        xlb_rel* r = store_get(c, name);
+        mine.push_back(r ? r->rows : 0);
+        if (!r || !r->rows) return;
+        Keys k = ops_rel_packed(c, r);
+        if (k.bound == ~0ull) unknown = true;
+        else values |= (k.bound >> 32) | (k.bound & 0xFFFFFFFFull);
+    };
+    for (auto& n : names) look(n);
+    for (auto& p : preds) look(p);
+    mine.push_back(unknown ? 64 : (uint64_t)bit_len(values));
+    mine.push_back(resume ? 1 : 0);
+    const uint32_t K = (uint32_t)mine.size(), W = c->comm_world;
+    std::vector<uint64_t> all((size_t)W * K);
+    {
+        PhaseTimer t(c, &rs.st.ms_exchange);
+        comm_allgather_words(c, mine.data(), K, all.data());
+    }
+    std::map<std::string, uint64_t> rows;
+    uint64_t head_rows = 0, vb = 1, any_resume = 0;
+    for (uint32_t r = 0; r < W; ++r) {
+        for (size_t i = 0; i < names.size(); ++i) rows[names[i]] += all[(size_t)r * K + i];
+        for (size_t i = 0; i < preds.size(); ++i) head_rows += all[(size_t)r * K + names.size() + i];
+        vb = std::max(vb, all[(size_t)r * K + K - 2]);
+        any_resume |= all[(size_t)r * K + K - 1];
+    }
+    bool repl = scc.is_recursive && !any_resume && !(c->flags & (XLB_FLAG_NO_DENSE | XLB_FLAG_KEEP_DELTAS));
+    for (auto& p : preds) repl = repl && schema[p].arity * vb <= 27;
+    std::set<std::string> sliced, copy;
+    if (repl) {
+        // the largest stored relations stay in slices where no rule would then join two sliced atoms
+        std::vector<std::string> by_size(names);
+        std::sort(by_size.begin(), by_size.end(), [&](const std::string& a, const std::string& b) { return rows[a] != rows[b] ? rows[a] > rows[b] : a < b; });
+        for (auto& n : by_size) {
+            if (rows[n] < repl_slice_min() || checked.count(n)) continue;
+            bool ok = true;
+            for (auto& fr : rules) {
+                int mine_n = 0, others = 0;
+                for (auto& a : fr.atoms) {
+                    mine_n += a.rel == n;
+                    others += sliced.count(a.rel) > 0;
+                }
+                if (mine_n > 1 || (mine_n == 1 && others > 0)) ok = false;
+            }
+            if (ok) sliced.insert(n);
+        }
+        for (auto& n : names)
+            if (!sliced.count(n)) {
+                copy.insert(n);
+                if (rows[n] > REPL_COPY_MAX) repl = false;
+            }
+    }
+    if (!repl) {
+        sliced.clear();
+        copy.clear();
+        for (auto& n : names)
+            if (rows[n] <= BROADCAST_MAX) copy.insert(n);
+    }
+    // the copies: all ranks' rows of the relation, under an alias the rules are pointed to
+    for (auto& n : copy) {
+        xlb_rel* r = store_get(c, n);
+        const std::string alias = "__all_" + n;
+        Keys everything;
+        {
+            PhaseTimer t(c, &rs.st.ms_exchange);
+            Keys local = ops_rel_packed(c, r);
+            everything = comm_allgather_keys(c, local);
+            rs.st.exchange_bytes += local.n * 8 * (uint64_t)(W - 1);
+        }
+        store_put(c, alias, ops_rel_from_keys(c, r->schema, everything, false));
+        rs.aliases.push_back(alias);
+        rs.replicated.insert(alias);
+        for (auto& fr : rules) {
+            for (auto& a : fr.atoms)
+                if (a.rel == n) a.rel = alias;
+            for (auto& k : fr.checks)
+                if (k.rel == n) k.rel = alias;
+        }
+    }
+    if (!repl) return;
+    rs.repl.on = true;
+    rs.repl.rank = c->comm_rank;
+    rs.repl.world = W;
+    rs.repl.vb = (int)vb;
+    rs.repl.sliced = sliced;
+    for (auto& p : preds) {
+        rs.replicated.insert(p);
+        if (!head_rows) continue;
+        // a head that holds rows already: every rank gets all of them, sorted and unique
+        Keys everything;
+        {
+            PhaseTimer t(c, &rs.st.ms_exchange);
+            everything = comm_allgather_keys(c, ops_rel_packed(c, store_get(c, p)));
+        }
+        {
+            PhaseTimer t(c, &rs.st.ms_sort);
+            ops_sort(c, everything);
+        }
+        PhaseTimer t(c, &rs.st.ms_setops);
+        ops_dedup_sorted(c, everything);
+        store_put(c, p, ops_rel_from_keys(c, schema[p], everything, true));
+    }
+}
+
+// Removes the full copies made for a component (and the indexes built over them).
+static void drop_aliases(xlb_ctx* c, RunState& rs) {
+    for (auto& alias : rs.aliases) {
+        auto it = c->store.find(alias);
+        if (it != c->store.end()) {
+            delete it->second;
+            c->store.erase(it);
+            c->versions[alias]++;
+        }
+        for (int kc = 0; kc <= ROW_INDEX; ++kc) cache(c).m.erase({alias, kc});
+        rs.replicated.erase(alias);
+    }
+    rs.aliases.clear();
+}
+
+// Partitioned mode, one head whose recursive rules all carry one of its columns over unchanged
+// from their one recursive atom while every other atom is a relation all ranks hold in full: with
+// the head placed by that column a rank derives only tuples it owns, and no tuple is exchanged.
+static int carried_home(const std::vector<FlatRule>& rules, const std::string& pred, const std::set<std::string>& rec, uint32_t arity, const RunState& rs) {
+    if (arity != 2 || rec.size() != 1) return -1;
+    for (int q = 0; q < 2; ++q) {
+        bool ok = true, any = false;
+        for (auto& fr : rules) {
+            if (fr.head != pred) continue;
+            int nrec = 0, at = -1;
+            for (size_t i = 0; i < fr.atoms.size(); ++i) {
+                if (rec.count(fr.atoms[i].rel)) { ++nrec; at = (int)i; }
+                else if (!rs.replicated.count(fr.atoms[i].rel)) ok = false;
+            }
+            for (auto& k : fr.checks)
+                if (!rs.replicated.count(k.rel)) ok = false;
+            if (nrec == 0) continue;  // a seeding rule: its tuples are sent home once
+            any = true;
+            if (nrec != 1 || fr.atoms[at].arity != 2 || fr.head_vars.size() != 2 || fr.atoms[at].var[q] != fr.head_vars[q]) ok = false;
+        }
+        if (ok && any) return q == 0 ? SRC_HI : SRC_LO;
+    }
+    return -1;
 }
 
 static void run_scc(xlb_ctx* c, const xlb_scc& scc, RunState& rs) {
@@ -929,8 +1263,25 @@ static void run_scc(xlb_ctx* c, const xlb_scc& scc, RunState& rs) {
             rules.push_back(Flattener{c, {}, {}}.run(r));
         }
     }
+    for (auto& p : preds) rs.head_schema[p] = schema[p];
+    struct Cleanup {  // the full copies go when the component is done, however it ends
+        xlb_ctx* c;
+        RunState& rs;
+        ~Cleanup() {
+            drop_aliases(c, rs);
+            rs.repl = RunState::Repl();
+            rs.replicated.clear();
+        }
+    } cleanup{c, rs};
+    PlanAsOneRank one_rank;
+    setup_ranks(c, scc, rules, preds, rec, schema, rs);
     std::map<std::string, int> home;
-    for (auto& p : preds) home[p] = home_half(rules, p, rec, schema[p].arity);
+    for (auto& p : preds) {
+        home[p] = home_half(rules, p, rec, schema[p].arity);
+        const int carried = c->world > 1 && !rs.repl.on && scc.is_recursive ? carried_home(rules, p, rec, schema[p].arity, rs) : -1;
+        if (carried >= 0) home[p] = carried;
+    }
+    if (rs.repl.on) one_rank.begin(c);  // from here to the sharding of the result the component plans as a single rank
     // Heads whose sorted list some rule reads during the loop: the other recursive atoms of a rule
     // with several (a variant reads their full relations), and relations tested by a semi / anti
     // join.  For every other head the merge of an iteration's delta can wait.
@@ -942,7 +1293,6 @@ static void run_scc(xlb_ctx* c, const xlb_scc& scc, RunState& rs) {
             if (nrec >= 2 && rec.count(a.rel)) list_read.insert(a.rel);
         for (auto& k : fr.checks) list_read.insert(k.rel);
     }
-    for (auto& p : preds) rs.head_schema[p] = schema[p];
     if (c->world > 1) {
         // a head relation that already holds rows is re-homed so that equal tuples meet on one rank
         for (auto& p : preds) {
@@ -1016,11 +1366,25 @@ static void run_scc(xlb_ctx* c, const xlb_scc& scc, RunState& rs) {
                 eval_variant(c, fr, i, ops_rel_packed(c, d), false, home[fr.atoms[i].rel], full, home[fr.head], novel[fr.head], rs);
             }
         }
+        if (rs.repl.on)
+            for (auto& p : preds) novel[p] = repl_finish(c, rs, p, full_view(c, rs, p));  // the same tuples on every rank: no vote
         uint64_t changed = 0;
         for (auto& p : preds) changed += novel[p].n;
         if (c->world > 1) {
+            // the emptiness vote; with it the ranks agree on the join chunks of the next iteration
+            // (candidates of one chunk, doubled for growth, within the tightest rank's bound)
             PhaseTimer t(c, &rs.st.ms_exchange);
-            changed = comm_allreduce_sum(c, changed);  // the emptiness vote
+            const uint64_t lim = chunk_limit(c);
+            uint64_t mine[2] = {changed, std::min<uint64_t>((2 * rs.max_cand_local * std::max<uint64_t>(rs.agreed_chunks, 1) + lim - 1) / lim, 4096)};
+            std::vector<uint64_t> all((size_t)c->comm_world * 2);
+            comm_allgather_words(c, mine, 2, all.data());
+            changed = 0;
+            rs.agreed_chunks = 1;
+            for (uint32_t r = 0; r < c->comm_world; ++r) {
+                changed += all[2 * r];
+                rs.agreed_chunks = std::max(rs.agreed_chunks, all[2 * r + 1]);
+            }
+            rs.max_cand_local = 0;
         }
         for (auto& p : preds) {  // :735-858
             Keys& d = novel[p];
@@ -1054,6 +1418,16 @@ static void run_scc(xlb_ctx* c, const xlb_scc& scc, RunState& rs) {
         }
     }
     for (auto& p : preds) materialize_full(c, rs, p);
+    if (rs.repl.on) {
+        // every rank holds the whole result: each keeps the tuples it owns, as the partitioned
+        // evaluation would have left them (sorted, unique, disjoint between ranks)
+        one_rank.end();
+        for (auto& p : preds) {
+            PhaseTimer t(c, &rs.st.ms_setops);
+            Keys mine = ops_filter_owner(c, ops_rel_packed(c, store_get(c, p)), home[p], c->comm_world, c->comm_rank);
+            store_put(c, p, ops_rel_from_keys(c, schema[p], mine, true));
+        }
+    }
     guard.armed = false;  // the loop ended by itself: what follows decides about the deltas
     for (auto& p : preds) {  // :940-945
         if (!fix && (c->flags & XLB_FLAG_KEEP_DELTAS)) break;  // left for a checkpoint

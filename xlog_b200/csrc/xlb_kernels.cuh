@@ -572,7 +572,6 @@ static __global__ void __launch_bounds__(BLOCK) radix_tile_hist_k(const uint64_t
 // A tile only waits for tiles that took an earlier number, which are running already; every
 // wait is bounded and reports XLB_ERR_TIMEOUT through `dst` instead of spinning for ever.
 constexpr unsigned LB_FLAG_AGG = 1u << 30, LB_FLAG_INC = 2u << 30, LB_MASK = (1u << 30) - 1;
-constexpr unsigned LB_SPIN_LIMIT = 1u << 22;
 
 #ifndef XLB_SORT_MINB
 #define XLB_SORT_MINB 4
@@ -581,7 +580,8 @@ template <bool HAS_VALUES, bool LOOKBACK>
 static __global__ void __launch_bounds__(SORT_THREADS, XLB_SORT_MINB) radix_scatter_k(const uint64_t* __restrict__ keys_in, uint64_t* __restrict__ keys_out,
                                                           const uint32_t* __restrict__ vals_in, uint32_t* __restrict__ vals_out,
                                                           uint64_t n, int shift, const uint32_t* __restrict__ offs, uint32_t ntiles,
-                                                          unsigned int* __restrict__ tile_counter, volatile unsigned int* status, DevStatus* dst) {
+                                                          unsigned int* __restrict__ tile_counter, volatile unsigned int* status, DevStatus* dst,
+                                                          unsigned spin_limit) {
     extern __shared__ __align__(16) unsigned char sort_smem[];
     uint64_t* skeys = reinterpret_cast<uint64_t*>(sort_smem);
     unsigned int (*whist)[256] = reinterpret_cast<unsigned int (*)[256]>(sort_smem + SORT_TILE * 8);
@@ -596,6 +596,7 @@ static __global__ void __launch_bounds__(SORT_THREADS, XLB_SORT_MINB) radix_scat
         if (threadIdx.x == 0) tile_s = atomicAdd(tile_counter, 1u);
         __syncthreads();
         tile = tile_s;
+        if (tile >= ntiles) return;  // only when the counter did not start at zero (the bounded-wait test)
     }
     const uint64_t tile_base = (uint64_t)tile * SORT_TILE;
     const uint64_t rem = n - tile_base;
@@ -660,7 +661,7 @@ static __global__ void __launch_bounds__(SORT_THREADS, XLB_SORT_MINB) radix_scat
                     unsigned v = status[(uint64_t)t * 256 + d];
                     unsigned f = v & ~LB_MASK;
                     if (f == 0) {
-                        if (++spins > LB_SPIN_LIMIT) {
+                        if (++spins > spin_limit) {
                             set_status(dst, XLB_ERR_TIMEOUT, 2, tile);
                             break;
                         }
@@ -721,9 +722,10 @@ static __global__ void __launch_bounds__(SORT_THREADS, XLB_SORT_MINB) radix_scat
 
 constexpr size_t SORT_SMEM = (size_t)SORT_TILE * 8 + SORT_WARPS * 1024 + 256 * 4 * 2 + 64 * 4;
 
-// The scatter kernel takes more than the 48 KB a launch gets by default: opt in once per process.
-inline void radix_sort_setup() {
-    static bool done = false;
+// The scatter kernel takes more than the 48 KB a launch gets by default: opt in once per context
+// (the attribute belongs to the device that is current when it is set).
+inline void radix_sort_setup(xlb_ctx* c) {
+    bool& done = c->sort_attr_set;
     if (done) return;
     cudaFuncSetAttribute(radix_scatter_k<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SORT_SMEM);
     cudaFuncSetAttribute(radix_scatter_k<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SORT_SMEM);
@@ -765,7 +767,7 @@ inline SortPlan plan_sort(xlb_ctx* c, const uint64_t* keys, uint64_t n) {
 inline void radix_sort(xlb_ctx* c, Buf& keys, Buf* vals, uint64_t n, unsigned digit_mask = 0xFFu, uint64_t known_bound = ~0ull, bool keep_input = false) {
     if (n <= 1) return;
     if (n >= (1ull << 32)) xlb_fail(XLB_ERR_CAPACITY, "sort of %llu keys exceeds the 2^32 limit of one sort", (unsigned long long)n);
-    radix_sort_setup();
+    radix_sort_setup(c);
     uint32_t ntiles = (uint32_t)((n + SORT_TILE - 1) / SORT_TILE);
     Buf tmpk = make_buf(c, n * 8);
     Buf tmpv = vals ? make_buf(c, n * 4) : Buf();
@@ -776,12 +778,12 @@ inline void radix_sort(xlb_ctx* c, Buf& keys, Buf* vals, uint64_t n, unsigned di
         unsigned int* bases = ghist + 8 * 256;
         unsigned long long* varies = (unsigned long long*)(bases + 8 * 256);
         CUDA_OK(cudaMemsetAsync(ghist, 0, 8 * 256 * 4, c->stream));
-        prof_begin(c, "radix_upfront", n * 8ull);
         unsigned want = digit_mask & 0xFFu;
         if (known_bound != ~0ull)
             for (int d = 0; d < 8; ++d)
                 if (!((known_bound >> (8 * d)) & 255)) want &= ~(1u << d);
         if (want == 0) return;
+        prof_begin(c, "radix_upfront", n * 8ull);
         radix_upfront_k<<<grid_for(c, n, BLOCK * 8), BLOCK, 0, c->stream>>>(keys->as<uint64_t>(), n, ghist, want);
         check_launch(c, "radix_upfront");
         prof_begin(c, "radix_bases", 0);
@@ -801,14 +803,18 @@ inline void radix_sort(xlb_ctx* c, Buf& keys, Buf* vals, uint64_t n, unsigned di
         Buf status = make_buf(c, (status_words * np + 8) * 4);  // per pass: tile status; then 8 tile counters
         CUDA_OK(cudaMemsetAsync(status->p, 0, (status_words * np + 8) * 4, c->stream));
         unsigned int* counters = status->as<unsigned int>() + status_words * np;
+        if (c->lb_first_tile) {  // test knob: tiles take their numbers from here on, so tile 0 never publishes
+            for (int q = 0; q < 8; ++q) ((unsigned int*)&c->h_scalar[56])[q] = c->lb_first_tile;
+            CUDA_OK(cudaMemcpyAsync(counters, &c->h_scalar[56], 8 * 4, cudaMemcpyHostToDevice, c->stream));
+        }
         for (int q = 0; q < np; ++q) {
             int d = digits[q];
             unsigned int* st = status->as<unsigned int>() + status_words * q;
             prof_begin(c, "radix_scatter", n * (vals ? 24ull : 16ull));
             if (vals)
-                radix_scatter_k<true, true><<<ntiles, SORT_THREADS, SORT_SMEM, c->stream>>>(keys->as<uint64_t>(), tmpk->as<uint64_t>(), (*vals)->as<uint32_t>(), tmpv->as<uint32_t>(), n, 8 * d, bases + d * 256, ntiles, counters + q, st, c->d_status);
+                radix_scatter_k<true, true><<<ntiles, SORT_THREADS, SORT_SMEM, c->stream>>>(keys->as<uint64_t>(), tmpk->as<uint64_t>(), (*vals)->as<uint32_t>(), tmpv->as<uint32_t>(), n, 8 * d, bases + d * 256, ntiles, counters + q, st, c->d_status, c->lb_spin_limit);
             else
-                radix_scatter_k<false, true><<<ntiles, SORT_THREADS, SORT_SMEM, c->stream>>>(keys->as<uint64_t>(), tmpk->as<uint64_t>(), nullptr, nullptr, n, 8 * d, bases + d * 256, ntiles, counters + q, st, c->d_status);
+                radix_scatter_k<false, true><<<ntiles, SORT_THREADS, SORT_SMEM, c->stream>>>(keys->as<uint64_t>(), tmpk->as<uint64_t>(), nullptr, nullptr, n, 8 * d, bases + d * 256, ntiles, counters + q, st, c->d_status, c->lb_spin_limit);
             check_launch(c, "radix_scatter");
             if (keep_input && q == 0) {
                 keys = tmpk;
@@ -835,9 +841,9 @@ inline void radix_sort(xlb_ctx* c, Buf& keys, Buf* vals, uint64_t n, unsigned di
         exclusive_scan<LoadU32, uint32_t>(c, LoadU32{hist->as<uint32_t>()}, (uint64_t)256 * ntiles, offs->as<uint32_t>(), total->as<uint32_t>());
         prof_begin(c, "radix_scatter", n * (vals ? 24ull : 16ull));
         if (vals)
-            radix_scatter_k<true, false><<<ntiles, SORT_THREADS, SORT_SMEM, c->stream>>>(keys->as<uint64_t>(), tmpk->as<uint64_t>(), (*vals)->as<uint32_t>(), tmpv->as<uint32_t>(), n, shift, offs->as<uint32_t>(), ntiles, nullptr, nullptr, c->d_status);
+            radix_scatter_k<true, false><<<ntiles, SORT_THREADS, SORT_SMEM, c->stream>>>(keys->as<uint64_t>(), tmpk->as<uint64_t>(), (*vals)->as<uint32_t>(), tmpv->as<uint32_t>(), n, shift, offs->as<uint32_t>(), ntiles, nullptr, nullptr, c->d_status, 0u);
         else
-            radix_scatter_k<false, false><<<ntiles, SORT_THREADS, SORT_SMEM, c->stream>>>(keys->as<uint64_t>(), tmpk->as<uint64_t>(), nullptr, nullptr, n, shift, offs->as<uint32_t>(), ntiles, nullptr, nullptr, c->d_status);
+            radix_scatter_k<false, false><<<ntiles, SORT_THREADS, SORT_SMEM, c->stream>>>(keys->as<uint64_t>(), tmpk->as<uint64_t>(), nullptr, nullptr, n, shift, offs->as<uint32_t>(), ntiles, nullptr, nullptr, c->d_status, 0u);
         check_launch(c, "radix_scatter");
         if (keep_input && q == 0) {
             keys = tmpk;

@@ -142,6 +142,17 @@ struct PredCmp {
         }
     }
 };
+struct PredOwner {
+    const uint64_t* in;
+    int keysel;
+    uint32_t world, rank;
+    __device__ __forceinline__ bool operator()(uint64_t i) const {
+        uint64_t w = in[i];
+        uint64_t key = keysel == 0 ? (w >> 32) : (w & 0xFFFFFFFFull);
+        return (uint32_t)(mix64(key) % world) == rank;
+    }
+};
+__global__ void add_word_k(unsigned long long* dst, const unsigned long long* src) { *dst += *src; }
 struct PredFlag {
     const uint64_t* match;
     bool want;
@@ -512,6 +523,22 @@ Keys ops_dense_novel(xlb_ctx* c, const Keys& cand, const Keys& full, int hi_bits
     return ops_dense_finish(c, d, cand.n ? full : none);
 }
 
+void ops_dense_mark_into(xlb_ctx* c, DenseSet& d, const Keys& cand) {
+    if (cand.n == 0) return;
+    d.bound |= cand.bound;
+    prof_begin(c, "dense_mark", cand.n * 8ull);
+    dense_mark_k<true><<<grid_for(c, cand.n), BLOCK, 0, c->stream>>>(cand.ptr(), cand.n, d.lo_bits, d.bitmap->as<unsigned int>(), d.words, c->d_status, d.visited);
+    check_launch(c, "dense_mark");
+}
+
+Keys ops_filter_owner(xlb_ctx* c, const Keys& in, int keysel, uint32_t world, uint32_t rank) {
+    Keys o;
+    o.bound = in.bound;
+    o.buf = make_buf(c, in.n * 8);
+    o.n = select(c, PredOwner{in.ptr(), keysel == SRC_HI ? 0 : 1, world, rank}, EmitKey{in.ptr(), o.buf->as<uint64_t>()}, in.n);
+    return o;
+}
+
 Keys ops_merge_disjoint(xlb_ctx* c, const Keys& a, const Keys& b) {
     Keys o;
     o.bound = (a.n ? a.bound : 0) | (b.n ? b.bound : 0);
@@ -706,12 +733,18 @@ static Keys join_expand(xlb_ctx* c, const Keys& bag, int keysel, const uint64_t*
         // Nothing is allocated by the count, so it stays on the device: a fixed grid walks the
         // tiles and the host reads the count later, together with the bitmap's.
         // (one marking join per DenseSet: the scan leaves its total in the set's count word)
-        exclusive_scan<LoadLow32, uint64_t>(c, LoadLow32{match->as<uint64_t>()}, bag.n, off->as<uint64_t>(), dense->counts + 1);
+        Buf own_total = dense->shared ? make_buf(c, 8) : Buf();
+        uint64_t* total_dev = dense->shared ? own_total->as<uint64_t>() : dense->counts + 1;
+        exclusive_scan<LoadLow32, uint64_t>(c, LoadLow32{match->as<uint64_t>()}, bag.n, off->as<uint64_t>(), total_dev);
         const unsigned grid = (unsigned)c->sm_count * 8;
         prof_begin(c, "expand_mark", bag.n * 24ull);
         expand_k<true><<<grid, BLOCK, 0, c->stream>>>(bag.ptr(), match->as<uint64_t>(), off->as<uint64_t>(), bag.n, 0, ix.S ? ix.S->as<uint64_t>() : nullptr, pay, hi_src, lo_src,
-                                                       nullptr, dense->bitmap->as<unsigned int>(), dense->words, dense->lo_bits, c->d_status, dense->counts + 1, dense->visited);
+                                                       nullptr, dense->bitmap->as<unsigned int>(), dense->words, dense->lo_bits, c->d_status, total_dev, dense->visited);
         check_launch(c, "expand_mark");
+        if (dense->shared) {
+            add_word_k<<<1, 1, 0, c->stream>>>((unsigned long long*)(dense->counts + 1), (const unsigned long long*)total_dev);
+            check_launch(c, "add_word");
+        }
         dense->bound |= out.bound;
         return out;
     }
@@ -764,7 +797,8 @@ Keys ops_partition_by_owner_dev(xlb_ctx* c, const Keys& in, int keysel, uint32_t
 // ------------------------------------------------------------------------------ C ABI: context
 #define API_BEGIN(ctxp) \
     xlb_ctx* ctx__ = (ctxp); \
-    try {
+    try {                    \
+        if (ctx__) CUDA_OK(cudaSetDevice(ctx__->device));
 #define API_END()                                  \
     }                                              \
     catch (const XlbError& e) {                    \
@@ -828,6 +862,15 @@ extern "C" void xlb_ctx_destroy(xlb_ctx* c) {
     c->arena.destroy();
     if (c->stream) cudaStreamDestroy(c->stream);
     delete c;
+}
+
+// Test support: how long a sort tile polls for its predecessors before it gives up, and the number
+// the first tile takes (see include/xlb.h).
+extern "C" xlb_status xlb_test_set_lookback(xlb_ctx* c, uint32_t spin_limit, uint32_t first_tile) {
+    if (!c) return XLB_ERR_INVALID;
+    c->lb_spin_limit = spin_limit ? spin_limit : 1u << 22;
+    c->lb_first_tile = first_tile;
+    return XLB_OK;
 }
 
 extern "C" const char* xlb_last_error(const xlb_ctx* c) { return c ? c->last_error.c_str() : g_create_error.c_str(); }
@@ -956,6 +999,19 @@ extern "C" void xlb_rel_free(xlb_rel* r) {
 }
 
 // ------------------------------------------------------------------------------ operators
+// An operator builds its result under this guard and hands it over only after the device status
+// word has been read clean: a failure a kernel reported (a bounded wait that ran out, a capacity
+// check) then fails the call that caused it, and the half-written relation is freed.
+struct ResultGuard {
+    xlb_rel* r = nullptr;
+    ~ResultGuard() { delete r; }
+    void deliver(xlb_ctx* c, xlb_rel** to) {
+        check_dev_status(c);  // waits for the stream
+        *to = r;
+        r = nullptr;
+    }
+};
+
 static bool schemas_compatible(const xlb_schema& a, const xlb_schema& b) {
     if (a.arity != b.arity) return false;
     for (uint32_t i = 0; i < a.arity; ++i) {
@@ -1045,15 +1101,17 @@ static xlb_rel* gather_rel(xlb_ctx* c, const xlb_rel* r, const uint32_t* idx, ui
     return o.release();
 }
 
-static xlb_status sort_unsigned(xlb_ctx* c, const xlb_rel* in, const uint32_t* key_cols, uint32_t nk, xlb_rel** out) {
-    if (!c || !in || !out) return XLB_ERR_INVALID;
+static xlb_status sort_unsigned(xlb_ctx* c, const xlb_rel* in, const uint32_t* key_cols, uint32_t nk, xlb_rel** out_final) {
+    if (!c || !in || !out_final) return XLB_ERR_INVALID;
     API_BEGIN(c)
+    ResultGuard guard;
+    xlb_rel** out = &guard.r;
     for (uint32_t i = 0; i < nk; ++i)
         if (key_cols[i] >= in->schema.arity) xlb_fail(XLB_ERR_INVALID, "sort key column %u out of range", key_cols[i]);
     ops_rel_columns(c, in);
     Buf idx = sort_permutation(c, in, key_cols, nk);
     *out = gather_rel(c, in, idx->as<uint32_t>(), in->rows);
-    CUDA_OK(cudaStreamSynchronize(c->stream));
+    guard.deliver(c, out_final);
     API_END()
 }
 
@@ -1112,9 +1170,11 @@ static xlb_rel* canonicalize(xlb_ctx* c, const xlb_rel* in) {
     return wide_dedup(c, in, nullptr, 0);
 }
 
-static xlb_status dedup_unsigned(xlb_ctx* c, const xlb_rel* in, const uint32_t* key_cols, uint32_t nk, xlb_rel** out) {
-    if (!c || !in || !out) return XLB_ERR_INVALID;
+static xlb_status dedup_unsigned(xlb_ctx* c, const xlb_rel* in, const uint32_t* key_cols, uint32_t nk, xlb_rel** out_final) {
+    if (!c || !in || !out_final) return XLB_ERR_INVALID;
     API_BEGIN(c)
+    ResultGuard guard;
+    xlb_rel** out = &guard.r;
     bool full = nk == 0 || nk >= in->schema.arity;
     if (full) {
         *out = canonicalize(c, in);
@@ -1134,13 +1194,15 @@ static xlb_status dedup_unsigned(xlb_ctx* c, const xlb_rel* in, const uint32_t* 
         uint64_t m = select(c, PredRowHead{cs}, EmitIndex{heads->as<uint32_t>()}, in->rows);
         *out = gather_rel(c, sorted.get(), heads->as<uint32_t>(), m);
     }
-    CUDA_OK(cudaStreamSynchronize(c->stream));
+    guard.deliver(c, out_final);
     API_END()
 }
 
-static xlb_status union_unsigned(xlb_ctx* c, const xlb_rel* const* ins, uint32_t n, xlb_rel** out) {
-    if (!c || !out) return XLB_ERR_INVALID;
+static xlb_status union_unsigned(xlb_ctx* c, const xlb_rel* const* ins, uint32_t n, xlb_rel** out_final) {
+    if (!c || !out_final) return XLB_ERR_INVALID;
     API_BEGIN(c)
+    ResultGuard guard;
+    xlb_rel** out = &guard.r;
     if (n == 0 || !ins) xlb_fail(XLB_ERR_INVALID, "union of no inputs");
     for (uint32_t i = 0; i < n; ++i) {
         if (!ins[i]) xlb_fail(XLB_ERR_INVALID, "union input %u is null", i);
@@ -1187,13 +1249,15 @@ static xlb_status union_unsigned(xlb_ctx* c, const xlb_rel* const* ins, uint32_t
         std::unique_ptr<xlb_rel> cat(concat_cols(c, ins, n));
         *out = wide_dedup(c, cat.get(), nullptr, 0);
     }
-    CUDA_OK(cudaStreamSynchronize(c->stream));
+    guard.deliver(c, out_final);
     API_END()
 }
 
-static xlb_status diff_unsigned(xlb_ctx* c, const xlb_rel* a, const xlb_rel* b, xlb_rel** out) {
-    if (!c || !a || !b || !out) return XLB_ERR_INVALID;
+static xlb_status diff_unsigned(xlb_ctx* c, const xlb_rel* a, const xlb_rel* b, xlb_rel** out_final) {
+    if (!c || !a || !b || !out_final) return XLB_ERR_INVALID;
     API_BEGIN(c)
+    ResultGuard guard;
+    xlb_rel** out = &guard.r;
     if (!schemas_compatible(a->schema, b->schema)) xlb_fail(XLB_ERR_TYPE, "difference of incompatible schemas");
     const xlb_schema& s = a->schema;
     if (s.arity == 0) {
@@ -1213,7 +1277,7 @@ static xlb_status diff_unsigned(xlb_ctx* c, const xlb_rel* a, const xlb_rel* b, 
         if (b->rows >= (1ull << 32)) xlb_fail(XLB_ERR_CAPACITY, "difference input exceeds the 2^32 row limit");
         *out = wide_dedup(c, cat.get(), nullptr, (uint32_t)b->rows);
     }
-    CUDA_OK(cudaStreamSynchronize(c->stream));
+    guard.deliver(c, out_final);
     API_END()
 }
 
@@ -1452,8 +1516,9 @@ static xlb_status with_typed(xlb_ctx* c, const xlb_rel* const* ins, uint32_t n, 
     if (st != XLB_OK) return st;
     std::unique_ptr<xlb_rel> ur(u);
     try {
-        *out = map_rel(c, u, ins[0]->schema, true);
-        CUDA_OK(cudaStreamSynchronize(c->stream));
+        ResultGuard guard;
+        guard.r = map_rel(c, u, ins[0]->schema, true);
+        guard.deliver(c, out);
     } catch (const XlbError& e) {
         c->last_error = e.msg;
         return e.st;
@@ -1486,9 +1551,11 @@ extern "C" xlb_status xlb_diff(xlb_ctx* c, const xlb_rel* a, const xlb_rel* b, x
 // find the group boundaries, reduce every aggregate per group.  Output: key columns, then one
 // column per aggregate in the order given; one row per group, ascending by key.
 extern "C" xlb_status xlb_groupby(xlb_ctx* c, const xlb_rel* in, const uint32_t* key_cols, uint32_t nk, const uint32_t* agg_cols, const uint32_t* agg_ops,
-                                  uint32_t na, xlb_rel** out) {
-    if (!c || !in || !out) return XLB_ERR_INVALID;
+                                  uint32_t na, xlb_rel** out_final) {
+    if (!c || !in || !out_final) return XLB_ERR_INVALID;
     API_BEGIN(c)
+    ResultGuard guard;
+    xlb_rel** out = &guard.r;
     if (nk == 0 || !key_cols) xlb_fail(XLB_ERR_INVALID, "GroupBy requires at least one key column");
     if (na == 0 || !agg_cols || !agg_ops) xlb_fail(XLB_ERR_INVALID, "GroupBy requires at least one aggregation");
     if (nk + na > XLB_MAX_ARITY) xlb_fail(XLB_ERR_UNSUPPORTED, "GroupBy output arity above %u", XLB_MAX_ARITY);
@@ -1561,8 +1628,8 @@ extern "C" xlb_status xlb_groupby(xlb_ctx* c, const xlb_rel* in, const uint32_t*
         }
         o->canonical = false;
         *out = o.release();
-        CUDA_OK(cudaStreamSynchronize(c->stream));
     }
+    guard.deliver(c, out_final);
     API_END()
 }
 
@@ -1583,9 +1650,11 @@ static Buf join_keys(xlb_ctx* c, const xlb_rel* r, const uint32_t* keys, uint32_
 }
 
 extern "C" xlb_status xlb_hash_join(xlb_ctx* c, const xlb_rel* l, const xlb_rel* r, const uint32_t* lk, const uint32_t* rk, uint32_t nk,
-                                    xlb_join_type type, xlb_rel** out) {
-    if (!c || !l || !r || !out) return XLB_ERR_INVALID;
+                                    xlb_join_type type, xlb_rel** out_final) {
+    if (!c || !l || !r || !out_final) return XLB_ERR_INVALID;
     API_BEGIN(c)
+    ResultGuard guard;
+    xlb_rel** out = &guard.r;
     if (nk < 1 || nk > XLB_MAX_KEYS || !lk || !rk) xlb_fail(XLB_ERR_INVALID, "join needs 1..%u key columns", XLB_MAX_KEYS);
     for (uint32_t i = 0; i < nk; ++i) {
         if (lk[i] >= l->schema.arity || rk[i] >= r->schema.arity) xlb_fail(XLB_ERR_INVALID, "join key column out of range");
@@ -1649,6 +1718,6 @@ extern "C" xlb_status xlb_hash_join(xlb_ctx* c, const xlb_rel* l, const xlb_rel*
             *out = gather_rel(c, l, sel->as<uint32_t>(), m);
         }
     }
-    check_dev_status(c);
+    guard.deliver(c, out_final);
     API_END()
 }

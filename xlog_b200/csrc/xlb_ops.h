@@ -67,6 +67,10 @@ struct DenseSet {
     // Optional bitmap (same domain) of the tuples known already: marking skips them, and
     // ops_dense_finish emits only what it lacks and adds that to it.
     unsigned int* visited = nullptr;
+    // Several marking steps share the set (every rule variant of an iteration, on ranks that hold
+    // replicated relations): a marking join then adds its tuple count to counts[1] instead of
+    // leaving it there.
+    bool shared = false;
 };
 // The tuples of one relation as a bitmap that lives across the iterations of a fixpoint, so that
 // no iteration has to subtract the whole relation from its candidates again.
@@ -88,6 +92,10 @@ uint64_t ops_expand_bound(const Keys& bag, const Index& ix, int hi_src, int lo_s
 // ops_join_expand that marks instead of materialising.  No count comes back to the host here:
 // the number of tuples marked is d.marked after ops_dense_finish.
 void ops_join_expand_mark(xlb_ctx* c, const Keys& bag, int keysel, const Index& ix, int hi_src, int lo_src, DenseSet& d);
+// mark the rows of `cand` in d (skipping what d.visited holds)
+void ops_dense_mark_into(xlb_ctx* c, DenseSet& d, const Keys& cand);
+// rows whose half `keysel` belongs to `rank` of `world` (owner = mix64(key) mod world), in input order
+Keys ops_filter_owner(xlb_ctx* c, const Keys& in, int keysel, uint32_t world, uint32_t rank);
 Keys ops_merge_disjoint(xlb_ctx* c, const Keys& a, const Keys& b);
 Keys ops_union(xlb_ctx* c, const Keys& a, const Keys& b);        // sorted unique a U b
 Keys ops_remap(xlb_ctx* c, const Keys& in, int hi_src, int lo_src);

@@ -8,6 +8,8 @@
 // (xlb_dedup and friends) take their scratch from the context's stream-ordered pool; this one
 // takes none: the caller passes device pointers for the input, the output and the count, and
 // the tile counters, tile offsets and scan partials live in `g_static_scratch` below.
+#include <atomic>
+
 #include "xlb_kernels.cuh"
 
 using namespace xk;
@@ -28,7 +30,8 @@ static __device__ __align__(256) unsigned char g_static_scratch[STATIC_BYTES];
 
 // In host code the array's name is only a handle for the runtime, not a device address; the
 // address kernels can use comes from cudaGetSymbolAddress, per device.
-static unsigned char* g_scratch_ptr[64] = {};
+// (looked up once per device; several host threads may race to store the same value)
+static std::atomic<unsigned char*> g_scratch_ptr[64];
 
 static thread_local char g_static_error[256] = "";
 
@@ -48,18 +51,28 @@ extern "C" xlb_status xlb_dedup_sorted_u64_static(const uint64_t* d_sorted, uint
                  (unsigned long long)STATIC_MAX_KEYS);
         return XLB_ERR_CAPACITY;
     }
+    if (n) {
+        // blocks write output positions while other blocks still read input: the two ranges must not overlap
+        const uintptr_t in0 = (uintptr_t)d_sorted, in1 = in0 + n * 8, out0 = (uintptr_t)d_unique, out1 = out0 + n * 8;
+        if (in0 < out1 && out0 < in1) return fail(XLB_ERR_INVALID, "the input and output key ranges overlap; pass separate buffers", cudaSuccess);
+    }
+    // An error some earlier work of the caller left pending would be taken for (and cleared as) a
+    // launch failure of this call: refuse to start, and leave it for the caller to read.
+    cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess) return fail(XLB_ERR_CUDA, "a CUDA error was already pending when the call began", e);
     int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
+    e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return fail(XLB_ERR_CUDA, "cudaGetDevice", e);
     if (dev < 0 || dev >= 64) return fail(XLB_ERR_UNSUPPORTED, "device ordinal above 63", cudaSuccess);
-    if (!g_scratch_ptr[dev]) {
+    unsigned char* base = g_scratch_ptr[dev].load(std::memory_order_acquire);
+    if (!base) {
         // set-up, once per device, with that device current
         void* p = nullptr;
         e = cudaGetSymbolAddress(&p, g_static_scratch);
         if (e != cudaSuccess || !p) return fail(XLB_ERR_CUDA, "cudaGetSymbolAddress(g_static_scratch)", e);
-        g_scratch_ptr[dev] = (unsigned char*)p;
+        base = (unsigned char*)p;
+        g_scratch_ptr[dev].store(base, std::memory_order_release);
     }
-    unsigned char* base = g_scratch_ptr[dev];
     uint64_t* total = (uint64_t*)base;
     uint32_t* counts = (uint32_t*)(base + OFF_COUNTS);
     uint64_t* offs = (uint64_t*)(base + OFF_OFFS);

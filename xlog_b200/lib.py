@@ -51,6 +51,8 @@ PROTOTYPES = {
     "xlb_comm_unique_id": (C.c_int, [C.POINTER(C.c_uint8)]),
     "xlb_comm_init": (C.c_int, [P, C.POINTER(C.c_uint8), C.c_uint32, C.c_uint32]),
     "xlb_owner_of": (C.c_uint32, [C.c_uint64, C.c_uint32]),
+    "xlb_comm_mark_aborted_for_test": (C.c_int, [P]),
+    "xlb_test_set_lookback": (C.c_int, [P, C.c_uint32, C.c_uint32]),
 }
 
 
