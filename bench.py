@@ -4,13 +4,19 @@
   python bench.py --gpus N --steps K --warmup W            # the CUDA path (libxlb.so)
   python bench.py --impl reference --steps K --warmup W    # the CPU restatement of the reference
 
-Workload: single-source reachability r(Y) :- edge(0,Y). r(Z) :- r(Y), edge(Y,Z). over a seeded
-R-MAT graph, scale 20, edge factor 16 (a=.57 b=.19 c=.19 d=.05), self-loops and duplicates removed.
-One step is one complete fixpoint: from the edge relation resident as column-major u32 columns to
-the final relation, sorted, on the device.  Metric: derived tuples per second (final tuple count
-divided by the fixpoint time).  With N > 1 ranks every rank holds 1/N of the edge rows; relations
-are hash-partitioned and exchanged by all-to-all inside the fixpoint (total work fixed: strong
-scaling).  One JSON line is printed by rank 0.
+Headline workload (config 2): single-source reachability r(Y) :- edge(0,Y). r(Z) :- r(Y), edge(Y,Z).
+over a seeded R-MAT graph, scale 20, edge factor 16 (a=.57 b=.19 c=.19 d=.05), self-loops and
+duplicates removed.  One step is one complete fixpoint: from the edge relation resident as
+column-major u32 columns to the final relation, sorted, on the device.  Metric: derived tuples per
+second (final tuple count divided by the fixpoint time).  With N > 1 ranks every rank holds 1/N of
+the edge rows (total work fixed: strong scaling).
+
+The same line carries a `secondary` object: the full transitive closure of the banded R-MAT DAG of
+config 5 at a reduced scale (16 instead of 24: the stated scale derives about 5e12 tuples), which
+is the workload that runs the radix sort, the hash probe, the merge-path set operations and, on
+several ranks, the tuple exchange.  It reports its own time, the per-iteration exchange, the
+roofline of `radix_scatter` and `hash_probe`, and a checksum of the result that is the same at
+every N.  One JSON line is printed by rank 0.
 """
 from __future__ import annotations
 
@@ -37,24 +43,32 @@ def emit(line: dict) -> None:
     sys.stdout.flush()
     os.write(_REAL_STDOUT, (json.dumps(line) + "\n").encode())
 
+
 METRIC = "derived_tuples_per_sec"
 UNIT = "tuples/s"
+L2_NOTE = "256 MB buffer written between steps"
+TIMING_NOTE = "CUDA events on the library's stream around xlb_execute_plan, max over ranks"
+# algorithmic bytes per launch are counted by the library (xlb_profile_read); the DRAM traffic of
+# one launch was measured with ncu on a small case of the same kernel and grows with the rows of a
+# launch, so it is scaled from the algorithmic bytes: the summary that holds the capture is named
+TRAFFIC = {"radix_scatter": (13.2 / 16.0, "profiles/radix_scatter_sort_16M_keys.md"),
+           "scan_join_mark": (1.03, "profiles/scan_join_mark_c2.md")}
 
 
-def make_workload(args):
+def make_workload(name: str, scale: int):
     from xlog_b200 import programs, workloads
-    if args.workload == "c2":
-        c0, c1 = workloads.rmat_graph(args.scale, 16)
+    if name == "c2":
+        c0, c1 = workloads.rmat_graph(scale, 16)
         return programs.reach_from_source(0), {"edge": [c0, c1]}, "r", \
-            f"single-source reachability, R-MAT scale {args.scale} edge factor 16 ({len(c0)} edges)"
-    if args.workload == "c1":
+            f"single-source reachability, R-MAT scale {scale} edge factor 16 ({len(c0)} edges)"
+    if name == "c1":
         c0, c1 = workloads.uniform_digraph()
         return programs.transitive_closure(), {"edge": [c0, c1]}, "reach", "transitive closure, 2000 nodes / 10000 uniform edges"
-    if args.workload == "c5":
-        c0, c1 = workloads.rmat_dag(args.scale, 8)
+    if name == "c5":
+        c0, c1 = workloads.rmat_dag(scale, 8)
         return programs.transitive_closure(), {"edge": [c0, c1]}, "reach", \
-            f"transitive closure, banded R-MAT DAG scale {args.scale} edge factor 8 ({len(c0)} edges)"
-    raise SystemExit(f"unknown workload {args.workload}")
+            f"transitive closure, banded R-MAT DAG scale {scale} edge factor 8 ({len(c0)} edges)"
+    raise SystemExit(f"unknown workload {name}")
 
 
 class ClockSampler:
@@ -110,6 +124,47 @@ def measured_peak_gbs():
     return 6650.0, "fallback"
 
 
+def result_checksum(cols) -> tuple[int, int, int]:
+    """Order-independent digest of a set of tuples: (count, XOR, sum of the low 32 bits) of the
+    64-bit mix of every packed tuple.  Shards of disjoint tuples combine by adding the counts and
+    sums and XOR-ing the XORs, so the digest of a sharded result equals that of the whole."""
+    from xlog_b200.dist import mix64
+    n = len(cols[0]) if cols else 0
+    if n == 0:
+        return 0, 0, 0
+    xor, low = 0, 0
+    step = 1 << 24
+    for at in range(0, n, step):
+        k = cols[0][at:at + step].astype(np.uint64)
+        if len(cols) > 1:
+            k = (k << np.uint64(32)) | cols[1][at:at + step].astype(np.uint64)
+        h = mix64(k)
+        xor ^= int(np.bitwise_xor.reduce(h))
+        low += int((h & np.uint64(0xFFFFFFFF)).sum(dtype=np.uint64))
+    return n, xor, low
+
+
+def checksum_text(parts) -> str:
+    n = sum(p[0] for p in parts)
+    xor = 0
+    for p in parts:
+        xor ^= p[1]
+    low = sum(p[2] for p in parts) & ((1 << 64) - 1)
+    return f"{n:x}-{xor:016x}-{low:016x}"
+
+
+def roofline_of(prof: dict, kernel: str, peak: float, peak_kind: str):
+    k = prof.get(kernel)
+    if not k or k["ms"] <= 0 or not k["launches"]:
+        return None
+    achieved = k["bytes"] / (k["ms"] / 1e3) / 1e9
+    per_alg, source = TRAFFIC.get(kernel, (None, None))
+    return {"bound": "hbm", "kernel": kernel, "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+            "frac": achieved / peak, "traffic": (k["bytes"] / k["launches"]) * per_alg if per_alg else None,
+            "traffic_source": source, "launches": k["launches"], "avg_launch_us": 1e3 * k["ms"] / k["launches"],
+            "algorithmic_bytes_per_launch": k["bytes"] / k["launches"]}
+
+
 def run_reference(args):
     """The reference arm: the CPU restatement of the reference's evaluation of the same program
     (the reference itself is Rust + CUDA and cannot be built without a Rust toolchain), on all
@@ -118,10 +173,10 @@ def run_reference(args):
     if rank != 0:
         return
     from oracle import oracle as O
-    plan, inputs, out_name, desc = make_workload(args)
+    plan, inputs, out_name, desc = make_workload(args.workload, args.scale)
     cores = os.cpu_count() or 1
     O.set_threads(cores)
-    times, derived = [], 0
+    times, derived, ex, out = [], 0, None, None
     for i in range(args.warmup + args.steps):
         t0 = time.perf_counter()
         out, ex = O.run_program(plan, inputs, [out_name])
@@ -135,12 +190,174 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "u32", "data": "synthetic",
-        "config": {"workload": desc, "derived_tuples": derived},
+        "config": {"workload": desc, "derived_tuples": derived, "iterations": int(ex.iterations),
+                   "candidate_tuples": int(ex.candidates), "l2": L2_NOTE, "timing": TIMING_NOTE},
+        "checksum": checksum_text([result_checksum(out[out_name])]),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
                          "sample": "the whole fixpoint of the same workload, once per step"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "secondary": None,
+        "note": "wall clock of the CPU port of the reference's semi-naive loop (config keys l2 / timing describe the CUDA arm); "
+                "the secondary workload is not run on the CPU port: its 9e8 join candidates take minutes there",
     }
     emit(line)
+
+
+class Job:
+    """One context on this rank's GPU with a workload loaded: runs device-resident and end-to-end
+    steps of one fixpoint."""
+
+    def __init__(self, env, workload: str, scale: int, flags: int = 0):
+        import torch
+        from xlog_b200.executor import Executor
+        from xlog_b200.provider import KernelProvider
+        self.env = env
+        self.torch = torch
+        self.plan, inputs, self.out_name, self.desc = make_workload(workload, scale)
+        self.edge_name = next(iter(inputs))
+        cols = inputs[self.edge_name]
+        self.inputs = inputs
+        n_rows = len(cols[0])
+        lo, hi = n_rows * env.rank // env.world, n_rows * (env.rank + 1) // env.world
+        # this rank's slice of the input, in pinned host memory (the end-to-end path copies from here)
+        self.pinned = [torch.empty(hi - lo, dtype=torch.int32).pin_memory() for _ in cols]
+        self.host_cols = []
+        for t, c in zip(self.pinned, cols):
+            a = t.numpy().view(np.uint32)
+            a[:] = c[lo:hi]
+            self.host_cols.append(a)
+        self.prov = KernelProvider(device=env.local, flags=flags)
+        if env.world > 1:
+            from xlog_b200 import dist as D
+            D.init_comm(self.prov, env.rank, env.world, device="cuda")
+        self.ex = Executor(self.prov)
+        for name, rid in self.plan.rel_ids.items():
+            self.ex.register_relation(rid, name)
+        self.master = self.prov.create_buffer_from_slices(self.host_cols)
+        self.cplan = self.plan.compile()
+
+    def _drop_result(self):
+        try:
+            self.ex.remove(self.out_name)
+        except Exception:
+            pass
+
+    def device_step(self, salt: int = 1):
+        self._drop_result()
+        self.ex.put_relation(self.edge_name, self.prov.clone_buffer(self.master))
+        self.env.flush.fill_(self.env.rank + salt)
+        self.env.barrier()
+        return self.ex.execute_plan(self.cplan)
+
+    def e2e_step(self):
+        """Host buffers in, host result out: the copies are inside the timed region."""
+        self._drop_result()
+        self.env.flush.fill_(self.env.rank + 3)
+        self.env.barrier()
+        t0 = time.perf_counter()
+        self.ex.put_relation(self.edge_name, self.prov.create_buffer_from_slices(self.host_cols))
+        self.ex.execute_plan(self.cplan)
+        res = self.prov.download(self.ex.get(self.out_name))
+        self.torch.cuda.synchronize()
+        return (time.perf_counter() - t0) * 1e3, sum(c.nbytes for c in res)
+
+    def result(self):
+        return self.prov.download(self.ex.get(self.out_name))
+
+    def close(self):
+        self.prov.close()
+
+
+class Env:
+    def __init__(self, args):
+        import torch
+        import torch.distributed as dist
+        self.torch, self.dist = torch, dist
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        if self.world != args.gpus and self.world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N")
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
+        torch.cuda.set_device(self.local)
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local))
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")  # larger than the 126 MB L2
+
+    def barrier(self):
+        self.torch.cuda.synchronize()
+        if self.world > 1:
+            self.dist.barrier()
+            self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, values):
+        t = self.torch.tensor(values, dtype=self.torch.float64, device="cuda")
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return t
+
+    def gather(self, obj):
+        if self.world == 1:
+            return [obj]
+        out = [None] * self.world
+        self.dist.all_gather_object(out, obj)
+        return out
+
+
+def timed_steps(env, job, steps, kernels):
+    """`steps` device-resident fixpoints with the launches of `kernels` bracketed by CUDA events."""
+    job.prov.profile_enable(kernels)
+    ms, host, stats, launches = [], [], None, 0
+    env.barrier()
+    for _ in range(steps):
+        stats = job.device_step()
+        host.append([round(stats["ms_host_total"], 3), round(stats["ms_host_wait"], 3), round(stats["ms_host_alloc"], 3)])
+        ms.append(stats["ms_total"])
+        launches += stats["kernel_launches"]
+    env.barrier()
+    prof = job.prov.profile_read()
+    job.prov.profile_enable(None)
+    return env.max_over_ranks(ms), host, stats, launches, prof
+
+
+def secondary_block(env, args, peak, peak_kind, flags, label):
+    """The sort / probe / exchange workload at reduced scale, in one evaluation mode."""
+    from xlog_b200 import _abi as A
+    job = Job(env, "c5", args.secondary_scale, flags | A.FLAG_PROFILE)   # phase timers on: they give the exchange time
+    for _ in range(args.secondary_warmup):
+        job.device_step()
+    ms_t, _, stats, launches, prof = timed_steps(env, job, args.secondary_steps, "radix_scatter,hash_probe")
+    ms = float(ms_t.mean().item())
+    shard = job.result()
+    parts = env.gather((result_checksum(shard), len(shard[0]), stats["ms_exchange"], stats["exchange_bytes"],
+                        stats["ms_sort"], stats["ms_join"], stats["ms_setops"]))
+    job.close()
+    if env.rank != 0:
+        return None
+    derived, iters = stats["derived_tuples"], max(stats["iterations"], 1)
+    sizes = [p[1] for p in parts]
+    ex_ms = [p[2] for p in parts]
+    ex_bytes = [p[3] for p in parts]
+    return {
+        "mode": label,
+        "workload": job.desc + " (config 5 at a reduced scale)",
+        "metric": METRIC, "unit": UNIT, "value": derived / (ms / 1e3), "ms_per_step": ms,
+        "steps": args.secondary_steps, "warmup": args.secondary_warmup, "ms_steps": [round(float(x), 3) for x in ms_t.tolist()],
+        "derived_tuples": derived, "iterations": stats["iterations"], "candidate_tuples": stats["candidate_tuples"],
+        "checksum": checksum_text([p[0] for p in parts]),
+        "shards": {"max": max(sizes), "mean": sum(sizes) / len(sizes)},
+        # device time between the events around every exchange step of the last timed fixpoint
+        # (partition by owner, count all-gather, all-to-all, vote), and the bytes a rank sent
+        "exchange": {"ms_per_step_max": max(ex_ms), "ms_per_step_mean": sum(ex_ms) / len(ex_ms),
+                     "ms_per_iteration_max": max(ex_ms) / iters,
+                     "bytes_sent_per_rank_per_iteration_max": max(ex_bytes) / iters,
+                     "bytes_sent_per_rank_per_step_max": max(ex_bytes)},
+        "phases_ms_rank0": {"sort": round(parts[0][4], 3), "join": round(parts[0][5], 3), "setops": round(parts[0][6], 3),
+                            "exchange": round(parts[0][2], 3)},
+        "gpu_launches": int(launches),
+        "roofline": {k: roofline_of(prof, k, peak, peak_kind) for k in ("radix_scatter", "hash_probe")},
+    }
 
 
 def main():
@@ -156,6 +373,11 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (large results)")
     ap.add_argument("--no-clocks", action="store_true", help="do not run nvidia-smi beside the timed region")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the reduced-scale config 5 block")
+    ap.add_argument("--secondary-scale", type=int, default=16)
+    ap.add_argument("--secondary-steps", type=int, default=5)
+    ap.add_argument("--secondary-warmup", type=int, default=3)
+    ap.add_argument("--shuffle-only", action="store_true", help="headline workload with XLB_FLAG_SHUFFLE_ONLY (several ranks: no replicated relations)")
     ap.add_argument("--phases", action="store_true", help="time the executor's phases with events (fills phases_last_step; adds event records to the timed steps)")
     ap.add_argument("--breakdown", action="store_true", help="extra untimed pass with every kernel timed, to stderr")
     args = ap.parse_args()
@@ -165,130 +387,47 @@ def main():
         run_reference(args)
         return
 
-    import torch
-    import torch.distributed as dist
-
-    from xlog_b200.executor import Executor
-    from xlog_b200.provider import KernelProvider
     from xlog_b200 import _abi as A
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        if world == 1 and args.gpus > 1:
-            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N")
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-
-    plan, inputs, out_name, desc = make_workload(args)
-    edge_name = next(iter(inputs))
-    cols = inputs[edge_name]
-    n_rows = len(cols[0])
-    lo, hi = n_rows * rank // world, n_rows * (rank + 1) // world
-    # this rank's slice of the input, in pinned host memory (the end-to-end path copies from here)
-    pinned = [torch.empty(hi - lo, dtype=torch.int32).pin_memory() for _ in cols]
-    host_cols = []
-    for t, c in zip(pinned, cols):
-        a = t.numpy().view(np.uint32)
-        a[:] = c[lo:hi]
-        host_cols.append(a)
-
-    prov = KernelProvider(device=local, flags=A.FLAG_PROFILE if args.phases else 0)
-    if world > 1:
-        from xlog_b200 import dist as D
-        D.init_comm(prov, rank, world, device="cuda")
-
-    ex = Executor(prov)
-    for name, rid in plan.rel_ids.items():
-        ex.register_relation(rid, name)
-    master = prov.create_buffer_from_slices(host_cols)
-    cplan = plan.compile()
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")  # larger than the 126 MB L2
-
-    def reset_store():
-        try:
-            ex.remove(out_name)
-        except Exception:
-            pass
-        ex.put_relation(edge_name, prov.clone_buffer(master))
-
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
-
-    def device_step():
-        reset_store()
-        flush.fill_(rank + 1)
-        barrier()
-        return ex.execute_plan(cplan)
+    env = Env(args)
+    world, rank = env.world, env.rank
+    flags = (A.FLAG_PROFILE if args.phases else 0) | (A.FLAG_SHUFFLE_ONLY if args.shuffle_only else 0)
+    job = Job(env, args.workload, args.scale, flags)
+    prov = job.prov
 
     # ---- device-resident steps: warm-up, then K timed steps ---------------------------------
     # clocks are sampled from the first warm-up step to the last end-to-end step: the timed region
     # alone lasts tens of milliseconds, less than one nvidia-smi sampling period
-    sampler = ClockSampler(local) if rank == 0 and not args.no_clocks else None
+    sampler = ClockSampler(env.local) if rank == 0 and not args.no_clocks else None
     if sampler:
         time.sleep(1.0)  # let nvidia-smi finish starting up: its first query stalls CUDA calls for milliseconds
     for w in range(args.warmup):
         if args.kernel == "auto" and w == args.warmup - 1:
             prov.profile_enable("*")  # untimed step: find the kernel that dominates this workload
-        device_step()
+        job.device_step()
     if args.kernel == "auto":
         seen = {k: v for k, v in prov.profile_read().items() if v["bytes"]}
         prov.profile_enable(None)
-        args.kernel = max(seen, key=lambda k: seen[k]["ms"]) if seen else "radix_scatter"
-    prov.profile_enable(args.kernel)
-    ms_steps, host_steps, stats = [], [], None
-    launches = 0
-    barrier()
-    for _ in range(args.steps):
-        stats = device_step()
-        host_steps.append([round(stats["ms_host_total"], 3), round(stats["ms_host_wait"], 3), round(stats["ms_host_alloc"], 3)])
-        ms_steps.append(stats["ms_total"])
-        launches += stats["kernel_launches"]
-    barrier()
-    prof = prov.profile_read()
-    prov.profile_enable(None)
-    ms_t = torch.tensor(ms_steps, dtype=torch.float64, device="cuda")
-    if world > 1:
-        dist.all_reduce(ms_t, op=dist.ReduceOp.MAX)
+        mine = max(seen, key=lambda k: seen[k]["ms"]) if seen else "radix_scatter"
+        args.kernel = env.gather(mine)[0]   # every rank times rank 0's choice
+    ms_t, host_steps, stats, launches, prof = timed_steps(env, job, args.steps, args.kernel)
     ms_per_step = float(ms_t.mean().item())
     derived = stats["derived_tuples"]
     value = derived / (ms_per_step / 1e3)
+    digest = checksum_text([p for p in env.gather(result_checksum(job.result()))])
 
     # ---- end to end: host buffers in, host result out, copies inside the timed region ------
     e2e_ms, d2h_bytes = [], 0
     for i in range(0 if args.no_e2e else args.warmup + args.steps):
-        try:
-            ex.remove(out_name)
-        except Exception:
-            pass
-        flush.fill_(rank + 3)
-        barrier()
-        t0 = time.perf_counter()
-        ex.put_relation(edge_name, prov.create_buffer_from_slices(host_cols))
-        ex.execute_plan(cplan)
-        res = prov.download(ex.get(out_name))
-        torch.cuda.synchronize()
-        dt = (time.perf_counter() - t0) * 1e3
-        d2h_bytes = sum(c.nbytes for c in res)
+        dt, d2h_bytes = job.e2e_step()
         if i >= args.warmup:
             e2e_ms.append(dt)
     clocks = sampler.stop() if sampler else None
-    e2e_t = torch.tensor(e2e_ms, dtype=torch.float64, device="cuda")
-    if world > 1:
-        dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
-    e2e_ms_per_step = float(e2e_t.mean().item()) if e2e_ms else float("nan")
+    e2e_ms_per_step = float(env.max_over_ranks(e2e_ms).mean().item()) if e2e_ms else float("nan")
 
     if args.breakdown and rank == 0 and world == 1:
         prov.profile_enable("*")
         for _ in range(3):
-            device_step()
+            job.device_step()
         full = prov.profile_read()
         prov.profile_enable(None)
         tot = sum(v["ms"] for v in full.values())
@@ -297,26 +436,27 @@ def main():
             gbs = v["bytes"] / v["ms"] / 1e6 if v["ms"] > 0 and v["bytes"] else 0.0
             print(f"#   {k:20s} launches {v['launches']:5d}  ms {v['ms']:9.3f}  share {100 * v['ms'] / tot:5.1f}%  alg GB/s {gbs:8.1f}", file=sys.stderr)
 
-    if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
+    h2d_bytes = int(sum(c.nbytes for c in job.host_cols))
+    plan, inputs, out_name, desc = job.plan, job.inputs, job.out_name, job.desc
+    job.close()
 
     peak, peak_kind = measured_peak_gbs()
-    roof = None
-    k = prof.get(args.kernel)
-    if k and k["ms"] > 0 and k["launches"]:
-        achieved = k["bytes"] / (k["ms"] / 1e3) / 1e9
-        # DRAM bytes per launch: ncu captures of these kernels measured 13.2 B per key against 16
-        # algorithmic for one radix pass over 16 M keys, and 1.0 x the algorithmic bytes for the
-        # scan join over the 16 M edge rows; both grow with the rows of a launch, so they are
-        # scaled to the rows an average launch of this run processed
-        per_alg = {"radix_scatter": 13.2 / 16.0, "scan_join_mark": 1.0}.get(args.kernel)
-        traffic = (k["bytes"] / k["launches"]) * per_alg if per_alg else None
-        roof = {"bound": "hbm", "kernel": args.kernel, "achieved": achieved, "peak": peak, "peak_kind": peak_kind,
-                "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
-                "launches": k["launches"], "avg_launch_us": 1e3 * k["ms"] / k["launches"],
-                "algorithmic_bytes_per_launch": k["bytes"] / k["launches"]}
+    secondary = None
+    if not args.no_secondary and args.workload == "c2":
+        secondary = secondary_block(env, args, peak, peak_kind, 0, "one rank" if world == 1 else
+                                    "stored relation copied to every rank, closure placed by its carried column: no tuple exchange")
+        if world > 1:
+            shuffle = secondary_block(env, args, peak, peak_kind, A.FLAG_SHUFFLE_ONLY,
+                                      "hash-partitioned on the join key, all-to-all per iteration (XLB_FLAG_SHUFFLE_ONLY)")
+            if rank == 0:
+                secondary["shuffle"] = shuffle
+
+    if rank != 0:
+        if world > 1:
+            env.dist.destroy_process_group()
+        return
+
+    roof = roofline_of(prof, args.kernel, peak, peak_kind)
 
     cpu = None
     if not args.no_cpu_baseline and world == 1:
@@ -327,30 +467,32 @@ def main():
         out, _ = O.run_program(plan, inputs, [out_name])
         dt = time.perf_counter() - t0
         cpu = {"value": len(out[out_name][0]) / dt, "unit": UNIT, "cores": cores, "kind": "port",
-               "sample": "one whole fixpoint of the same workload", "seconds": dt}
+               "sample": "one whole fixpoint of the same workload", "seconds": dt,
+               "checksum": checksum_text([result_checksum(out[out_name])])}
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "u32", "data": "synthetic", "ms_steps": [round(float(x), 4) for x in ms_t.tolist()],
         "config": {"workload": desc, "derived_tuples": derived, "iterations": stats["iterations"],
-                   "candidate_tuples": stats["candidate_tuples"], "l2": "256 MB buffer written between steps",
-                   "timing": "CUDA events on the library's stream around xlb_execute_plan, max over ranks"},
+                   "candidate_tuples": stats["candidate_tuples"], "l2": L2_NOTE, "timing": TIMING_NOTE},
+        "checksum": digest,
         "e2e": None if args.no_e2e else {"value": derived / (e2e_ms_per_step / 1e3), "unit": UNIT, "ms_per_step": e2e_ms_per_step,
-                                         "h2d_bytes_per_step": int(sum(c.nbytes for c in host_cols)), "d2h_bytes_per_step": int(d2h_bytes)},
+                                         "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": int(d2h_bytes)},
         "gpu_launches": int(launches),
         "clocks": clocks,
         "roofline": roof,
         "cpu_baseline": cpu,
         "host_last_step": {k: stats[k] for k in ("host_syncs", "ms_host_wait", "ms_host_total")},
-        # device time per phase in the last step (rank 0; only with XLB_FLAG_PROFILE, else zeros) and exchanged bytes
+        # device time per phase in the last step (rank 0; only with --phases, else zeros) and exchanged bytes
         "phases_last_step": {k: round(stats[k], 4) if isinstance(stats[k], float) else stats[k]
                              for k in ("ms_join", "ms_sort", "ms_setops", "ms_exchange", "exchange_bytes")},
         "host_ms_total_wait_alloc_per_step": host_steps,
+        "secondary": secondary,
     }
     emit(line)
     if world > 1:
-        dist.destroy_process_group()
+        env.dist.destroy_process_group()
 
 
 if __name__ == "__main__":

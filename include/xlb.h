@@ -302,7 +302,7 @@ const char* xlb_static_last_error(void);
 /* ---- per-kernel timing -------------------------------------------------------------------- */
 /* Counterpart of the reference's feature-gated per-phase CUDA-event timing
  * (crates/xlog-runtime/src/profiler.rs:355-640, feature `wcoj-phase-timing`): brackets every
- * launch of the named kernel ("*" = every kernel, NULL = off) with CUDA events on the launching
+ * launch of the named kernels (names separated by commas; "*" = every kernel, NULL = off) with CUDA events on the launching
  * stream.  xlb_profile_read waits for the stream, then reports per kernel its launches, device
  * time and algorithmic bytes since xlb_profile_enable. */
 typedef struct xlb_kernel_profile {

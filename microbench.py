@@ -1,9 +1,9 @@
 """Kernel microbenchmarks through the C ABI: one operator on seeded keys, every kernel timed with
 CUDA events (xlb_profile_enable) and reported against its algorithmic bytes.
 
-  python -m xlog_b200.microbench sort  --rows 32000000 --bits 32
-  python -m xlog_b200.microbench setops --rows 32000000 --bits 24
-  python -m xlog_b200.microbench join  --rows 16000000 --bits 20 --probe 4000000
+  python microbench.py sort  --rows 32000000 --bits 32
+  python microbench.py setops --rows 32000000 --bits 24
+  python microbench.py join  --rows 16000000 --bits 20 --probe 4000000
 
 These are the small cases that ncu captures of single kernels run; the figures the benchmark
 reports come from bench.py.
@@ -16,8 +16,11 @@ import os
 
 import numpy as np
 
-from .provider import KernelProvider
-from .workloads import splitmix64
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from xlog_b200.provider import KernelProvider  # noqa: E402
+from xlog_b200.workloads import splitmix64  # noqa: E402
 
 
 def _cols(n, bits, seed):
@@ -26,7 +29,7 @@ def _cols(n, bits, seed):
 
 
 def _peak():
-    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")
     if os.path.exists(path):
         return float(json.load(open(path))["hbm_gbs"]), "measured"
     return 6650.0, "fallback"

@@ -376,7 +376,7 @@ struct xlb_ctx {
         std::vector<std::pair<cudaEvent_t, cudaEvent_t>> pending;
     };
     std::map<std::string, ProfEntry> prof;
-    std::string prof_filter;  // "" = off, "*" = every kernel, else one kernel name
+    std::string prof_filter;  // "" = off, "*" = every kernel, else kernel names separated by commas
     ProfEntry* prof_open = nullptr;
     cudaEvent_t prof_e0 = nullptr;
 };
@@ -384,7 +384,14 @@ struct xlb_ctx {
 // Bracket one launch with CUDA events on the launching stream when its kernel is profiled.
 inline void prof_begin(xlb_ctx* c, const char* name, uint64_t bytes) {
     if (c->prof_filter.empty()) return;
-    if (c->prof_filter != "*" && c->prof_filter != name) return;
+    if (c->prof_filter != "*") {  // a kernel name, or several separated by commas
+        const std::string& f = c->prof_filter;
+        const size_t len = strlen(name);
+        bool hit = false;
+        for (size_t at = f.find(name); at != std::string::npos && !hit; at = f.find(name, at + 1))
+            hit = (at == 0 || f[at - 1] == ',') && (at + len == f.size() || f[at + len] == ',');
+        if (!hit) return;
+    }
     auto& e = c->prof[name];
     e.launches++;
     e.bytes += bytes;
