@@ -207,11 +207,16 @@ uint64_t comm_allreduce_sum(xlb_ctx* c, uint64_t v) {
     return s;
 }
 
-void comm_or_bitmaps(xlb_ctx* c, unsigned int* bitmap, uint64_t words) {
+Buf comm_gather_bitmaps(xlb_ctx* c, const unsigned int* bitmap, uint64_t words) {
     Comm* cm = live_comm(c);
-    const uint32_t W = c->comm_world;
-    Buf gathered = make_buf(c, (uint64_t)W * words * 4);
+    Buf gathered = make_buf(c, (uint64_t)c->comm_world * words * 4);
     NCCL_OK(api().AllGather(bitmap, gathered->p, words, ncclUint32, cm->comm, c->stream));
+    return gathered;
+}
+
+void comm_or_bitmaps(xlb_ctx* c, unsigned int* bitmap, uint64_t words) {
+    const uint32_t W = c->comm_world;
+    Buf gathered = comm_gather_bitmaps(c, bitmap, words);
     uint64_t blocks = (words + 255) / 256;
     if (blocks > (uint64_t)c->sm_count * 8) blocks = (uint64_t)c->sm_count * 8;
     prof_begin(c, "bitmap_or", (uint64_t)W * words * 4 + words * 4);

@@ -20,3 +20,5 @@ Keys comm_allgather_keys(xlb_ctx* c, const Keys& in);
 // bitmap <- OR over all ranks of their bitmaps (`words` 32-bit words each, the same on every rank):
 // an all-gather and one pass over the gathered copies; no host wait.
 void comm_or_bitmaps(xlb_ctx* c, unsigned int* bitmap, uint64_t words);
+// the ranks' bitmaps back to back, in rank order (an all-gather; no host wait)
+Buf comm_gather_bitmaps(xlb_ctx* c, const unsigned int* bitmap, uint64_t words);

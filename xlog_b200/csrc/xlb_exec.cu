@@ -15,6 +15,7 @@
 #include <deque>
 #include <functional>
 #include <set>
+#include <tuple>
 
 #include "xlb_comm.h"
 #include "xlb_ops.h"
@@ -253,6 +254,8 @@ struct RunState {
     std::map<std::string, Pending> pending;
     std::map<std::string, xlb_schema> head_schema;
     std::map<std::pair<std::string, int>, int> scans;  // scan joins run so far per (relation, key column)
+    // rows of a stored relation with column `col` equal to `value`, collected while the relation was packed
+    std::map<std::tuple<std::string, int, uint64_t>, Keys> prefiltered;
     // Several ranks.  Relations whose rows every rank holds in full while the running component is
     // evaluated: full copies of small stored relations (kept in the store under an alias name) and,
     // in replicated mode, the component's own heads.  A join against one of them needs no exchange.
@@ -934,6 +937,40 @@ static void eval_variant(xlb_ctx* c, const FlatRule& fr_in, size_t start, const 
     }
 }
 
+// The constant filter of a single-atom rule over `atom` (`rel(c, Y)`): column and value, or false.
+static bool single_atom_filter(const FlatRule& fr, int* col, uint64_t* value, size_t* which) {
+    if (fr.atoms.size() != 1 || fr.atoms[0].arity != 2 || fr.atoms[0].var[0] == fr.atoms[0].var[1]) return false;
+    for (size_t i = 0; i < fr.filters.size(); ++i) {
+        const FilterC& f = fr.filters[i];
+        if (f.applied || f.cmp != XLB_EQ || !f.rhs_const || f.rhs > 0xFFFFFFFFull) continue;
+        for (int j = 0; j < 2; ++j)
+            if (fr.atoms[0].var[j] == f.lhs) {
+                *col = j;
+                *value = f.rhs;
+                *which = i;
+                return true;
+            }
+    }
+    return false;
+}
+
+// Pack relation `name` (the first use of a relation given as columns).  When a single-atom rule
+// filters it by a constant, the matching rows are collected in the same pass over the columns.
+static Keys packed_for_rules(xlb_ctx* c, const std::string& name, const std::vector<FlatRule>& rules, RunState& rs) {
+    xlb_rel* r = store_get(c, name);
+    if (!r->packed)
+        for (auto& fr : rules) {
+            int col;
+            uint64_t value;
+            size_t which;
+            if (fr.atoms.size() != 1 || fr.atoms[0].rel != name || !single_atom_filter(fr, &col, &value, &which)) continue;
+            Keys rows;
+            if (ops_rel_packed_filtered(c, r, col, (uint32_t)value, &rows)) rs.prefiltered[std::make_tuple(name, col, value)] = rows;
+            break;
+        }
+    return ops_rel_packed(c, r);
+}
+
 static xlb_rel* empty_rel(xlb_ctx* c, const xlb_schema& s) {
     Keys k;
     k.buf = make_buf(c, 0);
@@ -1002,10 +1039,22 @@ static void seed_pass(xlb_ctx* c, const std::vector<FlatRule>& rules, const std:
         }
         if (any_empty) continue;
         size_t start = pick_seed_start(c, fr);
-        xlb_rel* sr = store_get(c, fr.atoms[start].rel);
-        Keys rows = ops_rel_packed(c, sr);
+        Keys rows = packed_for_rules(c, fr.atoms[start].rel, rules, rs);
+        FlatRule use = fr;
+        {
+            int col;
+            uint64_t value;
+            size_t which;
+            if (single_atom_filter(fr, &col, &value, &which)) {
+                auto hit = rs.prefiltered.find(std::make_tuple(fr.atoms[0].rel, col, value));
+                if (hit != rs.prefiltered.end()) {  // collected while the relation was packed
+                    rows = hit->second;
+                    use.filters[which].applied = true;
+                }
+            }
+        }
         Keys full_old = canonical_keys(c, store_get(c, fr.head), rs);
-        eval_variant(c, fr, start, rows, true, rec.count(fr.atoms[start].rel) ? home[fr.atoms[start].rel] : -1, full_old, home[fr.head], novel[fr.head], rs);
+        eval_variant(c, use, start, rows, true, rec.count(fr.atoms[start].rel) ? home[fr.atoms[start].rel] : -1, full_old, home[fr.head], novel[fr.head], rs);
     }
     for (auto& p : preds) {
         Keys full_old = canonical_keys(c, store_get(c, p), rs);
@@ -1089,7 +1138,7 @@ static void setup_ranks(xlb_ctx* c, const xlb_scc& scc, std::vector<FlatRule>& r
         xlb_rel* r = store_get(c, name);
         mine.push_back(r ? r->rows : 0);
         if (!r || !r->rows) return;
-        Keys k = ops_rel_packed(c, r);
+        Keys k = packed_for_rules(c, name, rules, rs);
         if (k.bound == ~0ull) unknown = true;
         else values |= (k.bound >> 32) | (k.bound & 0xFFFFFFFFull);
     };
@@ -1229,6 +1278,205 @@ static int carried_home(const std::vector<FlatRule>& rules, const std::string& p
     return -1;
 }
 
+// ------------------------------------------------------------------------------ frontier loop
+// A component of the shape  p(Z) :- p(Y), e(Y, Z)  — one head of one column, one recursive rule
+// that joins the frontier with one stored relation, evaluated by streaming over the relation
+// against a bitmap of the frontier, new tuples found on the head's bitmap — needs nothing from
+// the host between iterations but the decision to stop.  So iteration k + 1 is enqueued before
+// the row count of iteration k has come back: its frontier's length is read from device memory
+// and its buffers are sized by what the domain still has room for.  The host reads the counts one
+// iteration behind; the iteration that was enqueued on top of an empty frontier marks nothing
+// and is dropped.  Every rank of a replicated component sees the same counts, so all ranks stop
+// after the same number of exchanges.
+struct FrontierPlan {
+    const FlatRule* fr = nullptr;
+    size_t ei = 0;   // the stored atom
+    int kc = 0;      // its join column
+    int rel_lo = 0;  // what the head's column takes from a row of it: 0 the key, 1 the other column
+};
+
+static bool frontier_shape(xlb_ctx* c, const std::vector<FlatRule>& rules, const std::vector<std::string>& preds, const std::set<std::string>& rec,
+                           const std::map<std::string, xlb_schema>& schema, RunState& rs, FrontierPlan* fp) {
+    if (c->world != 1 || (c->flags & (XLB_FLAG_NO_DENSE | XLB_FLAG_KEEP_DELTAS)) || preds.size() != 1) return false;
+    if (schema.at(preds[0]).arity != 1 || getenv("XLB_NO_FRONTIER_LOOP")) return false;
+    const FlatRule* only = nullptr;
+    for (auto& fr : rules) {
+        int nrec = 0;
+        for (auto& a : fr.atoms) nrec += rec.count(a.rel) ? 1 : 0;
+        if (!nrec) continue;
+        if (only) return false;
+        only = &fr;
+    }
+    if (!only || only->atoms.size() != 2 || !only->filters.empty() || !only->checks.empty() || only->head_vars.size() != 1) return false;
+    const size_t ai = rec.count(only->atoms[0].rel) ? 0 : 1, ei = 1 - ai;
+    const Atom& pa = only->atoms[ai];
+    const Atom& ea = only->atoms[ei];
+    if (rec.count(ea.rel) || pa.arity != 1 || ea.arity != 2 || ea.var[0] == ea.var[1]) return false;
+    int kc = ea.var[0] == pa.var[0] ? 0 : ea.var[1] == pa.var[0] ? 1 : -1;
+    if (kc < 0) return false;
+    const int hv = only->head_vars[0];
+    if (hv != ea.var[0] && hv != ea.var[1]) return false;
+    if (index_ready(c, ea.rel, kc, rs)) return false;  // an index exists: probing it beats streaming
+    fp->fr = only;
+    fp->ei = ei;
+    fp->kc = kc;
+    fp->rel_lo = hv == ea.var[kc] ? 0 : 1;
+    return true;
+}
+
+// Wait for one event of the context's stream (work enqueued behind it keeps running).
+static void wait_event(xlb_ctx* c, cudaEvent_t ev) {
+    auto t0 = std::chrono::steady_clock::now();
+    for (;;) {
+        cudaError_t q = cudaEventQuery(ev);
+        if (q == cudaSuccess) break;
+        if (q != cudaErrorNotReady) CUDA_OK(q);
+        if (std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count() > 20.0) {
+            stream_wait(c);  // something is slow (a late peer?): the full wait knows how to give up
+            return;
+        }
+    }
+    c->ms_sync_wait += std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+    c->syncs++;
+}
+
+// Runs iterations from the state the seeding pass left (the head's list and "__delta_<head>" in the
+// store).  `it` counts finished iterations; `fix` is set when one of them found nothing.  Returns
+// with fix unset when the relation has been streamed over as often as building its index would
+// have cost (or the iteration limit is near): the general loop carries on from the stored state.
+// Inside, the head and the frontier exist as bitmaps only: an iteration is one stream over the
+// relation (candidates marked unless the head has them) and one pass over the bitmaps (what is new
+// becomes the next frontier and joins the head); on several ranks an all-gather of the candidate
+// bitmaps sits between the two.  The sorted list is read off the head's bitmap once, at the end.
+static void frontier_loop(xlb_ctx* c, const FrontierPlan& fp, const std::string& p, const xlb_schema& hs, RunState& rs, uint64_t& it, bool& fix) {
+    const Atom& ea = fp.fr->atoms[fp.ei];
+    xlb_rel* er = store_get(c, ea.rel);
+    xlb_rel* d0 = store_get(c, "__delta_" + p);
+    if (!er || !d0 || d0->rows == 0) return;
+    Keys rows = ops_rel_packed(c, er);
+    Keys delta = ops_rel_packed(c, d0);
+    Keys full = full_view(c, rs, p);
+    if (rows.bound == ~0ull || delta.bound == ~0ull || (full.n && full.bound == ~0ull)) return;
+    int hb = 0, lb = 0;
+    if (rs.repl.on) repl_bits(rs, 1, &hb, &lb);
+    else {
+        const uint64_t taken = fp.rel_lo == 0 ? (fp.kc == 0 ? rows.bound >> 32 : rows.bound & 0xFFFFFFFFull) : (fp.kc == 0 ? rows.bound & 0xFFFFFFFFull : rows.bound >> 32);
+        const uint64_t all = taken | delta.bound | (full.n ? full.bound : 0);
+        if (all >> 32) return;
+        lb = std::max(bit_len(all), 1);
+    }
+    if (lb > 27) return;
+    int& scans = rs.scans[{ea.rel, fp.kc}];
+    const int scan_limit = er->canonical && fp.kc == 0 ? 3 : 12;
+    if (scans >= scan_limit || it + 1 > c->max_iterations) return;
+    Keys none;
+    DenseState* ds = dense_state(c, rs, p, hb, lb, full, none);
+    if (ds->hi_bits != 0) return;
+    lb = ds->lo_bits;
+    const uint64_t domain = 1ull << lb, words = ds->words;
+    const int rel_keysel = fp.kc == 0 ? SRC_HI : SRC_LO;
+    if (rs.repl.on && !rs.repl.sliced.count(ea.rel)) {
+        // every rank holds all rows of this relation: each streams over its share of them
+        const uint64_t n = rows.n, lo = n * c->comm_rank / c->comm_world, hi = n * (c->comm_rank + 1) / c->comm_world;
+        rows = ops_slice(c, rows, lo, hi);
+    }
+    if ((uintptr_t)rows.ptr() & 15) return;
+
+    // frontier bitmaps (two, used in turn), this rank's candidate bitmap, and per iteration two
+    // counters: new tuples, and rows of the relation with a key in the frontier
+    const uint64_t bitmap_bytes = std::max<uint64_t>(words * 4, 16);
+    const int max_launches = scan_limit + 1;
+    Buf frontier[2] = {ops_keyset(c, delta, SRC_LO, lb), make_buf(c, bitmap_bytes)};
+    Buf cand = make_buf(c, bitmap_bytes);
+    Buf counts = make_buf(c, (uint64_t)max_launches * 16);
+    CUDA_OK(cudaMemsetAsync(cand->p, 0, bitmap_bytes, c->stream));
+    CUDA_OK(cudaMemsetAsync(counts->p, 0, (uint64_t)max_launches * 16, c->stream));
+    unsigned int* visited = ds->visited->as<unsigned int>();
+    struct Events {  // every event made here is destroyed, however the loop ends
+        std::vector<cudaEvent_t> all;
+        ~Events() {
+            for (auto e : all) cudaEventDestroy(e);
+        }
+    } events;
+    struct Flight {
+        cudaEvent_t ev = nullptr;
+        unsigned slot = 0;
+        unsigned long long* count = nullptr;  // device: [0] new tuples, [1] rows whose key was in the frontier
+    };
+    int launched = 0, cur_frontier = 0;
+    auto launch = [&](const unsigned long long* keys_in_frontier) {
+        Flight f;
+        f.count = counts->as<unsigned long long>() + 2 * launched;
+        {
+            PhaseTimer t(c, &rs.st.ms_join);
+            ops_frontier_scan(c, rows, rel_keysel, lb, frontier[cur_frontier]->as<unsigned int>(), fp.rel_lo, cand->as<unsigned int>(), visited, f.count + 1, keys_in_frontier);
+        }
+        Buf gathered;
+        if (rs.repl.on) {
+            PhaseTimer t(c, &rs.st.ms_exchange);
+            gathered = comm_gather_bitmaps(c, cand->as<unsigned int>(), words);
+            rs.st.exchange_bytes += words * 4 * (uint64_t)(rs.repl.world - 1);
+        }
+        {
+            PhaseTimer t(c, &rs.st.ms_setops);
+            ops_frontier_step(c, gathered ? gathered->as<unsigned int>() : cand->as<unsigned int>(), gathered ? rs.repl.world : 1, words, cand->as<unsigned int>(), visited,
+                              frontier[1 - cur_frontier]->as<unsigned int>(), f.count);
+        }
+        cur_frontier = 1 - cur_frontier;
+        f.slot = 20 + 2 * (launched & 3);
+        CUDA_OK(cudaMemcpyAsync(&c->h_scalar[f.slot], f.count, 16, cudaMemcpyDeviceToHost, c->stream));
+        CUDA_OK(cudaEventCreateWithFlags(&f.ev, cudaEventDisableTiming));
+        events.all.push_back(f.ev);
+        CUDA_OK(cudaEventRecord(f.ev, c->stream));
+        ++launched;
+        ++scans;
+        return f;
+    };
+    uint64_t last_new = delta.n;
+    int last_frontier = 0;  // which bitmap holds the tuples of the last finished iteration
+    Flight cur = launch(nullptr);
+    for (;;) {
+        // `cur` is the iteration in flight whose counts the host has not seen: the next one is
+        // enqueued on top of it (it does nothing if cur finds nothing new)
+        const bool more = scans < scan_limit && launched < max_launches && it + 2 <= c->max_iterations;
+        const int cur_out = cur_frontier;
+        Flight next;
+        if (more) next = launch(cur.count);
+        wait_event(c, cur.ev);
+        const uint64_t tot = c->h_scalar[cur.slot], marked = c->h_scalar[cur.slot + 1];
+        ++it;
+        rs.st.iterations++;
+        rs.st.candidate_tuples += marked;
+        ds->rows += tot;
+        last_new = tot;
+        last_frontier = cur_out;
+        if (tot == 0) {
+            fix = true;
+            break;
+        }
+        if (!more) break;
+        cur = next;
+    }
+    // back to lists: the head in order off its bitmap, and the last iteration's tuples as the delta
+    {
+        PhaseTimer t(c, &rs.st.ms_setops);
+        if (ds->rows != full.n) install_full(c, p, hs, ops_dense_state_rows(c, *ds, domain - 1), nullptr, rs);
+        Keys d;
+        d.buf = make_buf(c, 0);
+        if (last_new) {
+            DenseState last;
+            last.visited = frontier[last_frontier];
+            last.words = words;
+            last.hi_bits = 0;
+            last.lo_bits = lb;
+            last.rows = last_new;
+            last.valid = true;
+            d = ops_dense_state_rows(c, last, domain - 1);
+        }
+        store_put(c, "__delta_" + p, ops_rel_from_keys(c, hs, d, true));
+    }
+}
+
 static void run_scc(xlb_ctx* c, const xlb_scc& scc, RunState& rs) {
     if (!scc.rules && scc.n_rules) xlb_fail(XLB_ERR_INVALID, "SCC %u has no rule array", scc.id);
     std::vector<std::string> preds;
@@ -1349,7 +1597,12 @@ static void run_scc(xlb_ctx* c, const xlb_scc& scc, RunState& rs) {
             }
         }
     } guard{c, rs, preds};
-    for (uint64_t it = 0; it < c->max_iterations; ++it) {  // recursive.rs:619-937
+    uint64_t it = 0;
+    {
+        FrontierPlan fp;
+        if (frontier_shape(c, rules, preds, rec, schema, rs, &fp)) frontier_loop(c, fp, preds[0], schema[preds[0]], rs, it, fix);
+    }
+    for (; !fix && it < c->max_iterations; ++it) {  // recursive.rs:619-937
         rs.st.iterations++;
         std::map<std::string, Keys> novel;
         for (auto& fr : rules) {

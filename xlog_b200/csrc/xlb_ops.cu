@@ -288,7 +288,7 @@ extern "C" xlb_status xlb_profile_read(xlb_ctx* c, xlb_kernel_profile* out, uint
 }
 
 // ------------------------------------------------------------------------------ key-array ops
-Keys ops_rel_packed(xlb_ctx* c, const xlb_rel* r) {
+static Keys rel_packed(xlb_ctx* c, const xlb_rel* r, int fcol, uint32_t fval, Keys* filtered) {
     Keys k;
     k.n = r->rows;
     k.bound = r->or_bound;
@@ -298,24 +298,43 @@ Keys ops_rel_packed(xlb_ctx* c, const xlb_rel* r) {
     if (r->rows) {
         // pack and, in the same sweep, reduce the OR of all rows: later sorts of anything derived
         // from this relation plan their digits from it without a read-back
-        Buf oa = make_buf(c, 8);
-        CUDA_OK(cudaMemsetAsync(oa->p, 0, 8, c->stream));
+        Buf oa = make_buf(c, 16);
+        CUDA_OK(cudaMemsetAsync(oa->p, 0, 16, c->stream));
         prof_begin(c, "pack", r->rows * 16ull);
+        const bool fuse = filtered && r->schema.arity == 2 && fcol >= 0 && fcol < 2;
+        if (fuse) filtered->buf = make_buf(c, r->rows * 8);  // at most every row; trimmed below
         if (r->schema.arity == 2) {
             const bool vec = (((uintptr_t)r->cols[0]->p | (uintptr_t)r->cols[1]->p | (uintptr_t)b->p) & 15) == 0;
             pack2_k<<<grid_for(c, r->rows, BLOCK * 4), BLOCK, 0, c->stream>>>(r->cols[0]->as<uint32_t>(), r->cols[1]->as<uint32_t>(), b->as<uint64_t>(), r->rows,
-                                                                              oa->as<unsigned long long>(), vec);
+                                                                              oa->as<unsigned long long>(), vec, fuse ? fcol : -1, fval,
+                                                                              fuse ? filtered->buf->as<uint64_t>() : nullptr, oa->as<unsigned long long>() + 1);
         }
         else pack1_k<<<grid_for(c, r->rows), BLOCK, 0, c->stream>>>(r->cols[0]->as<uint32_t>(), b->as<uint64_t>(), r->rows, oa->as<unsigned long long>());
         check_launch(c, "pack");
-        unsigned long long h[1];
-        read_words(c, oa->p, 1, h);
+        unsigned long long h[2];
+        read_words(c, oa->p, 2, h);
         r->or_bound = h[0];
-    } else r->or_bound = 0;
+        if (fuse) {
+            filtered->n = h[1];
+            filtered->bound = h[0];
+            if (filtered->n * 2 < r->rows) filtered->buf = ops_slice(c, *filtered, 0, filtered->n).buf;  // give the large buffer back
+        }
+    } else {
+        r->or_bound = 0;
+        if (filtered) filtered->buf = make_buf(c, 0);
+    }
     r->packed = b;
     k.buf = b;
     k.bound = r->or_bound;
     return k;
+}
+
+Keys ops_rel_packed(xlb_ctx* c, const xlb_rel* r) { return rel_packed(c, r, -1, 0, nullptr); }
+
+bool ops_rel_packed_filtered(xlb_ctx* c, const xlb_rel* r, int fcol, uint32_t fval, Keys* filtered) {
+    if (r->packed || r->schema.arity != 2 || !rel_packable(r->schema)) return false;
+    rel_packed(c, r, fcol, fval, filtered);
+    return true;
 }
 
 void ops_rel_columns(xlb_ctx* c, const xlb_rel* r) {
@@ -659,9 +678,9 @@ uint64_t ops_scan_join_bound(const Keys& bag, int keysel, const Keys& rel, int r
     return (pick(rel_hi) << 32) | pick(rel_lo);
 }
 
-static Buf scan_join_keyset(xlb_ctx* c, const Keys& bag, int keysel, int key_bits) {
+Buf ops_keyset(xlb_ctx* c, const Keys& bag, int keysel, int key_bits) {
     const uint64_t domain = 1ull << key_bits;
-    const uint64_t bytes = std::max<uint64_t>(domain / 8, 4);
+    const uint64_t bytes = std::max<uint64_t>(domain / 8, 16);  // whole 16-byte words: the streaming kernel copies it that way
     Buf keyset = make_buf(c, bytes);
     CUDA_OK(cudaMemsetAsync(keyset->p, 0, bytes, c->stream));
     if (bag.n) {
@@ -679,7 +698,7 @@ Keys ops_scan_join(xlb_ctx* c, const Keys& bag, int keysel, int key_bits, const 
         o.buf = make_buf(c, 0);
         return o;
     }
-    Buf keyset = scan_join_keyset(c, bag, keysel, key_bits);
+    Buf keyset = ops_keyset(c, bag, keysel, key_bits);
     // the output is at most the relation
     Buf out = make_buf(c, rel.n * 8);
     o.n = select_unordered(c, PredKeyIn{rel.ptr(), rel_keysel, keyset->as<unsigned int>(), 1ull << key_bits}, EmitScanRow{rel.ptr(), rel_keysel, rel_hi, rel_lo, out->as<uint64_t>()}, rel.n);
@@ -695,12 +714,30 @@ Keys ops_scan_join(xlb_ctx* c, const Keys& bag, int keysel, int key_bits, const 
 void ops_scan_join_mark(xlb_ctx* c, const Keys& bag, int keysel, int key_bits, const Keys& rel, int rel_keysel, int rel_hi, int rel_lo, DenseSet& d) {
     d.bound |= ops_scan_join_bound(bag, keysel, rel, rel_keysel, rel_hi, rel_lo);
     if (bag.n == 0 || rel.n == 0) return;
-    Buf keyset = scan_join_keyset(c, bag, keysel, key_bits);
+    Buf keyset = ops_keyset(c, bag, keysel, key_bits);
     prof_begin(c, "scan_join_mark", rel.n * 8ull);
     if ((uintptr_t)rel.ptr() & 15) xlb_fail(XLB_ERR_INVALID, "internal: scan join over a row array that is not 16-byte aligned");
     scan_join_mark_k<<<grid_for(c, rel.n, SJ_TILE), BLOCK, 0, c->stream>>>(rel.ptr(), rel.n, rel_keysel, keyset->as<unsigned int>(), 1ull << key_bits, rel_hi, rel_lo,
                                                                   d.bitmap->as<unsigned int>(), d.words, d.lo_bits, (unsigned long long*)(d.counts + 1), c->d_status, d.visited);
     check_launch(c, "scan_join_mark");
+}
+
+void ops_frontier_scan(xlb_ctx* c, const Keys& rel, int rel_keysel, int bits, const unsigned int* frontier, int rel_lo, unsigned int* cand, const unsigned int* visited,
+                       unsigned long long* count_marked, const unsigned long long* keys_in_frontier) {
+    if (rel.n == 0) return;
+    if ((uintptr_t)rel.ptr() & 15) xlb_fail(XLB_ERR_INVALID, "internal: scan join over a row array that is not 16-byte aligned");
+    const uint64_t domain = 1ull << bits, words = (domain + 31) / 32;
+    prof_begin(c, "scan_join_mark", rel.n * 8ull);
+    scan_join_mark_k<<<grid_for(c, rel.n, SJ_TILE), BLOCK, 0, c->stream>>>(rel.ptr(), rel.n, rel_keysel, frontier, domain, /*hi_src=*/2, rel_lo, cand, words, bits, count_marked,
+                                                                  c->d_status, visited, keys_in_frontier);
+    check_launch(c, "scan_join_mark");
+}
+
+void ops_frontier_step(xlb_ctx* c, const unsigned int* cand_parts, uint32_t parts, uint64_t words, unsigned int* clear, unsigned int* visited, unsigned int* next_frontier,
+                       unsigned long long* count_new) {
+    prof_begin(c, "frontier_step", words * 4ull * (parts + 3));
+    frontier_step_k<<<grid_for(c, words), BLOCK, 0, c->stream>>>(cand_parts, parts, words, clear, visited, next_frontier, count_new);
+    check_launch(c, "frontier_step");
 }
 
 Keys ops_semi_filter(xlb_ctx* c, const Keys& bag, int keysel, const Index& ix, bool anti, const uint64_t* pkeys) {

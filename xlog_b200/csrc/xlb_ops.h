@@ -35,6 +35,9 @@ struct Index {
 };
 
 Keys ops_rel_packed(xlb_ctx* c, const xlb_rel* r);             // packed view (cached on the relation)
+// The same for a two-column relation that is not packed yet, with the rows whose column fcol equals
+// fval collected in the same pass (`filtered`, a bag).  False (nothing done): already packed.
+bool ops_rel_packed_filtered(xlb_ctx* c, const xlb_rel* r, int fcol, uint32_t fval, Keys* filtered);
 void ops_rel_columns(xlb_ctx* c, const xlb_rel* r);            // materialise column view (cached)
 xlb_rel* ops_rel_from_keys(xlb_ctx* c, const xlb_schema& s, Keys k, bool canonical);
 
@@ -118,6 +121,19 @@ uint64_t ops_scan_join_bound(const Keys& bag, int keysel, const Keys& rel, int r
 Keys ops_scan_join(xlb_ctx* c, const Keys& bag, int keysel, int key_bits, const Keys& rel, int rel_keysel, int rel_hi, int rel_lo);
 // the same, marking into d (one marking step per DenseSet; count in d.marked after ops_dense_finish)
 void ops_scan_join_mark(xlb_ctx* c, const Keys& bag, int keysel, int key_bits, const Keys& rel, int rel_keysel, int rel_hi, int rel_lo, DenseSet& d);
+// The key set of a scan join: a bitmap over 2^key_bits keys with the bits of the bag's keys set
+// (whole 16-byte words).
+Buf ops_keyset(xlb_ctx* c, const Keys& bag, int keysel, int key_bits);
+// Frontier loop on bitmaps over one domain of 2^bits values (a head of one column).
+//   scan: every row of `rel` whose key is in `frontier` marks its head value in `cand` unless
+//         `visited` holds it; *count_marked += the rows with a key in the frontier.  With
+//         keys_in_frontier (device) the launch does nothing when that count is zero.
+//   step: the candidates (OR of `parts` bitmaps back to back) that `visited` lacks become
+//         `next_frontier` and join `visited`; *count_new += their number; `clear` is zeroed.
+void ops_frontier_scan(xlb_ctx* c, const Keys& rel, int rel_keysel, int bits, const unsigned int* frontier, int rel_lo, unsigned int* cand, const unsigned int* visited,
+                       unsigned long long* count_marked, const unsigned long long* keys_in_frontier);
+void ops_frontier_step(xlb_ctx* c, const unsigned int* cand_parts, uint32_t parts, uint64_t words, unsigned int* clear, unsigned int* visited, unsigned int* next_frontier,
+                       unsigned long long* count_new);
 // rows of `bag` whose key has (semi) or lacks (anti) a match in the index, in bag order
 // (pkeys, when given, holds the key word of every bag row instead of a half named by keysel)
 Keys ops_semi_filter(xlb_ctx* c, const Keys& bag, int keysel, const Index& ix, bool anti, const uint64_t* pkeys = nullptr);
