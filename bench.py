@@ -378,6 +378,7 @@ def main():
     ap.add_argument("--secondary-steps", type=int, default=5)
     ap.add_argument("--secondary-warmup", type=int, default=3)
     ap.add_argument("--shuffle-only", action="store_true", help="headline workload with XLB_FLAG_SHUFFLE_ONLY (several ranks: no replicated relations)")
+    ap.add_argument("--flags", type=int, default=0, help="extra XLB_FLAG_* bits for the headline workload's context (A/B runs)")
     ap.add_argument("--phases", action="store_true", help="time the executor's phases with events (fills phases_last_step; adds event records to the timed steps)")
     ap.add_argument("--breakdown", action="store_true", help="extra untimed pass with every kernel timed, to stderr")
     args = ap.parse_args()
@@ -390,7 +391,7 @@ def main():
     from xlog_b200 import _abi as A
     env = Env(args)
     world, rank = env.world, env.rank
-    flags = (A.FLAG_PROFILE if args.phases else 0) | (A.FLAG_SHUFFLE_ONLY if args.shuffle_only else 0)
+    flags = (A.FLAG_PROFILE if args.phases else 0) | (A.FLAG_SHUFFLE_ONLY if args.shuffle_only else 0) | args.flags
     job = Job(env, args.workload, args.scale, flags)
     prov = job.prov
 

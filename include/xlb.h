@@ -92,6 +92,10 @@ typedef struct xlb_config {
                                       the state (full, delta) can be saved; a later
                                       xlb_execute_plan that finds the delta of every head of an SCC
                                       in the store resumes that SCC from them instead of seeding it */
+#define XLB_FLAG_NO_TUPLE_SET 16u  /* never keep a derived relation as a hash set: candidates of a head
+                                      too wide for a bitmap are then always sorted, deduplicated and
+                                      subtracted by merging (the counterpart of the reference's
+                                      XLOG_DISABLE_FACTORIZED_DELTA for its sparse route)            */
 #define XLB_FLAG_SHUFFLE_ONLY 8u   /* several ranks: never give every rank a full copy of a relation
                                       (no replicated evaluation of small-domain components, no
                                       broadcast of small stored relations): every join runs on hash

@@ -23,7 +23,7 @@ def _executor(p, plan, edge):
     return ex
 
 
-@pytest.mark.parametrize("flags", [0, A.FLAG_NO_DENSE])
+@pytest.mark.parametrize("flags", [0, A.FLAG_NO_DENSE, A.FLAG_NO_DENSE | A.FLAG_NO_TUPLE_SET])
 @pytest.mark.parametrize("builder,out", [(programs.transitive_closure, "reach"), (programs.reach_from_source, "r")])
 def test_resume_equals_an_uninterrupted_run(oracle, tmp_path, builder, out, flags):
     a = np.arange(0, 40, dtype=np.uint32)

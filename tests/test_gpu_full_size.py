@@ -33,7 +33,7 @@ def test_config2_full_size_equals_an_independent_bfs(c2_edges):
 
     plan = programs.reach_from_source(0)
     results = []
-    for flags in (0, A.FLAG_NO_DENSE):
+    for flags in (0, A.FLAG_NO_DENSE, A.FLAG_NO_DENSE | A.FLAG_NO_TUPLE_SET):
         p = KernelProvider(device=0, flags=flags)
         got, stats = run_program(p, plan, {"edge": [c0, c1]}, ["r"])
         results.append((got["r"][0], stats["candidate_tuples"], stats["iterations"]))

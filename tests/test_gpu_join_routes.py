@@ -32,7 +32,7 @@ def _chain(n, extra, seed):
     return shuffle_rows([c0, c1], seed + 2)
 
 
-@pytest.mark.parametrize("flags", [0, A.FLAG_NO_DENSE])
+@pytest.mark.parametrize("flags", [0, A.FLAG_NO_DENSE, A.FLAG_NO_DENSE | A.FLAG_NO_TUPLE_SET])
 def test_long_chain_goes_from_scans_to_an_index(oracle, flags):
     # 80 iterations: more than the scans a relation is given before its index is built
     c0, c1 = _chain(81, 40, 5)
@@ -73,7 +73,7 @@ def test_duplicate_rows_count_once_per_row_on_every_route(oracle):
     c0, c1 = np.concatenate([c0, c0[:30]]), np.concatenate([c1, c1[:30]])  # 30 rows twice
     plan = programs.reach_from_source(0)
     want, ex = oracle.run_program(plan, {"edge": [c0, c1]}, ["r"])
-    for flags in (0, A.FLAG_NO_DENSE):
+    for flags in (0, A.FLAG_NO_DENSE, A.FLAG_NO_DENSE | A.FLAG_NO_TUPLE_SET):
         p = KernelProvider(device=0, flags=flags)
         got, stats = run_program(p, plan, {"edge": [c0, c1]}, ["r"])
         _same(got["r"], want["r"], f"flags={flags}")
@@ -105,7 +105,7 @@ def _two_source_plan():
     return ExecutionPlan([Scc(0, True, [base, rec])], ids)
 
 
-@pytest.mark.parametrize("flags", [0, A.FLAG_NO_DENSE])
+@pytest.mark.parametrize("flags", [0, A.FLAG_NO_DENSE, A.FLAG_NO_DENSE | A.FLAG_NO_TUPLE_SET])
 def test_head_bitmap_widens_with_the_domain(oracle, flags):
     a = [np.array([1, 2, 3, 5], dtype=np.uint32)]
     b0 = np.array([1, 2, 3, 900, 70000, 5, 1 << 20], dtype=np.uint32)
@@ -128,7 +128,7 @@ def test_head_that_already_holds_rows_is_not_derived_again(oracle):
     h0 = [np.array([30, 11, 11, 500], dtype=np.uint32)]  # unsorted, with a duplicate
     plan = _two_source_plan()
     want, ex = oracle.run_program(plan, {"a": a, "b": [b0, b1], "h": h0}, ["h"])
-    for flags in (0, A.FLAG_NO_DENSE):
+    for flags in (0, A.FLAG_NO_DENSE, A.FLAG_NO_DENSE | A.FLAG_NO_TUPLE_SET):
         p = KernelProvider(device=0, flags=flags)
         got, _ = run_program(p, plan, {"a": a, "b": [b0, b1], "h": h0}, ["h"])
         _same(got["h"], want["h"], f"flags={flags}")
@@ -142,7 +142,7 @@ def test_scan_join_at_bench_shape_matches_the_index_route():
     c0, c1 = workloads.rmat_graph(16, 16)
     plan = programs.reach_from_source(0)
     res = []
-    for flags in (0, A.FLAG_NO_DENSE):
+    for flags in (0, A.FLAG_NO_DENSE, A.FLAG_NO_DENSE | A.FLAG_NO_TUPLE_SET):
         p = KernelProvider(device=0, flags=flags)
         got, stats = run_program(p, plan, {"edge": [c0, c1]}, ["r"])
         res.append((got["r"], stats["candidate_tuples"], stats["derived_tuples"]))

@@ -11,7 +11,9 @@ Every program runs in each way the library evaluates a component on several rank
                the size from which a relation counts as large);
   broadcast    hash-partitioned heads, stored relations copied to every rank (XLB_FLAG_NO_DENSE
                switches the bitmaps off);
-  shuffle      everything hash-partitioned, an all-to-all per join step (XLB_FLAG_SHUFFLE_ONLY).
+  shuffle      everything hash-partitioned, an all-to-all per join step (XLB_FLAG_SHUFFLE_ONLY);
+               once more with the heads kept as hash sets (bitmaps off), and once with neither, so
+               that candidates are sorted and subtracted by merging.
 """
 import os
 import socket
@@ -58,7 +60,8 @@ def _cases():
 def _modes():
     from xlog_b200 import _abi as A
     return [("replicated", 0, None), ("sliced", 0, "64"), ("broadcast", A.FLAG_NO_DENSE, None),
-            ("shuffle", A.FLAG_SHUFFLE_ONLY, None), ("shuffle_sorted", A.FLAG_SHUFFLE_ONLY | A.FLAG_NO_DENSE, None)]
+            ("shuffle", A.FLAG_SHUFFLE_ONLY, None), ("shuffle_set", A.FLAG_SHUFFLE_ONLY | A.FLAG_NO_DENSE, None),
+            ("shuffle_sorted", A.FLAG_SHUFFLE_ONLY | A.FLAG_NO_DENSE | A.FLAG_NO_TUPLE_SET, None)]
 
 
 def _rank_main(rank, world, port, out_dir):

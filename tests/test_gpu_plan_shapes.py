@@ -49,7 +49,7 @@ def test_shape_against_oracle(oracle, name, rows, bits):
     plan = _plans()[name]
     inputs = {"e": _rel(rows, 2, bits, 11), "n": _rel(max(rows // 3, 0), 1, bits, 29)}
     want, ex = oracle.run_program(plan, inputs, ["h"])
-    for flags in (0, A.FLAG_NO_DENSE):
+    for flags in (0, A.FLAG_NO_DENSE, A.FLAG_NO_DENSE | A.FLAG_NO_TUPLE_SET):
         p = KernelProvider(device=0, flags=flags)
         got, stats = run_program(p, plan, inputs, ["h"])
         assert len(got["h"]) == len(want["h"])

@@ -171,7 +171,7 @@ def test_triangle_body_with_a_closing_atom(oracle):
     plan = ExecutionPlan([Scc(0, False, [CompiledRule("tri", body, (A.U32,))])], {"edge": 0, "tri": 1})
     want, _ = oracle.run_program(plan, {"edge": [c0, c1]}, ["tri"])
     assert len(want["tri"][0]) > 50
-    for flags in (0, A.FLAG_NO_DENSE):
+    for flags in (0, A.FLAG_NO_DENSE, A.FLAG_NO_DENSE | A.FLAG_NO_TUPLE_SET):
         p = KernelProvider(device=0, flags=flags)
         got, _ = run_program(p, plan, {"edge": [c0, c1]}, ["tri"])
         assert all(np.array_equal(g, w) for g, w in zip(got["tri"], want["tri"]))
@@ -207,7 +207,7 @@ def test_dense_route_on_and_off_agree(oracle, name):
         plan, inputs, out = programs.same_generation(), {"edge": [c0, c1]}, "sg"
     want, _ = oracle.run_program(plan, inputs, [out])
     results = []
-    for flags in (0, A.FLAG_NO_DENSE):
+    for flags in (0, A.FLAG_NO_DENSE, A.FLAG_NO_DENSE | A.FLAG_NO_TUPLE_SET):
         p = KernelProvider(device=0, flags=flags)
         p.profile_enable("*")
         got, _ = run_program(p, plan, inputs, [out])

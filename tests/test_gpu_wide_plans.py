@@ -49,7 +49,7 @@ def test_u64_three_cycle_gives_all_nine_pairs(oracle):
     p.close()
 
 
-@pytest.mark.parametrize("flags", [0, A.FLAG_NO_DENSE])
+@pytest.mark.parametrize("flags", [0, A.FLAG_NO_DENSE, A.FLAG_NO_DENSE | A.FLAG_NO_TUPLE_SET])
 @pytest.mark.parametrize("dtype,code", [(np.uint64, A.U64), (np.int64, A.I64), (np.int32, A.I32), (np.float64, A.F64)])
 def test_typed_closure_against_the_oracle(oracle, dtype, code, flags):
     rng = np.random.default_rng(11)

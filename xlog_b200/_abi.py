@@ -28,6 +28,7 @@ FLAG_PROFILE = 1
 FLAG_NO_DENSE = 2
 FLAG_KEEP_DELTAS = 4
 FLAG_SHUFFLE_ONLY = 8
+FLAG_NO_TUPLE_SET = 16
 
 
 class Schema(C.Structure):

@@ -245,6 +245,7 @@ struct Flattener {
 struct RunState {
     xlb_run_stats st{};
     std::map<std::string, DenseState> dense;  // per head relation: its tuples as a bitmap, while they fit one
+    std::map<std::string, TupleSet> tset;     // per head relation too wide for a bitmap: its tuples as a hash set
     // Deltas of a head whose merge into the stored sorted list is put off: while the bitmap serves
     // the set difference and no rule reads the list, merging it every iteration is wasted work.
     struct Pending {
@@ -511,8 +512,14 @@ static void materialize_full(xlb_ctx* c, RunState& rs, const std::string& head) 
     if (ds.valid && ds.rows == full.n + pd.rows) {
         merged = ops_dense_state_rows(c, ds, (full.n ? full.bound : 0) | pd.bound);
     } else {
+        // the deltas are sorted and pairwise disjoint: two are merged, more are sorted together once
         Keys acc = pd.deltas[0];
-        for (size_t i = 1; i < pd.deltas.size(); ++i) acc = ops_merge_disjoint(c, acc, pd.deltas[i]);
+        if (pd.deltas.size() == 2) acc = ops_merge_disjoint(c, acc, pd.deltas[1]);
+        else if (pd.deltas.size() > 2) {
+            acc = ops_concat(c, pd.deltas);
+            pd.deltas.clear();
+            ops_sort(c, acc);
+        }
         merged = full.n ? ops_merge_disjoint(c, full, acc) : acc;
     }
     install_full(c, head, rs.head_schema[head], merged, nullptr, rs);
@@ -923,8 +930,21 @@ static void eval_variant(xlb_ctx* c, const FlatRule& fr_in, size_t start, const 
             DenseState* ds = dense_state(c, rs, fr.head, hb, lb, full, novel);
             fresh = ops_dense_novel(c, cand, full, ds->hi_bits, ds->lo_bits, ds->visited->as<unsigned int>());
             ds->rows += fresh.n;
+        } else if (!(c->flags & XLB_FLAG_NO_TUPLE_SET)) {
+            // the head as a hash set: a candidate is new when its insertion takes an empty slot, and
+            // only the new tuples are sorted
+            rs.dense[fr.head].valid = false;
+            TupleSet& ts = rs.tset[fr.head];
+            {
+                PhaseTimer t(c, &rs.st.ms_setops);
+                if (!ts.valid || ts.rows != full.n + novel.n) ops_tuple_set_build(c, ts, real_full(c, rs, fr.head), novel, cand.n);
+                fresh = ops_tuple_set_novel(c, ts, cand);
+            }
+            PhaseTimer t(c, &rs.st.ms_sort);
+            ops_sort(c, fresh);
         } else {
             rs.dense[fr.head].valid = false;  // this route does not keep the bitmap: rebuilt when next wanted
+            rs.tset[fr.head].valid = false;
             {
                 PhaseTimer t(c, &rs.st.ms_sort);
                 ops_sort(c, cand, /*keep_input=*/cand.buf == start_rows.buf);  // a single-atom body hands over a stored relation
@@ -1515,12 +1535,14 @@ static void run_scc(xlb_ctx* c, const xlb_scc& scc, RunState& rs) {
     struct Cleanup {  // the full copies go when the component is done, however it ends
         xlb_ctx* c;
         RunState& rs;
+        const std::vector<std::string>& preds;
         ~Cleanup() {
+            for (auto& p : preds) rs.tset.erase(p);  // the hash sets can be gigabytes: they go with the component
             drop_aliases(c, rs);
             rs.repl = RunState::Repl();
             rs.replicated.clear();
         }
-    } cleanup{c, rs};
+    } cleanup{c, rs, preds};
     PlanAsOneRank one_rank;
     setup_ranks(c, scc, rules, preds, rec, schema, rs);
     std::map<std::string, int> home;
@@ -1651,8 +1673,11 @@ static void run_scc(xlb_ctx* c, const xlb_scc& scc, RunState& rs) {
             {
                 // nobody reads the list and the bitmap is in step with full + delta: put the merge off
                 const DenseState& ds = rs.dense[p];
+                const TupleSet& ts = rs.tset[p];
                 const Keys view = full_view(c, rs, p);
-                if (c->world == 1 && !(c->flags & XLB_FLAG_NO_DENSE) && !list_read.count(p) && ds.valid && ds.rows == view.n + d.n) {
+                const bool on_bitmap = c->world == 1 && !(c->flags & XLB_FLAG_NO_DENSE) && ds.valid && ds.rows == view.n + d.n;
+                const bool in_set = ts.valid && ts.rows == view.n + d.n;  // (holds on every rank or none: the route is chosen from agreed bounds)
+                if (!list_read.count(p) && (on_bitmap || in_set)) {
                     RunState::Pending& pd = rs.pending[p];
                     pd.deltas.push_back(d);
                     pd.rows += d.n;

@@ -378,14 +378,14 @@ static __global__ void __launch_bounds__(SA_BLOCK) select_append_k(Pred pred, Em
 
 // Returns the number of selected rows (one host read-back); output order unspecified.
 template <class Pred, class Emit>
-uint64_t select_unordered(xlb_ctx* c, Pred pred, Emit emit, uint64_t n) {
+uint64_t select_unordered(xlb_ctx* c, Pred pred, Emit emit, uint64_t n, const char* name = "select_append", uint64_t bytes = 0) {
     if (n == 0) return 0;
     uint64_t ntiles = (n + SA_TILE - 1) / SA_TILE;
     Buf total = make_buf(c, 8);
     CUDA_OK(cudaMemsetAsync(total->p, 0, 8, c->stream));
-    prof_begin(c, "select_append", 0);
+    prof_begin(c, name, bytes);
     select_append_k<Pred, Emit><<<(unsigned)ntiles, SA_BLOCK, 0, c->stream>>>(pred, emit, n, total->as<unsigned long long>());
-    check_launch(c, "select_append");
+    check_launch(c, name);
     unsigned long long h;
     read_words(c, total->p, 1, &h);
     return h;
@@ -1237,6 +1237,76 @@ static __global__ void __launch_bounds__(BLOCK) hash_probe_k(LoadKey load_key, u
         match[i] = m;
     }
 }
+
+// ------------------------------------------------------------------------------ tuple hash set
+// The tuples of one relation as an open-addressing set of 64-bit words (linear probing, at most
+// half full, empty = all ones), kept across the iterations of a fixpoint: a candidate is new
+// exactly when its insertion takes an empty slot, so "sort the candidates, drop duplicates,
+// subtract the relation" becomes one table access per candidate and only the new tuples are
+// ever sorted.  The reference has the same route for heads too wide for a bitmap
+// (fj_delta_sparse_novel, kernels/wcoj.cu:4008-4121).
+//
+// Random accesses to a table of gigabytes run at a fraction of the memory's streaming rate
+// (measured: 17 G insertions/s into an 8 GB table).  So the set stores mix64(tuple) — a bijection,
+// inverted when tuples leave the set — and a slot's index is the TOP bits of that word: one pass of
+// the radix sort over the top byte then groups the candidates into 256 runs that each fall into
+// one 256th of the table, a window the L2 holds, and the insertions of a run are L2 accesses.
+constexpr unsigned long long HSET_EMPTY = ~0ull;
+
+// Inverse of mix64: x ^= x >> 33 undoes itself (33 >= 32), the multipliers are inverted mod 2^64.
+__host__ __device__ __forceinline__ uint64_t unmix64(uint64_t x) {
+    x ^= x >> 33;
+    x *= 0x9cb4b2f8129337dbull;  // inverse of 0xc4ceb9fe1a85ec53
+    x ^= x >> 33;
+    x *= 0x4f74430c22a54005ull;  // inverse of 0xff51afd7ed558ccd
+    x ^= x >> 33;
+    return x;
+}
+static __global__ void mix_k(const uint64_t* __restrict__ in, uint64_t* __restrict__ out, uint64_t n, int inverse) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) out[i] = inverse ? unmix64(in[i]) : mix64(in[i]);
+}
+
+// true: the (mixed) word was not in the set and is now.  Bounded by the table size.
+// The one word that equals the empty mark is kept in a flag of its own.
+__device__ __forceinline__ bool hset_insert(unsigned long long* __restrict__ table, int index_shift, uint64_t mask, uint64_t word, unsigned int* __restrict__ has_empty_word,
+                                            DevStatus* st) {
+    if (word == HSET_EMPTY) return atomicExch(has_empty_word, 1u) == 0u;
+    uint64_t h = word >> index_shift;
+    for (uint64_t probe = 0; probe <= mask; ++probe) {
+        unsigned long long cur = table[h];
+        if (cur == word) return false;
+        if (cur == HSET_EMPTY) {
+            unsigned long long old = atomicCAS(&table[h], HSET_EMPTY, (unsigned long long)word);
+            if (old == HSET_EMPTY) return true;
+            if (old == word) return false;  // another thread stored the same tuple first
+        }
+        h = (h + 1) & mask;
+    }
+    set_status(st, XLB_ERR_CAPACITY, 12, word);
+    return false;
+}
+
+// Insert every word (already mixed) without reporting which were new: filling the set from a
+// relation, or from an older table, whose empty slots are skipped.
+static __global__ void __launch_bounds__(BLOCK) hset_fill_k(const uint64_t* __restrict__ words, uint64_t n, unsigned long long* __restrict__ table, int index_shift, uint64_t mask,
+                                                       unsigned int* __restrict__ has_empty_word, bool skip_empty, DevStatus* st) {
+    for (uint64_t i = (uint64_t)blockIdx.x * BLOCK + threadIdx.x; i < n; i += (uint64_t)gridDim.x * BLOCK) {
+        const uint64_t w = words[i];
+        if (!(skip_empty && w == HSET_EMPTY)) hset_insert(table, index_shift, mask, w, has_empty_word, st);
+    }
+}
+// Insertion as the predicate of a one-pass compaction (select_append_k): the words that were new
+// come out as a bag, and a block of 8192 candidates costs one atomic add on the output counter
+// (a warp-level append was measured at 26 G insertions/s, all of it the queue on that one address).
+struct PredInsert {
+    const uint64_t* words;
+    unsigned long long* table;
+    int index_shift;
+    uint64_t mask;
+    unsigned int* has_empty_word;
+    DevStatus* st;
+    __device__ __forceinline__ bool operator()(uint64_t i) const { return hset_insert(table, index_shift, mask, words[i], has_empty_word, st); }
+};
 
 // The host sized an output from a count it kept itself: the device's own count must agree.
 static __global__ void verify_count_k(const uint64_t* device_count, uint64_t host_count, DevStatus* st) {

@@ -529,6 +529,82 @@ Keys ops_dense_state_rows(xlb_ctx* c, const DenseState& s, uint64_t bound) {
     return dense_finish(c, d, none, &s.rows);  // nothing to subtract, no second bitmap: every set bit comes out, s.rows of them
 }
 
+static void tuple_set_alloc(xlb_ctx* c, TupleSet& s, uint64_t tuples) {
+    s.log2cap = 10;
+    while ((1ull << s.log2cap) < 2 * tuples) ++s.log2cap;
+    s.cap = 1ull << s.log2cap;
+    s.table = make_buf(c, s.cap * 8 + 8);
+    CUDA_OK(cudaMemsetAsync(s.table->p, 0xFF, s.cap * 8, c->stream));
+    CUDA_OK(cudaMemsetAsync((char*)s.table->p + s.cap * 8, 0, 8, c->stream));
+}
+
+static unsigned int* tuple_set_flag(const TupleSet& s) { return (unsigned int*)((char*)s.table->p + s.cap * 8); }
+
+// mix64 of every key (or its inverse), into a fresh buffer
+static Buf mixed_copy(xlb_ctx* c, const uint64_t* in, uint64_t n, bool inverse) {
+    Buf out = make_buf(c, n * 8);
+    if (n) {
+        prof_begin(c, "mix", n * 16ull);
+        mix_k<<<grid_for(c, n, BLOCK * 4), BLOCK, 0, c->stream>>>(in, out->as<uint64_t>(), n, inverse ? 1 : 0);
+        check_launch(c, "mix");
+    }
+    return out;
+}
+
+// The candidates as mixed words, grouped by the top byte (= by the 256th of the table they fall into)
+// when there are enough of them for the grouping pass to pay.
+static Buf tuple_set_words(xlb_ctx* c, const TupleSet& s, const uint64_t* keys, uint64_t n) {
+    Buf words = mixed_copy(c, keys, n, false);
+    const bool table_in_l2 = s.cap * 8 <= (48ull << 20);  // then any order of insertion is an L2 access
+    if (!table_in_l2 && n >= (1ull << 20) && n < (1ull << 30)) radix_sort(c, words, nullptr, n, 0x80u, 0xFF00000000000000ull);
+    return words;
+}
+
+static void tuple_set_fill(xlb_ctx* c, TupleSet& s, const uint64_t* words, uint64_t n, bool skip_empty) {
+    if (!n) return;
+    prof_begin(c, "hset_fill", n * 16ull);
+    hset_fill_k<<<grid_for(c, n), BLOCK, 0, c->stream>>>(words, n, s.table->as<unsigned long long>(), 64 - s.log2cap, s.cap - 1, tuple_set_flag(s), skip_empty, c->d_status);
+    check_launch(c, "hset_fill");
+}
+
+void ops_tuple_set_build(xlb_ctx* c, TupleSet& s, const Keys& full, const Keys& novel, uint64_t extra) {
+    s.table.reset();
+    tuple_set_alloc(c, s, full.n + novel.n + extra);
+    for (const Keys* k : {&full, &novel}) {
+        if (!k->n) continue;
+        Buf words = tuple_set_words(c, s, k->ptr(), k->n);
+        tuple_set_fill(c, s, words->as<uint64_t>(), k->n, false);
+    }
+    s.rows = full.n + novel.n;
+    s.valid = true;
+}
+
+Keys ops_tuple_set_novel(xlb_ctx* c, TupleSet& s, const Keys& cand) {
+    Keys o;
+    o.bound = cand.bound;
+    if (cand.n == 0) {
+        o.buf = make_buf(c, 0);
+        return o;
+    }
+    if (2 * (s.rows + cand.n) > s.cap) {
+        // every candidate could be new: grow (to twice what is needed, so that this is rare) and
+        // move the stored words over, straight from the old table (in slot order, which is the new
+        // table's order too: the insertions walk through it front to back)
+        TupleSet old = s;
+        tuple_set_alloc(c, s, 2 * (s.rows + cand.n));
+        tuple_set_fill(c, s, old.table->as<uint64_t>(), old.cap, true);
+        CUDA_OK(cudaMemcpyAsync(tuple_set_flag(s), tuple_set_flag(old), 4, cudaMemcpyDeviceToDevice, c->stream));
+    }
+    Buf words = tuple_set_words(c, s, cand.ptr(), cand.n);
+    Buf out = make_buf(c, cand.n * 8);
+    o.n = select_unordered(c, PredInsert{words->as<uint64_t>(), s.table->as<unsigned long long>(), 64 - s.log2cap, s.cap - 1, tuple_set_flag(s), c->d_status},
+                           EmitKey{words->as<uint64_t>(), out->as<uint64_t>()}, cand.n, "hset_insert", cand.n * 16ull);
+    s.rows += o.n;
+    words.reset();
+    o.buf = mixed_copy(c, out->as<uint64_t>(), o.n, true);  // back to tuples, in a buffer of their own size
+    return o;
+}
+
 Keys ops_dense_novel(xlb_ctx* c, const Keys& cand, const Keys& full, int hi_bits, int lo_bits, unsigned int* visited) {
     DenseSet d = ops_dense_begin(c, hi_bits, lo_bits);
     d.bound = cand.bound;

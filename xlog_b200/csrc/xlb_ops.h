@@ -84,6 +84,20 @@ struct DenseState {
     uint64_t rows = 0;  // tuples marked (the relation's rows plus what the running iteration found)
     bool valid = false;
 };
+// The tuples of one relation as a hash set that lives across the iterations of a fixpoint (heads
+// too wide for a bitmap).
+struct TupleSet {
+    Buf table;          // slots of mix64(tuple); then one 32-bit flag: the word that equals the empty mark is stored
+    uint64_t cap = 0;   // slots, a power of two; at most half of them are ever used
+    int log2cap = 0;
+    uint64_t rows = 0;  // tuples stored
+    bool valid = false;
+};
+// (Re)build the set from the sorted lists `full` and `novel`, with room for `extra` more tuples.
+void ops_tuple_set_build(xlb_ctx* c, TupleSet& s, const Keys& full, const Keys& novel, uint64_t extra);
+// Insert the candidates; returns those that were new (a bag: once each, in no particular order).
+// The set grows first when it could pass half full.
+Keys ops_tuple_set_novel(xlb_ctx* c, TupleSet& s, const Keys& cand);
 void ops_dense_state_build(xlb_ctx* c, DenseState& s, int hi_bits, int lo_bits, const Keys& full, const Keys& novel);
 Keys ops_dense_state_rows(xlb_ctx* c, const DenseState& s, uint64_t bound);  // all its tuples, in order
 DenseSet ops_dense_begin(xlb_ctx* c, int hi_bits, int lo_bits);
