@@ -96,6 +96,10 @@ typedef struct xlb_config {
                                       too wide for a bitmap are then always sorted, deduplicated and
                                       subtracted by merging (the counterpart of the reference's
                                       XLOG_DISABLE_FACTORIZED_DELTA for its sparse route)            */
+#define XLB_FLAG_GENERAL_ONLY 32u  /* evaluate every rule body node by node on column-major relations
+                                      (the general evaluator that otherwise only takes rules with
+                                      more than two live columns): the reference's own evaluation
+                                      order, for comparing the two engines                           */
 #define XLB_FLAG_SHUFFLE_ONLY 8u   /* several ranks: never give every rank a full copy of a relation
                                       (no replicated evaluation of small-domain components, no
                                       broadcast of small stored relations): every join runs on hash

@@ -145,8 +145,9 @@ def test_rerun_after_new_facts_extends_the_fixpoint(oracle):
     p.close()
 
 
-def test_unsupported_rule_shape_is_refused_not_miscomputed():
-    """A three-column head is outside the built scope: refused with a message, never miscomputed."""
+def test_rules_on_several_ranks_outside_the_packed_scope_are_refused_not_miscomputed():
+    """The general evaluator (three and more live columns) runs on one rank; a context that belongs to a
+    group of ranks refuses such a rule with a message instead of computing on a shard."""
     from xlog_b200.lib import XlbError
     from xlog_b200 import _abi as A
     from xlog_b200.plan import CompiledRule, ExecutionPlan, Join, Project, Scan, Scc
@@ -154,9 +155,10 @@ def test_unsupported_rule_shape_is_refused_not_miscomputed():
     plan = ExecutionPlan([Scc(0, False, [CompiledRule("path3", body, (A.U32, A.U32, A.U32))])], {"edge": 0, "path3": 1})
     c0, c1 = workloads.uniform_digraph(50, 200, 2)
     p = fresh()
+    p._check(p._lib.xlb_comm_mark_aborted_for_test(p._ctx))      # records a world of two ranks; no peer is involved
     with pytest.raises(XlbError) as e:
         run_program(p, plan, {"edge": [c0, c1]}, ["path3"])
-    assert e.value.status == A.ERR_UNSUPPORTED and "path3" in e.value.message
+    assert e.value.status == A.ERR_UNSUPPORTED and "one rank" in e.value.message
     p.close()
 
 

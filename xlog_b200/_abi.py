@@ -29,6 +29,7 @@ FLAG_NO_DENSE = 2
 FLAG_KEEP_DELTAS = 4
 FLAG_SHUFFLE_ONLY = 8
 FLAG_NO_TUPLE_SET = 16
+FLAG_GENERAL_ONLY = 32
 
 
 class Schema(C.Structure):

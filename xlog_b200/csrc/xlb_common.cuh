@@ -514,7 +514,7 @@ inline uint32_t type_width(uint8_t t) {
         default: return 1;
     }
 }
-inline bool type_built(uint8_t t) { return t != XLB_BOOL && t <= XLB_SYMBOL; }
+inline bool type_built(uint8_t t) { return t <= XLB_SYMBOL; }
 inline bool type_unsigned(uint8_t t) { return t == XLB_U32 || t == XLB_SYMBOL || t == XLB_U64; }
 inline bool rel_packable(const xlb_schema& s) {
     if (s.arity < 1 || s.arity > 2) return false;

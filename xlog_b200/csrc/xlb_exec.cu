@@ -19,6 +19,7 @@
 
 #include "xlb_comm.h"
 #include "xlb_ops.h"
+#include "xlb_tree.h"
 
 void xlb_resolve_phase_timers(xlb_ctx* c);
 
@@ -135,6 +136,7 @@ struct FlatRule {
     std::vector<FilterC> filters;
     std::vector<CheckC> checks;
     std::vector<int> head_vars;
+    std::vector<char> start_ok;  // per atom: a pipeline that starts there keeps at most two columns live throughout
 };
 
 struct Flattener {
@@ -464,6 +466,109 @@ static std::set<int> needed_vars(const FlatRule& fr, const std::vector<bool>& do
     return s;
 }
 
+// The next atom a pipeline joins: the first one with exactly one column bound by the bag (hi, lo)
+// such that what must stay live afterwards fits two columns.  pick = -1: there is none.
+static void pick_next_atom(const FlatRule& fr, std::vector<bool>& done, int hi, int lo, int* pick_out, int* kc_out, std::set<int>* keep_out) {
+    int pick = -1, kc = -1;
+    std::set<int> keep;
+    for (size_t i = 0; i < fr.atoms.size() && pick < 0; ++i) {
+        if (done[i]) continue;
+        const Atom& a = fr.atoms[i];
+        int bound = 0, which = -1;
+        for (uint32_t j = 0; j < a.arity; ++j)
+            if (a.var[j] == hi || a.var[j] == lo) { bound++; which = (int)j; }
+        if (a.arity == 2 && a.var[0] == a.var[1]) continue;
+        if (bound != 1) continue;
+        done[i] = true;
+        std::set<int> need = needed_vars(fr, done);
+        done[i] = false;
+        std::set<int> avail{hi, lo};
+        if (a.arity == 2) avail.insert(a.var[1 - which]);
+        avail.erase(-1);
+        std::set<int> k2;
+        for (int v : need)
+            if (avail.count(v)) k2.insert(v);
+        if (k2.size() > 2) continue;
+        pick = (int)i;
+        kc = which;
+        keep = k2;
+    }
+    *pick_out = pick;
+    *kc_out = kc;
+    *keep_out = keep;
+}
+
+// Would run_pipeline, started at atom `start`, get through the rule?  The same walk without data.
+static bool pipeline_feasible(FlatRule fr /*by value: filter flags*/, size_t start) {
+    std::vector<bool> done(fr.atoms.size(), false);
+    const Atom& sa = fr.atoms[start];
+    int hi = -1, lo = -1;
+    if (sa.arity == 2) { hi = sa.var[0]; lo = sa.var[1]; }
+    else lo = sa.var[0];
+    done[start] = true;
+    if (sa.arity == 2 && sa.var[0] == sa.var[1]) hi = -1;
+    auto ready = [&]() {
+        for (auto& k : fr.checks)
+            if (!k.applied && (k.var == hi || k.var == lo)) k.applied = true;
+        for (auto& f : fr.filters) {
+            if (f.applied) continue;
+            bool lhs_ok = f.lhs == hi || f.lhs == lo;
+            bool rhs_ok = f.rhs_const || (int)f.rhs == hi || (int)f.rhs == lo;
+            if (lhs_ok && rhs_ok) f.applied = true;
+        }
+    };
+    ready();
+    size_t remaining = fr.atoms.size() - 1;
+    while (remaining) {
+        bool filtered = false;
+        for (size_t i = 0; i < fr.atoms.size(); ++i) {
+            const Atom& a = fr.atoms[i];
+            if (done[i] || a.arity != 2 || a.var[0] == a.var[1]) continue;
+            bool b0 = a.var[0] == hi || a.var[0] == lo, b1 = a.var[1] == hi || a.var[1] == lo;
+            if (!b0 || !b1) continue;
+            done[i] = true;
+            remaining--;
+            filtered = true;
+        }
+        if (filtered) {
+            ready();
+            continue;
+        }
+        int pick = -1, kc = -1;
+        std::set<int> keep;
+        pick_next_atom(fr, done, hi, lo, &pick, &kc, &keep);
+        if (pick < 0) return false;
+        const Atom& a = fr.atoms[pick];
+        done[pick] = true;
+        remaining--;
+        const int othervar = a.arity == 2 ? a.var[1 - kc] : -1;
+        bool pending = false;
+        for (auto& f : fr.filters) pending |= !f.applied;
+        for (auto& k : fr.checks) pending |= !k.applied;
+        int out_hi = -1, out_lo = -1;
+        if (remaining == 0 && !pending) {
+            if (fr.head_vars.size() == 2) { out_hi = fr.head_vars[0]; out_lo = fr.head_vars[1]; }
+            else out_lo = fr.head_vars[0];
+        } else {
+            std::vector<int> kv(keep.begin(), keep.end());
+            if (kv.size() == 2) { out_hi = kv[0]; out_lo = kv[1]; }
+            else if (kv.size() == 1) out_lo = kv[0];
+        }
+        for (int v : {out_hi, out_lo})
+            if (v >= 0 && v != hi && v != lo && v != othervar) return false;
+        hi = out_hi;
+        lo = out_lo;
+        ready();
+    }
+    for (auto& f : fr.filters)
+        if (!f.applied) return false;
+    for (auto& k : fr.checks)
+        if (!k.applied) return false;
+    for (int v : fr.head_vars)
+        if (v != hi && v != lo) return false;
+    return true;
+}
+
 // Evaluate the rule with atom `start` read from `start_rows` (the delta, a chunk of it, or a
 // full relation) and every other atom from the store.  Returns candidate head tuples (a bag).
 // `sink`: when the last join writes the head layout directly and the head fits a dense domain, its
@@ -656,28 +761,7 @@ static Keys run_pipeline(xlb_ctx* c, FlatRule fr /*by value: filter flags*/, siz
         // next atom: exactly one of its columns is bound by the bag, and what must stay live fits two columns
         int pick = -1, kc = -1;
         std::set<int> keep;
-        for (size_t i = 0; i < fr.atoms.size() && pick < 0; ++i) {
-            if (done[i]) continue;
-            const Atom& a = fr.atoms[i];
-            int bound = 0, which = -1;
-            for (uint32_t j = 0; j < a.arity; ++j)
-                if (a.var[j] == bag.hi || a.var[j] == bag.lo) { bound++; which = (int)j; }
-            if (a.arity == 2 && a.var[0] == a.var[1]) continue;
-            if (bound != 1) continue;
-            done[i] = true;
-            std::set<int> need = needed_vars(fr, done);
-            done[i] = false;
-            std::set<int> avail{bag.hi, bag.lo};
-            if (a.arity == 2) avail.insert(a.var[1 - which]);
-            avail.erase(-1);
-            std::set<int> k2;
-            for (int v : need)
-                if (avail.count(v)) k2.insert(v);
-            if (k2.size() > 2) continue;
-            pick = (int)i;
-            kc = which;
-            keep = k2;
-        }
+        pick_next_atom(fr, done, bag.hi, bag.lo, &pick, &kc, &keep);
         if (pick < 0)
             xlb_fail(XLB_ERR_UNSUPPORTED, "rule for %s: no join order keeps at most two live columns with single-column keys", fr.head.c_str());
         const Atom& a = fr.atoms[pick];
@@ -1033,6 +1117,7 @@ static size_t pick_seed_start(xlb_ctx* c, const FlatRule& fr) {
     size_t best = 0;
     uint64_t rows = ~0ull;
     for (size_t i = 0; i < fr.atoms.size(); ++i) {
+        if (i < fr.start_ok.size() && !fr.start_ok[i]) continue;  // no pipeline from there keeps two columns
         xlb_rel* r = store_get(c, fr.atoms[i].rel);
         uint64_t n = r ? r->rows : 0;
         if (n < rows) { rows = n; best = i; }
@@ -1513,23 +1598,47 @@ static void run_scc(xlb_ctx* c, const xlb_scc& scc, RunState& rs) {
     std::set<std::string> rec(preds.begin(), preds.end());
     for (auto& p : preds)
         if (!store_get(c, p)) store_put(c, p, empty_rel(c, schema[p]));  // recursive.rs:471-486
+    // A rule the packed pipelines do not take (more than two live columns, relations of three and
+    // more columns, two-column join keys that are not a membership test, a Union below the top of a
+    // body) sends the whole component to the general, node-by-node evaluator.
     std::vector<FlatRule> rules;
-    for (uint32_t i = 0; i < scc.n_rules; ++i) {
-        // a Union at the top of a body is one rule per input (RirNode::Union concatenates its inputs)
-        std::vector<const xlb_node*> bodies{scc.rules[i].body};
-        for (size_t q = 0; q < bodies.size();) {
-            const xlb_node* b = bodies[q];
-            if (b->kind == XLB_NODE_UNION) {
-                if (!b->inputs && b->n_inputs) xlb_fail(XLB_ERR_INVALID, "Union node without inputs");
-                bodies.erase(bodies.begin() + q);
-                for (uint32_t u = 0; u < b->n_inputs; ++u) bodies.push_back(b->inputs[u]);
-            } else ++q;
+    bool packed = !(c->flags & XLB_FLAG_GENERAL_ONLY);
+    try {
+        for (uint32_t i = 0; packed && i < scc.n_rules; ++i) {
+            // a Union at the top of a body is one rule per input (RirNode::Union concatenates its inputs)
+            std::vector<const xlb_node*> bodies{scc.rules[i].body};
+            for (size_t q = 0; q < bodies.size();) {
+                const xlb_node* b = bodies[q];
+                if (b->kind == XLB_NODE_UNION) {
+                    if (!b->inputs && b->n_inputs) xlb_fail(XLB_ERR_INVALID, "Union node without inputs");
+                    bodies.erase(bodies.begin() + q);
+                    for (uint32_t u = 0; u < b->n_inputs; ++u) bodies.push_back(b->inputs[u]);
+                } else ++q;
+            }
+            for (const xlb_node* b : bodies) {
+                xlb_rule r = scc.rules[i];
+                r.body = b;
+                rules.push_back(Flattener{c, {}, {}}.run(r));
+            }
         }
-        for (const xlb_node* b : bodies) {
-            xlb_rule r = scc.rules[i];
-            r.body = b;
-            rules.push_back(Flattener{c, {}, {}}.run(r));
+    } catch (const XlbError& e) {
+        if (e.st != XLB_ERR_UNSUPPORTED) throw;
+        packed = false;
+    }
+    for (auto& fr : rules) {
+        if (!packed) break;
+        bool any = false;
+        fr.start_ok.assign(fr.atoms.size(), 0);
+        for (size_t a = 0; a < fr.atoms.size(); ++a) {
+            fr.start_ok[a] = pipeline_feasible(fr, a) ? 1 : 0;
+            any |= fr.start_ok[a] != 0;
+            if (!fr.start_ok[a] && rec.count(fr.atoms[a].rel)) packed = false;  // its delta variant would have to start there
         }
+        if (!any || (c->world > 1 && !fr.start_ok[0])) packed = false;
+    }
+    if (!packed) {
+        run_scc_tree(c, scc, rs.st);
+        return;
     }
     for (auto& p : preds) rs.head_schema[p] = schema[p];
     struct Cleanup {  // the full copies go when the component is done, however it ends
@@ -1810,14 +1919,14 @@ struct EncodedRun {
         if (c->world > 1) xlb_fail(XLB_ERR_UNSUPPORTED, "plans over u64, signed or floating columns run on one GPU");
         if (c->flags & XLB_FLAG_KEEP_DELTAS) xlb_fail(XLB_ERR_UNSUPPORTED, "XLB_FLAG_KEEP_DELTAS with u64, signed or floating columns is not built");
         for (const xlb_rel* r : rels) {
-            if (r->schema.arity < 1 || r->schema.arity > 2) xlb_fail(XLB_ERR_UNSUPPORTED, "plans take relations of one or two columns");
+            if (r->schema.arity < 1) xlb_fail(XLB_ERR_UNSUPPORTED, "plans take relations of at least one column");
             for (uint32_t k = 0; k < r->schema.arity; ++k)
-                if (!type_built(r->schema.types[k])) xlb_fail(XLB_ERR_UNSUPPORTED, "bool columns are not built");
+                if (!type_built(r->schema.types[k])) xlb_fail(XLB_ERR_INVALID, "unknown column type");
         }
         for (auto& h : head_types) {
-            if (h.second.arity < 1 || h.second.arity > 2) xlb_fail(XLB_ERR_UNSUPPORTED, "head %s: derived relations of one or two columns are built", h.first.c_str());
+            if (h.second.arity < 1 || h.second.arity > XLB_MAX_ARITY) xlb_fail(XLB_ERR_UNSUPPORTED, "head %s: derived relations of 1 to %u columns are built", h.first.c_str(), XLB_MAX_ARITY);
             for (uint32_t k = 0; k < h.second.arity; ++k)
-                if (!type_built(h.second.types[k])) xlb_fail(XLB_ERR_UNSUPPORTED, "bool columns are not built");
+                if (!type_built(h.second.types[k])) xlb_fail(XLB_ERR_INVALID, "unknown column type");
             if (store_get(c, "__delta_" + h.first)) xlb_fail(XLB_ERR_UNSUPPORTED, "resuming a fixpoint over u64, signed or floating columns is not built");
         }
         if (!const_filters.empty()) {

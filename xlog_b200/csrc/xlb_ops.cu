@@ -21,7 +21,7 @@ __global__ void iota64_k(uint64_t* out, uint64_t n) {
 __global__ void build_key_k(const void* c0, int w0, const void* c1, int w1, const uint32_t* idx, uint64_t* out, uint64_t n) {
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
         uint64_t r = idx ? idx[i] : i;
-        uint64_t a = w0 == 4 ? ((const uint32_t*)c0)[r] : ((const uint64_t*)c0)[r];
+        uint64_t a = w0 == 4 ? ((const uint32_t*)c0)[r] : w0 == 8 ? ((const uint64_t*)c0)[r] : ((const uint8_t*)c0)[r];
         if (c1) {
             uint64_t b = ((const uint32_t*)c1)[r];
             a = (a << 32) | b;
@@ -49,8 +49,8 @@ struct ColSet {  // columns of a gathered (sorted) relation for multi-column run
 };
 __device__ __forceinline__ bool rows_equal(const ColSet& cs, uint64_t a, uint64_t b) {
     for (int c = 0; c < cs.n; ++c) {
-        uint64_t x = cs.width[c] == 4 ? ((const uint32_t*)cs.col[c])[a] : ((const uint64_t*)cs.col[c])[a];
-        uint64_t y = cs.width[c] == 4 ? ((const uint32_t*)cs.col[c])[b] : ((const uint64_t*)cs.col[c])[b];
+        uint64_t x = cs.width[c] == 4 ? ((const uint32_t*)cs.col[c])[a] : cs.width[c] == 8 ? ((const uint64_t*)cs.col[c])[a] : ((const uint8_t*)cs.col[c])[a];
+        uint64_t y = cs.width[c] == 4 ? ((const uint32_t*)cs.col[c])[b] : cs.width[c] == 8 ? ((const uint64_t*)cs.col[c])[b] : ((const uint8_t*)cs.col[c])[b];
         if (x != y) return false;
     }
     return true;
@@ -153,6 +153,26 @@ struct PredOwner {
     }
 };
 __global__ void add_word_k(unsigned long long* dst, const unsigned long long* src) { *dst += *src; }
+struct PredCmpCols {  // comparison between a column and a constant or another column (values widened to 64 bits)
+    ColSet cs;
+    uint32_t cmp, lhs;
+    bool rhs_const;
+    uint64_t rhs;
+    __device__ __forceinline__ uint64_t at(uint32_t col, uint64_t i) const {
+        return cs.width[col] == 4 ? ((const uint32_t*)cs.col[col])[i] : cs.width[col] == 8 ? ((const uint64_t*)cs.col[col])[i] : ((const uint8_t*)cs.col[col])[i];
+    }
+    __device__ __forceinline__ bool operator()(uint64_t i) const {
+        const uint64_t a = at(lhs, i), b = rhs_const ? rhs : at((uint32_t)rhs, i);
+        switch (cmp) {
+            case XLB_EQ: return a == b;
+            case XLB_NE: return a != b;
+            case XLB_LT: return a < b;
+            case XLB_LE: return a <= b;
+            case XLB_GT: return a > b;
+            default: return a >= b;
+        }
+    }
+};
 struct PredFlag {
     const uint64_t* match;
     bool want;
@@ -999,10 +1019,10 @@ extern "C" xlb_status xlb_memory_stats(const xlb_ctx* c, uint64_t* allocated, ui
 static void check_schema(const xlb_schema* s) {
     if (!s || s->arity > XLB_MAX_ARITY) xlb_fail(XLB_ERR_INVALID, "schema missing or arity above %u", XLB_MAX_ARITY);
     for (uint32_t i = 0; i < s->arity; ++i)
-        if (!type_built(s->types[i])) xlb_fail(XLB_ERR_UNSUPPORTED, "column %u: type code %u is not built (u32, u64, i32, i64, f32, f64 and symbol are)", i, s->types[i]);
+        if (!type_built(s->types[i])) xlb_fail(XLB_ERR_UNSUPPORTED, "column %u: type code %u is not a column type", i, s->types[i]);
 }
 
-static xlb_rel* rel_empty(xlb_ctx* c, const xlb_schema& s) {
+xlb_rel* rel_empty(xlb_ctx* c, const xlb_schema& s) {
     auto* r = new xlb_rel;
     r->ctx = c;
     r->schema = s;
@@ -1208,7 +1228,8 @@ static xlb_rel* gather_rel(xlb_ctx* c, const xlb_rel* r, const uint32_t* idx, ui
         if (!n) continue;
         prof_begin(c, "gather", 0);
         if (w == 4) gather_k<uint32_t><<<grid_for(c, n), BLOCK, 0, c->stream>>>(r->cols[i]->as<uint32_t>(), idx, o->cols[i]->as<uint32_t>(), n);
-        else gather_k<uint64_t><<<grid_for(c, n), BLOCK, 0, c->stream>>>(r->cols[i]->as<uint64_t>(), idx, o->cols[i]->as<uint64_t>(), n);
+        else if (w == 8) gather_k<uint64_t><<<grid_for(c, n), BLOCK, 0, c->stream>>>(r->cols[i]->as<uint64_t>(), idx, o->cols[i]->as<uint64_t>(), n);
+        else gather_k<uint8_t><<<grid_for(c, n), BLOCK, 0, c->stream>>>(r->cols[i]->as<uint8_t>(), idx, o->cols[i]->as<uint8_t>(), n);
         check_launch(c, "gather");
     }
     return o.release();
@@ -1228,6 +1249,42 @@ static xlb_status sort_unsigned(xlb_ctx* c, const xlb_rel* in, const uint32_t* k
     API_END()
 }
 
+xlb_rel* rel_view(xlb_ctx* c, const xlb_rel* r) {
+    auto* o = new xlb_rel;
+    o->ctx = c;
+    o->schema = r->schema;
+    o->rows = r->rows;
+    for (uint32_t i = 0; i < r->schema.arity; ++i) o->cols[i] = r->cols[i];
+    o->packed = r->packed;
+    o->or_bound = r->or_bound;
+    o->canonical = r->canonical;
+    return o;
+}
+
+xlb_rel* rel_project(xlb_ctx* c, const xlb_rel* in, const uint32_t* cols, uint32_t n) {
+    ops_rel_columns(c, in);
+    auto* o = new xlb_rel;
+    o->ctx = c;
+    o->schema.arity = n;
+    o->rows = n ? in->rows : std::min<uint64_t>(in->rows, 1);
+    for (uint32_t i = 0; i < n; ++i) {
+        o->schema.types[i] = in->schema.types[cols[i]];
+        o->cols[i] = in->cols[cols[i]];
+    }
+    return o;
+}
+
+xlb_rel* rel_filter(xlb_ctx* c, const xlb_rel* in, uint32_t cmp, uint32_t lhs, bool rhs_is_const, uint64_t rhs) {
+    if (in->rows == 0) return rel_view(c, in);
+    if (in->rows >= (1ull << 32)) xlb_fail(XLB_ERR_CAPACITY, "filter input exceeds the 2^32 row limit");
+    ops_rel_columns(c, in);
+    Buf idx = make_buf(c, in->rows * 4);
+    uint64_t m = select(c, PredCmpCols{colset_of(in), cmp, lhs, rhs_is_const, rhs}, EmitIndex{idx->as<uint32_t>()}, in->rows);
+    xlb_rel* o = gather_rel(c, in, idx->as<uint32_t>(), m);
+    o->canonical = in->canonical;  // a subsequence of a sorted unique list is one
+    return o;
+}
+
 // Full-row canonicalisation of a wide relation (more than one 64-bit word per row).
 static xlb_rel* wide_dedup(xlb_ctx* c, const xlb_rel* in, const uint32_t* origin_excl, uint32_t n_excl) {
     (void)origin_excl;
@@ -1244,7 +1301,7 @@ static xlb_rel* wide_dedup(xlb_ctx* c, const xlb_rel* in, const uint32_t* origin
     return o;
 }
 
-static xlb_rel* concat_cols(xlb_ctx* c, const xlb_rel* const* ins, uint32_t n) {
+xlb_rel* rel_concat(xlb_ctx* c, const xlb_rel* const* ins, uint32_t n) {
     std::unique_ptr<xlb_rel> o(new xlb_rel);
     o->ctx = c;
     o->schema = ins[0]->schema;
@@ -1266,7 +1323,7 @@ static xlb_rel* concat_cols(xlb_ctx* c, const xlb_rel* const* ins, uint32_t n) {
     return o.release();
 }
 
-static xlb_rel* canonicalize(xlb_ctx* c, const xlb_rel* in) {
+xlb_rel* rel_canonical(xlb_ctx* c, const xlb_rel* in) {
     if (in->schema.arity == 0) {  // the 0-arity relation is {} or {()} (set_ops_tests.rs:160-183)
         xlb_rel* o = rel_empty(c, in->schema);
         o->rows = in->rows ? 1 : 0;
@@ -1290,7 +1347,7 @@ static xlb_status dedup_unsigned(xlb_ctx* c, const xlb_rel* in, const uint32_t* 
     xlb_rel** out = &guard.r;
     bool full = nk == 0 || nk >= in->schema.arity;
     if (full) {
-        *out = canonicalize(c, in);
+        *out = rel_canonical(c, in);
     } else {
         for (uint32_t i = 0; i < nk; ++i)
             if (key_cols[i] >= in->schema.arity) xlb_fail(XLB_ERR_INVALID, "dedup key column %u out of range", key_cols[i]);
@@ -1311,11 +1368,8 @@ static xlb_status dedup_unsigned(xlb_ctx* c, const xlb_rel* in, const uint32_t* 
     API_END()
 }
 
-static xlb_status union_unsigned(xlb_ctx* c, const xlb_rel* const* ins, uint32_t n, xlb_rel** out_final) {
-    if (!c || !out_final) return XLB_ERR_INVALID;
-    API_BEGIN(c)
-    ResultGuard guard;
-    xlb_rel** out = &guard.r;
+// Set union of n >= 1 type-compatible relations: sorted, unique, certified (union_many_gpu).
+xlb_rel* rel_union_many(xlb_ctx* c, const xlb_rel* const* ins, uint32_t n) {
     if (n == 0 || !ins) xlb_fail(XLB_ERR_INVALID, "union of no inputs");
     for (uint32_t i = 0; i < n; ++i) {
         if (!ins[i]) xlb_fail(XLB_ERR_INVALID, "union input %u is null", i);
@@ -1326,8 +1380,9 @@ static xlb_status union_unsigned(xlb_ctx* c, const xlb_rel* const* ins, uint32_t
         xlb_rel* o = rel_empty(c, s);
         for (uint32_t i = 0; i < n; ++i)
             if (ins[i]->rows) o->rows = 1;
-        *out = o;
-    } else if (single_word(s)) {
+        return o;
+    }
+    if (single_word(s)) {
         // canonical inputs are merged; the rest are concatenated, sorted and deduplicated once
         std::vector<Keys> loose;
         Keys acc;
@@ -1347,49 +1402,56 @@ static xlb_status union_unsigned(xlb_ctx* c, const xlb_rel* const* ins, uint32_t
             acc = have_acc ? ops_union(c, acc, cat) : cat;
             have_acc = true;
         }
-        if (!have_acc) *out = rel_empty(c, s);
-        else {
-            bool aliased = false;
-            for (uint32_t i = 0; i < n; ++i) {
-                if (!ins[i]->rows) continue;
-                Keys k = rel_word_keys(c, ins[i]);
-                if (k.buf == acc.buf) aliased = true;
-            }
-            if (aliased) acc = ops_copy(c, acc);
-            *out = rel_from_word_keys(c, s, acc, true);
+        if (!have_acc) return rel_empty(c, s);
+        bool aliased = false;
+        for (uint32_t i = 0; i < n; ++i) {
+            if (!ins[i]->rows) continue;
+            Keys k = rel_word_keys(c, ins[i]);
+            if (k.buf == acc.buf) aliased = true;
         }
-    } else {
-        std::unique_ptr<xlb_rel> cat(concat_cols(c, ins, n));
-        *out = wide_dedup(c, cat.get(), nullptr, 0);
+        if (aliased) acc = ops_copy(c, acc);
+        return rel_from_word_keys(c, s, acc, true);
     }
+    std::unique_ptr<xlb_rel> cat(rel_concat(c, ins, n));
+    return wide_dedup(c, cat.get(), nullptr, 0);
+}
+
+static xlb_status union_unsigned(xlb_ctx* c, const xlb_rel* const* ins, uint32_t n, xlb_rel** out_final) {
+    if (!c || !out_final) return XLB_ERR_INVALID;
+    API_BEGIN(c)
+    ResultGuard guard;
+    guard.r = rel_union_many(c, ins, n);
     guard.deliver(c, out_final);
     API_END()
+}
+
+// a \ b with set semantics on full rows: sorted, unique, certified (diff_gpu).
+xlb_rel* rel_difference(xlb_ctx* c, const xlb_rel* a, const xlb_rel* b) {
+    if (!schemas_compatible(a->schema, b->schema)) xlb_fail(XLB_ERR_TYPE, "difference of incompatible schemas");
+    const xlb_schema& s = a->schema;
+    if (s.arity == 0) {
+        xlb_rel* o = rel_empty(c, s);
+        o->rows = (a->rows && !b->rows) ? 1 : 0;
+        return o;
+    }
+    if (a->rows == 0) return rel_empty(c, s);
+    if (single_word(s)) {
+        std::unique_ptr<xlb_rel> ca(rel_canonical(c, a)), cb(rel_canonical(c, b));
+        Keys d = ops_diff(c, rel_word_keys(c, ca.get()), rel_word_keys(c, cb.get()));
+        return rel_from_word_keys(c, s, d, true);
+    }
+    // rows of b first: a run of equal rows that starts with a row of b is dropped whole
+    const xlb_rel* both[2] = {b, a};
+    std::unique_ptr<xlb_rel> cat(rel_concat(c, both, 2));
+    if (b->rows >= (1ull << 32)) xlb_fail(XLB_ERR_CAPACITY, "difference input exceeds the 2^32 row limit");
+    return wide_dedup(c, cat.get(), nullptr, (uint32_t)b->rows);
 }
 
 static xlb_status diff_unsigned(xlb_ctx* c, const xlb_rel* a, const xlb_rel* b, xlb_rel** out_final) {
     if (!c || !a || !b || !out_final) return XLB_ERR_INVALID;
     API_BEGIN(c)
     ResultGuard guard;
-    xlb_rel** out = &guard.r;
-    if (!schemas_compatible(a->schema, b->schema)) xlb_fail(XLB_ERR_TYPE, "difference of incompatible schemas");
-    const xlb_schema& s = a->schema;
-    if (s.arity == 0) {
-        xlb_rel* o = rel_empty(c, s);
-        o->rows = (a->rows && !b->rows) ? 1 : 0;
-        *out = o;
-    } else if (a->rows == 0) {
-        *out = rel_empty(c, s);
-    } else if (single_word(s)) {
-        std::unique_ptr<xlb_rel> ca(canonicalize(c, a)), cb(canonicalize(c, b));
-        Keys d = ops_diff(c, rel_word_keys(c, ca.get()), rel_word_keys(c, cb.get()));
-        *out = rel_from_word_keys(c, s, d, true);
-    } else {
-        // rows of b first: a run of equal rows that starts with a row of b is dropped whole
-        const xlb_rel* both[2] = {b, a};
-        std::unique_ptr<xlb_rel> cat(concat_cols(c, both, 2));
-        if (b->rows >= (1ull << 32)) xlb_fail(XLB_ERR_CAPACITY, "difference input exceeds the 2^32 row limit");
-        *out = wide_dedup(c, cat.get(), nullptr, (uint32_t)b->rows);
-    }
+    guard.r = rel_difference(c, a, b);
     guard.deliver(c, out_final);
     API_END()
 }
@@ -1401,6 +1463,13 @@ static xlb_status diff_unsigned(xlb_ctx* c, const xlb_rel* a, const xlb_rel* b, 
 // the result back.  Equality stays bitwise (NaN payloads and signed zeros are distinct), as in
 // crates/xlog-cuda/tests/test_full_row_set_algebra.rs:234-310.
 namespace {
+// a bool column (one byte per value, ordered false < true: kernels/sort.cu:331-345) as 32-bit words and back
+__global__ void bool_widen_k(const uint8_t* __restrict__ in, uint32_t* __restrict__ out, uint64_t n) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) out[i] = in[i];
+}
+__global__ void bool_narrow_k(const uint32_t* __restrict__ in, uint8_t* __restrict__ out, uint64_t n) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) out[i] = (uint8_t)in[i];
+}
 // kind 1: signed; kind 2: float.  Forward then inverse is the identity.
 template <class T>
 __global__ void order_map_k(const T* __restrict__ in, T* __restrict__ out, uint64_t n, int kind, int inverse) {
@@ -1415,7 +1484,7 @@ __global__ void order_map_k(const T* __restrict__ in, T* __restrict__ out, uint6
 }
 }  // namespace
 
-static int order_kind(uint8_t t) { return (t == XLB_I32 || t == XLB_I64) ? 1 : (t == XLB_F32 || t == XLB_F64) ? 2 : 0; }
+static int order_kind(uint8_t t) { return (t == XLB_I32 || t == XLB_I64) ? 1 : (t == XLB_F32 || t == XLB_F64) ? 2 : t == XLB_BOOL ? 3 : 0; }
 static bool schema_typed(const xlb_schema& s) {
     for (uint32_t i = 0; i < s.arity; ++i)
         if (order_kind(s.types[i])) return true;
@@ -1426,6 +1495,7 @@ static bool schema_typed(const xlb_schema& s) {
 namespace {
 // order-preserving unsigned image of one value, widened to 64 bits (kind as in order_map_k)
 __device__ __forceinline__ uint64_t dict_image(const void* col, int width, int kind, uint64_t i) {
+    if (width == 1) return ((const uint8_t*)col)[i];
     if (width == 4) {
         uint32_t x = ((const uint32_t*)col)[i];
         const uint32_t sign = 0x80000000u;
@@ -1472,7 +1542,9 @@ __global__ void dict_decode_k(const uint32_t* __restrict__ ranks, const uint64_t
             continue;
         }
         uint64_t x = dict[r];
-        if (width == 4) {
+        if (width == 1) {
+            ((uint8_t*)out)[i] = (uint8_t)x;
+        } else if (width == 4) {
             uint32_t y = (uint32_t)x;
             const uint32_t sign = 0x80000000u;
             if (kind == 1) y ^= sign;
@@ -1591,8 +1663,17 @@ static xlb_rel* map_rel(xlb_ctx* c, const xlb_rel* r, const xlb_schema& types, b
     for (uint32_t i = 0; i < types.arity; ++i) {
         int kind = order_kind(types.types[i]);
         uint32_t w = type_width(types.types[i]);
-        if (!inverse) o->schema.types[i] = kind ? (w == 4 ? XLB_U32 : XLB_U64) : types.types[i];
+        if (!inverse) o->schema.types[i] = kind ? (w == 8 ? XLB_U64 : XLB_U32) : types.types[i];
         if (!kind) { o->cols[i] = r->cols[i]; continue; }  // relations are immutable: share the column
+        if (kind == 3) {  // bool: bytes <-> words
+            o->cols[i] = make_buf(c, r->rows * (inverse ? 1 : 4));
+            if (!r->rows) continue;
+            prof_begin(c, "order_map", r->rows * 5ull);
+            if (!inverse) bool_widen_k<<<grid_for(c, r->rows), BLOCK, 0, c->stream>>>(r->cols[i]->as<uint8_t>(), o->cols[i]->as<uint32_t>(), r->rows);
+            else bool_narrow_k<<<grid_for(c, r->rows), BLOCK, 0, c->stream>>>(r->cols[i]->as<uint32_t>(), o->cols[i]->as<uint8_t>(), r->rows);
+            check_launch(c, "order_map");
+            continue;
+        }
         o->cols[i] = make_buf(c, r->rows * w);
         if (!r->rows) continue;
         prof_begin(c, "order_map", r->rows * 2ull * w);
@@ -1762,18 +1843,15 @@ static Buf join_keys(xlb_ctx* c, const xlb_rel* r, const uint32_t* keys, uint32_
     return kw;
 }
 
-extern "C" xlb_status xlb_hash_join(xlb_ctx* c, const xlb_rel* l, const xlb_rel* r, const uint32_t* lk, const uint32_t* rk, uint32_t nk,
-                                    xlb_join_type type, xlb_rel** out_final) {
-    if (!c || !l || !r || !out_final) return XLB_ERR_INVALID;
-    API_BEGIN(c)
-    ResultGuard guard;
-    xlb_rel** out = &guard.r;
+// hash_join_v2: see include/xlb.h.  Returns a fresh relation.
+xlb_rel* rel_join(xlb_ctx* c, const xlb_rel* l, const xlb_rel* r, const uint32_t* lk, const uint32_t* rk, uint32_t nk, xlb_join_type type) {
     if (nk < 1 || nk > XLB_MAX_KEYS || !lk || !rk) xlb_fail(XLB_ERR_INVALID, "join needs 1..%u key columns", XLB_MAX_KEYS);
     for (uint32_t i = 0; i < nk; ++i) {
         if (lk[i] >= l->schema.arity || rk[i] >= r->schema.arity) xlb_fail(XLB_ERR_INVALID, "join key column out of range");
         uint8_t a = l->schema.types[lk[i]] == XLB_SYMBOL ? XLB_U32 : l->schema.types[lk[i]];
         uint8_t b = r->schema.types[rk[i]] == XLB_SYMBOL ? XLB_U32 : r->schema.types[rk[i]];
         if (a != b) xlb_fail(XLB_ERR_TYPE, "join key %u: type mismatch", i);
+        if (a == XLB_BOOL) xlb_fail(XLB_ERR_UNSUPPORTED, "join key %u: bool key columns are not built", i);
     }
     xlb_schema os = l->schema;
     if (type == XLB_JOIN_INNER) {
@@ -1782,55 +1860,63 @@ extern "C" xlb_status xlb_hash_join(xlb_ctx* c, const xlb_rel* l, const xlb_rel*
     }
     bool empty = l->rows == 0 || (r->rows == 0 && type != XLB_JOIN_ANTI);
     if (empty) {
-        *out = rel_empty(c, os);
-        (*out)->canonical = false;
-    } else {
-        if (l->rows >= (1ull << 32)) xlb_fail(XLB_ERR_CAPACITY, "join probe side exceeds the 2^32 row limit");
-        ops_rel_columns(c, l);
-        ops_rel_columns(c, r);
-        // build side: rows ordered by key word (stable, so equal keys keep right-row order)
-        Buf rkeys = join_keys(c, r, rk, nk);
-        Buf ridx = make_buf(c, r->rows * 4);
-        if (r->rows) {
-            prof_begin(c, "iota", 0);
-            iota_k<<<grid_for(c, r->rows), BLOCK, 0, c->stream>>>(ridx->as<uint32_t>(), r->rows);
-            check_launch(c, "iota");
-            radix_sort(c, rkeys, &ridx, r->rows);
-        }
-        Index ix = ops_index_build(c, rkeys, r->rows, 0, ridx);
-        Buf lkeys = join_keys(c, l, lk, nk);
-        Keys lrows;
-        lrows.n = l->rows;
-        lrows.buf = make_buf(c, l->rows * 8);
-        prof_begin(c, "iota64", 0);
-        iota64_k<<<grid_for(c, l->rows), BLOCK, 0, c->stream>>>(lrows.buf->as<uint64_t>(), l->rows);
-        check_launch(c, "iota64");
-        if (type == XLB_JOIN_INNER) {
-            Keys pairs = ops_join_expand(c, lrows, SRC_LO, lkeys->as<uint64_t>(), ix, SRC_LO, SRC_OTHER);
-            std::unique_ptr<xlb_rel> o(new xlb_rel);
-            o->ctx = c;
-            o->schema = os;
-            o->rows = pairs.n;
-            for (uint32_t i = 0; i < os.arity; ++i) {
-                bool left = i < l->schema.arity;
-                const xlb_rel* src = left ? l : r;
-                uint32_t sc = left ? i : i - l->schema.arity;
-                uint32_t w = type_width(os.types[i]);
-                o->cols[i] = make_buf(c, pairs.n * w);
-                if (!pairs.n) continue;
-                prof_begin(c, "gather_pair", 0);
-                if (w == 4) gather_pair_k<uint32_t><<<grid_for(c, pairs.n), BLOCK, 0, c->stream>>>(src->cols[sc]->as<uint32_t>(), pairs.ptr(), left ? 0 : 1, o->cols[i]->as<uint32_t>(), pairs.n);
-                else gather_pair_k<uint64_t><<<grid_for(c, pairs.n), BLOCK, 0, c->stream>>>(src->cols[sc]->as<uint64_t>(), pairs.ptr(), left ? 0 : 1, o->cols[i]->as<uint64_t>(), pairs.n);
-                check_launch(c, "gather_pair");
-            }
-            *out = o.release();
-        } else {
-            Buf match = ops_probe_match(c, lrows, SRC_LO, lkeys->as<uint64_t>(), ix);
-            Buf sel = make_buf(c, l->rows * 4);
-            uint64_t m = select(c, PredFlag{match->as<uint64_t>(), type == XLB_JOIN_SEMI}, EmitIndex{sel->as<uint32_t>()}, l->rows);
-            *out = gather_rel(c, l, sel->as<uint32_t>(), m);
-        }
+        xlb_rel* o = rel_empty(c, os);
+        o->canonical = false;
+        return o;
     }
+    if (l->rows >= (1ull << 32)) xlb_fail(XLB_ERR_CAPACITY, "join probe side exceeds the 2^32 row limit");
+    ops_rel_columns(c, l);
+    ops_rel_columns(c, r);
+    // build side: rows ordered by key word (stable, so equal keys keep right-row order)
+    Buf rkeys = join_keys(c, r, rk, nk);
+    Buf ridx = make_buf(c, r->rows * 4);
+    if (r->rows) {
+        prof_begin(c, "iota", 0);
+        iota_k<<<grid_for(c, r->rows), BLOCK, 0, c->stream>>>(ridx->as<uint32_t>(), r->rows);
+        check_launch(c, "iota");
+        radix_sort(c, rkeys, &ridx, r->rows);
+    }
+    Index ix = ops_index_build(c, rkeys, r->rows, 0, ridx);
+    Buf lkeys = join_keys(c, l, lk, nk);
+    Keys lrows;
+    lrows.n = l->rows;
+    lrows.buf = make_buf(c, l->rows * 8);
+    prof_begin(c, "iota64", 0);
+    iota64_k<<<grid_for(c, l->rows), BLOCK, 0, c->stream>>>(lrows.buf->as<uint64_t>(), l->rows);
+    check_launch(c, "iota64");
+    if (type == XLB_JOIN_INNER) {
+        Keys pairs = ops_join_expand(c, lrows, SRC_LO, lkeys->as<uint64_t>(), ix, SRC_LO, SRC_OTHER);
+        std::unique_ptr<xlb_rel> o(new xlb_rel);
+        o->ctx = c;
+        o->schema = os;
+        o->rows = pairs.n;
+        for (uint32_t i = 0; i < os.arity; ++i) {
+            bool left = i < l->schema.arity;
+            const xlb_rel* src = left ? l : r;
+            uint32_t sc = left ? i : i - l->schema.arity;
+            uint32_t w = type_width(os.types[i]);
+            o->cols[i] = make_buf(c, pairs.n * w);
+            if (!pairs.n) continue;
+            prof_begin(c, "gather_pair", 0);
+            if (w == 4) gather_pair_k<uint32_t><<<grid_for(c, pairs.n), BLOCK, 0, c->stream>>>(src->cols[sc]->as<uint32_t>(), pairs.ptr(), left ? 0 : 1, o->cols[i]->as<uint32_t>(), pairs.n);
+            else if (w == 8) gather_pair_k<uint64_t><<<grid_for(c, pairs.n), BLOCK, 0, c->stream>>>(src->cols[sc]->as<uint64_t>(), pairs.ptr(), left ? 0 : 1, o->cols[i]->as<uint64_t>(), pairs.n);
+            else gather_pair_k<uint8_t><<<grid_for(c, pairs.n), BLOCK, 0, c->stream>>>(src->cols[sc]->as<uint8_t>(), pairs.ptr(), left ? 0 : 1, o->cols[i]->as<uint8_t>(), pairs.n);
+            check_launch(c, "gather_pair");
+        }
+        return o.release();
+    }
+    Buf match = ops_probe_match(c, lrows, SRC_LO, lkeys->as<uint64_t>(), ix);
+    Buf sel = make_buf(c, l->rows * 4);
+    uint64_t m = select(c, PredFlag{match->as<uint64_t>(), type == XLB_JOIN_SEMI}, EmitIndex{sel->as<uint32_t>()}, l->rows);
+    return gather_rel(c, l, sel->as<uint32_t>(), m);
+}
+
+extern "C" xlb_status xlb_hash_join(xlb_ctx* c, const xlb_rel* l, const xlb_rel* r, const uint32_t* lk, const uint32_t* rk, uint32_t nk,
+                                    xlb_join_type type, xlb_rel** out_final) {
+    if (!c || !l || !r || !out_final) return XLB_ERR_INVALID;
+    API_BEGIN(c)
+    ResultGuard guard;
+    guard.r = rel_join(c, l, r, lk, rk, nk, type);
     guard.deliver(c, out_final);
     API_END()
 }

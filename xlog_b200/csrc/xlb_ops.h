@@ -178,3 +178,17 @@ struct PhaseTimer {
     PhaseTimer(xlb_ctx* ctx, double* into);
     ~PhaseTimer();
 };
+
+// Relation-level operators on column-major relations of any arity: what the C ABI's operator
+// entry points run, and what the general evaluator of rule bodies (xlb_tree.cu) is written in.
+// Every function returns a fresh, caller-owned relation; inputs are never modified.
+xlb_rel* rel_empty(xlb_ctx* c, const xlb_schema& s);
+xlb_rel* rel_view(xlb_ctx* c, const xlb_rel* r);                                  // another handle on the same buffers
+xlb_rel* rel_project(xlb_ctx* c, const xlb_rel* in, const uint32_t* cols, uint32_t n);  // columns shared, not copied
+// rows where column lhs <cmp> (rhs_is_const ? rhs : column rhs), in input order; unsigned comparison
+xlb_rel* rel_filter(xlb_ctx* c, const xlb_rel* in, uint32_t cmp, uint32_t lhs, bool rhs_is_const, uint64_t rhs);
+xlb_rel* rel_concat(xlb_ctx* c, const xlb_rel* const* ins, uint32_t n);
+xlb_rel* rel_canonical(xlb_ctx* c, const xlb_rel* in);                             // sorted by all columns, unique
+xlb_rel* rel_union_many(xlb_ctx* c, const xlb_rel* const* ins, uint32_t n);
+xlb_rel* rel_difference(xlb_ctx* c, const xlb_rel* a, const xlb_rel* b);
+xlb_rel* rel_join(xlb_ctx* c, const xlb_rel* l, const xlb_rel* r, const uint32_t* lk, const uint32_t* rk, uint32_t nk, xlb_join_type type);

@@ -18,9 +18,9 @@ from . import _abi as A
 from .lib import XlbError, load
 
 _NP = {A.U32: np.uint32, A.SYMBOL: np.uint32, A.U64: np.uint64, A.I32: np.int32, A.I64: np.int64,
-       A.F32: np.float32, A.F64: np.float64}
+       A.F32: np.float32, A.F64: np.float64, A.BOOL: np.uint8}
 _CODE = {np.dtype(np.uint32): A.U32, np.dtype(np.uint64): A.U64, np.dtype(np.int32): A.I32, np.dtype(np.int64): A.I64,
-         np.dtype(np.float32): A.F32, np.dtype(np.float64): A.F64}
+         np.dtype(np.float32): A.F32, np.dtype(np.float64): A.F64, np.dtype(np.bool_): A.BOOL}
 
 
 def _u32s(xs):
