@@ -189,7 +189,11 @@ typedef enum xlb_node_kind {
     XLB_NODE_FILTER = 2,  /* RirNode::Filter { input, predicate } with a column comparison      */
     XLB_NODE_PROJECT = 3, /* RirNode::Project { input, columns } with pass-through columns      */
     XLB_NODE_JOIN = 4,    /* RirNode::Join { left, right, left_keys, right_keys, join_type }    */
-    XLB_NODE_UNION = 5    /* RirNode::Union { inputs }: at the top of a rule body (one rule per input) */
+    XLB_NODE_UNION = 5,   /* RirNode::Union { inputs }                                          */
+    XLB_NODE_DIFF = 6,    /* RirNode::Diff { left, right } (rir.rs:429-434): set difference,
+                             sorted and unique, as diff_gpu (executor/node_dispatch.rs:264)     */
+    XLB_NODE_DISTINCT = 7 /* RirNode::Distinct { input, key_cols } (rir.rs:421-426): `cols` holds
+                             the key columns; all columns or none = full-row, as xlb_dedup      */
 } xlb_node_kind;
 
 /* CompareOp (rir.rs:296-310). */
@@ -200,14 +204,14 @@ typedef enum xlb_cmp { XLB_EQ = 0, XLB_NE = 1, XLB_LT = 2, XLB_LE = 3, XLB_GT = 
 typedef struct xlb_node {
     uint32_t kind;
     uint32_t rel_id;                      /* SCAN                                             */
-    const struct xlb_node* input;         /* FILTER, PROJECT                                  */
-    const struct xlb_node* left;          /* JOIN                                             */
-    const struct xlb_node* right;         /* JOIN                                             */
+    const struct xlb_node* input;         /* FILTER, PROJECT, DISTINCT                        */
+    const struct xlb_node* left;          /* JOIN, DIFF                                       */
+    const struct xlb_node* right;         /* JOIN, DIFF                                       */
     uint32_t n_keys;                      /* JOIN                                             */
     uint32_t left_keys[XLB_MAX_KEYS];     /* JOIN: column indices of the left input           */
     uint32_t right_keys[XLB_MAX_KEYS];    /* JOIN: column indices of the right input          */
-    uint32_t n_cols;                      /* PROJECT                                          */
-    uint32_t cols[XLB_MAX_ARITY];         /* PROJECT: input column per output column          */
+    uint32_t n_cols;                      /* PROJECT, DISTINCT                                */
+    uint32_t cols[XLB_MAX_ARITY];         /* PROJECT: input column per output column; DISTINCT: key columns */
     uint32_t cmp;                         /* FILTER: xlb_cmp                                  */
     uint32_t cmp_lhs_col;                 /* FILTER: left operand column                      */
     uint32_t cmp_rhs_is_const;            /* FILTER: 0 = column, 1 = constant                 */

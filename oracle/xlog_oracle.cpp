@@ -390,6 +390,17 @@ Rel eval(Exec& ex, const xlb_node* n, const std::map<const xlb_node*, std::strin
             }
             return cat;
         }
+        case XLB_NODE_DIFF: {  // execute_diff (executor/node_dispatch.rs:264)
+            Rel l = eval(ex, n->left, subst), r = eval(ex, n->right, subst);
+            if (!compatible(l, r)) throw Fail{XLB_ERR_TYPE, "difference of incompatible schemas"};
+            return op_diff(l, r);
+        }
+        case XLB_NODE_DISTINCT: {  // execute_distinct -> dedup (relational.rs:238)
+            Rel in = eval(ex, n->input, subst);
+            for (uint32_t c = 0; c < n->n_cols; ++c)
+                if (n->cols[c] >= in.arity) throw Fail{XLB_ERR_INVALID, "dedup key column out of range"};
+            return (n->n_cols == 0 || n->n_cols >= in.arity) ? op_dedup_full(in) : op_dedup_keys(in, n->cols, n->n_cols);
+        }
     }
     throw Fail{XLB_ERR_INVALID, "unknown plan node kind"};
 }
@@ -398,7 +409,9 @@ void collect_scans(const xlb_node* n, std::vector<const xlb_node*>& out) {
     switch (n->kind) {
         case XLB_NODE_SCAN: out.push_back(n); break;
         case XLB_NODE_FILTER:
+        case XLB_NODE_DISTINCT:
         case XLB_NODE_PROJECT: collect_scans(n->input, out); break;
+        case XLB_NODE_DIFF:
         case XLB_NODE_JOIN: collect_scans(n->left, out); collect_scans(n->right, out); break;
         case XLB_NODE_UNION: for (uint32_t i = 0; i < n->n_inputs; ++i) collect_scans(n->inputs[i], out); break;
     }

@@ -12,7 +12,7 @@ import pytest
 from xlog_b200 import _abi as A
 from xlog_b200 import programs, workloads
 from xlog_b200.executor import run_program
-from xlog_b200.plan import CompiledRule, ExecutionPlan, Filter, Join, Project, Scan, Scc, Union
+from xlog_b200.plan import CompiledRule, Diff, Distinct, ExecutionPlan, Filter, Join, Project, Scan, Scc, Union
 from xlog_b200.provider import KernelProvider
 
 pytestmark = pytest.mark.gpu
@@ -86,6 +86,27 @@ def test_union_below_the_top_and_anti_join_against_a_subtree(oracle):
     plan = ExecutionPlan([Scc(0, False, [sym]), Scc(1, False, [sink])], {"edge": 0, "node": 1, "sym": 2, "sink": 3})
     got, _ = _check(oracle, plan, {"edge": [c0, c1], "node": [nodes]}, ["sym", "sink"])
     assert set(got["sink"][0].tolist()) == set(nodes.tolist()) - set(c0.tolist())
+
+
+def test_diff_and_distinct_nodes(oracle):
+    """RirNode::Diff (crates/xlog-ir/src/rir.rs:429-434, executed at executor/node_dispatch.rs:264) and
+    RirNode::Distinct as plan nodes: one_way(X,Y) = edges without their reverse edge; first(X,Y) = one
+    successor per node (the first in stable key order); also a Diff inside a recursive component."""
+    c0, c1 = workloads.uniform_digraph(70, 400, 10)
+    one_way = CompiledRule("one_way", Diff(Scan(0), Project(Scan(0), [1, 0])), (A.U32, A.U32))
+    first = CompiledRule("first", Distinct(Scan(0), [0]), (A.U32, A.U32))
+    every = CompiledRule("every", Distinct(Union([Scan(0), Scan(0)])), (A.U32, A.U32))
+    plan = ExecutionPlan([Scc(0, False, [one_way]), Scc(1, False, [first]), Scc(2, False, [every])],
+                         {"edge": 0, "one_way": 1, "first": 2, "every": 3})
+    got, _ = _check(oracle, plan, {"edge": [c0, c1]}, ["one_way", "first", "every"])
+    pairs = set(zip(c0.tolist(), c1.tolist()))
+    assert set(zip(*[c.tolist() for c in got["one_way"]])) == {p for p in pairs if (p[1], p[0]) not in pairs}
+    assert len(got["first"][0]) == len(set(c0.tolist()))
+    # reach over the one-way edges only, with the Diff inside the recursive component's base rule
+    base = CompiledRule("r", Diff(Scan(0), Project(Scan(0), [1, 0])), (A.U32, A.U32))
+    rec = CompiledRule("r", Project(Join(Scan(1), Diff(Scan(0), Project(Scan(0), [1, 0])), [1], [0]), [0, 3]), (A.U32, A.U32))
+    plan2 = ExecutionPlan([Scc(0, True, [base, rec])], {"edge": 0, "r": 1})
+    _check(oracle, plan2, {"edge": [c0, c1]}, ["r"])
 
 
 @pytest.mark.parametrize("name", ["tc", "tc_nonlinear", "reach0", "sg", "andersen", "negation"])

@@ -111,3 +111,22 @@ def test_malformed_documents_are_errors():
     bad["rules_by_scc"][0][0]["head"] = "nobody"
     with pytest.raises(XlbError, match="no RelId"):
         PJ.plan_from_json(bad, rel_names={0: "edge", 1: "reach"})
+
+
+def test_diff_and_distinct_round_trip(oracle):
+    """RirNode::Diff and RirNode::Distinct survive export and import, and the imported plan computes
+    what the hand-built one does."""
+    from xlog_b200.plan import CompiledRule, Diff, Distinct, ExecutionPlan, Scc
+    one_way = CompiledRule("one_way", Diff(Scan(0), Project(Scan(0), [1, 0])), (A.U32, A.U32))
+    first = CompiledRule("first", Distinct(Scan(0), [0]), (A.U32, A.U32))
+    plan = ExecutionPlan([Scc(0, False, [one_way]), Scc(1, False, [first])], {"edge": 0, "one_way": 1, "first": 2})
+    back = PJ.plan_from_json(PJ.plan_to_json(plan))
+    assert isinstance(back.sccs[0].rules[0].body, Diff) and isinstance(back.sccs[1].rules[0].body, Distinct)
+    assert list(back.sccs[1].rules[0].body.key_cols) == [0]
+    c0, c1 = workloads.uniform_digraph(40, 160, 3)
+    want, _ = oracle.run_program(plan, {"edge": [c0, c1]}, ["one_way", "first"])
+    got, _ = oracle.run_program(back, {"edge": [c0, c1]}, ["one_way", "first"])
+    for name in ("one_way", "first"):
+        assert all(np.array_equal(g, w) for g, w in zip(got[name], want[name]))
+    pairs = set(zip(c0.tolist(), c1.tolist()))
+    assert set(zip(*[c.tolist() for c in want["one_way"]])) == {p for p in pairs if (p[1], p[0]) not in pairs}

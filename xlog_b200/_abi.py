@@ -20,7 +20,7 @@ JOIN_INNER, JOIN_SEMI, JOIN_ANTI = range(3)
 # xlb_agg_op (AggOp, crates/xlog-ir/src/rir.rs)
 AGG_COUNT, AGG_SUM, AGG_MIN, AGG_MAX = range(4)
 # xlb_node_kind
-NODE_SCAN, NODE_FILTER, NODE_PROJECT, NODE_JOIN, NODE_UNION = 1, 2, 3, 4, 5
+NODE_SCAN, NODE_FILTER, NODE_PROJECT, NODE_JOIN, NODE_UNION, NODE_DIFF, NODE_DISTINCT = 1, 2, 3, 4, 5, 6, 7
 # xlb_cmp
 EQ, NE, LT, LE, GT, GE = range(6)
 

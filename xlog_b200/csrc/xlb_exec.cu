@@ -218,7 +218,9 @@ struct Flattener {
                 return l;
             }
             case XLB_NODE_UNION:
-                xlb_fail(XLB_ERR_UNSUPPORTED, "a Union node below the top of a rule body is not built");
+            case XLB_NODE_DIFF:
+            case XLB_NODE_DISTINCT:
+                xlb_fail(XLB_ERR_UNSUPPORTED, "Union below the top of a body, Diff and Distinct nodes run on the general evaluator");
         }
         xlb_fail(XLB_ERR_INVALID, "unknown plan node kind %u", n->kind);
     }

@@ -1340,30 +1340,31 @@ xlb_rel* rel_canonical(xlb_ctx* c, const xlb_rel* in) {
     return wide_dedup(c, in, nullptr, 0);
 }
 
+// dedup (relational.rs:238): key columns covering every column (or none) = full-row form; a proper
+// subset keeps, for every distinct key, the first row in stable key order.
+xlb_rel* rel_distinct(xlb_ctx* c, const xlb_rel* in, const uint32_t* key_cols, uint32_t nk) {
+    if (nk == 0 || nk >= in->schema.arity) return rel_canonical(c, in);
+    for (uint32_t i = 0; i < nk; ++i)
+        if (key_cols[i] >= in->schema.arity) xlb_fail(XLB_ERR_INVALID, "dedup key column %u out of range", key_cols[i]);
+    ops_rel_columns(c, in);
+    Buf idx = sort_permutation(c, in, key_cols, nk);
+    std::unique_ptr<xlb_rel> sorted(gather_rel(c, in, idx->as<uint32_t>(), in->rows));
+    ColSet cs{};
+    cs.n = (int)nk;
+    for (uint32_t i = 0; i < nk; ++i) {
+        cs.col[i] = sorted->cols[key_cols[i]]->p;
+        cs.width[i] = (int)type_width(in->schema.types[key_cols[i]]);
+    }
+    Buf heads = make_buf(c, in->rows * 4);
+    uint64_t m = select(c, PredRowHead{cs}, EmitIndex{heads->as<uint32_t>()}, in->rows);
+    return gather_rel(c, sorted.get(), heads->as<uint32_t>(), m);
+}
+
 static xlb_status dedup_unsigned(xlb_ctx* c, const xlb_rel* in, const uint32_t* key_cols, uint32_t nk, xlb_rel** out_final) {
     if (!c || !in || !out_final) return XLB_ERR_INVALID;
     API_BEGIN(c)
     ResultGuard guard;
-    xlb_rel** out = &guard.r;
-    bool full = nk == 0 || nk >= in->schema.arity;
-    if (full) {
-        *out = rel_canonical(c, in);
-    } else {
-        for (uint32_t i = 0; i < nk; ++i)
-            if (key_cols[i] >= in->schema.arity) xlb_fail(XLB_ERR_INVALID, "dedup key column %u out of range", key_cols[i]);
-        ops_rel_columns(c, in);
-        Buf idx = sort_permutation(c, in, key_cols, nk);
-        std::unique_ptr<xlb_rel> sorted(gather_rel(c, in, idx->as<uint32_t>(), in->rows));
-        ColSet cs{};
-        cs.n = (int)nk;
-        for (uint32_t i = 0; i < nk; ++i) {
-            cs.col[i] = sorted->cols[key_cols[i]]->p;
-            cs.width[i] = (int)type_width(in->schema.types[key_cols[i]]);
-        }
-        Buf heads = make_buf(c, in->rows * 4);
-        uint64_t m = select(c, PredRowHead{cs}, EmitIndex{heads->as<uint32_t>()}, in->rows);
-        *out = gather_rel(c, sorted.get(), heads->as<uint32_t>(), m);
-    }
+    guard.r = rel_distinct(c, in, key_cols, nk);
     guard.deliver(c, out_final);
     API_END()
 }

@@ -189,6 +189,7 @@ xlb_rel* rel_project(xlb_ctx* c, const xlb_rel* in, const uint32_t* cols, uint32
 xlb_rel* rel_filter(xlb_ctx* c, const xlb_rel* in, uint32_t cmp, uint32_t lhs, bool rhs_is_const, uint64_t rhs);
 xlb_rel* rel_concat(xlb_ctx* c, const xlb_rel* const* ins, uint32_t n);
 xlb_rel* rel_canonical(xlb_ctx* c, const xlb_rel* in);                             // sorted by all columns, unique
+xlb_rel* rel_distinct(xlb_ctx* c, const xlb_rel* in, const uint32_t* key_cols, uint32_t nk);  // dedup: full rows or by key columns
 xlb_rel* rel_union_many(xlb_ctx* c, const xlb_rel* const* ins, uint32_t n);
 xlb_rel* rel_difference(xlb_ctx* c, const xlb_rel* a, const xlb_rel* b);
 xlb_rel* rel_join(xlb_ctx* c, const xlb_rel* l, const xlb_rel* r, const uint32_t* lk, const uint32_t* rk, uint32_t nk, xlb_join_type type);

@@ -93,6 +93,15 @@ RelPtr eval(Tree& t, const xlb_node* n) {
             }
             return RelPtr(rel_concat(c, ptrs.data(), (uint32_t)ptrs.size()));  // RirNode::Union concatenates; the head's union removes duplicates
         }
+        case XLB_NODE_DIFF: {
+            RelPtr l = eval(t, n->left), r = eval(t, n->right);
+            return RelPtr(rel_difference(c, l.get(), r.get()));
+        }
+        case XLB_NODE_DISTINCT: {
+            RelPtr in = eval(t, n->input);
+            if (n->n_cols > XLB_MAX_ARITY) xlb_fail(XLB_ERR_INVALID, "more than %u key columns", XLB_MAX_ARITY);
+            return RelPtr(rel_distinct(c, in.get(), n->cols, n->n_cols));
+        }
     }
     xlb_fail(XLB_ERR_INVALID, "unknown plan node kind %u", n->kind);
 }
@@ -102,7 +111,9 @@ void collect_scans(const xlb_node* n, std::vector<const xlb_node*>& out) {
     switch (n->kind) {
         case XLB_NODE_SCAN: out.push_back(n); break;
         case XLB_NODE_FILTER:
+        case XLB_NODE_DISTINCT:
         case XLB_NODE_PROJECT: collect_scans(n->input, out); break;
+        case XLB_NODE_DIFF:
         case XLB_NODE_JOIN: collect_scans(n->left, out); collect_scans(n->right, out); break;
         case XLB_NODE_UNION:
             for (uint32_t i = 0; n->inputs && i < n->n_inputs; ++i) collect_scans(n->inputs[i], out);

@@ -72,6 +72,26 @@ class Union(RirNode):
 
 
 @dataclass
+class Diff(RirNode):
+    """``left`` minus ``right`` with set semantics on full rows (``RirNode::Diff``)."""
+    left: RirNode
+    right: RirNode
+
+    def arity(self, arities):
+        return self.left.arity(arities)
+
+
+@dataclass
+class Distinct(RirNode):
+    """One row per distinct value of ``key_cols`` (``RirNode::Distinct``); no key columns = full rows."""
+    input: RirNode
+    key_cols: Sequence[int] = ()
+
+    def arity(self, arities):
+        return self.input.arity(arities)
+
+
+@dataclass
 class CompiledRule:
     head: str
     body: RirNode
@@ -146,6 +166,16 @@ class CompiledPlan:
                 arr[i] = C.pointer(self._node(x))
             self._keep.append(arr)
             c.inputs, c.n_inputs = arr, len(n.inputs)
+        elif isinstance(n, Diff):
+            c.kind = A.NODE_DIFF
+            c.left = C.pointer(self._node(n.left))
+            c.right = C.pointer(self._node(n.right))
+        elif isinstance(n, Distinct):
+            c.kind = A.NODE_DISTINCT
+            c.input = C.pointer(self._node(n.input))
+            c.n_cols = len(n.key_cols)
+            for i, x in enumerate(n.key_cols):
+                c.cols[i] = x
         else:
             raise TypeError(f"unsupported plan node {n!r}")
         return c

@@ -33,7 +33,7 @@ from typing import Any, Mapping
 
 from . import _abi as A
 from .lib import XlbError
-from .plan import CompiledRule, ExecutionPlan, Filter, Join, Project, RirNode, Scan, Scc, Union
+from .plan import CompiledRule, Diff, Distinct, ExecutionPlan, Filter, Join, Project, RirNode, Scan, Scc, Union
 
 _CMP = {"Eq": A.EQ, "Ne": A.NE, "Lt": A.LT, "Le": A.LE, "Gt": A.GT, "Ge": A.GE}
 _FLIP = {A.EQ: A.EQ, A.NE: A.NE, A.LT: A.GT, A.LE: A.GE, A.GT: A.LT, A.GE: A.LE}
@@ -114,6 +114,10 @@ def node_from_json(obj: Any) -> RirNode:
                     [int(k) for k in v["right_keys"]], _JOIN[jt])
     if kind == "Union":
         return Union([node_from_json(i) for i in v["inputs"]])
+    if kind == "Diff":
+        return Diff(node_from_json(v["left"]), node_from_json(v["right"]))
+    if kind == "Distinct":
+        return Distinct(node_from_json(v["input"]), [int(k) for k in v.get("key_cols", [])])
     if kind in ("ChainJoin", "MultiWayJoin"):
         return node_from_json(v["fallback"])   # the promoted forms keep the plain tree they came from
     _unsupported(f"RirNode::{kind}")
@@ -209,6 +213,10 @@ def node_to_json(n: RirNode) -> Any:
                          "right_keys": list(n.right_keys), "join_type": _JOIN_NAME[n.join_type]}}
     if isinstance(n, Union):
         return {"Union": {"inputs": [node_to_json(i) for i in n.inputs]}}
+    if isinstance(n, Diff):
+        return {"Diff": {"left": node_to_json(n.left), "right": node_to_json(n.right)}}
+    if isinstance(n, Distinct):
+        return {"Distinct": {"input": node_to_json(n.input), "key_cols": [int(k) for k in n.key_cols]}}
     raise TypeError(f"not a plan node: {n!r}")
 
 
