@@ -92,3 +92,19 @@ def test_plan_lowering_builds_the_c_tree():
     assert j.left.contents.kind == A.NODE_JOIN and j.right.contents.kind == A.NODE_SCAN
     base = cp.c.sccs[0].rules[0].body.contents.input.contents
     assert base.kind == A.NODE_FILTER and base.cmp == A.NE and base.cmp_lhs_col == 1 and base.cmp_rhs == 3
+
+
+def test_rust_binding_names_every_entry_point():
+    """rust/xlb-sys cannot be compiled here (no Rust toolchain); at least its extern block must
+    declare every function of include/xlb.h (the two test hooks aside), with the header's flags."""
+    import re
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    header = open(os.path.join(root, "include", "xlb.h")).read()
+    rust = open(os.path.join(root, "rust", "xlb-sys", "src", "lib.rs")).read()
+    declared = set(re.findall(r"^(?:xlb_status|void|const char\*|uint32_t|uint64_t)\s+(xlb_[a-z0-9_]+)\s*\(", header, re.M))
+    assert len(declared) > 30
+    hooks = {"xlb_comm_mark_aborted_for_test", "xlb_test_set_lookback"}
+    bound = set(re.findall(r"pub fn (xlb_[a-z0-9_]+)\s*\(", rust))
+    assert declared - hooks <= bound, sorted(declared - hooks - bound)
+    for name, value in re.findall(r"#define (XLB_FLAG_[A-Z_]+) (\d+)u", header):
+        assert re.search(rf"pub const {name}: u32 = {value};", rust), name
