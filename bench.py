@@ -68,6 +68,10 @@ def make_workload(name: str, scale: int):
         c0, c1 = workloads.rmat_dag(scale, 8)
         return programs.transitive_closure(), {"edge": [c0, c1]}, "reach", \
             f"transitive closure, banded R-MAT DAG scale {scale} edge factor 8 ({len(c0)} edges)"
+    if name == "c3":
+        c0, c1, _ = workloads.tree_dag(scale, 0.05)
+        return programs.same_generation(), {"edge": [c0, c1]}, "sg", \
+            f"same generation, tree of {scale} nodes (2-6 children) plus 5% forward edges ({len(c0)} edges)"
     raise SystemExit(f"unknown workload {name}")
 
 
@@ -124,33 +128,7 @@ def measured_peak_gbs():
     return 6650.0, "fallback"
 
 
-def result_checksum(cols) -> tuple[int, int, int]:
-    """Order-independent digest of a set of tuples: (count, XOR, sum of the low 32 bits) of the
-    64-bit mix of every packed tuple.  Shards of disjoint tuples combine by adding the counts and
-    sums and XOR-ing the XORs, so the digest of a sharded result equals that of the whole."""
-    from xlog_b200.dist import mix64
-    n = len(cols[0]) if cols else 0
-    if n == 0:
-        return 0, 0, 0
-    xor, low = 0, 0
-    step = 1 << 24
-    for at in range(0, n, step):
-        k = cols[0][at:at + step].astype(np.uint64)
-        if len(cols) > 1:
-            k = (k << np.uint64(32)) | cols[1][at:at + step].astype(np.uint64)
-        h = mix64(k)
-        xor ^= int(np.bitwise_xor.reduce(h))
-        low += int((h & np.uint64(0xFFFFFFFF)).sum(dtype=np.uint64))
-    return n, xor, low
-
-
-def checksum_text(parts) -> str:
-    n = sum(p[0] for p in parts)
-    xor = 0
-    for p in parts:
-        xor ^= p[1]
-    low = sum(p[2] for p in parts) & ((1 << 64) - 1)
-    return f"{n:x}-{xor:016x}-{low:016x}"
+from xlog_b200.digest import checksum_text, result_checksum  # noqa: E402
 
 
 def roofline_of(prof: dict, kernel: str, peak: float, peak_kind: str):
@@ -264,6 +242,11 @@ class Job:
     def result(self):
         return self.prov.download(self.ex.get(self.out_name))
 
+    def result_digest(self):
+        """Digest of this rank's shard, computed on the device (no download)."""
+        buf = self.ex.get(self.out_name)
+        return self.prov.checksum(buf), buf.num_rows()
+
     def close(self):
         self.prov.close()
 
@@ -329,8 +312,8 @@ def secondary_block(env, args, peak, peak_kind, flags, label):
         job.device_step()
     ms_t, _, stats, launches, prof = timed_steps(env, job, args.secondary_steps, "radix_scatter,hash_probe")
     ms = float(ms_t.mean().item())
-    shard = job.result()
-    parts = env.gather((result_checksum(shard), len(shard[0]), stats["ms_exchange"], stats["exchange_bytes"],
+    digest, shard_rows = job.result_digest()
+    parts = env.gather((digest, shard_rows, stats["ms_exchange"], stats["exchange_bytes"],
                         stats["ms_sort"], stats["ms_join"], stats["ms_setops"]))
     job.close()
     if env.rank != 0:
@@ -366,8 +349,8 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="xlb", choices=["xlb", "reference"])
-    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c5"])
-    ap.add_argument("--scale", type=int, default=20)
+    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c5"])
+    ap.add_argument("--scale", type=int, default=20, help="R-MAT scale (c2, c5) or number of tree nodes (c3)")
     ap.add_argument("--kernel", default="auto",
                     help="kernel whose launches are timed for the roofline object (auto: the one with the most device time in the last warm-up step)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -414,7 +397,7 @@ def main():
     ms_per_step = float(ms_t.mean().item())
     derived = stats["derived_tuples"]
     value = derived / (ms_per_step / 1e3)
-    digest = checksum_text([p for p in env.gather(result_checksum(job.result()))])
+    digest = checksum_text([p for p in env.gather(job.result_digest()[0])])  # computed on the device, shard by shard
 
     # ---- end to end: host buffers in, host result out, copies inside the timed region ------
     e2e_ms, d2h_bytes = [], 0

@@ -138,6 +138,14 @@ xlb_status xlb_rel_to_host(xlb_ctx* ctx, const xlb_rel* rel, void* const* cols, 
 /* clone_buffer (relational.rs:6113). */
 xlb_status xlb_rel_clone(xlb_ctx* ctx, const xlb_rel* rel, xlb_rel** out);
 void xlb_rel_free(xlb_rel* rel);
+/* No counterpart in the reference (its tests download and compare).  An order-independent digest of
+ * a relation's rows, computed on the device: every row is folded into one 64-bit word — for one or
+ * two 32-bit columns the packed row (c0, or c0 << 32 | c1), for anything else h = 0, then for each
+ * column h = mix(h ^ value) with mix the 64-bit finaliser xlb_owner_of uses — and mixed once more;
+ * digest[0] = row count, digest[1] = XOR of the mixed words, digest[2] = sum of their low 32 bits
+ * (mod 2^64).  Digests of disjoint shards combine by adding [0] and [2] and XOR-ing [1], so a
+ * result spread over several ranks can be compared with the same result held by one. */
+xlb_status xlb_rel_checksum(xlb_ctx* ctx, const xlb_rel* rel, uint64_t digest[3]);
 
 /* ---- relational operators ----------------------------------------------------------------- */
 

@@ -166,6 +166,7 @@ pub mod ffi {
         pub fn xlb_rel_to_host(ctx: *mut xlb_ctx, rel: *const xlb_rel, cols: *const *mut c_void, cap_rows: u64, rows: *mut u64) -> c_int;
         pub fn xlb_rel_clone(ctx: *mut xlb_ctx, rel: *const xlb_rel, out: *mut *mut xlb_rel) -> c_int;
         pub fn xlb_rel_free(rel: *mut xlb_rel);
+        pub fn xlb_rel_checksum(ctx: *mut xlb_ctx, rel: *const xlb_rel, digest: *mut u64) -> c_int;
 
         pub fn xlb_hash_join(ctx: *mut xlb_ctx, left: *const xlb_rel, right: *const xlb_rel, left_keys: *const u32, right_keys: *const u32,
                              n_keys: u32, join_type: c_int, out: *mut *mut xlb_rel) -> c_int;

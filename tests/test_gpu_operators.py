@@ -228,3 +228,31 @@ def test_join_at_the_size_edges_of_the_prefix_sum(provider, nl):
     keep = lk % 2 == 0
     assert np.array_equal(out[0], lk[keep]) and np.array_equal(out[1], l[1][keep])     # left row order kept
     assert np.array_equal(out[2], lk[keep]) and np.array_equal(out[3], lk[keep] + 5)
+
+
+def test_device_checksum_matches_the_host_digest_and_combines_over_shards(provider):
+    """xlb_rel_checksum: the digest bench.py compares across rank counts.  The device result must
+    equal the same function computed with numpy, and digests of disjoint shards must combine to the
+    digest of the whole (also for rows of three columns, which are folded column by column)."""
+    from xlog_b200.digest import checksum_text, result_checksum
+    from xlog_b200.dist import mix64
+    from xlog_b200.workloads import splitmix64
+    n = 100_003
+    c0 = (splitmix64(3, 0, n) >> np.uint64(40)).astype(np.uint32)
+    c1 = (splitmix64(4, 0, n) >> np.uint64(38)).astype(np.uint32)
+    whole = provider.checksum(provider.create_buffer_from_slices([c0, c1]))
+    assert checksum_text([whole]) == checksum_text([result_checksum([c0, c1])])
+    cut = 40_000
+    parts = [provider.checksum(provider.create_buffer_from_slices([c0[:cut], c1[:cut]])),
+             provider.checksum(provider.create_buffer_from_slices([c0[cut:], c1[cut:]]))]
+    assert checksum_text(parts) == checksum_text([whole])
+    one = provider.checksum(provider.create_buffer_from_slices([c0]))
+    assert checksum_text([one]) == checksum_text([result_checksum([c0])])
+    # three columns: h = mix(mix(mix(0 ^ a) ^ b) ^ c), mixed once more
+    c2 = (splitmix64(5, 0, n) >> np.uint64(50)).astype(np.uint32)
+    h = np.zeros(n, np.uint64)
+    for col in (c0, c1, c2):
+        h = mix64(h ^ col.astype(np.uint64))
+    h = mix64(h)
+    want = (n, int(np.bitwise_xor.reduce(h)), int((h & np.uint64(0xFFFFFFFF)).sum(dtype=np.uint64)))
+    assert provider.checksum(provider.create_buffer_from_slices([c0, c1, c2])) == want

@@ -1806,7 +1806,10 @@ static void run_scc(xlb_ctx* c, const xlb_scc& scc, RunState& rs) {
             install_full(c, p, schema[p], merged, &d, rs);
         }
     }
-    for (auto& p : preds) materialize_full(c, rs, p);
+    for (auto& p : preds) {
+        rs.tset.erase(p);  // gigabytes, and the lists are about to be written out
+        materialize_full(c, rs, p);
+    }
     if (rs.repl.on) {
         // every rank holds the whole result: each keeps the tuples it owns, as the partitioned
         // evaluation would have left them (sorted, unique, disjoint between ranks)

@@ -173,6 +173,46 @@ struct PredCmpCols {  // comparison between a column and a constant or another c
         }
     }
 };
+// Order-independent digest of rows: XOR and low-32-bit sum of one mixed word per row.
+__global__ void digest_packed_k(const uint64_t* __restrict__ rows, uint64_t n, unsigned long long* out) {
+    unsigned long long x = 0, lo = 0;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t h = mix64(rows[i]);
+        x ^= h;
+        lo += h & 0xFFFFFFFFull;
+    }
+#pragma unroll
+    for (int d = 16; d; d >>= 1) {
+        x ^= __shfl_xor_sync(FULL, x, d);
+        lo += __shfl_xor_sync(FULL, lo, d);
+    }
+    if (lane_id() == 0) {
+        atomicXor(&out[0], x);
+        atomicAdd(&out[1], lo);
+    }
+}
+__global__ void digest_cols_k(ColSet cs, uint64_t n, unsigned long long* out) {
+    unsigned long long x = 0, lo = 0;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        uint64_t h = 0;
+        for (int c = 0; c < cs.n; ++c) {
+            const uint64_t v = cs.width[c] == 4 ? ((const uint32_t*)cs.col[c])[i] : cs.width[c] == 8 ? ((const uint64_t*)cs.col[c])[i] : ((const uint8_t*)cs.col[c])[i];
+            h = mix64(h ^ v);
+        }
+        h = mix64(h);
+        x ^= h;
+        lo += h & 0xFFFFFFFFull;
+    }
+#pragma unroll
+    for (int d = 16; d; d >>= 1) {
+        x ^= __shfl_xor_sync(FULL, x, d);
+        lo += __shfl_xor_sync(FULL, lo, d);
+    }
+    if (lane_id() == 0) {
+        atomicXor(&out[0], x);
+        atomicAdd(&out[1], lo);
+    }
+}
 struct PredFlag {
     const uint64_t* match;
     bool want;
@@ -611,7 +651,8 @@ Keys ops_tuple_set_novel(xlb_ctx* c, TupleSet& s, const Keys& cand) {
         // move the stored words over, straight from the old table (in slot order, which is the new
         // table's order too: the insertions walk through it front to back)
         TupleSet old = s;
-        tuple_set_alloc(c, s, 2 * (s.rows + cand.n));
+        const uint64_t need = s.rows + cand.n;
+        tuple_set_alloc(c, s, need < (1ull << 27) ? 2 * need : need);  // (a table of gigabytes grows to what is needed only)
         tuple_set_fill(c, s, old.table->as<uint64_t>(), old.cap, true);
         CUDA_OK(cudaMemcpyAsync(tuple_set_flag(s), tuple_set_flag(old), 4, cudaMemcpyDeviceToDevice, c->stream));
     }
@@ -1122,6 +1163,32 @@ extern "C" xlb_status xlb_rel_clone(xlb_ctx* c, const xlb_rel* r, xlb_rel** out)
     API_BEGIN(c)
     *out = rel_clone(c, r);
     CUDA_OK(cudaStreamSynchronize(c->stream));
+    API_END()
+}
+
+static ColSet colset_of(const xlb_rel* r);
+
+extern "C" xlb_status xlb_rel_checksum(xlb_ctx* c, const xlb_rel* r, uint64_t digest[3]) {
+    if (!c || !r || !digest) return XLB_ERR_INVALID;
+    API_BEGIN(c)
+    Buf acc = make_buf(c, 16);
+    CUDA_OK(cudaMemsetAsync(acc->p, 0, 16, c->stream));
+    if (r->rows && r->schema.arity) {
+        prof_begin(c, "digest", 0);
+        if (rel_packable(r->schema)) {
+            Keys k = ops_rel_packed(c, r);
+            digest_packed_k<<<grid_for(c, k.n, BLOCK * 4), BLOCK, 0, c->stream>>>(k.ptr(), k.n, acc->as<unsigned long long>());
+        } else {
+            ops_rel_columns(c, r);
+            digest_cols_k<<<grid_for(c, r->rows, BLOCK * 4), BLOCK, 0, c->stream>>>(colset_of(r), r->rows, acc->as<unsigned long long>());
+        }
+        check_launch(c, "digest");
+    }
+    unsigned long long h[2];
+    read_words(c, acc->p, 2, h);
+    digest[0] = r->rows;
+    digest[1] = h[0];
+    digest[2] = h[1];
     API_END()
 }
 

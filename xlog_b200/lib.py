@@ -31,6 +31,7 @@ PROTOTYPES = {
     "xlb_rel_to_host": (C.c_int, [P, P, C.POINTER(P), C.c_uint64, C.POINTER(C.c_uint64)]),
     "xlb_rel_clone": (C.c_int, [P, P, C.POINTER(P)]),
     "xlb_rel_free": (None, [P]),
+    "xlb_rel_checksum": (C.c_int, [P, P, C.POINTER(C.c_uint64)]),
     "xlb_hash_join": (C.c_int, [P, P, P, U32P, U32P, C.c_uint32, C.c_int, C.POINTER(P)]),
     "xlb_sort": (C.c_int, [P, P, U32P, C.c_uint32, C.POINTER(P)]),
     "xlb_dedup": (C.c_int, [P, P, U32P, C.c_uint32, C.POINTER(P)]),

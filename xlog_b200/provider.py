@@ -138,6 +138,13 @@ class KernelProvider:
     def download_column(self, buf: Buffer, col: int) -> np.ndarray:
         return self.download(buf)[col]
 
+    def checksum(self, buf: Buffer) -> tuple[int, int, int]:
+        """(row count, XOR, low-32-bit sum) of the mixed rows, computed on the device: shards of a
+        relation combine by adding the first and last and XOR-ing the middle (``xlb_rel_checksum``)."""
+        d = (C.c_uint64 * 3)()
+        self._check(self._lib.xlb_rel_checksum(self._ctx, buf._h, d))
+        return int(d[0]), int(d[1]), int(d[2])
+
     def clone_buffer(self, buf: Buffer) -> Buffer:
         return self._out(self._lib.xlb_rel_clone, buf._h)
 
