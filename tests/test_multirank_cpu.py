@@ -86,3 +86,41 @@ def test_partitioned_fixpoint_equals_single_rank(oracle, tmp_path, world):
     assert np.array_equal(out["c0"], want["reach"][0]) and np.array_equal(out["c1"], want["reach"][1])
     assert int(out["sizes"].sum()) == len(want["reach"][0])      # shards are disjoint
     assert int(out["iters"]) == ex.iterations                     # the vote ends every rank in the same round
+
+
+def _bad_count_rank(rank, world, port, out_dir):
+    import sys
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import torch.distributed as dist
+    from xlog_b200 import dist as D
+
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        rows = np.arange(100 * rank, 100 * rank + 50, dtype=np.uint64)
+        wrong = None
+        if rank == 1:                      # this rank claims one row more for rank 0 than it has
+            wrong = np.bincount(D.owner_of(rows, world), minlength=world)
+            wrong[0] += 1
+        try:
+            D.exchange_by_owner(rows, rows, world, _send_counts=wrong)
+            outcome = "exchanged"
+        except D.ExchangeCountError as e:
+            outcome = str(e)
+        # the ranks are still in step: a second, correct exchange goes through
+        got = D.exchange_by_owner(rows, rows, world)
+        assert np.all(D.owner_of(got, world) == rank)
+        with open(os.path.join(out_dir, f"rank{rank}.txt"), "w") as f:
+            f.write(outcome)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_a_wrong_send_count_fails_every_rank_the_same_way(tmp_path):
+    """Failure made on the host: one rank's count row does not add up.  Every rank must see it in
+    the gathered matrix and raise before the all-to-all, none may hang, and the group stays usable."""
+    world = 3
+    mp.spawn(_bad_count_rank, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    outcomes = [open(tmp_path / f"rank{r}.txt").read() for r in range(world)]
+    assert all("rank(s) [1]" in o for o in outcomes), outcomes

@@ -261,13 +261,17 @@ Keys comm_repartition(xlb_ctx* c, const Keys& in, int keysel, bool sorted_unique
     // the all-gather, so every rank learns the whole count matrix with a single host wait.  Each
     // row of the matrix carries one more word: the sender's OR bound of its rows, so the receiver
     // knows the bits of what it gets without looking at it.
-    const uint32_t RW = W + 1;
+    // and the number of rows the sender holds: a row of counts that does not add up to it is seen by
+    // every rank in the gathered matrix, so all of them fail the same way before any receive is
+    // posted with a size nobody will send.
+    const uint32_t RW = W + 2;
     unsigned long long* dev = cm->counts_dev->as<unsigned long long>();
     unsigned long long* mine = dev + (uint64_t)c->comm_rank * RW;
     Keys part = ops_partition_by_owner_dev(c, in, keysel, W, mine);
-    unsigned long long* send_bound = cm->h_stage + (size_t)W * STAGE_ROW;
-    *send_bound = in.n ? in.bound : 0;
-    CUDA_OK(cudaMemcpyAsync(mine + W, send_bound, 8, cudaMemcpyHostToDevice, c->stream));
+    unsigned long long* send_tail = cm->h_stage + (size_t)W * STAGE_ROW;
+    send_tail[0] = in.n ? in.bound : 0;
+    send_tail[1] = in.n;
+    CUDA_OK(cudaMemcpyAsync(mine + W, send_tail, 16, cudaMemcpyHostToDevice, c->stream));
     NCCL_OK(api().AllGather(mine, dev, RW, ncclUint64, cm->comm, c->stream));
     CUDA_OK(cudaMemcpyAsync(cm->h_stage, dev, (size_t)W * RW * 8, cudaMemcpyDeviceToHost, c->stream));
     comm_wait(c);
@@ -275,6 +279,11 @@ Keys comm_repartition(xlb_ctx* c, const Keys& in, int keysel, bool sorted_unique
     std::vector<uint64_t> send(W), recv(W);
     uint64_t bound = 0, total = 0;
     for (uint32_t r = 0; r < W; ++r) {
+        uint64_t row_sum = 0;
+        for (uint32_t d = 0; d < W; ++d) row_sum += all[(size_t)r * RW + d];
+        if (row_sum != all[(size_t)r * RW + W + 1])
+            xlb_fail(XLB_ERR_NCCL, "exchange: the send counts of rank %u add up to %llu, it holds %llu rows", r, (unsigned long long)row_sum,
+                     (unsigned long long)all[(size_t)r * RW + W + 1]);
         send[r] = all[(size_t)c->comm_rank * RW + r];
         recv[r] = all[(size_t)r * RW + c->comm_rank];
         bound |= all[(size_t)r * RW + W];

@@ -57,10 +57,19 @@ def init_comm(provider, rank: int, world: int, device=None) -> None:
     provider._check(lib.xlb_comm_init(provider._ctx, arr, rank, world))
 
 
-def exchange_by_owner(rows: np.ndarray, keys: np.ndarray, world: int) -> np.ndarray:
+class ExchangeCountError(RuntimeError):
+    """A rank's send counts do not add up to the rows it holds: nothing was exchanged."""
+
+
+def exchange_by_owner(rows: np.ndarray, keys: np.ndarray, world: int, _send_counts=None) -> np.ndarray:
     """Send every packed row to ``owner_of(key)``; returns the rows this rank receives, grouped by
     source rank.  Same steps as the library's exchange: stable partition by owner, all-gather of the
-    send counts, variable-size all-to-all."""
+    send counts, variable-size all-to-all.
+
+    Every rank's count row travels with the number of rows that rank holds; a row that does not add
+    up to it is caught by **every** rank from the gathered matrix, before any rank posts a receive
+    sized by it, so a bad count ends the exchange with the same error everywhere instead of leaving
+    the other ranks waiting in the all-to-all.  (``_send_counts`` lets a test put a wrong row in.)"""
     import torch
     import torch.distributed as dist
 
@@ -69,8 +78,13 @@ def exchange_by_owner(rows: np.ndarray, keys: np.ndarray, world: int) -> np.ndar
     order = np.argsort(own, kind="stable")
     part = rows[order]
     send = np.bincount(own, minlength=world).astype(np.int64)
-    counts = [torch.zeros(world, dtype=torch.int64) for _ in range(world)]
-    dist.all_gather(counts, torch.from_numpy(send))
+    if _send_counts is not None:
+        send = np.asarray(_send_counts, dtype=np.int64)
+    counts = [torch.zeros(world + 1, dtype=torch.int64) for _ in range(world)]
+    dist.all_gather(counts, torch.from_numpy(np.append(send, len(rows)).astype(np.int64)))
+    bad = [r for r in range(world) if int(counts[r][:world].sum()) != int(counts[r][world]) or int(counts[r][:world].min()) < 0]
+    if bad:
+        raise ExchangeCountError(f"send counts of rank(s) {bad} do not add up to their row counts")
     rank = dist.get_rank()
     recv = [int(counts[r][rank]) for r in range(world)]
     out = torch.empty(sum(recv), dtype=torch.int64)
