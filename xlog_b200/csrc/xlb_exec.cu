@@ -250,11 +250,17 @@ struct RunState {
     xlb_run_stats st{};
     std::map<std::string, DenseState> dense;  // per head relation: its tuples as a bitmap, while they fit one
     std::map<std::string, TupleSet> tset;     // per head relation too wide for a bitmap: its tuples as a hash set
+    // The new tuples a hash set hands back are unique but in no order.  They are sorted only for
+    // heads whose sorted list a rule reads (`ordered_heads`); for the others an iteration's new
+    // tuples stay a bag (`bag_novel` names the heads for which that holds right now) and the whole
+    // relation is sorted once, when the component is done.
+    std::set<std::string> ordered_heads, bag_novel;
     // Deltas of a head whose merge into the stored sorted list is put off: while the bitmap serves
     // the set difference and no rule reads the list, merging it every iteration is wasted work.
     struct Pending {
         std::vector<Keys> deltas;
         uint64_t rows = 0, bound = 0;
+        bool bags = false;  // some of the deltas are in no order
     };
     std::map<std::string, Pending> pending;
     std::map<std::string, xlb_schema> head_schema;
@@ -621,9 +627,10 @@ static void materialize_full(xlb_ctx* c, RunState& rs, const std::string& head) 
     } else {
         // the deltas are sorted and pairwise disjoint: two are merged, more are sorted together once
         Keys acc = pd.deltas[0];
-        if (pd.deltas.size() == 2) acc = ops_merge_disjoint(c, acc, pd.deltas[1]);
-        else if (pd.deltas.size() > 2) {
-            acc = ops_concat(c, pd.deltas);
+        if (pd.deltas.size() == 2 && !pd.bags) acc = ops_merge_disjoint(c, acc, pd.deltas[1]);
+        else if (pd.deltas.size() > 2 || pd.bags) {
+            if (pd.deltas.size() > 1) acc = ops_concat(c, pd.deltas);
+            else if (acc.buf.use_count() > 2) acc = ops_copy(c, acc);  // the sort below may scribble on its input: not on a stored delta
             pd.deltas.clear();
             ops_sort(c, acc);
         }
@@ -1026,6 +1033,12 @@ static void eval_variant(xlb_ctx* c, const FlatRule& fr_in, size_t start, const 
                 if (!ts.valid || ts.rows != full.n + novel.n) ops_tuple_set_build(c, ts, real_full(c, rs, fr.head), novel, cand.n);
                 fresh = ops_tuple_set_novel(c, ts, cand);
             }
+            if (!rs.ordered_heads.count(fr.head)) {
+                // unique, disjoint from everything found before: joining the bags is their union
+                novel = novel.n ? ops_concat(c, {novel, fresh}) : fresh;
+                rs.bag_novel.insert(fr.head);
+                continue;
+            }
             PhaseTimer t(c, &rs.st.ms_sort);
             ops_sort(c, fresh);
         } else {
@@ -1038,9 +1051,20 @@ static void eval_variant(xlb_ctx* c, const FlatRule& fr_in, size_t start, const 
             PhaseTimer t(c, &rs.st.ms_setops);
             fresh = ops_dedup_diff(c, cand, real_full(c, rs, fr.head));  // duplicates dropped and `full` subtracted in one merge pass
         }
+        if (rs.bag_novel.erase(fr.head) && novel.n) {  // an earlier variant left a bag: order it before the merge below
+            PhaseTimer t(c, &rs.st.ms_sort);
+            ops_sort(c, novel, /*keep_input=*/true);
+        }
         PhaseTimer t2(c, &rs.st.ms_setops);
         novel = novel.n ? ops_union(c, novel, fresh) : fresh;
     }
+}
+
+// Orders the new tuples of `head` if they are still a bag (a merge into a sorted list is next).
+static void order_novel(xlb_ctx* c, RunState& rs, const std::string& head, Keys& d) {
+    if (!rs.bag_novel.erase(head) || d.n < 2) return;
+    PhaseTimer t(c, &rs.st.ms_sort);
+    ops_sort(c, d, /*keep_input=*/true);  // (a stored delta may share the buffer)
 }
 
 // The constant filter of a single-atom rule over `atom` (`rel(c, Y)`): column and value, or false.
@@ -1168,6 +1192,7 @@ static void seed_pass(xlb_ctx* c, const std::vector<FlatRule>& rules, const std:
         if (rs.repl.on) novel[p] = repl_finish(c, rs, p, full_old);
         Keys& d = novel[p];
         if (!d.buf) d.buf = make_buf(c, 0);
+        order_novel(c, rs, p, d);
         Keys full_new;
         {
             PhaseTimer t(c, &rs.st.ms_setops);
@@ -1562,6 +1587,7 @@ static void frontier_loop(xlb_ctx* c, const FrontierPlan& fp, const std::string&
             break;
         }
         if (!more) break;
+        prof_add_bytes(c, "scan_join_mark", rows.n * 8ull);  // the launch enqueued on top of this iteration streams over the relation
         cur = next;
     }
     // back to lists: the head in order off its bitmap, and the last iteration's tuples as the delta
@@ -1674,6 +1700,8 @@ static void run_scc(xlb_ctx* c, const xlb_scc& scc, RunState& rs) {
             if (nrec >= 2 && rec.count(a.rel)) list_read.insert(a.rel);
         for (auto& k : fr.checks) list_read.insert(k.rel);
     }
+    rs.ordered_heads = list_read;
+    rs.bag_novel.clear();
     if (c->world > 1) {
         // a head relation that already holds rows is re-homed so that equal tuples meet on one rank
         for (auto& p : preds) {
@@ -1737,6 +1765,7 @@ static void run_scc(xlb_ctx* c, const xlb_scc& scc, RunState& rs) {
     }
     for (; !fix && it < c->max_iterations; ++it) {  // recursive.rs:619-937
         rs.st.iterations++;
+        rs.bag_novel.clear();
         std::map<std::string, Keys> novel;
         for (auto& fr : rules) {
             for (size_t i = 0; i < fr.atoms.size(); ++i) {  // one variant per recursive occurrence (:636-664)
@@ -1775,7 +1804,8 @@ static void run_scc(xlb_ctx* c, const xlb_scc& scc, RunState& rs) {
         for (auto& p : preds) {  // :735-858
             Keys& d = novel[p];
             if (!d.buf) d.buf = make_buf(c, 0);
-            store_put(c, "__delta_" + p, ops_rel_from_keys(c, schema[p], d, true));
+            if (c->flags & XLB_FLAG_KEEP_DELTAS) order_novel(c, rs, p, d);  // a delta that may be saved is a sorted list
+            store_put(c, "__delta_" + p, ops_rel_from_keys(c, schema[p], d, !rs.bag_novel.count(p)));
         }
         if (changed == 0) { fix = true; break; }  // :861-865
         for (auto& p : preds) {                    // :868-937
@@ -1793,9 +1823,11 @@ static void run_scc(xlb_ctx* c, const xlb_scc& scc, RunState& rs) {
                     pd.deltas.push_back(d);
                     pd.rows += d.n;
                     pd.bound |= d.bound;
+                    pd.bags |= rs.bag_novel.erase(p) > 0;
                     continue;
                 }
             }
+            order_novel(c, rs, p, d);
             materialize_full(c, rs, p);
             Keys full = ops_rel_packed(c, store_get(c, p));
             Keys merged;

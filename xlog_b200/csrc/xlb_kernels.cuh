@@ -417,10 +417,15 @@ static __global__ void pack2_k(const uint32_t* __restrict__ c0, const uint32_t* 
         o2[2 * q] = lo;
         o2[2 * q + 1] = hi;
         acc |= lo.x | lo.y | hi.x | hi.y;
-        keep(a.x, b.x);
-        keep(a.y, b.y);
-        keep(a.z, b.z);
-        keep(a.w, b.w);
+        if (fcol >= 0) {  // one test for the four rows: a match is rare
+            const uint4 f = fcol == 0 ? a : b;
+            if (f.x == fval || f.y == fval || f.z == fval || f.w == fval) {
+                keep(a.x, b.x);
+                keep(a.y, b.y);
+                keep(a.z, b.z);
+                keep(a.w, b.w);
+            }
+        }
     }
     for (uint64_t i = n4 * 4 + (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
         uint64_t k = ((uint64_t)c0[i] << 32) | c1[i];
@@ -1264,6 +1269,53 @@ __host__ __device__ __forceinline__ uint64_t unmix64(uint64_t x) {
 }
 static __global__ void mix_k(const uint64_t* __restrict__ in, uint64_t* __restrict__ out, uint64_t n, int inverse) {
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) out[i] = inverse ? unmix64(in[i]) : mix64(in[i]);
+}
+
+// mix_k that also counts the top byte of every mixed word (the digit the grouping pass sorts by),
+// so the pass needs no histogram read of its own.
+static __global__ void __launch_bounds__(BLOCK) mix_hist_k(const uint64_t* __restrict__ in, uint64_t* __restrict__ out, uint64_t n, unsigned int* __restrict__ ghist /* 256 */) {
+    __shared__ unsigned int sh[256];
+    sh[threadIdx.x] = 0;
+    __syncthreads();
+    for (uint64_t i = (uint64_t)blockIdx.x * BLOCK + threadIdx.x; i < n; i += (uint64_t)gridDim.x * BLOCK) {
+        const uint64_t w = mix64(in[i]);
+        out[i] = w;
+        atomicAdd(&sh[w >> 56], 1u);
+    }
+    __syncthreads();
+    if (sh[threadIdx.x]) atomicAdd(&ghist[threadIdx.x], sh[threadIdx.x]);
+}
+
+// Mixed copies of `n` words, grouped by their top byte (stable): mix + histogram in one pass, then
+// one scatter pass of the radix sort.  n < 2^30.
+inline Buf mix_and_group(xlb_ctx* c, const uint64_t* in, uint64_t n) {
+    radix_sort_setup(c);
+    const uint32_t ntiles = (uint32_t)((n + SORT_TILE - 1) / SORT_TILE);
+    Buf words = make_buf(c, n * 8), out = make_buf(c, n * 8);
+    Buf gh = make_buf(c, 8 * 256 * 4 * 2 + 64);  // histograms | bases | varies, laid out as the sort's
+    unsigned int* ghist = gh->as<unsigned int>();
+    unsigned int* bases = ghist + 8 * 256;
+    unsigned long long* varies = (unsigned long long*)(bases + 8 * 256);
+    CUDA_OK(cudaMemsetAsync(ghist, 0, 8 * 256 * 4, c->stream));
+    prof_begin(c, "mix", n * 16ull);
+    mix_hist_k<<<grid_for(c, n, BLOCK * 8), BLOCK, 0, c->stream>>>(in, words->as<uint64_t>(), n, ghist + 7 * 256);
+    check_launch(c, "mix");
+    prof_begin(c, "radix_bases", 0);
+    radix_bases_k<<<1, BLOCK, 0, c->stream>>>(ghist, n, bases, varies);
+    check_launch(c, "radix_bases");
+    const uint64_t status_words = (uint64_t)ntiles * 256;
+    Buf status = make_buf(c, (status_words + 8) * 4);
+    CUDA_OK(cudaMemsetAsync(status->p, 0, (status_words + 8) * 4, c->stream));
+    unsigned int* counters = status->as<unsigned int>() + status_words;
+    if (c->lb_first_tile) {
+        for (int q = 0; q < 8; ++q) ((unsigned int*)&c->h_scalar[56])[q] = c->lb_first_tile;
+        CUDA_OK(cudaMemcpyAsync(counters, &c->h_scalar[56], 8 * 4, cudaMemcpyHostToDevice, c->stream));
+    }
+    prof_begin(c, "radix_scatter", n * 16ull);
+    radix_scatter_k<false, true><<<ntiles, SORT_THREADS, SORT_SMEM, c->stream>>>(words->as<uint64_t>(), out->as<uint64_t>(), nullptr, nullptr, n, 56, bases + 7 * 256, ntiles, counters,
+                                                                               status->as<unsigned int>(), c->d_status, c->lb_spin_limit);
+    check_launch(c, "radix_scatter");
+    return out;
 }
 
 // true: the (mixed) word was not in the set and is now.  Bounded by the table size.

@@ -614,10 +614,9 @@ static Buf mixed_copy(xlb_ctx* c, const uint64_t* in, uint64_t n, bool inverse) 
 // The candidates as mixed words, grouped by the top byte (= by the 256th of the table they fall into)
 // when there are enough of them for the grouping pass to pay.
 static Buf tuple_set_words(xlb_ctx* c, const TupleSet& s, const uint64_t* keys, uint64_t n) {
-    Buf words = mixed_copy(c, keys, n, false);
     const bool table_in_l2 = s.cap * 8 <= (48ull << 20);  // then any order of insertion is an L2 access
-    if (!table_in_l2 && n >= (1ull << 20) && n < (1ull << 30)) radix_sort(c, words, nullptr, n, 0x80u, 0xFF00000000000000ull);
-    return words;
+    if (!table_in_l2 && n >= (1ull << 20) && n < (1ull << 30)) return mix_and_group(c, keys, n);
+    return mixed_copy(c, keys, n, false);
 }
 
 static void tuple_set_fill(xlb_ctx* c, TupleSet& s, const uint64_t* words, uint64_t n, bool skip_empty) {
@@ -864,7 +863,9 @@ void ops_frontier_scan(xlb_ctx* c, const Keys& rel, int rel_keysel, int bits, co
     if (rel.n == 0) return;
     if ((uintptr_t)rel.ptr() & 15) xlb_fail(XLB_ERR_INVALID, "internal: scan join over a row array that is not 16-byte aligned");
     const uint64_t domain = 1ull << bits, words = (domain + 31) / 32;
-    prof_begin(c, "scan_join_mark", rel.n * 8ull);
+    // a launch enqueued on top of a frontier of unknown size may find it empty and do nothing: its
+    // bytes are added by the caller once the frontier is known to have held keys
+    prof_begin(c, "scan_join_mark", keys_in_frontier ? 0 : rel.n * 8ull);
     scan_join_mark_k<<<grid_for(c, rel.n, SJ_TILE), BLOCK, 0, c->stream>>>(rel.ptr(), rel.n, rel_keysel, frontier, domain, /*hi_src=*/2, rel_lo, cand, words, bits, count_marked,
                                                                   c->d_status, visited, keys_in_frontier);
     check_launch(c, "scan_join_mark");
