@@ -63,3 +63,60 @@ def test_config2_full_size_is_idempotent(c2_edges):
     assert np.array_equal(first, again) and s1["derived_tuples"] == len(first)
     assert s2["iterations"] <= 2
     p.close()
+
+
+def _closure_bitsets(c0, c1, n):
+    """Transitive closure of a DAG whose edges all lead from a lower to a higher id, as one bit row
+    per vertex, filled from the highest id down: a row is the OR of its successors' rows plus the
+    successors themselves.  Shares nothing with the library or with the CPU port of the engine."""
+    words = (n + 63) // 64
+    rows = np.zeros((n, words), dtype=np.uint64)
+    order = np.argsort(c0, kind="stable")
+    dst = c1[order]
+    starts = np.searchsorted(c0[order], np.arange(n + 1))
+    for v in range(n - 1, -1, -1):
+        kids = dst[starts[v]:starts[v + 1]]
+        if len(kids):
+            row = np.bitwise_or.reduce(rows[kids], axis=0)
+            np.bitwise_or.at(row, kids >> 6, np.uint64(1) << (kids & 63).astype(np.uint64))
+            rows[v] = row
+    return rows
+
+
+@pytest.mark.parametrize("scale,want_rows", [(14, None), (16, 178_519_106)])
+def test_closure_of_the_banded_dag_at_middle_scales(scale, want_rows):
+    # the secondary workload of the benchmark at 2^14 and 2^16 vertices: the count, the per-source
+    # counts and a digest of the rows are checked against bit rows computed on the host, and the
+    # three routes of the engine (bitmap, hash set, sort) must deliver the same sorted relation
+    from xlog_b200 import digest
+    n = 1 << scale
+    c0, c1 = workloads.rmat_dag(scale, 8)
+    assert (c0 < c1).all()
+    rows = _closure_bitsets(c0, c1, n)
+    per_source = np.bitwise_count(rows).sum(axis=1, dtype=np.int64)
+    total = int(per_source.sum())
+    if want_rows is not None:
+        assert total == want_rows
+    plan = programs.transitive_closure()
+    digests = []
+    for flags in (0, A.FLAG_NO_DENSE, A.FLAG_NO_DENSE | A.FLAG_NO_TUPLE_SET):
+        p = KernelProvider(device=0, flags=flags)
+        ex = Executor(p)
+        for name, rid in plan.rel_ids.items():
+            ex.register_relation(rid, name)
+        ex.put_relation("edge", p.create_buffer_from_slices([c0, c1]))
+        stats = ex.execute_plan(plan)
+        assert stats["derived_tuples"] == total
+        digests.append(p.checksum(ex.get("reach")))
+        if flags == 0 or scale == 14:
+            a, b = p.download(ex.get("reach"))
+            assert len(a) == total
+            key = (a.astype(np.uint64) << np.uint64(32)) | b
+            assert (key[1:] > key[:-1]).all()                                   # sorted, no repeats
+            assert np.array_equal(np.bincount(a, minlength=n), per_source)      # as many rows per source
+            hit = (rows[a, b >> 6] >> (b & 63).astype(np.uint64)) & np.uint64(1)
+            assert hit.all()                                                    # and every one of them reachable
+            assert digest.result_checksum([a, b]) == digests[-1]                    # the device digest is of these rows
+            del a, b, key, hit
+        p.close()
+    assert digests[0] == digests[1] == digests[2]

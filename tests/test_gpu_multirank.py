@@ -13,7 +13,8 @@ Every program runs in each way the library evaluates a component on several rank
                switches the bitmaps off);
   shuffle      everything hash-partitioned, an all-to-all per join step (XLB_FLAG_SHUFFLE_ONLY);
                once more with the heads kept as hash sets (bitmaps off), and once with neither, so
-               that candidates are sorted and subtracted by merging.
+               that candidates are sorted and subtracted by merging; and once with a small bound
+               on join candidates, so that the ranks agree on several chunks per rule variant.
 """
 import os
 import socket
@@ -58,10 +59,14 @@ def _cases():
 
 
 def _modes():
+    """(name, context flags, XLB_REPL_SLICE_MIN or None, join_chunk_tuples)"""
     from xlog_b200 import _abi as A
-    return [("replicated", 0, None), ("sliced", 0, "64"), ("broadcast", A.FLAG_NO_DENSE, None),
-            ("shuffle", A.FLAG_SHUFFLE_ONLY, None), ("shuffle_set", A.FLAG_SHUFFLE_ONLY | A.FLAG_NO_DENSE, None),
-            ("shuffle_sorted", A.FLAG_SHUFFLE_ONLY | A.FLAG_NO_DENSE | A.FLAG_NO_TUPLE_SET, None)]
+    return [("replicated", 0, None, 0), ("sliced", 0, "64", 0), ("broadcast", A.FLAG_NO_DENSE, None, 0),
+            ("shuffle", A.FLAG_SHUFFLE_ONLY, None, 0), ("shuffle_set", A.FLAG_SHUFFLE_ONLY | A.FLAG_NO_DENSE, None, 0),
+            ("shuffle_sorted", A.FLAG_SHUFFLE_ONLY | A.FLAG_NO_DENSE | A.FLAG_NO_TUPLE_SET, None, 0),
+            # a small bound on join candidates: from the second iteration on the ranks agree on several
+            # chunks per rule variant, and every rank runs that many rounds of exchanges
+            ("shuffle_chunked", A.FLAG_SHUFFLE_ONLY | A.FLAG_NO_DENSE, None, 1500)]
 
 
 def _rank_main(rank, world, port, out_dir):
@@ -81,14 +86,14 @@ def _rank_main(rank, world, port, out_dir):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         results = {}
-        for mode, flags, slice_min in _modes():
+        for mode, flags, slice_min, chunk in _modes():
           if slice_min is None:
               os.environ.pop("XLB_REPL_SLICE_MIN", None)
           else:
               os.environ["XLB_REPL_SLICE_MIN"] = slice_min
           for case, plan, inputs, out in _cases():
             name = f"{mode}/{case}"
-            prov = KernelProvider(device=rank, flags=flags)
+            prov = KernelProvider(device=rank, flags=flags, join_chunk_tuples=chunk)
             D.init_comm(prov, rank, world)
             ex = Executor(prov)
             for rel, rid in plan.rel_ids.items():
@@ -122,7 +127,7 @@ def test_sharded_fixpoints_match_the_oracle(oracle, tmp_path):
     results = np.load(tmp_path / "results.npy", allow_pickle=True).item()
     for case, plan, inputs, out in _cases():
       want, ex = oracle.run_program(plan, inputs, [out])
-      for mode, _, _ in _modes():
+      for mode, _, _, _ in _modes():
         name = f"{mode}/{case}"
         if name not in results:
             continue

@@ -231,3 +231,40 @@ def test_stratified_negation_and_union_body(oracle):
         assert np.array_equal(got[name][0], want[name][0])
     assert got["un"][0].tolist() == sorted(unreach)
     p.close()
+
+
+def test_the_tuple_whose_mixed_word_is_the_empty_mark(oracle):
+    """The hash set of a wide head stores mix64(tuple) and marks empty slots with all ones; exactly one
+    tuple mixes to that word and is kept in a flag of its own.  It must be derived once, however
+    often it is a candidate, and must not be lost."""
+    from xlog_b200 import _abi as A
+    from xlog_b200.dist import mix64
+    M = (1 << 64) - 1
+
+    def unmix(x):
+        x ^= x >> 33
+        x = (x * pow(0xC4CEB9FE1A85EC53, -1, 1 << 64)) & M
+        x ^= x >> 33
+        x = (x * pow(0xFF51AFD7ED558CCD, -1, 1 << 64)) & M
+        x ^= x >> 33
+        return x
+
+    k0 = unmix(M)
+    assert int(mix64(np.array([k0], np.uint64))[0]) == M
+    a, b = k0 >> 32, k0 & 0xFFFFFFFF
+    # the edge (a, b) three times, a way around it (a -> 7 -> b is not an edge pair that gives (a, b) again, but
+    # (9, a) and (a, b) give (9, b)), and unrelated edges; ids this large never fit a bitmap
+    c0 = np.array([a, a, a, 9, b, 5, 9], np.uint32)
+    c1 = np.array([b, b, b, a, 11, 6, 11], np.uint32)
+    plan = programs.transitive_closure()
+    want, ex = oracle.run_program(plan, {"edge": [c0, c1]}, ["reach"])
+    for flags in (0, A.FLAG_NO_TUPLE_SET):
+        p = KernelProvider(device=0, flags=flags)
+        p.profile_enable("*")
+        got, stats = run_program(p, plan, {"edge": [c0, c1]}, ["reach"])
+        used_set = "hset_insert" in p.profile_read()
+        assert used_set == (flags == 0)
+        assert all(np.array_equal(g, w) for g, w in zip(got["reach"], want["reach"]))
+        assert (a, b) in set(zip(got["reach"][0].tolist(), got["reach"][1].tolist()))
+        assert stats["candidate_tuples"] == ex.candidates
+        p.close()
