@@ -192,7 +192,9 @@ void comm_allgather_words(xlb_ctx* c, const uint64_t* mine, uint32_t k, uint64_t
     unsigned long long* send = cm->h_stage + (size_t)W * STAGE_ROW;
     for (uint32_t i = 0; i < k; ++i) send[i] = mine[i];
     CUDA_OK(cudaMemcpyAsync(dev + (size_t)c->comm_rank * k, send, (size_t)k * 8, cudaMemcpyHostToDevice, c->stream));
+    const double tr0 = c->trace_on ? trace_now() : 0;
     NCCL_OK(api().AllGather(dev + (size_t)c->comm_rank * k, dev, k, ncclUint64, cm->comm, c->stream));
+    trace_note(c, "ncclAllGather (enqueue)", tr0);
     CUDA_OK(cudaMemcpyAsync(cm->h_stage, dev, (size_t)W * k * 8, cudaMemcpyDeviceToHost, c->stream));
     comm_wait(c);
     for (size_t i = 0; i < (size_t)W * k; ++i) all[i] = cm->h_stage[i];
@@ -210,7 +212,9 @@ uint64_t comm_allreduce_sum(xlb_ctx* c, uint64_t v) {
 Buf comm_gather_bitmaps(xlb_ctx* c, const unsigned int* bitmap, uint64_t words) {
     Comm* cm = live_comm(c);
     Buf gathered = make_buf(c, (uint64_t)c->comm_world * words * 4);
+    const double tr0 = c->trace_on ? trace_now() : 0;
     NCCL_OK(api().AllGather(bitmap, gathered->p, words, ncclUint32, cm->comm, c->stream));
+    trace_note(c, "ncclAllGather (enqueue)", tr0);
     return gathered;
 }
 
@@ -272,7 +276,9 @@ Keys comm_repartition(xlb_ctx* c, const Keys& in, int keysel, bool sorted_unique
     send_tail[0] = in.n ? in.bound : 0;
     send_tail[1] = in.n;
     CUDA_OK(cudaMemcpyAsync(mine + W, send_tail, 16, cudaMemcpyHostToDevice, c->stream));
+    const double tr0 = c->trace_on ? trace_now() : 0;
     NCCL_OK(api().AllGather(mine, dev, RW, ncclUint64, cm->comm, c->stream));
+    trace_note(c, "ncclAllGather (enqueue)", tr0);
     CUDA_OK(cudaMemcpyAsync(cm->h_stage, dev, (size_t)W * RW * 8, cudaMemcpyDeviceToHost, c->stream));
     comm_wait(c);
     const unsigned long long* all = cm->h_stage;

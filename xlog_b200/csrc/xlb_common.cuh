@@ -352,6 +352,8 @@ struct xlb_ctx {
     std::string last_error;
     // pinned scratch for scalar read-backs
     unsigned long long* h_scalar = nullptr;  // 64 words
+    unsigned long long* h_scalar_dev = nullptr;  // the same words as the device sees them (mapped): a kernel can leave counts there
+    unsigned long long publish_seq = 0;          // number of the last set of counts a kernel was asked to leave there
     DevStatus* d_status = nullptr;
     int sm_count = 148;
     // executor state
@@ -379,10 +381,24 @@ struct xlb_ctx {
     std::string prof_filter;  // "" = off, "*" = every kernel, else kernel names separated by commas
     ProfEntry* prof_open = nullptr;
     cudaEvent_t prof_e0 = nullptr;
+    // host timeline of one plan execution (XLB_TRACE_HOST=1): every launch and every wait with its
+    // wall-clock interval, printed to stderr when the plan is done
+    struct TraceNote {
+        double t0, t1;
+        const char* what;
+    };
+    bool trace_on = false;
+    std::vector<TraceNote> trace;
 };
+
+inline double trace_now() { return std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now().time_since_epoch()).count(); }
+inline void trace_note(xlb_ctx* c, const char* what, double t0) {
+    if (c->trace_on) c->trace.push_back({t0, trace_now(), what});
+}
 
 // Bracket one launch with CUDA events on the launching stream when its kernel is profiled.
 inline void prof_begin(xlb_ctx* c, const char* name, uint64_t bytes) {
+    if (c->trace_on) trace_note(c, name, trace_now());
     if (c->prof_filter.empty()) return;
     if (c->prof_filter != "*") {  // a kernel name, or several separated by commas
         const std::string& f = c->prof_filter;
@@ -456,8 +472,10 @@ inline void check_launch(xlb_ctx* c, const char* what) {
 
 // Read `n` 64-bit words from device memory (one stream synchronisation).
 inline void stream_wait(xlb_ctx* c) {
+    const double tr0 = c->trace_on ? trace_now() : 0;
     if (c->wait_hook) {  // several ranks: never block for good on a stream a late peer may be holding up
         c->wait_hook(c);
+        trace_note(c, "wait (communicator watched)", tr0);
         return;
     }
     auto t0 = std::chrono::steady_clock::now();
@@ -474,6 +492,7 @@ inline void stream_wait(xlb_ctx* c) {
     CUDA_OK(cudaStreamSynchronize(c->stream));
     c->ms_sync_wait += std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
     c->syncs++;
+    trace_note(c, "wait", tr0);
 }
 
 inline void read_words(xlb_ctx* c, const void* dptr, int n, unsigned long long* out) {

@@ -11,6 +11,7 @@
 //   - full relations stay sorted and unique, so the per-iteration difference and union are
 //     merges, never a re-sort of the full relation (relational.rs:976-999 re-sorts).
 #include <algorithm>
+#include <atomic>
 #include <cstring>
 #include <deque>
 #include <functional>
@@ -267,6 +268,7 @@ struct RunState {
     std::map<std::pair<std::string, int>, int> scans;  // scan joins run so far per (relation, key column)
     // rows of a stored relation with column `col` equal to `value`, collected while the relation was packed
     std::map<std::tuple<std::string, int, uint64_t>, Keys> prefiltered;
+    std::set<std::string> keep_cols;  // stored relations a frontier loop will stream over as columns: not packed ahead of it
     // Several ranks.  Relations whose rows every rank holds in full while the running component is
     // evaluated: full copies of small stored relations (kept in the store under an alias name) and,
     // in replicated mode, the component's own heads.  A join against one of them needs no exchange.
@@ -1084,20 +1086,35 @@ static bool single_atom_filter(const FlatRule& fr, int* col, uint64_t* value, si
     return false;
 }
 
-// Pack relation `name` (the first use of a relation given as columns).  When a single-atom rule
-// filters it by a constant, the matching rows are collected in the same pass over the columns.
-static Keys packed_for_rules(xlb_ctx* c, const std::string& name, const std::vector<FlatRule>& rules, RunState& rs) {
+// Relation `name` before its first use by a rule (it may have come as columns).  When a
+// single-atom rule filters it by a constant, the matching rows are collected in the pass over the
+// columns that packs it.  A relation in rs.keep_cols is not packed at all: that pass only reads it
+// (bound of its values, filtered rows), and the returned keys carry no rows unless need_rows.
+static Keys packed_for_rules(xlb_ctx* c, const std::string& name, const std::vector<FlatRule>& rules, RunState& rs, bool need_rows = true) {
     xlb_rel* r = store_get(c, name);
-    if (!r->packed)
+    const bool keep = rs.keep_cols.count(name) != 0;
+    if (!r->packed && (!keep || r->or_bound == ~0ull)) {
+        bool done = false;
         for (auto& fr : rules) {
             int col;
             uint64_t value;
             size_t which;
             if (fr.atoms.size() != 1 || fr.atoms[0].rel != name || !single_atom_filter(fr, &col, &value, &which)) continue;
             Keys rows;
-            if (ops_rel_packed_filtered(c, r, col, (uint32_t)value, &rows)) rs.prefiltered[std::make_tuple(name, col, value)] = rows;
+            if (keep ? ops_rel_bound_filtered(c, r, col, (uint32_t)value, &rows) : ops_rel_packed_filtered(c, r, col, (uint32_t)value, &rows)) {
+                rs.prefiltered[std::make_tuple(name, col, value)] = rows;
+                done = true;
+            }
             break;
         }
+        if (keep && !done) ops_rel_bound_filtered(c, r, -1, 0, nullptr);
+    }
+    if (keep && !need_rows && !r->packed && r->or_bound != ~0ull) {
+        Keys k;
+        k.n = r->rows;
+        k.bound = r->or_bound;
+        return k;
+    }
     return ops_rel_packed(c, r);
 }
 
@@ -1170,7 +1187,7 @@ static void seed_pass(xlb_ctx* c, const std::vector<FlatRule>& rules, const std:
         }
         if (any_empty) continue;
         size_t start = pick_seed_start(c, fr);
-        Keys rows = packed_for_rules(c, fr.atoms[start].rel, rules, rs);
+        Keys rows = packed_for_rules(c, fr.atoms[start].rel, rules, rs, /*need_rows=*/false);
         FlatRule use = fr;
         {
             int col;
@@ -1178,12 +1195,13 @@ static void seed_pass(xlb_ctx* c, const std::vector<FlatRule>& rules, const std:
             size_t which;
             if (single_atom_filter(fr, &col, &value, &which)) {
                 auto hit = rs.prefiltered.find(std::make_tuple(fr.atoms[0].rel, col, value));
-                if (hit != rs.prefiltered.end()) {  // collected while the relation was packed
+                if (hit != rs.prefiltered.end()) {  // collected in the first pass over the relation
                     rows = hit->second;
                     use.filters[which].applied = true;
                 }
             }
         }
+        if (!rows.buf) rows = ops_rel_packed(c, store_get(c, fr.atoms[start].rel));
         Keys full_old = canonical_keys(c, store_get(c, fr.head), rs);
         eval_variant(c, use, start, rows, true, rec.count(fr.atoms[start].rel) ? home[fr.atoms[start].rel] : -1, full_old, home[fr.head], novel[fr.head], rs);
     }
@@ -1270,7 +1288,7 @@ static void setup_ranks(xlb_ctx* c, const xlb_scc& scc, std::vector<FlatRule>& r
         xlb_rel* r = store_get(c, name);
         mine.push_back(r ? r->rows : 0);
         if (!r || !r->rows) return;
-        Keys k = packed_for_rules(c, name, rules, rs);
+        Keys k = packed_for_rules(c, name, rules, rs, /*need_rows=*/false);
         if (k.bound == ~0ull) unknown = true;
         else values |= (k.bound >> 32) | (k.bound & 0xFFFFFFFFull);
     };
@@ -1427,10 +1445,11 @@ struct FrontierPlan {
     int rel_lo = 0;  // what the head's column takes from a row of it: 0 the key, 1 the other column
 };
 
-static bool frontier_shape(xlb_ctx* c, const std::vector<FlatRule>& rules, const std::vector<std::string>& preds, const std::set<std::string>& rec,
-                           const std::map<std::string, xlb_schema>& schema, RunState& rs, FrontierPlan* fp) {
-    if (c->world != 1 || (c->flags & (XLB_FLAG_NO_DENSE | XLB_FLAG_KEEP_DELTAS)) || preds.size() != 1) return false;
-    if (schema.at(preds[0]).arity != 1 || getenv("XLB_NO_FRONTIER_LOOP")) return false;
+// The static part: one recursive rule, `head(V) :- head(K), rel(..)` with rel a stored two-column
+// relation joined on K and V one of its columns, and a head of one column.
+static bool frontier_rule_shape(const std::vector<FlatRule>& rules, const std::vector<std::string>& preds, const std::set<std::string>& rec,
+                                const std::map<std::string, xlb_schema>& schema, FrontierPlan* fp) {
+    if (preds.size() != 1 || schema.at(preds[0]).arity != 1) return false;
     const FlatRule* only = nullptr;
     for (auto& fr : rules) {
         int nrec = 0;
@@ -1448,7 +1467,6 @@ static bool frontier_shape(xlb_ctx* c, const std::vector<FlatRule>& rules, const
     if (kc < 0) return false;
     const int hv = only->head_vars[0];
     if (hv != ea.var[0] && hv != ea.var[1]) return false;
-    if (index_ready(c, ea.rel, kc, rs)) return false;  // an index exists: probing it beats streaming
     fp->fr = only;
     fp->ei = ei;
     fp->kc = kc;
@@ -1456,20 +1474,34 @@ static bool frontier_shape(xlb_ctx* c, const std::vector<FlatRule>& rules, const
     return true;
 }
 
-// Wait for one event of the context's stream (work enqueued behind it keeps running).
-static void wait_event(xlb_ctx* c, cudaEvent_t ev) {
+static bool frontier_flags_ok(xlb_ctx* c) { return !(c->flags & (XLB_FLAG_NO_DENSE | XLB_FLAG_KEEP_DELTAS)) && !getenv("XLB_NO_FRONTIER_LOOP"); }
+
+static bool frontier_shape(xlb_ctx* c, const std::vector<FlatRule>& rules, const std::vector<std::string>& preds, const std::set<std::string>& rec,
+                           const std::map<std::string, xlb_schema>& schema, RunState& rs, FrontierPlan* fp) {
+    if (c->world != 1 || !frontier_flags_ok(c)) return false;
+    if (!frontier_rule_shape(rules, preds, rec, schema, fp)) return false;
+    if (index_ready(c, fp->fr->atoms[fp->ei].rel, fp->kc, rs)) return false;  // an index exists: probing it beats streaming
+    return true;
+}
+
+// Wait until a kernel has left the number `seq` in a word of pinned memory (work enqueued behind
+// that kernel keeps running: no event, no copy).  After 20 ms the full wait on the stream takes
+// over, which knows how to give up on a late peer.
+static void wait_published(xlb_ctx* c, const unsigned long long* word, unsigned long long seq) {
+    const double tr0 = c->trace_on ? trace_now() : 0;
     auto t0 = std::chrono::steady_clock::now();
-    for (;;) {
-        cudaError_t q = cudaEventQuery(ev);
-        if (q == cudaSuccess) break;
-        if (q != cudaErrorNotReady) CUDA_OK(q);
-        if (std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count() > 20.0) {
-            stream_wait(c);  // something is slow (a late peer?): the full wait knows how to give up
+    const volatile unsigned long long* w = word;
+    for (uint64_t polls = 0; *w != seq; ++polls) {
+        if ((polls & 255) == 255 && std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count() > 20.0) {
+            stream_wait(c);  // everything enqueued has run when this returns
+            if (*w != seq) xlb_fail(XLB_ERR_CUDA, "internal: a frontier step finished without leaving its counts");
             return;
         }
     }
+    std::atomic_thread_fence(std::memory_order_acquire);
     c->ms_sync_wait += std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
     c->syncs++;
+    trace_note(c, "wait (counts in pinned memory)", tr0);
 }
 
 // Runs iterations from the state the seeding pass left (the head's list and "__delta_<head>" in the
@@ -1485,7 +1517,18 @@ static void frontier_loop(xlb_ctx* c, const FrontierPlan& fp, const std::string&
     xlb_rel* er = store_get(c, ea.rel);
     xlb_rel* d0 = store_get(c, "__delta_" + p);
     if (!er || !d0 || d0->rows == 0) return;
-    Keys rows = ops_rel_packed(c, er);
+    // a relation that came as two columns and has not been packed is streamed over as it is: one
+    // pass for the bound of its values instead of a pass that also writes the packed copy
+    bool from_cols = !er->packed && er->schema.arity == 2 && rel_packable(er->schema) && er->cols[0] && er->cols[1];
+    if (from_cols && er->or_bound == ~0ull) ops_rel_bound_filtered(c, er, -1, 0, nullptr);
+    Keys rows;
+    if (from_cols && er->or_bound != ~0ull) {
+        rows.n = er->rows;
+        rows.bound = er->or_bound;
+    } else {
+        from_cols = false;
+        rows = ops_rel_packed(c, er);
+    }
     Keys delta = ops_rel_packed(c, d0);
     Keys full = full_view(c, rs, p);
     if (rows.bound == ~0ull || delta.bound == ~0ull || (full.n && full.bound == ~0ull)) return;
@@ -1507,41 +1550,90 @@ static void frontier_loop(xlb_ctx* c, const FrontierPlan& fp, const std::string&
     lb = ds->lo_bits;
     const uint64_t domain = 1ull << lb, words = ds->words;
     const int rel_keysel = fp.kc == 0 ? SRC_HI : SRC_LO;
+    uint64_t row_lo = 0, row_hi = rows.n;
     if (rs.repl.on && !rs.repl.sliced.count(ea.rel)) {
-        // every rank holds all rows of this relation: each streams over its share of them
-        const uint64_t n = rows.n, lo = n * c->comm_rank / c->comm_world, hi = n * (c->comm_rank + 1) / c->comm_world;
-        rows = ops_slice(c, rows, lo, hi);
+        // every rank holds all rows of this relation: each streams over its share of them (shares
+        // start at multiples of four rows, so that 16-byte loads stay aligned)
+        const uint64_t n = rows.n;
+        row_lo = (n * c->comm_rank / c->comm_world) & ~3ull;
+        row_hi = c->comm_rank + 1 == c->comm_world ? n : (n * (c->comm_rank + 1) / c->comm_world) & ~3ull;
     }
-    if ((uintptr_t)rows.ptr() & 15) return;
+    ScanRows src;  // what the next scan streams over
+    src.n_max = row_hi - row_lo;
+    if (from_cols) {
+        src.kcol = er->cols[fp.kc]->as<uint32_t>() + row_lo;
+        src.ocol = er->cols[1 - fp.kc]->as<uint32_t>() + row_lo;
+        if (((uintptr_t)src.kcol | (uintptr_t)src.ocol) & 15) return;
+    } else {
+        src.packed = rows.ptr() + row_lo;
+        if ((uintptr_t)src.packed & 15) return;
+    }
+    const uint64_t share = src.n_max;
 
-    // frontier bitmaps (two, used in turn), this rank's candidate bitmap, and per iteration two
-    // counters: new tuples, and rows of the relation with a key in the frontier
+    // frontier bitmaps (two, used in turn), this rank's marks (the head plus the candidates of the
+    // iteration under way: it starts as a copy of the head and every step leaves it so), and per launch four
+    // counters: new tuples, rows of the relation with a key in the frontier, rows written to the
+    // list of rows that can still match, (unused)
     const uint64_t bitmap_bytes = std::max<uint64_t>(words * 4, 16);
     const int max_launches = scan_limit + 1;
     Buf frontier[2] = {ops_keyset(c, delta, SRC_LO, lb), make_buf(c, bitmap_bytes)};
     Buf cand = make_buf(c, bitmap_bytes);
-    Buf counts = make_buf(c, (uint64_t)max_launches * 16);
-    CUDA_OK(cudaMemsetAsync(cand->p, 0, bitmap_bytes, c->stream));
-    CUDA_OK(cudaMemsetAsync(counts->p, 0, (uint64_t)max_launches * 16, c->stream));
+    Buf counts = make_buf(c, (uint64_t)max_launches * 32);
     unsigned int* visited = ds->visited->as<unsigned int>();
-    struct Events {  // every event made here is destroyed, however the loop ends
-        std::vector<cudaEvent_t> all;
-        ~Events() {
-            for (auto e : all) cudaEventDestroy(e);
-        }
-    } events;
+    CUDA_OK(cudaMemcpyAsync(cand->p, visited, words * 4, cudaMemcpyDeviceToDevice, c->stream));
+    CUDA_OK(cudaMemsetAsync(counts->p, 0, (uint64_t)max_launches * 32, c->stream));
+    // whether a row whose key the head holds must have it in the frontier: true of the relation
+    // when the head holds nothing but the frontier, and of a list written by the scan just before
+    bool visited_means_frontier = full.n == delta.n;
+    Buf ticket = make_buf(c, 16);  // the step kernel's count of finished blocks
+    CUDA_OK(cudaMemsetAsync(ticket->p, 0, 16, c->stream));
     struct Flight {
-        cudaEvent_t ev = nullptr;
+        unsigned long long seq = 0;  // the number the step kernel writes beside the counts it leaves in pinned memory
         unsigned slot = 0;
-        unsigned long long* count = nullptr;  // device: [0] new tuples, [1] rows whose key was in the frontier
+        int index = 0;
+        unsigned long long* count = nullptr;  // device: [0] new tuples, [1] rows whose key was in the frontier, [2] rows kept for later scans
     };
+    // A key enters the frontier once, so a row whose key the head holds is of no use to a later
+    // scan: a scan that expects to lose a good part of its rows writes the others to a list, and
+    // the next scan streams over that list.  The lists live in two buffers used in turn; their
+    // lengths stay on the device (the next scan is enqueued before the host has read them).
+    struct Launch {
+        int producer;   // the launch that wrote the list this one streamed over; -1: the relation itself
+        bool compacts;  // wrote a list of its own
+        uint64_t kept;  // rows in that list, once read
+    };
+    std::vector<Launch> log;
+    Buf live[2];
+    int src_buf = -1, producer = -1;
     int launched = 0, cur_frontier = 0;
-    auto launch = [&](const unsigned long long* keys_in_frontier) {
+    auto launch = [&](const unsigned long long* keys_in_frontier, bool compact) {
         Flight f;
-        f.count = counts->as<unsigned long long>() + 2 * launched;
+        f.index = launched;
+        f.count = counts->as<unsigned long long>() + 4 * launched;
+        f.slot = 20 + 4 * (launched & 3);  // (at most two launches are in flight)
+        f.seq = ++c->publish_seq;
+        uint64_t* out = nullptr;
+        int dst = -1;
+        if (compact) {
+            dst = src_buf == 0 ? 1 : 0;
+            if (!live[dst] || live[dst]->bytes < src.n_max * 8) live[dst] = make_buf(c, src.n_max * 8);
+            out = live[dst]->as<uint64_t>();
+        }
         {
             PhaseTimer t(c, &rs.st.ms_join);
-            ops_frontier_scan(c, rows, rel_keysel, lb, frontier[cur_frontier]->as<unsigned int>(), fp.rel_lo, cand->as<unsigned int>(), visited, f.count + 1, keys_in_frontier);
+            ops_frontier_scan(c, src, rel_keysel, lb, visited_means_frontier ? nullptr : frontier[cur_frontier]->as<unsigned int>(), fp.rel_lo, cand->as<unsigned int>(), visited,
+                              f.count + 1, keys_in_frontier, out, f.count + 2);
+        }
+        log.push_back({producer, compact, 0});
+        visited_means_frontier = compact;  // the list written now holds no row whose key the head held
+        if (compact) {
+            ScanRows next;
+            next.packed = out;
+            next.n_max = src.n_max;
+            next.n_dev = f.count + 2;
+            src = next;
+            src_buf = dst;
+            producer = launched;
         }
         Buf gathered;
         if (rs.repl.on) {
@@ -1552,30 +1644,36 @@ static void frontier_loop(xlb_ctx* c, const FrontierPlan& fp, const std::string&
         {
             PhaseTimer t(c, &rs.st.ms_setops);
             ops_frontier_step(c, gathered ? gathered->as<unsigned int>() : cand->as<unsigned int>(), gathered ? rs.repl.world : 1, words, cand->as<unsigned int>(), visited,
-                              frontier[1 - cur_frontier]->as<unsigned int>(), f.count);
+                              frontier[1 - cur_frontier]->as<unsigned int>(), f.count, ticket->as<unsigned int>(), c->h_scalar_dev + f.slot, f.seq);
         }
         cur_frontier = 1 - cur_frontier;
-        f.slot = 20 + 2 * (launched & 3);
-        CUDA_OK(cudaMemcpyAsync(&c->h_scalar[f.slot], f.count, 16, cudaMemcpyDeviceToHost, c->stream));
-        CUDA_OK(cudaEventCreateWithFlags(&f.ev, cudaEventDisableTiming));
-        events.all.push_back(f.ev);
-        CUDA_OK(cudaEventRecord(f.ev, c->stream));
         ++launched;
         ++scans;
         return f;
     };
+    // whether launch number k should write a list: the first two do (nothing is known yet); later
+    // ones if the last scan the host has the counts of lost at least an eighth of its rows
+    uint64_t seen_rows = 0, seen_matched = 0;
+    auto wants_list = [&](int k) { return k < 2 || seen_matched * 8 >= seen_rows; };
     uint64_t last_new = delta.n;
     int last_frontier = 0;  // which bitmap holds the tuples of the last finished iteration
-    Flight cur = launch(nullptr);
+    Flight cur = launch(nullptr, wants_list(0));
     for (;;) {
         // `cur` is the iteration in flight whose counts the host has not seen: the next one is
         // enqueued on top of it (it does nothing if cur finds nothing new)
         const bool more = scans < scan_limit && launched < max_launches && it + 2 <= c->max_iterations;
         const int cur_out = cur_frontier;
         Flight next;
-        if (more) next = launch(cur.count);
-        wait_event(c, cur.ev);
-        const uint64_t tot = c->h_scalar[cur.slot], marked = c->h_scalar[cur.slot + 1];
+        if (more) next = launch(cur.count, wants_list(launched));
+        wait_published(c, &c->h_scalar[cur.slot + 3], cur.seq);
+        const uint64_t tot = c->h_scalar[cur.slot], marked = c->h_scalar[cur.slot + 1], kept = c->h_scalar[cur.slot + 2];
+        Launch& done = log[cur.index];
+        done.kept = kept;
+        const uint64_t streamed = done.producer < 0 ? share : log[done.producer].kept;
+        seen_rows = streamed;
+        seen_matched = marked;
+        if (done.compacts && producer == cur.index) src.n_max = std::min(src.n_max, std::max<uint64_t>(kept, 1));  // the next launches size their grids by it
+        prof_add_bytes(c, "scan_join_mark", (streamed + (done.compacts ? kept : 0)) * 8ull);
         ++it;
         rs.st.iterations++;
         rs.st.candidate_tuples += marked;
@@ -1587,7 +1685,6 @@ static void frontier_loop(xlb_ctx* c, const FrontierPlan& fp, const std::string&
             break;
         }
         if (!more) break;
-        prof_add_bytes(c, "scan_join_mark", rows.n * 8ull);  // the launch enqueued on top of this iteration streams over the relation
         cur = next;
     }
     // back to lists: the head in order off its bitmap, and the last iteration's tuples as the delta
@@ -1680,6 +1777,24 @@ static void run_scc(xlb_ctx* c, const xlb_scc& scc, RunState& rs) {
             rs.replicated.clear();
         }
     } cleanup{c, rs, preds};
+    // The relation a frontier loop would stream over stays as columns while its other uses are
+    // single-atom rules (a constant filter reads the columns too); anything else packs it on demand.
+    rs.keep_cols.clear();
+    if (scc.is_recursive && frontier_flags_ok(c)) {
+        FrontierPlan probe;
+        if (frontier_rule_shape(rules, preds, rec, schema, &probe)) {
+            const std::string& rel = probe.fr->atoms[probe.ei].rel;
+            bool only_scans = true;
+            for (auto& fr : rules) {
+                if (&fr == probe.fr) continue;
+                for (auto& a : fr.atoms)
+                    if (a.rel == rel && fr.atoms.size() != 1) only_scans = false;
+                for (auto& k : fr.checks)
+                    if (k.rel == rel) only_scans = false;
+            }
+            if (only_scans) rs.keep_cols.insert(rel);
+        }
+    }
     PlanAsOneRank one_rank;
     setup_ranks(c, scc, rules, preds, rec, schema, rs);
     std::map<std::string, int> home;
@@ -2061,6 +2176,9 @@ extern "C" xlb_status xlb_execute_plan(xlb_ctx* c, const xlb_plan* plan, xlb_run
     uint64_t launches0 = c->launches, syncs0 = c->syncs;
     double wait0 = c->ms_sync_wait, alloc0 = c->ms_alloc;
     auto host_t0 = std::chrono::steady_clock::now();
+    c->trace_on = getenv("XLB_TRACE_HOST") != nullptr;
+    c->trace.clear();
+    const double trace_t0 = trace_now();
     c->peak = c->allocated;
     xlb_status result = XLB_OK;
     try {
@@ -2111,6 +2229,11 @@ extern "C" xlb_status xlb_execute_plan(xlb_ctx* c, const xlb_plan* plan, xlb_run
     rs.st.ms_host_alloc = c->ms_alloc - alloc0;
     rs.st.ms_host_total = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - host_t0).count();
     rs.st.peak_bytes = c->peak;
+    if (c->trace_on) {
+        fprintf(stderr, "[xlb %u] plan: %.1f us on the host, %.1f us on the device\n", c->comm_rank, rs.st.ms_host_total * 1e3, rs.st.ms_total * 1e3);
+        for (auto& n : c->trace) fprintf(stderr, "[xlb %u] %9.1f %8.1f  %s\n", c->comm_rank, n.t0 - trace_t0, n.t1 - n.t0, n.what);
+        c->trace_on = false;
+    }
     if (stats && result == XLB_OK) *stats = rs.st;
     return result;
 }

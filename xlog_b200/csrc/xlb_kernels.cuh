@@ -394,6 +394,7 @@ uint64_t select_unordered(xlb_ctx* c, Pred pred, Emit emit, uint64_t n, const ch
 // -------------------------------------------------------------------------------- pack/unpack
 // pack kernels also reduce the OR of the packed rows into *or_out (may be null)
 // (`vec`: all three arrays are 16-byte aligned, so whole groups of four rows move as 16-byte words)
+// Without `out` nothing is packed: the sweep only reduces the OR (and filters).
 // With `fcol` >= 0 the rows whose column fcol equals fval are also appended, packed, to `fout` in
 // no particular order (*fcount += their number): a rule that reads `rel(c, Y)` from a relation that
 // is packed for the first time gets its rows without a second pass over the relation.
@@ -414,8 +415,10 @@ static __global__ void pack2_k(const uint32_t* __restrict__ c0, const uint32_t* 
         lo.y = ((uint64_t)a.y << 32) | b.y;
         hi.x = ((uint64_t)a.z << 32) | b.z;
         hi.y = ((uint64_t)a.w << 32) | b.w;
-        o2[2 * q] = lo;
-        o2[2 * q + 1] = hi;
+        if (out) {
+            o2[2 * q] = lo;
+            o2[2 * q + 1] = hi;
+        }
         acc |= lo.x | lo.y | hi.x | hi.y;
         if (fcol >= 0) {  // one test for the four rows: a match is rare
             const uint4 f = fcol == 0 ? a : b;
@@ -429,13 +432,61 @@ static __global__ void pack2_k(const uint32_t* __restrict__ c0, const uint32_t* 
     }
     for (uint64_t i = n4 * 4 + (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
         uint64_t k = ((uint64_t)c0[i] << 32) | c1[i];
-        out[i] = k;
+        if (out) out[i] = k;
         acc |= k;
         keep(c0[i], c1[i]);
     }
 #pragma unroll
     for (int d = 16; d; d >>= 1) acc |= __shfl_xor_sync(FULL, acc, d);
     if (or_out && lane_id() == 0 && acc) atomicOr(or_out, (unsigned long long)acc);
+}
+// The read-only sweep of a two-column relation that is not packed: OR of the packed rows into
+// *or_out, and with fcol >= 0 the rows whose column fcol equals fval appended, packed, to `fout`
+// (*fcount += their number; a match is rare).  Sixteen rows per thread and step: eight 16-byte
+// loads in flight (the columns are 16-byte aligned; the host checks).
+static __global__ void __launch_bounds__(BLOCK) cols_or_filter_k(const uint32_t* __restrict__ c0, const uint32_t* __restrict__ c1, uint64_t n, unsigned long long* or_out, int fcol,
+                                                            uint32_t fval, uint64_t* __restrict__ fout, unsigned long long* fcount) {
+    uint32_t acc0 = 0, acc1 = 0;
+    auto keep = [&](uint32_t a, uint32_t b) {
+        if ((fcol == 0 ? a : b) == fval) fout[atomicAdd(fcount, 1ull)] = ((uint64_t)a << 32) | b;
+    };
+    constexpr int V = 4;  // 16-byte words per column, thread and step
+    const uint64_t per_step = (uint64_t)BLOCK * V * 4;
+    const uint64_t steps = n / per_step;
+    const uint4* a4 = reinterpret_cast<const uint4*>(c0);
+    const uint4* b4 = reinterpret_cast<const uint4*>(c1);
+    for (uint64_t s = blockIdx.x; s < steps; s += gridDim.x) {
+        uint4 a[V], b[V];
+#pragma unroll
+        for (int q = 0; q < V; ++q) {
+            a[q] = a4[s * (BLOCK * V) + q * BLOCK + threadIdx.x];
+            b[q] = b4[s * (BLOCK * V) + q * BLOCK + threadIdx.x];
+        }
+#pragma unroll
+        for (int q = 0; q < V; ++q) {
+            acc0 |= a[q].x | a[q].y | a[q].z | a[q].w;
+            acc1 |= b[q].x | b[q].y | b[q].z | b[q].w;
+            if (fcol >= 0) {
+                const uint4 f = fcol == 0 ? a[q] : b[q];
+                if (f.x == fval || f.y == fval || f.z == fval || f.w == fval) {
+                    keep(a[q].x, b[q].x);
+                    keep(a[q].y, b[q].y);
+                    keep(a[q].z, b[q].z);
+                    keep(a[q].w, b[q].w);
+                }
+            }
+        }
+    }
+    for (uint64_t i = steps * per_step + (uint64_t)blockIdx.x * BLOCK + threadIdx.x; i < n; i += (uint64_t)gridDim.x * BLOCK) {
+        const uint32_t a = c0[i], b = c1[i];
+        acc0 |= a;
+        acc1 |= b;
+        if (fcol >= 0) keep(a, b);
+    }
+    uint64_t acc = ((uint64_t)acc0 << 32) | acc1;
+#pragma unroll
+    for (int d = 16; d; d >>= 1) acc |= __shfl_xor_sync(FULL, acc, d);
+    if (lane_id() == 0 && acc) atomicOr(or_out, (unsigned long long)acc);
 }
 static __global__ void pack1_k(const uint32_t* __restrict__ c0, uint64_t* __restrict__ out, uint64_t n, unsigned long long* or_out) {
     uint64_t acc = 0;
@@ -1145,27 +1196,47 @@ static __global__ void __launch_bounds__(BLOCK) dense_emit_k(const unsigned int*
     }
 }
 
-// One step of a frontier loop on bitmaps over one domain: the candidates (the OR of `parts` bitmaps
-// laid out back to back) that the head lacks become the next frontier and join the head; their
-// number is added to *count_new.  `clear` (this rank's candidate bitmap) is zeroed for the next use.
-// (`clear` may be `cand_parts` itself: neither is declared restrict)
-static __global__ void __launch_bounds__(BLOCK) frontier_step_k(const unsigned int* cand_parts, uint32_t parts, uint64_t words, unsigned int* clear,
+// One step of a frontier loop on bitmaps over one domain: what the marks (the OR of `parts` bitmaps
+// laid out back to back, each the head plus one rank's candidates) hold beyond the head becomes the
+// next frontier and joins the head; their number is added to *count_new.  `own` (this rank's marks)
+// is left equal to the new head, which is what the next scan starts from.
+// (`own` may be `mark_parts` itself: neither is declared restrict)
+static __global__ void __launch_bounds__(BLOCK) frontier_step_k(const unsigned int* mark_parts, uint32_t parts, uint64_t words, unsigned int* own,
                                                            unsigned int* __restrict__ visited, unsigned int* __restrict__ next_frontier,
-                                                           unsigned long long* __restrict__ count_new) {
+                                                           unsigned long long* counts, unsigned int* ticket, unsigned long long* publish_to, unsigned long long seq) {
     unsigned mine = 0;
     for (uint64_t w = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; w < words; w += (uint64_t)gridDim.x * blockDim.x) {
-        unsigned cand = 0;
-        for (uint32_t p = 0; p < parts; ++p) cand |= cand_parts[(uint64_t)p * words + w];
+        unsigned all = 0;
+        for (uint32_t p = 0; p < parts; ++p) all |= mark_parts[(uint64_t)p * words + w];
         const unsigned vis = visited[w];
-        const unsigned fresh = cand & ~vis;
-        if (fresh) visited[w] = vis | fresh;
+        const unsigned fresh = all & ~vis;
+        if (fresh) {
+            visited[w] = vis | fresh;
+            own[w] = vis | fresh;
+        }
         next_frontier[w] = fresh;
-        if (cand) clear[w] = 0;
         mine += __popc(fresh);
     }
 #pragma unroll
     for (int d = 16; d; d >>= 1) mine += __shfl_down_sync(FULL, mine, d);
-    if (lane_id() == 0 && mine) atomicAdd(count_new, (unsigned long long)mine);
+    if (lane_id() == 0 && mine) atomicAdd(counts, (unsigned long long)mine);
+    if (!publish_to) return;
+    // the block that finishes last leaves the iteration's counts where the host is watching
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(ticket, 1u) == gridDim.x - 1) {
+            __threadfence();
+            volatile unsigned long long* in = counts;
+            volatile unsigned long long* out = publish_to;
+            out[0] = in[0];
+            out[1] = in[1];
+            out[2] = in[2];
+            __threadfence_system();
+            out[3] = seq;
+            *ticket = 0;
+        }
+    }
 }
 
 // ------------------------------------------------------------------------------ hash index
@@ -1552,6 +1623,159 @@ static __global__ void __launch_bounds__(BLOCK) scan_join_mark_k(const uint64_t*
     for (int d = 16; d; d >>= 1) mine += __shfl_down_sync(0xFFFFFFFFu, mine, d);
     if (lane_id() == 0 && mine) atomicAdd(count, mine);
 }
+// The scan of a frontier loop: rows whose key is in the frontier mark their value in `marks`
+// (*count_marked += their number), and — because a key enters the frontier of such a loop
+// exactly once — a row whose key the head already holds can never match again.  `visited` is the
+// head as the iteration found it; `marks` starts every iteration as a copy of it, so one look-up
+// tells whether a value is known or marked already.  `frontier` may be null when every row whose
+// key `visited` holds is known to have its key in the frontier (a list written by the scan before
+// this one holds no other rows; nor does a relation when the head holds the frontier only).
+// Random look-ups into the bitmaps, not the stream over the rows, are what a scan pays for (the
+// L1 serves one line per cycle): one per row and one more per matching row.  With `live_out`
+// the rows whose key the head does not hold yet are appended to it, packed (*live_count += their
+// number): the next scan streams over those instead of over the whole relation.  The rows come
+// either packed (`rows`) or as the relation's two columns (COLS: `kcol` the join column, `ocol` the
+// other one), so that a relation given as columns need not be packed for the first scan.
+// `n_ptr`, when set, holds the number of rows (a list written by an earlier launch whose length the
+// host has not read yet).  Every thread keeps 64 bytes of loads in flight; a tile is FS_TILE rows.
+#ifndef XLB_FS_MINBLOCKS
+#define XLB_FS_MINBLOCKS 8
+#endif
+constexpr int FS_IPT = 8, FS_TILE = BLOCK * FS_IPT;
+template <bool COLS>
+__device__ __forceinline__ void frontier_scan_body(const uint64_t* __restrict__ rows, const uint32_t* __restrict__ kcol, const uint32_t* __restrict__ ocol, uint64_t n, int keysel,
+                                                   const unsigned int* __restrict__ frontier, const unsigned int* __restrict__ visited, uint64_t domain, int value_is_key,
+                                                   unsigned int* __restrict__ marks,
+                                                   uint64_t words, int lo_bits, unsigned long long* count_marked, DevStatus* st, uint64_t* live_out,
+                                                   unsigned long long* live_count, unsigned* warp_sum, unsigned long long& base_s) {
+    const uint64_t ntiles = (n + FS_TILE - 1) / FS_TILE;
+    unsigned long long mine = 0;
+    for (uint64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        const uint64_t t0 = tile * FS_TILE;
+        uint32_t key[FS_IPT], other[FS_IPT];
+        unsigned have = 0;  // bit j: row j of this thread exists
+        if (t0 + FS_TILE <= n) {
+            have = (1u << FS_IPT) - 1;
+            if (COLS) {
+                const uint4* k4 = reinterpret_cast<const uint4*>(kcol + t0);
+                const uint4* o4 = reinterpret_cast<const uint4*>(ocol + t0);
+                uint4 a[FS_IPT / 4], b[FS_IPT / 4];
+#pragma unroll
+                for (int q = 0; q < FS_IPT / 4; ++q) {
+                    a[q] = k4[q * BLOCK + threadIdx.x];
+                    b[q] = o4[q * BLOCK + threadIdx.x];
+                }
+#pragma unroll
+                for (int q = 0; q < FS_IPT / 4; ++q) {
+                    key[4 * q] = a[q].x, key[4 * q + 1] = a[q].y, key[4 * q + 2] = a[q].z, key[4 * q + 3] = a[q].w;
+                    other[4 * q] = b[q].x, other[4 * q + 1] = b[q].y, other[4 * q + 2] = b[q].z, other[4 * q + 3] = b[q].w;
+                }
+            } else {
+                const ulonglong2* r2 = reinterpret_cast<const ulonglong2*>(rows + t0);
+                ulonglong2 v[FS_IPT / 2];
+#pragma unroll
+                for (int q = 0; q < FS_IPT / 2; ++q) v[q] = r2[q * BLOCK + threadIdx.x];
+#pragma unroll
+                for (int q = 0; q < FS_IPT / 2; ++q) {
+                    const uint64_t x = v[q].x, y = v[q].y;
+                    key[2 * q] = keysel == 0 ? (uint32_t)(x >> 32) : (uint32_t)x;
+                    other[2 * q] = keysel == 0 ? (uint32_t)x : (uint32_t)(x >> 32);
+                    key[2 * q + 1] = keysel == 0 ? (uint32_t)(y >> 32) : (uint32_t)y;
+                    other[2 * q + 1] = keysel == 0 ? (uint32_t)y : (uint32_t)(y >> 32);
+                }
+            }
+        } else {  // the last, partial tile
+#pragma unroll
+            for (int j = 0; j < FS_IPT; ++j) {
+                const uint64_t i = t0 + (uint64_t)j * BLOCK + threadIdx.x;
+                key[j] = other[j] = 0;
+                if (i < n) {
+                    have |= 1u << j;
+                    if (COLS) {
+                        key[j] = kcol[i];
+                        other[j] = ocol[i];
+                    } else {
+                        const uint64_t x = rows[i];
+                        key[j] = keysel == 0 ? (uint32_t)(x >> 32) : (uint32_t)x;
+                        other[j] = keysel == 0 ? (uint32_t)x : (uint32_t)(x >> 32);
+                    }
+                }
+            }
+        }
+        unsigned live = 0;  // bit j: the head does not hold row j's key yet
+#pragma unroll
+        for (int j = 0; j < FS_IPT; ++j) {
+            if (!((have >> j) & 1u) || key[j] >= domain) continue;  // (a key outside the domain can never be derived)
+            const unsigned bit = 1u << (key[j] & 31);
+            if (!(__ldg(&visited[key[j] >> 5]) & bit)) {
+                live |= 1u << j;
+                continue;
+            }
+            if (frontier && !(__ldg(&frontier[key[j] >> 5]) & bit)) continue;  // was in an earlier frontier
+            ++mine;
+            const uint32_t x = value_is_key ? key[j] : other[j];
+            if ((uint64_t)x >> lo_bits || (uint64_t)(x >> 5) >= words) {
+                set_status(st, XLB_ERR_CAPACITY, 7, x);
+                continue;
+            }
+            const unsigned xb = 1u << (x & 31);
+            // (a plain load, served by the L1: known already or marked already is the common case;
+            // a stale line only costs an atomic that changes nothing)
+            if (!(marks[x >> 5] & xb)) atomicOr(&marks[x >> 5], xb);
+        }
+        if (live_out) {
+            // The tile's live rows go out as one contiguous piece, without staging them in shared
+            // memory (which would take the L1 space the bitmaps live in): one reservation per
+            // block, and within a warp row j of every lane is written in round j, the lanes that
+            // hold one at consecutive addresses.
+            unsigned ballots[FS_IPT];
+            unsigned warp_total = 0;
+#pragma unroll
+            for (int j = 0; j < FS_IPT; ++j) {
+                ballots[j] = __ballot_sync(FULL, (live >> j) & 1u);
+                warp_total += __popc(ballots[j]);
+            }
+            const int w = threadIdx.x >> 5;
+            if (lane_id() == 0) warp_sum[w] = warp_total;
+            __syncthreads();
+            unsigned before = 0, total = 0;
+#pragma unroll
+            for (int q = 0; q < BLOCK / 32; ++q) {
+                const unsigned ws = warp_sum[q];
+                if (q < w) before += ws;
+                total += ws;
+            }
+            if (threadIdx.x == 0 && total) base_s = atomicAdd(live_count, (unsigned long long)total);
+            __syncthreads();  // (also: warp_sum is not rewritten before every warp has read it)
+            unsigned long long at = base_s + before;
+            const unsigned below = (1u << lane_id()) - 1;
+#pragma unroll
+            for (int j = 0; j < FS_IPT; ++j) {
+                if ((live >> j) & 1u)
+                    live_out[at + __popc(ballots[j] & below)] = keysel == 0 ? ((uint64_t)key[j] << 32) | other[j] : ((uint64_t)other[j] << 32) | key[j];
+                at += __popc(ballots[j]);
+            }
+        }
+    }
+#pragma unroll
+    for (int d = 16; d; d >>= 1) mine += __shfl_down_sync(FULL, mine, d);
+    if (lane_id() == 0 && mine) atomicAdd(count_marked, mine);
+}
+
+template <bool COLS>
+static __global__ void __launch_bounds__(BLOCK, XLB_FS_MINBLOCKS) frontier_scan_k(const uint64_t* __restrict__ rows, const uint32_t* __restrict__ kcol, const uint32_t* __restrict__ ocol,
+                                                           uint64_t n_max, const unsigned long long* __restrict__ n_ptr, int keysel, const unsigned int* frontier,
+                                                           const unsigned int* visited, uint64_t domain, int value_is_key, unsigned int* marks, uint64_t words, int lo_bits,
+                                                           unsigned long long* count_marked, DevStatus* st, const unsigned long long* __restrict__ keys_in_frontier,
+                                                           uint64_t* live_out, unsigned long long* live_count) {
+    if (keys_in_frontier && *keys_in_frontier == 0) return;  // enqueued on top of an iteration that found nothing
+    __shared__ unsigned warp_sum[BLOCK / 32];
+    __shared__ unsigned long long base_s;
+    uint64_t n = n_ptr ? (uint64_t)*n_ptr : n_max;
+    if (n > n_max) n = n_max;
+    frontier_scan_body<COLS>(rows, kcol, ocol, n, keysel, frontier, visited, domain, value_is_key, marks, words, lo_bits, count_marked, st, live_out, live_count, warp_sum, base_s);
+}
+
 struct PredKeyIn {  // the row's key is in the key set
     const uint64_t* rows;
     int keysel;

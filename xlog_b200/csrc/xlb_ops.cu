@@ -348,24 +348,28 @@ extern "C" xlb_status xlb_profile_read(xlb_ctx* c, xlb_kernel_profile* out, uint
 }
 
 // ------------------------------------------------------------------------------ key-array ops
-static Keys rel_packed(xlb_ctx* c, const xlb_rel* r, int fcol, uint32_t fval, Keys* filtered) {
+static Keys rel_packed(xlb_ctx* c, const xlb_rel* r, int fcol, uint32_t fval, Keys* filtered, bool materialize = true) {
     Keys k;
     k.n = r->rows;
     k.bound = r->or_bound;
     if (r->packed) { k.buf = r->packed; return k; }
     if (!rel_packable(r->schema)) xlb_fail(XLB_ERR_UNSUPPORTED, "relation is not a one- or two-column 32-bit relation");
-    Buf b = make_buf(c, r->rows * 8);
+    Buf b = make_buf(c, materialize ? r->rows * 8 : 0);
     if (r->rows) {
         // pack and, in the same sweep, reduce the OR of all rows: later sorts of anything derived
         // from this relation plan their digits from it without a read-back
         Buf oa = make_buf(c, 16);
         CUDA_OK(cudaMemsetAsync(oa->p, 0, 16, c->stream));
-        prof_begin(c, "pack", r->rows * 16ull);
+        prof_begin(c, "pack", r->rows * (materialize ? 16ull : 8ull));
         const bool fuse = filtered && r->schema.arity == 2 && fcol >= 0 && fcol < 2;
         if (fuse) filtered->buf = make_buf(c, r->rows * 8);  // at most every row; trimmed below
-        if (r->schema.arity == 2) {
+        if (r->schema.arity == 2 && !materialize && (((uintptr_t)r->cols[0]->p | (uintptr_t)r->cols[1]->p) & 15) == 0) {
+            cols_or_filter_k<<<grid_for(c, r->rows, BLOCK * 16), BLOCK, 0, c->stream>>>(r->cols[0]->as<uint32_t>(), r->cols[1]->as<uint32_t>(), r->rows, oa->as<unsigned long long>(),
+                                                                                         fuse ? fcol : -1, fval, fuse ? filtered->buf->as<uint64_t>() : nullptr,
+                                                                                         oa->as<unsigned long long>() + 1);
+        } else if (r->schema.arity == 2) {
             const bool vec = (((uintptr_t)r->cols[0]->p | (uintptr_t)r->cols[1]->p | (uintptr_t)b->p) & 15) == 0;
-            pack2_k<<<grid_for(c, r->rows, BLOCK * 4), BLOCK, 0, c->stream>>>(r->cols[0]->as<uint32_t>(), r->cols[1]->as<uint32_t>(), b->as<uint64_t>(), r->rows,
+            pack2_k<<<grid_for(c, r->rows, BLOCK * 4), BLOCK, 0, c->stream>>>(r->cols[0]->as<uint32_t>(), r->cols[1]->as<uint32_t>(), materialize ? b->as<uint64_t>() : nullptr, r->rows,
                                                                               oa->as<unsigned long long>(), vec, fuse ? fcol : -1, fval,
                                                                               fuse ? filtered->buf->as<uint64_t>() : nullptr, oa->as<unsigned long long>() + 1);
         }
@@ -383,13 +387,19 @@ static Keys rel_packed(xlb_ctx* c, const xlb_rel* r, int fcol, uint32_t fval, Ke
         r->or_bound = 0;
         if (filtered) filtered->buf = make_buf(c, 0);
     }
-    r->packed = b;
+    if (materialize) r->packed = b;
     k.buf = b;
     k.bound = r->or_bound;
     return k;
 }
 
 Keys ops_rel_packed(xlb_ctx* c, const xlb_rel* r) { return rel_packed(c, r, -1, 0, nullptr); }
+
+bool ops_rel_bound_filtered(xlb_ctx* c, const xlb_rel* r, int fcol, uint32_t fval, Keys* filtered) {
+    if (r->packed || r->schema.arity != 2 || !rel_packable(r->schema)) return false;
+    rel_packed(c, r, fcol, fval, filtered, /*materialize=*/false);
+    return true;
+}
 
 bool ops_rel_packed_filtered(xlb_ctx* c, const xlb_rel* r, int fcol, uint32_t fval, Keys* filtered) {
     if (r->packed || r->schema.arity != 2 || !rel_packable(r->schema)) return false;
@@ -858,23 +868,30 @@ void ops_scan_join_mark(xlb_ctx* c, const Keys& bag, int keysel, int key_bits, c
     check_launch(c, "scan_join_mark");
 }
 
-void ops_frontier_scan(xlb_ctx* c, const Keys& rel, int rel_keysel, int bits, const unsigned int* frontier, int rel_lo, unsigned int* cand, const unsigned int* visited,
-                       unsigned long long* count_marked, const unsigned long long* keys_in_frontier) {
-    if (rel.n == 0) return;
-    if ((uintptr_t)rel.ptr() & 15) xlb_fail(XLB_ERR_INVALID, "internal: scan join over a row array that is not 16-byte aligned");
+void ops_frontier_scan(xlb_ctx* c, const ScanRows& src, int rel_keysel, int bits, const unsigned int* frontier, int rel_lo, unsigned int* marks, const unsigned int* visited,
+                       unsigned long long* count_marked, const unsigned long long* keys_in_frontier, uint64_t* live_out, unsigned long long* live_count) {
+    if (src.n_max == 0) return;
+    const bool cols = src.packed == nullptr;
+    if (cols ? (((uintptr_t)src.kcol | (uintptr_t)src.ocol) & 15) != 0 : ((uintptr_t)src.packed & 15) != 0)
+        xlb_fail(XLB_ERR_INVALID, "internal: frontier scan over rows that are not 16-byte aligned");
     const uint64_t domain = 1ull << bits, words = (domain + 31) / 32;
-    // a launch enqueued on top of a frontier of unknown size may find it empty and do nothing: its
-    // bytes are added by the caller once the frontier is known to have held keys
-    prof_begin(c, "scan_join_mark", keys_in_frontier ? 0 : rel.n * 8ull);
-    scan_join_mark_k<<<grid_for(c, rel.n, SJ_TILE), BLOCK, 0, c->stream>>>(rel.ptr(), rel.n, rel_keysel, frontier, domain, /*hi_src=*/2, rel_lo, cand, words, bits, count_marked,
-                                                                  c->d_status, visited, keys_in_frontier);
+    // how many rows a launch streams over, and how many it writes back, is known only once its
+    // counts have been read: the caller adds the bytes then
+    prof_begin(c, "scan_join_mark", 0);
+    const unsigned grid = grid_for(c, src.n_max, FS_TILE);
+    if (cols)
+        frontier_scan_k<true><<<grid, BLOCK, 0, c->stream>>>(nullptr, src.kcol, src.ocol, src.n_max, src.n_dev, rel_keysel, frontier, visited, domain, rel_lo == 0, marks, words, bits,
+                                                             count_marked, c->d_status, keys_in_frontier, live_out, live_count);
+    else
+        frontier_scan_k<false><<<grid, BLOCK, 0, c->stream>>>(src.packed, nullptr, nullptr, src.n_max, src.n_dev, rel_keysel, frontier, visited, domain, rel_lo == 0, marks, words, bits,
+                                                              count_marked, c->d_status, keys_in_frontier, live_out, live_count);
     check_launch(c, "scan_join_mark");
 }
 
-void ops_frontier_step(xlb_ctx* c, const unsigned int* cand_parts, uint32_t parts, uint64_t words, unsigned int* clear, unsigned int* visited, unsigned int* next_frontier,
-                       unsigned long long* count_new) {
+void ops_frontier_step(xlb_ctx* c, const unsigned int* mark_parts, uint32_t parts, uint64_t words, unsigned int* own, unsigned int* visited, unsigned int* next_frontier,
+                       unsigned long long* counts, unsigned int* ticket, unsigned long long* publish_to, unsigned long long seq) {
     prof_begin(c, "frontier_step", words * 4ull * (parts + 3));
-    frontier_step_k<<<grid_for(c, words), BLOCK, 0, c->stream>>>(cand_parts, parts, words, clear, visited, next_frontier, count_new);
+    frontier_step_k<<<grid_for(c, words), BLOCK, 0, c->stream>>>(mark_parts, parts, words, own, visited, next_frontier, counts, ticket, publish_to, seq);
     check_launch(c, "frontier_step");
 }
 
@@ -1010,7 +1027,9 @@ extern "C" xlb_status xlb_ctx_create(const xlb_config* cfg, xlb_ctx** out) {
         c->max_iterations = cfg && cfg->max_iterations ? cfg->max_iterations : 1000000ull;
         c->join_chunk = cfg ? cfg->join_chunk_tuples : 0;
         c->flags = cfg ? cfg->flags : 0;
-        CUDA_OK(cudaMallocHost(&c->h_scalar, 64 * 8));
+        CUDA_OK(cudaHostAlloc((void**)&c->h_scalar, 64 * 8, cudaHostAllocMapped));
+        CUDA_OK(cudaHostGetDevicePointer((void**)&c->h_scalar_dev, c->h_scalar, 0));
+        memset(c->h_scalar, 0, 64 * 8);
         CUDA_OK(cudaMalloc(&c->d_status, sizeof(DevStatus)));
         CUDA_OK(cudaMemset(c->d_status, 0, sizeof(DevStatus)));
         cudaDeviceProp prop;

@@ -38,6 +38,10 @@ Keys ops_rel_packed(xlb_ctx* c, const xlb_rel* r);             // packed view (c
 // The same for a two-column relation that is not packed yet, with the rows whose column fcol equals
 // fval collected in the same pass (`filtered`, a bag).  False (nothing done): already packed.
 bool ops_rel_packed_filtered(xlb_ctx* c, const xlb_rel* r, int fcol, uint32_t fval, Keys* filtered);
+// One pass over the columns of such a relation without packing it: its OR bound becomes known (and
+// the filtered rows are collected, fcol >= 0).  False (nothing done): already packed, or not two
+// 32-bit columns.
+bool ops_rel_bound_filtered(xlb_ctx* c, const xlb_rel* r, int fcol, uint32_t fval, Keys* filtered);
 void ops_rel_columns(xlb_ctx* c, const xlb_rel* r);            // materialise column view (cached)
 xlb_rel* ops_rel_from_keys(xlb_ctx* c, const xlb_schema& s, Keys k, bool canonical);
 
@@ -139,15 +143,30 @@ void ops_scan_join_mark(xlb_ctx* c, const Keys& bag, int keysel, int key_bits, c
 // (whole 16-byte words).
 Buf ops_keyset(xlb_ctx* c, const Keys& bag, int keysel, int key_bits);
 // Frontier loop on bitmaps over one domain of 2^bits values (a head of one column).
-//   scan: every row of `rel` whose key is in `frontier` marks its head value in `cand` unless
-//         `visited` holds it; *count_marked += the rows with a key in the frontier.  With
-//         keys_in_frontier (device) the launch does nothing when that count is zero.
-//   step: the candidates (OR of `parts` bitmaps back to back) that `visited` lacks become
-//         `next_frontier` and join `visited`; *count_new += their number; `clear` is zeroed.
-void ops_frontier_scan(xlb_ctx* c, const Keys& rel, int rel_keysel, int bits, const unsigned int* frontier, int rel_lo, unsigned int* cand, const unsigned int* visited,
-                       unsigned long long* count_marked, const unsigned long long* keys_in_frontier);
-void ops_frontier_step(xlb_ctx* c, const unsigned int* cand_parts, uint32_t parts, uint64_t words, unsigned int* clear, unsigned int* visited, unsigned int* next_frontier,
-                       unsigned long long* count_new);
+//   scan: every row whose key is in `frontier` marks its head value in `marks`, a bitmap that
+//         holds `visited` plus what the iteration has marked so far; *count_marked += the rows
+//         with a key in the frontier.  `frontier` is a subset of `visited`, and null when every
+//         row whose key `visited` holds has it in the frontier.  With keys_in_frontier (device)
+//         the launch does nothing when that count is zero.  With live_out the rows whose key
+//         `visited` lacks are appended to it, packed (*live_count += their number): a key enters
+//         the frontier once, so no other row can match in a later scan.
+//   step: what the marks (OR of `parts` bitmaps back to back) hold beyond `visited` becomes
+//         `next_frontier` and joins `visited`; counts[0] += their number; `own` (this rank's
+//         marks) is left equal to the new `visited`.  The block that finishes last (`ticket`, a
+//         zeroed device word that is left zero) copies counts[0..2] to publish_to[0..2] and then
+//         writes `seq` to publish_to[3]: publish_to is pinned host memory as the device sees it,
+//         so the host can watch for `seq` instead of enqueuing a copy and an event.
+struct ScanRows {  // what a scan streams over: packed rows, or the join column and the other column of a relation
+    const uint64_t* packed = nullptr;
+    const uint32_t* kcol = nullptr;
+    const uint32_t* ocol = nullptr;
+    uint64_t n_max = 0;                         // rows (an upper bound when n_dev is set)
+    const unsigned long long* n_dev = nullptr;  // device word with the row count, for a list whose length the host has not read
+};
+void ops_frontier_scan(xlb_ctx* c, const ScanRows& src, int rel_keysel, int bits, const unsigned int* frontier, int rel_lo, unsigned int* marks, const unsigned int* visited,
+                       unsigned long long* count_marked, const unsigned long long* keys_in_frontier, uint64_t* live_out, unsigned long long* live_count);
+void ops_frontier_step(xlb_ctx* c, const unsigned int* mark_parts, uint32_t parts, uint64_t words, unsigned int* own, unsigned int* visited, unsigned int* next_frontier,
+                       unsigned long long* counts, unsigned int* ticket, unsigned long long* publish_to, unsigned long long seq);
 // rows of `bag` whose key has (semi) or lacks (anti) a match in the index, in bag order
 // (pkeys, when given, holds the key word of every bag row instead of a half named by keysel)
 Keys ops_semi_filter(xlb_ctx* c, const Keys& bag, int keysel, const Index& ix, bool anti, const uint64_t* pkeys = nullptr);
