@@ -52,7 +52,7 @@ TIMING_NOTE = "CUDA events on the library's stream around xlb_execute_plan, max 
 # one launch was measured with ncu on a small case of the same kernel and grows with the rows of a
 # launch, so it is scaled from the algorithmic bytes: the summary that holds the capture is named
 TRAFFIC = {"radix_scatter": (13.2 / 16.0, "profiles/radix_scatter_sort_16M_keys.md"),
-           "scan_join_mark": (1.03, "profiles/scan_join_mark_c2.md")}
+           "scan_join_mark": (0.90, "profiles/frontier_scan_c2.md")}
 
 
 def make_workload(name: str, scale: int):

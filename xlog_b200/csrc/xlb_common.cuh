@@ -391,6 +391,11 @@ struct xlb_ctx {
     std::vector<TraceNote> trace;
 };
 
+// Counts a kernel leaves in pinned memory for the host: low 40 bits the count, top 24 the number
+// of the launch that wrote it.
+constexpr int PUBLISH_COUNT_BITS = 40;
+constexpr unsigned long long PUBLISH_TAG_MASK = 0xFFFFFFull;
+
 inline double trace_now() { return std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now().time_since_epoch()).count(); }
 inline void trace_note(xlb_ctx* c, const char* what, double t0) {
     if (c->trace_on) c->trace.push_back({t0, trace_now(), what});

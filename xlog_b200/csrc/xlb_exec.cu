@@ -1484,21 +1484,24 @@ static bool frontier_shape(xlb_ctx* c, const std::vector<FlatRule>& rules, const
     return true;
 }
 
-// Wait until a kernel has left the number `seq` in a word of pinned memory (work enqueued behind
-// that kernel keeps running: no event, no copy).  After 20 ms the full wait on the stream takes
-// over, which knows how to give up on a late peer.
-static void wait_published(xlb_ctx* c, const unsigned long long* word, unsigned long long seq) {
+// Wait until a kernel has left three counts tagged with launch number `seq` in pinned memory
+// (work enqueued behind that kernel keeps running: no event, no copy), and return them.  After
+// 20 ms the full wait on the stream takes over, which knows how to give up on a late peer.
+static void wait_published(xlb_ctx* c, const unsigned long long* words, unsigned long long seq, uint64_t out[3]) {
     const double tr0 = c->trace_on ? trace_now() : 0;
     auto t0 = std::chrono::steady_clock::now();
-    const volatile unsigned long long* w = word;
-    for (uint64_t polls = 0; *w != seq; ++polls) {
+    const volatile unsigned long long* w = words;
+    const unsigned long long tag = seq & PUBLISH_TAG_MASK;
+    auto all_here = [&] { return (w[0] >> PUBLISH_COUNT_BITS) == tag && (w[1] >> PUBLISH_COUNT_BITS) == tag && (w[2] >> PUBLISH_COUNT_BITS) == tag; };
+    for (uint64_t polls = 0; !all_here(); ++polls) {
         if ((polls & 255) == 255 && std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count() > 20.0) {
             stream_wait(c);  // everything enqueued has run when this returns
-            if (*w != seq) xlb_fail(XLB_ERR_CUDA, "internal: a frontier step finished without leaving its counts");
-            return;
+            if (!all_here()) xlb_fail(XLB_ERR_CUDA, "internal: a frontier step finished without leaving its counts");
+            break;
         }
     }
     std::atomic_thread_fence(std::memory_order_acquire);
+    for (int i = 0; i < 3; ++i) out[i] = w[i] & ((1ull << PUBLISH_COUNT_BITS) - 1);
     c->ms_sync_wait += std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
     c->syncs++;
     trace_note(c, "wait (counts in pinned memory)", tr0);
@@ -1576,17 +1579,17 @@ static void frontier_loop(xlb_ctx* c, const FrontierPlan& fp, const std::string&
     // list of rows that can still match, (unused)
     const uint64_t bitmap_bytes = std::max<uint64_t>(words * 4, 16);
     const int max_launches = scan_limit + 1;
-    Buf frontier[2] = {ops_keyset(c, delta, SRC_LO, lb), make_buf(c, bitmap_bytes)};
-    Buf cand = make_buf(c, bitmap_bytes);
-    Buf counts = make_buf(c, (uint64_t)max_launches * 32);
-    unsigned int* visited = ds->visited->as<unsigned int>();
-    CUDA_OK(cudaMemcpyAsync(cand->p, visited, words * 4, cudaMemcpyDeviceToDevice, c->stream));
-    CUDA_OK(cudaMemsetAsync(counts->p, 0, (uint64_t)max_launches * 32, c->stream));
     // whether a row whose key the head holds must have it in the frontier: true of the relation
     // when the head holds nothing but the frontier, and of a list written by the scan just before
     bool visited_means_frontier = full.n == delta.n;
-    Buf ticket = make_buf(c, 16);  // the step kernel's count of finished blocks
-    CUDA_OK(cudaMemsetAsync(ticket->p, 0, 16, c->stream));
+    // (the first scan then never looks at the first frontier bitmap: it need not be filled)
+    Buf frontier[2] = {visited_means_frontier ? make_buf(c, bitmap_bytes) : ops_keyset(c, delta, SRC_LO, lb), make_buf(c, bitmap_bytes)};
+    Buf cand = make_buf(c, bitmap_bytes);
+    Buf counts = make_buf(c, (uint64_t)max_launches * 32 + 16);  // and, behind the counters, the step kernel's count of finished blocks
+    unsigned int* visited = ds->visited->as<unsigned int>();
+    CUDA_OK(cudaMemcpyAsync(cand->p, visited, words * 4, cudaMemcpyDeviceToDevice, c->stream));
+    CUDA_OK(cudaMemsetAsync(counts->p, 0, (uint64_t)max_launches * 32 + 16, c->stream));
+    unsigned int* ticket = reinterpret_cast<unsigned int*>(counts->as<unsigned long long>() + 4 * max_launches);
     struct Flight {
         unsigned long long seq = 0;  // the number the step kernel writes beside the counts it leaves in pinned memory
         unsigned slot = 0;
@@ -1611,7 +1614,8 @@ static void frontier_loop(xlb_ctx* c, const FrontierPlan& fp, const std::string&
         f.index = launched;
         f.count = counts->as<unsigned long long>() + 4 * launched;
         f.slot = 20 + 4 * (launched & 3);  // (at most two launches are in flight)
-        f.seq = ++c->publish_seq;
+        if ((++c->publish_seq & PUBLISH_TAG_MASK) == 0) ++c->publish_seq;  // tag 0 is what untouched words carry
+        f.seq = c->publish_seq;
         uint64_t* out = nullptr;
         int dst = -1;
         if (compact) {
@@ -1644,7 +1648,7 @@ static void frontier_loop(xlb_ctx* c, const FrontierPlan& fp, const std::string&
         {
             PhaseTimer t(c, &rs.st.ms_setops);
             ops_frontier_step(c, gathered ? gathered->as<unsigned int>() : cand->as<unsigned int>(), gathered ? rs.repl.world : 1, words, cand->as<unsigned int>(), visited,
-                              frontier[1 - cur_frontier]->as<unsigned int>(), f.count, ticket->as<unsigned int>(), c->h_scalar_dev + f.slot, f.seq);
+                              frontier[1 - cur_frontier]->as<unsigned int>(), f.count, ticket, c->h_scalar_dev + f.slot, f.seq);
         }
         cur_frontier = 1 - cur_frontier;
         ++launched;
@@ -1665,8 +1669,9 @@ static void frontier_loop(xlb_ctx* c, const FrontierPlan& fp, const std::string&
         const int cur_out = cur_frontier;
         Flight next;
         if (more) next = launch(cur.count, wants_list(launched));
-        wait_published(c, &c->h_scalar[cur.slot + 3], cur.seq);
-        const uint64_t tot = c->h_scalar[cur.slot], marked = c->h_scalar[cur.slot + 1], kept = c->h_scalar[cur.slot + 2];
+        uint64_t got[3];
+        wait_published(c, &c->h_scalar[cur.slot], cur.seq, got);
+        const uint64_t tot = got[0], marked = got[1], kept = got[2];
         Launch& done = log[cur.index];
         done.kept = kept;
         const uint64_t streamed = done.producer < 0 ? share : log[done.producer].kept;

@@ -1221,7 +1221,10 @@ static __global__ void __launch_bounds__(BLOCK) frontier_step_k(const unsigned i
     for (int d = 16; d; d >>= 1) mine += __shfl_down_sync(FULL, mine, d);
     if (lane_id() == 0 && mine) atomicAdd(counts, (unsigned long long)mine);
     if (!publish_to) return;
-    // the block that finishes last leaves the iteration's counts where the host is watching
+    // The block that finishes last leaves the iteration's counts where the host is watching.  Each
+    // of the three words carries the launch's number in its top 24 bits, so the host knows a word
+    // is of this launch whichever order the three writes arrive in: no fence towards the host (a
+    // round trip over the bus) is needed between them.
     __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence();
@@ -1229,11 +1232,11 @@ static __global__ void __launch_bounds__(BLOCK) frontier_step_k(const unsigned i
             __threadfence();
             volatile unsigned long long* in = counts;
             volatile unsigned long long* out = publish_to;
-            out[0] = in[0];
-            out[1] = in[1];
-            out[2] = in[2];
-            __threadfence_system();
-            out[3] = seq;
+            const unsigned long long tag = (seq & PUBLISH_TAG_MASK) << PUBLISH_COUNT_BITS;
+            const unsigned long long a = in[0], b = in[1], k = in[2];
+            out[0] = tag | a;
+            out[1] = tag | b;
+            out[2] = tag | k;
             *ticket = 0;
         }
     }

@@ -153,9 +153,10 @@ Buf ops_keyset(xlb_ctx* c, const Keys& bag, int keysel, int key_bits);
 //   step: what the marks (OR of `parts` bitmaps back to back) hold beyond `visited` becomes
 //         `next_frontier` and joins `visited`; counts[0] += their number; `own` (this rank's
 //         marks) is left equal to the new `visited`.  The block that finishes last (`ticket`, a
-//         zeroed device word that is left zero) copies counts[0..2] to publish_to[0..2] and then
-//         writes `seq` to publish_to[3]: publish_to is pinned host memory as the device sees it,
-//         so the host can watch for `seq` instead of enqueuing a copy and an event.
+//         zeroed device word that is left zero) copies counts[0..2] to publish_to[0..2], each with
+//         the low 24 bits of `seq` in its top 24 bits: publish_to is pinned host memory as the
+//         device sees it, so the host can watch for the three tags instead of enqueuing a copy
+//         and an event (counts stay below 2^40).
 struct ScanRows {  // what a scan streams over: packed rows, or the join column and the other column of a relation
     const uint64_t* packed = nullptr;
     const uint32_t* kcol = nullptr;
