@@ -11,31 +11,20 @@ from xlog_b200 import programs, workloads
 from xlog_b200.lib import XlbError
 from xlog_b200.plan import Filter, Join, Project, Scan
 
-# reach(X,Y) :- edge(X,Y).  reach(X,Z) :- reach(X,Y), edge(Y,Z).   as serde would print it: the
-# recursive body promoted to a ChainJoin whose fallback is the plain Join/Project tree, RirMeta
-# carried along, strata given
-TC_JSON = """
-{"sccs": [{"id": 0, "predicates": ["reach"], "is_recursive": true}],
- "strata": [{"id": 0, "sccs": [0]}],
- "rules_by_scc": [[
-   {"head": "reach", "body": {"Scan": {"rel": 0}}, "meta": {"est_rows": 3, "est_bytes": 24}},
-   {"head": "reach",
-    "body": {"ChainJoin": {"left": {"Scan": {"rel": 1}}, "right": {"Scan": {"rel": 0}}, "left_key": 1, "right_key": 0,
-                           "output_columns": [{"Column": 0}, {"Column": 3}],
-                           "fallback": {"Project": {"input": {"Join": {"left": {"Scan": {"rel": 1}}, "right": {"Scan": {"rel": 0}},
-                                                                        "left_keys": [1], "right_keys": [0], "join_type": "Inner"}},
-                                                    "columns": [{"Column": 0}, {"Column": 3}]}}}},
-    "meta": {"est_rows": 9, "est_bytes": 72}}]],
- "generated_query_rules": [], "est_memory_peak": 0,
- "rel_arities": {"0": 2, "1": 2}}
-"""
+# The serialized form of one plan is kept as a fixture: tests/golden/plan_tc_serde.json (its note
+# says what it is a reading of, and that no Rust toolchain has produced it yet).
+import os
+
+with open(os.path.join(os.path.dirname(__file__), "golden", "plan_tc_serde.json")) as _f:
+    TC_FIXTURE = json.load(_f)
+TC_JSON = json.dumps(TC_FIXTURE["plan"])
 
 
 def test_transitive_closure_known_answer(oracle):
-    plan = PJ.plan_from_json(TC_JSON, rel_names={0: "edge", 1: "reach"})
-    edge = [np.array([1, 2, 3], np.uint32), np.array([2, 3, 4], np.uint32)]
+    plan = PJ.plan_from_json(TC_JSON, rel_names={int(k): v for k, v in TC_FIXTURE["rel_names"].items()})
+    edge = [np.array(col, np.uint32) for col in TC_FIXTURE["input"]["edge"]]
     out, _ = oracle.run_program(plan, {"edge": edge}, ["reach"])
-    assert list(zip(*[c.tolist() for c in out["reach"]])) == [(1, 2), (1, 3), (1, 4), (2, 3), (2, 4), (3, 4)]
+    assert [list(t) for t in zip(*[c.tolist() for c in out["reach"]])] == TC_FIXTURE["expect"]["reach"]
     assert plan.sccs[0].is_recursive and plan.rel_ids == {"edge": 0, "reach": 1}
     assert isinstance(plan.sccs[0].rules[1].body, Project)      # the ChainJoin's fallback tree
 

@@ -268,6 +268,9 @@ struct RunState {
     std::map<std::pair<std::string, int>, int> scans;  // scan joins run so far per (relation, key column)
     // rows of a stored relation with column `col` equal to `value`, collected while the relation was packed
     std::map<std::tuple<std::string, int, uint64_t>, Keys> prefiltered;
+    // heads of 28 to 32 bits that moved from the hash set to bitmaps: an iteration brought more
+    // candidates than a 256th of the domain, from where on passes over the bitmaps are the cheaper dedup
+    std::set<std::string> wide_dense;
     std::set<std::string> keep_cols;  // stored relations a frontier loop will stream over as columns: not packed ahead of it
     // Several ranks.  Relations whose rows every rank holds in full while the running component is
     // evaluated: full copies of small stored relations (kept in the store under an alias name) and,
@@ -646,6 +649,10 @@ static Keys real_full(xlb_ctx* c, RunState& rs, const std::string& head) {
     return ops_rel_packed(c, store_get(c, head));
 }
 
+// Widest domain (bits of both columns together) the bitmap route takes for `head`.
+constexpr int DENSE_BITS = 27, WIDE_DENSE_BITS = 32;
+static int dense_max_bits(const RunState& rs, const std::string& head) { return rs.wide_dense.count(head) ? WIDE_DENSE_BITS : DENSE_BITS; }
+
 // The bitmap of `head` = full + novel over a domain of at least (hb, lb) bits, built or rebuilt
 // when it is missing, too narrow, or out of step with the rows (a route that does not keep it up
 // to date has added tuples).
@@ -653,7 +660,7 @@ static DenseState* dense_state(xlb_ctx* c, RunState& rs, const std::string& head
     DenseState& ds = rs.dense[head];
     if (ds.valid && ds.hi_bits >= hb && ds.lo_bits >= lb && ds.rows == full.n + novel.n) return &ds;
     int nh = hb, nl = lb;
-    if (ds.valid && std::max(hb, ds.hi_bits) + std::max(lb, ds.lo_bits) <= 27) {
+    if (ds.valid && std::max(hb, ds.hi_bits) + std::max(lb, ds.lo_bits) <= dense_max_bits(rs, head)) {
         nh = std::max(hb, ds.hi_bits);
         nl = std::max(lb, ds.lo_bits);
     }
@@ -839,7 +846,7 @@ static Keys run_pipeline(xlb_ctx* c, FlatRule fr /*by value: filter flags*/, siz
                 Keys shape;
                 shape.n = 1;
                 shape.bound = ops_scan_join_bound(probe, keysel, rows, rel_keysel, rel_src(hs), rel_src(ls));
-                if (sink && last && !pending && (rs.repl.on || ops_dense_bits(shape, sink->known(), &hb, &lb))) {
+                if (sink && last && !pending && (rs.repl.on || ops_dense_bits(shape, sink->known(), &hb, &lb, dense_max_bits(rs, sink->head)))) {
                     dense_sink_begin(c, rs, sink, hb, lb);
                     ops_scan_join_mark(c, probe, keysel, key_bits, rows, rel_keysel, rel_src(hs), rel_src(ls), sink->set);
                     Keys marked;  // no rows and no count: both are in the sink
@@ -865,7 +872,7 @@ static Keys run_pipeline(xlb_ctx* c, FlatRule fr /*by value: filter flags*/, siz
             Keys shape;  // stands for the rows this step would produce: only their OR bound matters here
             shape.n = 1;
             shape.bound = ops_expand_bound(probe, ix, hs, ls);
-            if (sink && last && !pending && c->world == 1 && !(c->flags & XLB_FLAG_NO_DENSE) && (rs.repl.on || ops_dense_bits(shape, sink->known(), &hb, &lb))) {
+            if (sink && last && !pending && c->world == 1 && !(c->flags & XLB_FLAG_NO_DENSE) && (rs.repl.on || ops_dense_bits(shape, sink->known(), &hb, &lb, dense_max_bits(rs, sink->head)))) {
                 dense_sink_begin(c, rs, sink, hb, lb);
                 ops_join_expand_mark(c, probe, keysel, ix, hs, ls, sink->set);
                 Keys marked;  // no rows and no count: both are in the sink
@@ -998,6 +1005,11 @@ static void eval_variant(xlb_ctx* c, const FlatRule& fr_in, size_t start, const 
         if (sink.used) {
             // the last join marked its tuples in the bitmap already (single rank only); how many
             // there were comes back with the count of the new ones
+            if (rs.wide_dense.count(fr.head)) rs.tset.erase(fr.head);  // the hash set this head started with: gigabytes, not kept up to date from here on
+            if (rs.bag_novel.erase(fr.head) && novel.n) {  // an earlier variant (hash-set route) left a bag: order it before the merge below
+                PhaseTimer t(c, &rs.st.ms_sort);
+                ops_sort(c, novel, /*keep_input=*/true);
+            }
             PhaseTimer t(c, &rs.st.ms_setops);
             Keys fresh = ops_dense_finish(c, sink.set, full);
             sink.state->rows += fresh.n;
@@ -1019,7 +1031,7 @@ static void eval_variant(xlb_ctx* c, const FlatRule& fr_in, size_t start, const 
         if (cand.n == 0) continue;
         Keys fresh;
         int hb = 0, lb = 0;
-        if (!(c->flags & XLB_FLAG_NO_DENSE) && ops_dense_bits(cand, sink.known(), &hb, &lb)) {
+        if (!(c->flags & XLB_FLAG_NO_DENSE) && ops_dense_bits(cand, sink.known(), &hb, &lb, dense_max_bits(rs, fr.head))) {
             // small dense domain: sort + dedup + difference on a bitmap
             PhaseTimer t(c, &rs.st.ms_setops);
             DenseState* ds = dense_state(c, rs, fr.head, hb, lb, full, novel);
@@ -1034,6 +1046,16 @@ static void eval_variant(xlb_ctx* c, const FlatRule& fr_in, size_t start, const 
                 PhaseTimer t(c, &rs.st.ms_setops);
                 if (!ts.valid || ts.rows != full.n + novel.n) ops_tuple_set_build(c, ts, real_full(c, rs, fr.head), novel, cand.n);
                 fresh = ops_tuple_set_novel(c, ts, cand);
+            }
+            // A domain of 28 to 32 bits: once one variant brings more candidates than a 256th of
+            // the domain, passes over bitmaps of the whole domain cost less than hashing every
+            // candidate, the last join can mark its output without writing it, and the new tuples
+            // come out in order.  From the next variant on this head takes the bitmap route (its
+            // bitmap is built from the rows then; the hash set is dropped at the end of the iteration).
+            if (c->world == 1 && !(c->flags & XLB_FLAG_NO_DENSE) && !rs.wide_dense.count(fr.head) && !getenv("XLB_NO_WIDE_DENSE") &&
+                ops_dense_bits(cand, sink.known(), &hb, &lb, WIDE_DENSE_BITS) && cand.n >= (1ull << (hb + lb)) / 256) {
+                const uint64_t bitmaps = 4 * ((1ull << (hb + lb)) / 8);  // head, candidates, and room for a rebuild
+                if (!c->budget || c->allocated + bitmaps <= c->budget) rs.wide_dense.insert(fr.head);
             }
             if (!rs.ordered_heads.count(fr.head)) {
                 // unique, disjoint from everything found before: joining the bags is their union
@@ -1778,6 +1800,7 @@ static void run_scc(xlb_ctx* c, const xlb_scc& scc, RunState& rs) {
         ~Cleanup() {
             for (auto& p : preds) rs.tset.erase(p);  // the hash sets can be gigabytes: they go with the component
             drop_aliases(c, rs);
+            rs.wide_dense.clear();
             rs.repl = RunState::Repl();
             rs.replicated.clear();
         }

@@ -503,13 +503,13 @@ Keys ops_dedup_diff(xlb_ctx* c, const Keys& a, const Keys& b) {
 
 static int bit_length(uint64_t v) { return v ? 64 - __builtin_clzll(v) : 0; }
 
-bool ops_dense_bits(const Keys& a, const Keys& b, int* hi_bits, int* lo_bits) {
+bool ops_dense_bits(const Keys& a, const Keys& b, int* hi_bits, int* lo_bits, int max_bits) {
     uint64_t ba = a.n ? a.bound : 0, bb = b.n ? b.bound : 0;
     if (ba == ~0ull || bb == ~0ull) return false;  // bits unknown
     uint64_t all = ba | bb;
     *hi_bits = bit_length(all >> 32);
     *lo_bits = bit_length(all & 0xFFFFFFFFull);
-    return *hi_bits + *lo_bits <= 27 && *hi_bits + *lo_bits >= 1;
+    return *hi_bits + *lo_bits <= max_bits && *hi_bits + *lo_bits >= 1;
 }
 
 DenseSet ops_dense_begin(xlb_ctx* c, int hi_bits, int lo_bits) {

@@ -58,7 +58,7 @@ Keys ops_diff(xlb_ctx* c, const Keys& a, const Keys& b);         // sorted uniqu
 Keys ops_dedup_diff(xlb_ctx* c, const Keys& a, const Keys& b);   // distinct rows of sorted a that are not in sorted unique b
 // The same result through a bitmap over a dense domain; `ops_dense_bits` says whether the rows of
 // both arrays fit one (returns false otherwise) and how many low-half bits to keep.
-bool ops_dense_bits(const Keys& a, const Keys& b, int* hi_bits, int* lo_bits);
+bool ops_dense_bits(const Keys& a, const Keys& b, int* hi_bits, int* lo_bits, int max_bits = 27);
 Keys ops_dense_novel(xlb_ctx* c, const Keys& cand, const Keys& full, int hi_bits, int lo_bits, unsigned int* visited = nullptr);
 // The same in pieces, so that a join can mark its output tuples straight into the bitmap:
 struct DenseSet {
