@@ -720,8 +720,7 @@ static void dense_sink_begin(xlb_ctx* c, RunState& rs, DenseSink* sink, int hb, 
         return;
     }
     sink->state = dense_state(c, rs, sink->head, hb, lb, *sink->full, *sink->novel);
-    sink->set = ops_dense_begin(c, sink->state->hi_bits, sink->state->lo_bits);
-    sink->set.visited = sink->state->visited->as<unsigned int>();
+    sink->set = ops_dense_begin_from(c, sink->state->hi_bits, sink->state->lo_bits, sink->state->visited->as<unsigned int>());
     sink->used = true;
 }
 

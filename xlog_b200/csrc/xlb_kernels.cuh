@@ -1196,6 +1196,111 @@ static __global__ void __launch_bounds__(BLOCK) dense_emit_k(const unsigned int*
     }
 }
 
+// The same two passes for bitmaps of a million words and more (domains of 2^25 bits and up): a
+// lane takes DW_WPL consecutive words with 16-byte loads, a warp 32 * DW_WPL words (one group), so
+// there are eight times fewer groups to scan and every thread has 64 bytes of loads in flight.
+// `words` is a multiple of 32 * DW_WPL (the host checks).  Most words of such a bitmap are empty:
+// a lane whose words hold nothing new touches nothing else.
+constexpr int DW_WPL = 8;
+static __global__ void __launch_bounds__(BLOCK) dense_count_wide_k(const unsigned int* __restrict__ bitmap, uint32_t* __restrict__ group_counts, uint64_t groups,
+                                                              const unsigned int* __restrict__ visited) {
+    const uint64_t g = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (g >= groups) return;
+    const uint64_t w0 = (g * 32 + lane_id()) * DW_WPL;
+    const uint4* b4 = reinterpret_cast<const uint4*>(bitmap + w0);
+    uint4 a = b4[0], b = b4[1];
+    if (visited && (a.x | a.y | a.z | a.w | b.x | b.y | b.z | b.w)) {
+        const uint4* v4 = reinterpret_cast<const uint4*>(visited + w0);
+        const uint4 va = v4[0], vb = v4[1];
+        a.x &= ~va.x, a.y &= ~va.y, a.z &= ~va.z, a.w &= ~va.w;
+        b.x &= ~vb.x, b.y &= ~vb.y, b.z &= ~vb.z, b.w &= ~vb.w;
+    }
+    unsigned cnt = __popc(a.x) + __popc(a.y) + __popc(a.z) + __popc(a.w) + __popc(b.x) + __popc(b.y) + __popc(b.z) + __popc(b.w);
+#pragma unroll
+    for (int d = 16; d; d >>= 1) cnt += __shfl_xor_sync(FULL, cnt, d);
+    if (lane_id() == 0) group_counts[g] = cnt;
+}
+static __global__ void __launch_bounds__(BLOCK) dense_emit_wide_k(const unsigned int* __restrict__ bitmap, const uint64_t* __restrict__ group_offs, uint64_t groups, int lo_bits,
+                                                             uint64_t* __restrict__ out, unsigned int* __restrict__ visited, uint64_t cap, DevStatus* st) {
+    const uint64_t g = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (g >= groups) return;
+    const unsigned lane = lane_id();
+    const uint64_t lo_mask = (1ull << lo_bits) - 1;
+    const uint64_t w0 = (g * 32 + lane) * DW_WPL;
+    const uint4* b4 = reinterpret_cast<const uint4*>(bitmap + w0);
+    const uint4 a = b4[0], b = b4[1];
+    unsigned m[DW_WPL] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    unsigned any = a.x | a.y | a.z | a.w | b.x | b.y | b.z | b.w;
+    if (visited && any) {
+        uint4* v4 = reinterpret_cast<uint4*>(visited + w0);
+        uint4 va = v4[0], vb = v4[1];
+        const unsigned v[DW_WPL] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
+        any = 0;
+#pragma unroll
+        for (int i = 0; i < DW_WPL; ++i) {
+            m[i] &= ~v[i];
+            any |= m[i];
+        }
+        if (any) {  // one thread per word: what comes out joins the head
+            va.x |= m[0], va.y |= m[1], va.z |= m[2], va.w |= m[3];
+            vb.x |= m[4], vb.y |= m[5], vb.z |= m[6], vb.w |= m[7];
+            v4[0] = va;
+            v4[1] = vb;
+        }
+    }
+    unsigned cnt = 0;
+#pragma unroll
+    for (int i = 0; i < DW_WPL; ++i) cnt += __popc(m[i]);
+    unsigned incl = cnt;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        unsigned o = __shfl_up_sync(FULL, incl, d);
+        if (lane >= (unsigned)d) incl += o;
+    }
+    const unsigned group_total = __shfl_sync(FULL, incl, 31);
+    if (!group_total) return;
+    if (__reduce_max_sync(FULL, cnt) >= 32) {
+        // A dense group: the warp walks its 256 words in order and lane b writes bit b of the word
+        // at hand, so the tuples of a word go out side by side (one lane writing its own 256 bits
+        // one after the other would scatter 8-byte stores over 32 places per step).
+        uint64_t base = group_offs[g];
+        if (base + group_total > cap) {
+            if (lane == 0) set_status(st, XLB_ERR_CAPACITY, 8, base + group_total);
+            return;
+        }
+        const unsigned below = (1u << lane) - 1;
+        for (int owner = 0; owner < 32; ++owner) {
+#pragma unroll
+            for (int i = 0; i < DW_WPL; ++i) {
+                const unsigned word = __shfl_sync(FULL, m[i], owner);
+                if (!word) continue;
+                if ((word >> lane) & 1u) {
+                    const uint64_t x = ((((g * 32 + owner) * DW_WPL) + i) << 5) | lane;
+                    out[base + __popc(word & below)] = ((x >> lo_bits) << 32) | (x & lo_mask);
+                }
+                base += __popc(word);
+            }
+        }
+        return;
+    }
+    if (!cnt) return;
+    uint64_t pos = group_offs[g] + (incl - cnt);
+#pragma unroll
+    for (int i = 0; i < DW_WPL; ++i) {
+        unsigned mm = m[i];
+        while (mm) {
+            const unsigned bit = __ffs(mm) - 1;
+            mm &= mm - 1;
+            const uint64_t x = ((w0 + i) << 5) | bit;
+            if (pos >= cap) {  // more bits than the rows the host sized the output for: report, never write past it
+                set_status(st, XLB_ERR_CAPACITY, 8, pos);
+                return;
+            }
+            out[pos++] = ((x >> lo_bits) << 32) | (x & lo_mask);
+        }
+    }
+}
+
 // One step of a frontier loop on bitmaps over one domain: what the marks (the OR of `parts` bitmaps
 // laid out back to back, each the head plus one rank's candidates) hold beyond the head becomes the
 // next frontier and joins the head; their number is added to *count_new.  `own` (this rank's marks)

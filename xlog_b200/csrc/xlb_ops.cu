@@ -524,6 +524,21 @@ DenseSet ops_dense_begin(xlb_ctx* c, int hi_bits, int lo_bits) {
     return d;
 }
 
+DenseSet ops_dense_begin_from(xlb_ctx* c, int hi_bits, int lo_bits, unsigned int* visited) {
+    DenseSet d;
+    d.hi_bits = hi_bits;
+    d.lo_bits = lo_bits;
+    d.words = ((1ull << (hi_bits + lo_bits)) + 31) / 32;
+    const uint64_t bitmap_bytes = (d.words * 4 + 7) & ~7ull;
+    d.bitmap = make_buf(c, bitmap_bytes + 24);
+    d.counts = (uint64_t*)((char*)d.bitmap->p + bitmap_bytes);
+    CUDA_OK(cudaMemcpyAsync(d.bitmap->p, visited, d.words * 4, cudaMemcpyDeviceToDevice, c->stream));
+    CUDA_OK(cudaMemsetAsync((char*)d.bitmap->p + d.words * 4, 0, bitmap_bytes + 24 - d.words * 4, c->stream));
+    d.visited = visited;
+    d.seeded = true;
+    return d;
+}
+
 static Keys dense_finish(xlb_ctx* c, DenseSet& d, const Keys& full, const uint64_t* known_total);
 Keys ops_dense_finish(xlb_ctx* c, DenseSet& d, const Keys& full) { return dense_finish(c, d, full, nullptr); }
 
@@ -537,11 +552,17 @@ static Keys dense_finish(xlb_ctx* c, DenseSet& d, const Keys& full, const uint64
         dense_mark_k<false><<<grid_for(c, full.n), BLOCK, 0, c->stream>>>(full.ptr(), full.n, d.lo_bits, d.bitmap->as<unsigned int>(), words, c->d_status);
         check_launch(c, "dense_clear");
     }
-    uint64_t groups = (words + 31) / 32;
+    // a bitmap of a million words and more is counted and emitted in groups of 256 words per warp
+    const bool wide = words >= (1ull << 20) && words % (32 * DW_WPL) == 0 && ((uintptr_t)d.bitmap->p & 15) == 0 && (!d.visited || ((uintptr_t)d.visited & 15) == 0);
+    uint64_t groups = wide ? words / (32 * DW_WPL) : (words + 31) / 32;
     Buf gcnt = make_buf(c, groups * 4);
     Buf offs = make_buf(c, groups * 8);
     prof_begin(c, "dense_count", words * 4ull);
-    if (groups <= (uint64_t)DENSE_FUSED_GROUPS) {
+    if (wide) {
+        dense_count_wide_k<<<(unsigned)((groups * 32 + BLOCK - 1) / BLOCK), BLOCK, 0, c->stream>>>(d.bitmap->as<unsigned int>(), gcnt->as<uint32_t>(), groups, d.visited);
+        check_launch(c, "dense_count");
+        exclusive_scan<LoadU32, uint64_t>(c, LoadU32{gcnt->as<uint32_t>()}, groups, offs->as<uint64_t>(), d.counts);
+    } else if (groups <= (uint64_t)DENSE_FUSED_GROUPS) {
         dense_count_scan_k<<<(unsigned)((groups * 32 + BLOCK - 1) / BLOCK), BLOCK, 0, c->stream>>>(d.bitmap->as<unsigned int>(), words, gcnt->as<uint32_t>(), groups, d.visited,
                                                                                                   offs->as<uint64_t>(), d.counts, (unsigned int*)(d.counts + 2));
         check_launch(c, "dense_count");
@@ -563,7 +584,11 @@ static Keys dense_finish(xlb_ctx* c, DenseSet& d, const Keys& full, const uint64
     o.buf = make_buf(c, tot * 8);
     if (tot) {
         prof_begin(c, "dense_emit", words * 4ull + tot * 8ull);
-        dense_emit_k<<<(unsigned)((groups * 32 + BLOCK - 1) / BLOCK), BLOCK, 0, c->stream>>>(d.bitmap->as<unsigned int>(), words, offs->as<uint64_t>(), groups, d.lo_bits, o.buf->as<uint64_t>(), d.visited, tot, c->d_status);
+        if (wide)
+            dense_emit_wide_k<<<(unsigned)((groups * 32 + BLOCK - 1) / BLOCK), BLOCK, 0, c->stream>>>(d.bitmap->as<unsigned int>(), offs->as<uint64_t>(), groups, d.lo_bits, o.buf->as<uint64_t>(),
+                                                                                                    d.visited, tot, c->d_status);
+        else
+            dense_emit_k<<<(unsigned)((groups * 32 + BLOCK - 1) / BLOCK), BLOCK, 0, c->stream>>>(d.bitmap->as<unsigned int>(), words, offs->as<uint64_t>(), groups, d.lo_bits, o.buf->as<uint64_t>(), d.visited, tot, c->d_status);
         check_launch(c, "dense_emit");
     }
     return o;
@@ -692,7 +717,7 @@ void ops_dense_mark_into(xlb_ctx* c, DenseSet& d, const Keys& cand) {
     if (cand.n == 0) return;
     d.bound |= cand.bound;
     prof_begin(c, "dense_mark", cand.n * 8ull);
-    dense_mark_k<true><<<grid_for(c, cand.n), BLOCK, 0, c->stream>>>(cand.ptr(), cand.n, d.lo_bits, d.bitmap->as<unsigned int>(), d.words, c->d_status, d.visited);
+    dense_mark_k<true><<<grid_for(c, cand.n), BLOCK, 0, c->stream>>>(cand.ptr(), cand.n, d.lo_bits, d.bitmap->as<unsigned int>(), d.words, c->d_status, d.seeded ? nullptr : d.visited);
     check_launch(c, "dense_mark");
 }
 
@@ -864,7 +889,7 @@ void ops_scan_join_mark(xlb_ctx* c, const Keys& bag, int keysel, int key_bits, c
     prof_begin(c, "scan_join_mark", rel.n * 8ull);
     if ((uintptr_t)rel.ptr() & 15) xlb_fail(XLB_ERR_INVALID, "internal: scan join over a row array that is not 16-byte aligned");
     scan_join_mark_k<<<grid_for(c, rel.n, SJ_TILE), BLOCK, 0, c->stream>>>(rel.ptr(), rel.n, rel_keysel, keyset->as<unsigned int>(), 1ull << key_bits, rel_hi, rel_lo,
-                                                                  d.bitmap->as<unsigned int>(), d.words, d.lo_bits, (unsigned long long*)(d.counts + 1), c->d_status, d.visited);
+                                                                  d.bitmap->as<unsigned int>(), d.words, d.lo_bits, (unsigned long long*)(d.counts + 1), c->d_status, d.seeded ? nullptr : d.visited);
     check_launch(c, "scan_join_mark");
 }
 
@@ -931,7 +956,7 @@ static Keys join_expand(xlb_ctx* c, const Keys& bag, int keysel, const uint64_t*
         const unsigned grid = (unsigned)c->sm_count * 8;
         prof_begin(c, "expand_mark", bag.n * 24ull);
         expand_k<true><<<grid, BLOCK, 0, c->stream>>>(bag.ptr(), match->as<uint64_t>(), off->as<uint64_t>(), bag.n, 0, ix.S ? ix.S->as<uint64_t>() : nullptr, pay, hi_src, lo_src,
-                                                       nullptr, dense->bitmap->as<unsigned int>(), dense->words, dense->lo_bits, c->d_status, total_dev, dense->visited);
+                                                       nullptr, dense->bitmap->as<unsigned int>(), dense->words, dense->lo_bits, c->d_status, total_dev, dense->seeded ? nullptr : dense->visited);
         check_launch(c, "expand_mark");
         if (dense->shared) {
             add_word_k<<<1, 1, 0, c->stream>>>((unsigned long long*)(dense->counts + 1), (const unsigned long long*)total_dev);

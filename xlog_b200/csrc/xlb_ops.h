@@ -78,6 +78,10 @@ struct DenseSet {
     // replicated relations): a marking join then adds its tuple count to counts[1] instead of
     // leaving it there.
     bool shared = false;
+    // The bitmap started as a copy of `visited` (ops_dense_begin_from): one look-up then tells a
+    // marking kernel both "known already" and "marked already", and it skips the look-up in
+    // `visited`.  ops_dense_finish takes `bitmap & ~visited` either way.
+    bool seeded = false;
 };
 // The tuples of one relation as a bitmap that lives across the iterations of a fixpoint, so that
 // no iteration has to subtract the whole relation from its candidates again.
@@ -104,6 +108,8 @@ void ops_tuple_set_build(xlb_ctx* c, TupleSet& s, const Keys& full, const Keys& 
 Keys ops_tuple_set_novel(xlb_ctx* c, TupleSet& s, const Keys& cand);
 void ops_dense_state_build(xlb_ctx* c, DenseState& s, int hi_bits, int lo_bits, const Keys& full, const Keys& novel);
 Keys ops_dense_state_rows(xlb_ctx* c, const DenseState& s, uint64_t bound);  // all its tuples, in order
+// A set whose bitmap starts as a copy of `visited` (same domain) instead of empty.
+DenseSet ops_dense_begin_from(xlb_ctx* c, int hi_bits, int lo_bits, unsigned int* visited);
 DenseSet ops_dense_begin(xlb_ctx* c, int hi_bits, int lo_bits);
 // Emit, in order, the marked tuples that are new: with d.visited those it lacks (which it then
 // gains; `full` is not read), else those not in `full` (cleared from the bitmap first).
