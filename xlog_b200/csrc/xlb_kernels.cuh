@@ -1936,12 +1936,16 @@ __device__ __forceinline__ uint32_t ex_pick(int src, uint64_t probe, uint32_t ot
 // MARK = true: instead of storing the output tuples, set their bits in a dense-domain bitmap (the
 // candidates of a small-domain head never touch memory as a list).
 template <bool MARK>
-static __global__ void __launch_bounds__(BLOCK) expand_k(const uint64_t* __restrict__ mbag, const uint64_t* __restrict__ mmatch, const uint64_t* __restrict__ off,
+static __global__ void __launch_bounds__(BLOCK, 8) expand_k(const uint64_t* __restrict__ mbag, const uint64_t* __restrict__ mmatch, const uint64_t* __restrict__ off,
                                                    uint64_t nrows, uint64_t total, const uint64_t* __restrict__ S,
                                                    const uint32_t* __restrict__ pay, int hi_src, int lo_src, uint64_t* __restrict__ out,
                                                    unsigned int* __restrict__ bitmap, uint64_t words, int lo_bits, DevStatus* st,
                                                    const uint64_t* __restrict__ total_dev, const unsigned int* __restrict__ visited) {
-    __shared__ uint64_t soff[EX_TILE + 2];
+    // Row offsets of the tile's span relative to the tile's first output, 32 bits each: rel[0] = 0
+    // stands for the row that owns that output (its offset may lie before the tile; `skip0` says by
+    // how much), every later row starts inside the tile or at EX_TILE (beyond it).  The search per
+    // output then runs on 32-bit words.
+    __shared__ unsigned rel[EX_TILE + 2];
     __shared__ uint64_t row_s[2];
     // With total_dev the output count is still on the device (the host launched a fixed grid
     // without reading it back): tiles are then walked grid-strided.
@@ -1962,34 +1966,45 @@ static __global__ void __launch_bounds__(BLOCK) expand_k(const uint64_t* __restr
     const uint64_t span = r1 - r0 + 1;
     const bool in_smem = span <= (uint64_t)(EX_TILE + 2);
     if (in_smem)
-        for (unsigned i = threadIdx.x; i < (unsigned)span; i += BLOCK) soff[i] = off[r0 + i];
+        for (unsigned i = threadIdx.x; i < (unsigned)span; i += BLOCK) {
+            const uint64_t at = off[r0 + i];
+            rel[i] = at <= o0 ? 0u : (at - o0 < (uint64_t)EX_TILE ? (unsigned)(at - o0) : (unsigned)EX_TILE);
+        }
+    const uint64_t skip0 = o0 - off[r0];  // outputs of row r0 that earlier tiles wrote
     __syncthreads();
+    const unsigned in_tile = (unsigned)(o1 - o0);
 #pragma unroll
     for (int k = 0; k < EX_IPT; ++k) {
-        uint64_t o = o0 + (uint64_t)k * BLOCK + threadIdx.x;
-        if (o >= o1) break;
-        uint64_t lo = 0, hi = span;  // first row of the span with offset > o; the one before it owns o
+        const unsigned t = (unsigned)k * BLOCK + threadIdx.x;  // the output's place in the tile
+        if (t >= in_tile) break;
+        uint64_t r, j_in_row;
         if (in_smem) {
+            unsigned lo = 0, hi = (unsigned)span;  // first row of the span that starts after t; the one before it owns t
             while (lo < hi) {
-                uint64_t mid = (lo + hi) >> 1;
-                if (soff[mid] <= o) lo = mid + 1;
+                const unsigned mid = (lo + hi) >> 1;
+                if (rel[mid] <= t) lo = mid + 1;
                 else hi = mid;
             }
+            r = r0 + lo - 1;
+            j_in_row = lo == 1 ? skip0 + t : (uint64_t)(t - rel[lo - 1]);
         } else {
+            const uint64_t o = o0 + t;
+            uint64_t lo = 0, hi = span;
             while (lo < hi) {
                 uint64_t mid = (lo + hi) >> 1;
                 if (off[r0 + mid] <= o) lo = mid + 1;
                 else hi = mid;
             }
+            r = r0 + lo - 1;
+            j_in_row = o - off[r];
         }
-        uint64_t r = r0 + lo - 1;
         uint64_t probe = mbag[r];
         uint64_t start = mmatch[r] >> 32;
-        uint64_t j = start + (o - (in_smem ? soff[lo - 1] : off[r]));
+        uint64_t j = start + j_in_row;
         uint32_t other = pay ? pay[j] : (uint32_t)S[j];
         uint64_t key = ((uint64_t)ex_pick(hi_src, probe, other) << 32) | ex_pick(lo_src, probe, other);
         if (!MARK) {
-            out[o] = key;
+            out[o0 + t] = key;
         } else {
             uint32_t x = dense_index(key, lo_bits);
             if ((key & 0xFFFFFFFFull) >> lo_bits || (uint64_t)(x >> 5) >= words) {
@@ -2000,7 +2015,7 @@ static __global__ void __launch_bounds__(BLOCK) expand_k(const uint64_t* __restr
             }
         }
     }
-    __syncthreads();  // the next tile refills soff / row_s
+    __syncthreads();  // the next tile refills rel / row_s
   }
 }
 
