@@ -141,3 +141,74 @@ def test_sharded_fixpoints_match_the_oracle(oracle, tmp_path):
         if case not in ("negation", "triangle"):
             assert got["iterations"] == ex.iterations, f"{name}: the ranks stopped in another round than one rank does"
         assert got["exchange_bytes"] > 0, name
+
+
+def _rank_wide(rank, world, port, out_dir, scale):
+    import sys
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    os.environ.setdefault("XLB_COMM_TIMEOUT_S", "60")
+    import torch
+    import torch.distributed as dist
+    from xlog_b200 import dist as D
+    from xlog_b200 import programs, workloads
+    from xlog_b200.executor import Executor
+    from xlog_b200.provider import KernelProvider
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        c0, c1 = workloads.rmat_dag(scale, 8)
+        plan = programs.transitive_closure()
+        prov = KernelProvider(device=rank, profile=True)
+        D.init_comm(prov, rank, world)
+        prov.profile_enable("*")
+        ex = Executor(prov)
+        for rel, rid in plan.rel_ids.items():
+            ex.register_relation(rid, rel)
+        lo, hi = D.shard_bounds(len(c0), rank, world)
+        ex.put_relation("edge", prov.create_buffer_from_slices([c0[lo:hi], c1[lo:hi]]))
+        stats = ex.execute_plan(plan)
+        mine = {"digest": prov.checksum(ex.get("reach")), "derived": stats["derived_tuples"], "kernels": sorted(prov.profile_read())}
+        everyone = [None] * world
+        dist.all_gather_object(everyone, mine)
+        prov.close()
+        if rank == 0:
+            np.save(os.path.join(out_dir, "wide.npy"), everyone, allow_pickle=True)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_closure_over_a_domain_of_28_bits_on_several_ranks(tmp_path):
+    # hash-partitioned heads that move from hash sets to bitmaps of their own shard once an
+    # iteration brings enough candidates: the shards' digests must add up to the digest of the
+    # closure computed on the host from bit rows, and the marking join must have run
+    import torch
+    import torch.multiprocessing as mp
+    from xlog_b200 import digest, workloads
+    n_gpus = torch.cuda.device_count()
+    if n_gpus < 2:
+        pytest.skip("needs at least two GPUs")
+    scale, world = 14, 2
+    mp.spawn(_rank_wide, args=(world, _free_port(), str(tmp_path), scale), nprocs=world, join=True)
+    got = np.load(tmp_path / "wide.npy", allow_pickle=True).tolist()
+
+    c0, c1 = workloads.rmat_dag(scale, 8)
+    n = 1 << scale
+    rows = np.zeros((n, n // 64), dtype=np.uint64)
+    order = np.argsort(c0, kind="stable")
+    dst, starts = c1[order], np.searchsorted(c0[order], np.arange(n + 1))
+    for v in range(n - 1, -1, -1):
+        kids = dst[starts[v]:starts[v + 1]]
+        if len(kids):
+            row = np.bitwise_or.reduce(rows[kids], axis=0)
+            np.bitwise_or.at(row, kids >> 6, np.uint64(1) << (kids & 63).astype(np.uint64))
+            rows[v] = row
+    bits = np.unpackbits(rows.view(np.uint8), axis=1, bitorder="little")
+    a, b = np.nonzero(bits)
+    want = digest.result_checksum([a.astype(np.uint32), b.astype(np.uint32)])
+    assert digest.checksum_text([g["digest"] for g in got]) == digest.checksum_text([want])
+    assert all(g["derived"] == len(a) for g in got)
+    assert all("expand_mark" in g["kernels"] for g in got)

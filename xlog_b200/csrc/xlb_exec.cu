@@ -592,6 +592,7 @@ struct DenseSink {
     const Keys* full = nullptr;   // the head relation before this iteration
     const Keys* novel = nullptr;  // what the iteration has found for it so far (disjoint from full)
     bool used = false;
+    int home_var = -1;            // several ranks on hash partitions: the head variable whose value decides a tuple's owner
     DenseSet set;
     DenseState* state = nullptr;
     Keys known() const {  // stands for full + novel: row count and OR bound
@@ -871,7 +872,11 @@ static Keys run_pipeline(xlb_ctx* c, FlatRule fr /*by value: filter flags*/, siz
             Keys shape;  // stands for the rows this step would produce: only their OR bound matters here
             shape.n = 1;
             shape.bound = ops_expand_bound(probe, ix, hs, ls);
-            if (sink && last && !pending && c->world == 1 && !(c->flags & XLB_FLAG_NO_DENSE) && (rs.repl.on || ops_dense_bits(shape, sink->known(), &hb, &lb, dense_max_bits(rs, sink->head)))) {
+            // (on hash partitions a rank marks into the bitmap of its own shard, which takes tuples
+            // that are already where they belong: only a head that moved to wide bitmaps, and only
+            // when this step leaves its rows placed by the head's owner column)
+            const bool marks_own_shard = c->world == 1 || (sink && rs.wide_dense.count(sink->head) && sink->home_var >= 0 && part_after == sink->home_var);
+            if (sink && last && !pending && marks_own_shard && !(c->flags & XLB_FLAG_NO_DENSE) && (rs.repl.on || ops_dense_bits(shape, sink->known(), &hb, &lb, dense_max_bits(rs, sink->head)))) {
                 dense_sink_begin(c, rs, sink, hb, lb);
                 ops_join_expand_mark(c, probe, keysel, ix, hs, ls, sink->set);
                 Keys marked;  // no rows and no count: both are in the sink
@@ -988,6 +993,7 @@ static void eval_variant(xlb_ctx* c, const FlatRule& fr_in, size_t start, const 
         sink.head = fr.head;
         sink.full = &full;
         sink.novel = &novel;
+        if (c->world > 1 && !fr.head_vars.empty()) sink.home_var = home_sel == SRC_HI && fr.head_vars.size() == 2 ? fr.head_vars[0] : fr.head_vars.back();
         int placed = -1;
         try {
             cand = run_pipeline(c, fr, start, part, start_is_set, start_part_half, limit, rs, &sink, &placed);
@@ -1051,7 +1057,8 @@ static void eval_variant(xlb_ctx* c, const FlatRule& fr_in, size_t start, const 
             // candidate, the last join can mark its output without writing it, and the new tuples
             // come out in order.  From the next variant on this head takes the bitmap route (its
             // bitmap is built from the rows then; the hash set is dropped at the end of the iteration).
-            if (c->world == 1 && !(c->flags & XLB_FLAG_NO_DENSE) && !rs.wide_dense.count(fr.head) && !getenv("XLB_NO_WIDE_DENSE") &&
+            const bool own_shard = c->world == 1 || (placed == home_sel && !(c->flags & XLB_FLAG_SHUFFLE_ONLY));  // several ranks: only tuples that need no exchange
+            if (own_shard && !(c->flags & XLB_FLAG_NO_DENSE) && !rs.wide_dense.count(fr.head) && !getenv("XLB_NO_WIDE_DENSE") &&
                 ops_dense_bits(cand, sink.known(), &hb, &lb, WIDE_DENSE_BITS) && cand.n >= (1ull << (hb + lb)) / 256) {
                 const uint64_t bitmaps = 4 * ((1ull << (hb + lb)) / 8);  // head, candidates, and room for a rebuild
                 if (!c->budget || c->allocated + bitmaps <= c->budget) rs.wide_dense.insert(fr.head);
