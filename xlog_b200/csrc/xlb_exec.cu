@@ -721,7 +721,7 @@ static void dense_sink_begin(xlb_ctx* c, RunState& rs, DenseSink* sink, int hb, 
         return;
     }
     sink->state = dense_state(c, rs, sink->head, hb, lb, *sink->full, *sink->novel);
-    sink->set = ops_dense_begin_from(c, sink->state->hi_bits, sink->state->lo_bits, sink->state->visited->as<unsigned int>());
+    sink->set = ops_dense_begin_state(c, *sink->state);
     sink->used = true;
 }
 
@@ -1059,7 +1059,7 @@ static void eval_variant(xlb_ctx* c, const FlatRule& fr_in, size_t start, const 
             // bitmap is built from the rows then; the hash set is dropped at the end of the iteration).
             const bool own_shard = c->world == 1 || (placed == home_sel && !(c->flags & XLB_FLAG_SHUFFLE_ONLY));  // several ranks: only tuples that need no exchange
             if (own_shard && !(c->flags & XLB_FLAG_NO_DENSE) && !rs.wide_dense.count(fr.head) && !getenv("XLB_NO_WIDE_DENSE") &&
-                ops_dense_bits(cand, sink.known(), &hb, &lb, WIDE_DENSE_BITS) && cand.n >= (1ull << (hb + lb)) / 256) {
+                ops_dense_bits(cand, sink.known(), &hb, &lb, WIDE_DENSE_BITS) && cand.n >= ((1ull << (hb + lb)) / 256) / c->comm_world) {  // (a rank touches its share of the domain only)
                 const uint64_t bitmaps = 4 * ((1ull << (hb + lb)) / 8);  // head, candidates, and room for a rebuild
                 if (!c->budget || c->allocated + bitmaps <= c->budget) rs.wide_dense.insert(fr.head);
             }

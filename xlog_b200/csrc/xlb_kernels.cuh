@@ -1093,9 +1093,13 @@ inline Buf merge_disjoint(xlb_ctx* c, const uint64_t* A, uint64_t na, const uint
 __device__ __forceinline__ uint32_t dense_index(uint64_t k, int lo_bits) {
     return (uint32_t)(((k >> 32) << lo_bits) | (k & 0xFFFFFFFFull));
 }
+// A marking kernel that sets a bit in a bitmap with a `touched` summary also sets the byte of the
+// bit's group of 256 words (8192 bits): counting and emitting then skip the groups nobody touched.
+constexpr int DENSE_TOUCH_SHIFT = 13;
 template <bool SET>
 static __global__ void __launch_bounds__(BLOCK) dense_mark_k(const uint64_t* __restrict__ keys, uint64_t n, int lo_bits, unsigned int* __restrict__ bitmap,
-                                                           uint64_t words, DevStatus* st, const unsigned int* __restrict__ visited = nullptr) {
+                                                           uint64_t words, DevStatus* st, const unsigned int* __restrict__ visited = nullptr,
+                                                           unsigned char* __restrict__ touched = nullptr) {
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
         uint64_t k = keys[i];
         uint32_t x = dense_index(k, lo_bits);
@@ -1107,8 +1111,12 @@ static __global__ void __launch_bounds__(BLOCK) dense_mark_k(const uint64_t* __r
         unsigned bit = 1u << (x & 31);
         if (SET && visited && (__ldg(&visited[x >> 5]) & bit)) continue;  // known already (read-only here: cacheable)
         unsigned cur = bitmap[x >> 5];  // most candidates repeat a tuple already seen: skip the atomic then
-        if (SET) { if (!(cur & bit)) atomicOr(&bitmap[x >> 5], bit); }
-        else     { if (cur & bit) atomicAnd(&bitmap[x >> 5], ~bit); }
+        if (SET) {
+            if (!(cur & bit)) {
+                atomicOr(&bitmap[x >> 5], bit);
+                if (touched) touched[x >> DENSE_TOUCH_SHIFT] = 1;
+            }
+        } else if (cur & bit) atomicAnd(&bitmap[x >> 5], ~bit);
     }
 }
 // The bitmap is counted and emitted in groups of 32 words (1024 tuples): one warp per group, so the
@@ -1203,9 +1211,13 @@ static __global__ void __launch_bounds__(BLOCK) dense_emit_k(const unsigned int*
 // a lane whose words hold nothing new touches nothing else.
 constexpr int DW_WPL = 8;
 static __global__ void __launch_bounds__(BLOCK) dense_count_wide_k(const unsigned int* __restrict__ bitmap, uint32_t* __restrict__ group_counts, uint64_t groups,
-                                                              const unsigned int* __restrict__ visited) {
+                                                              const unsigned int* __restrict__ visited, const unsigned char* __restrict__ touched) {
     const uint64_t g = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (g >= groups) return;
+    if (touched && !touched[g]) {  // nothing was marked in this group
+        if (lane_id() == 0) group_counts[g] = 0;
+        return;
+    }
     const uint64_t w0 = (g * 32 + lane_id()) * DW_WPL;
     const uint4* b4 = reinterpret_cast<const uint4*>(bitmap + w0);
     uint4 a = b4[0], b = b4[1];
@@ -1221,9 +1233,11 @@ static __global__ void __launch_bounds__(BLOCK) dense_count_wide_k(const unsigne
     if (lane_id() == 0) group_counts[g] = cnt;
 }
 static __global__ void __launch_bounds__(BLOCK) dense_emit_wide_k(const unsigned int* __restrict__ bitmap, const uint64_t* __restrict__ group_offs, uint64_t groups, int lo_bits,
-                                                             uint64_t* __restrict__ out, unsigned int* __restrict__ visited, uint64_t cap, DevStatus* st) {
+                                                             uint64_t* __restrict__ out, unsigned int* __restrict__ visited, uint64_t cap, DevStatus* st,
+                                                             const unsigned char* __restrict__ touched) {
     const uint64_t g = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (g >= groups) return;
+    if (touched && !touched[g]) return;
     const unsigned lane = lane_id();
     const uint64_t lo_mask = (1ull << lo_bits) - 1;
     const uint64_t w0 = (g * 32 + lane) * DW_WPL;
@@ -1689,7 +1703,7 @@ __device__ __forceinline__ bool sj_in(const unsigned int* __restrict__ keyset, u
 constexpr int SJ_VEC = 4, SJ_TILE = BLOCK * SJ_VEC * 2;
 __device__ __forceinline__ unsigned sj_mark_row(uint64_t t, int keysel, const unsigned int* __restrict__ keyset, uint64_t domain, int hi_src, int lo_src,
                                                 unsigned int* __restrict__ bitmap, uint64_t words, int lo_bits, DevStatus* st,
-                                                const unsigned int* __restrict__ visited) {
+                                                const unsigned int* __restrict__ visited, unsigned char* __restrict__ touched) {
     uint32_t key = keysel == 0 ? (uint32_t)(t >> 32) : (uint32_t)t;
     uint32_t other = keysel == 0 ? (uint32_t)t : (uint32_t)(t >> 32);
     if (!sj_in(keyset, domain, key)) return 0;
@@ -1703,13 +1717,16 @@ __device__ __forceinline__ unsigned sj_mark_row(uint64_t t, int keysel, const un
     if (visited && (__ldg(&visited[x >> 5]) & bit)) return 1;  // known already: most of a hub's tuples
     // (a plain load, served by the L1: reading the hot words of a hub through to the L2 instead
     // made the kernel three times slower)
-    if (!(bitmap[x >> 5] & bit)) atomicOr(&bitmap[x >> 5], bit);
+    if (!(bitmap[x >> 5] & bit)) {
+        atomicOr(&bitmap[x >> 5], bit);
+        if (touched) touched[x >> DENSE_TOUCH_SHIFT] = 1;
+    }
     return 1;
 }
 static __global__ void __launch_bounds__(BLOCK) scan_join_mark_k(const uint64_t* __restrict__ rows, uint64_t n, int keysel, const unsigned int* __restrict__ keyset,
                                                             uint64_t domain, int hi_src, int lo_src, unsigned int* __restrict__ bitmap, uint64_t words, int lo_bits,
                                                             unsigned long long* __restrict__ count, DevStatus* st, const unsigned int* __restrict__ visited,
-                                                            const unsigned long long* __restrict__ keys_in_set = nullptr) {
+                                                            const unsigned long long* __restrict__ keys_in_set = nullptr, unsigned char* __restrict__ touched = nullptr) {
     // (keys_in_set: the number of keys in the key set when the host enqueued this launch without
     // knowing it; over an empty set there is nothing to find)
     if (keys_in_set && *keys_in_set == 0) return;
@@ -1722,12 +1739,12 @@ static __global__ void __launch_bounds__(BLOCK) scan_join_mark_k(const uint64_t*
         for (int k = 0; k < SJ_VEC; ++k) v[k] = rows2[tile * (SJ_TILE / 2) + (uint64_t)k * BLOCK + threadIdx.x];
 #pragma unroll
         for (int k = 0; k < SJ_VEC; ++k) {
-            mine += sj_mark_row(v[k].x, keysel, keyset, domain, hi_src, lo_src, bitmap, words, lo_bits, st, visited);
-            mine += sj_mark_row(v[k].y, keysel, keyset, domain, hi_src, lo_src, bitmap, words, lo_bits, st, visited);
+            mine += sj_mark_row(v[k].x, keysel, keyset, domain, hi_src, lo_src, bitmap, words, lo_bits, st, visited, touched);
+            mine += sj_mark_row(v[k].y, keysel, keyset, domain, hi_src, lo_src, bitmap, words, lo_bits, st, visited, touched);
         }
     }
     for (uint64_t i = ntiles * SJ_TILE + (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
-        mine += sj_mark_row(rows[i], keysel, keyset, domain, hi_src, lo_src, bitmap, words, lo_bits, st, visited);
+        mine += sj_mark_row(rows[i], keysel, keyset, domain, hi_src, lo_src, bitmap, words, lo_bits, st, visited, touched);
     for (int d = 16; d; d >>= 1) mine += __shfl_down_sync(0xFFFFFFFFu, mine, d);
     if (lane_id() == 0 && mine) atomicAdd(count, mine);
 }
@@ -1940,7 +1957,8 @@ static __global__ void __launch_bounds__(BLOCK, 8) expand_k(const uint64_t* __re
                                                    uint64_t nrows, uint64_t total, const uint64_t* __restrict__ S,
                                                    const uint32_t* __restrict__ pay, int hi_src, int lo_src, uint64_t* __restrict__ out,
                                                    unsigned int* __restrict__ bitmap, uint64_t words, int lo_bits, DevStatus* st,
-                                                   const uint64_t* __restrict__ total_dev, const unsigned int* __restrict__ visited) {
+                                                   const uint64_t* __restrict__ total_dev, const unsigned int* __restrict__ visited,
+                                                   unsigned char* __restrict__ touched) {
     // Row offsets of the tile's span relative to the tile's first output, 32 bits each: rel[0] = 0
     // stands for the row that owns that output (its offset may lie before the tile; `skip0` says by
     // how much), every later row starts inside the tile or at EX_TILE (beyond it).  The search per
@@ -2011,7 +2029,10 @@ static __global__ void __launch_bounds__(BLOCK, 8) expand_k(const uint64_t* __re
                 set_status(st, XLB_ERR_CAPACITY, 4, key);
             } else {
                 unsigned bit = 1u << (x & 31);
-                if (!(visited && (__ldg(&visited[x >> 5]) & bit)) && !(bitmap[x >> 5] & bit)) atomicOr(&bitmap[x >> 5], bit);
+                if (!(visited && (__ldg(&visited[x >> 5]) & bit)) && !(bitmap[x >> 5] & bit)) {
+                    atomicOr(&bitmap[x >> 5], bit);
+                    if (touched) touched[x >> DENSE_TOUCH_SHIFT] = 1;
+                }
             }
         }
     }

@@ -539,6 +539,25 @@ DenseSet ops_dense_begin_from(xlb_ctx* c, int hi_bits, int lo_bits, unsigned int
     return d;
 }
 
+constexpr uint64_t DENSE_WIDE_WORDS = 1ull << 20;  // bitmaps from this size on are counted and emitted by the wide kernels
+
+DenseSet ops_dense_begin_state(xlb_ctx* c, DenseState& s) {
+    if (!s.marks) return ops_dense_begin_from(c, s.hi_bits, s.lo_bits, s.visited->as<unsigned int>());
+    DenseSet d;
+    d.hi_bits = s.hi_bits;
+    d.lo_bits = s.lo_bits;
+    d.words = s.words;
+    d.bitmap = s.marks;
+    d.counts_buf = make_buf(c, 24);
+    d.counts = d.counts_buf->as<uint64_t>();
+    CUDA_OK(cudaMemsetAsync(d.counts_buf->p, 0, 24, c->stream));
+    CUDA_OK(cudaMemsetAsync(s.touched->p, 0, s.touched->bytes, c->stream));
+    d.touched = s.touched->as<unsigned char>();
+    d.visited = s.visited->as<unsigned int>();
+    d.seeded = true;
+    return d;
+}
+
 static Keys dense_finish(xlb_ctx* c, DenseSet& d, const Keys& full, const uint64_t* known_total);
 Keys ops_dense_finish(xlb_ctx* c, DenseSet& d, const Keys& full) { return dense_finish(c, d, full, nullptr); }
 
@@ -553,13 +572,13 @@ static Keys dense_finish(xlb_ctx* c, DenseSet& d, const Keys& full, const uint64
         check_launch(c, "dense_clear");
     }
     // a bitmap of a million words and more is counted and emitted in groups of 256 words per warp
-    const bool wide = words >= (1ull << 20) && words % (32 * DW_WPL) == 0 && ((uintptr_t)d.bitmap->p & 15) == 0 && (!d.visited || ((uintptr_t)d.visited & 15) == 0);
+    const bool wide = words >= DENSE_WIDE_WORDS && words % (32 * DW_WPL) == 0 && ((uintptr_t)d.bitmap->p & 15) == 0 && (!d.visited || ((uintptr_t)d.visited & 15) == 0);
     uint64_t groups = wide ? words / (32 * DW_WPL) : (words + 31) / 32;
     Buf gcnt = make_buf(c, groups * 4);
     Buf offs = make_buf(c, groups * 8);
     prof_begin(c, "dense_count", words * 4ull);
     if (wide) {
-        dense_count_wide_k<<<(unsigned)((groups * 32 + BLOCK - 1) / BLOCK), BLOCK, 0, c->stream>>>(d.bitmap->as<unsigned int>(), gcnt->as<uint32_t>(), groups, d.visited);
+        dense_count_wide_k<<<(unsigned)((groups * 32 + BLOCK - 1) / BLOCK), BLOCK, 0, c->stream>>>(d.bitmap->as<unsigned int>(), gcnt->as<uint32_t>(), groups, d.visited, d.touched);
         check_launch(c, "dense_count");
         exclusive_scan<LoadU32, uint64_t>(c, LoadU32{gcnt->as<uint32_t>()}, groups, offs->as<uint64_t>(), d.counts);
     } else if (groups <= (uint64_t)DENSE_FUSED_GROUPS) {
@@ -586,7 +605,7 @@ static Keys dense_finish(xlb_ctx* c, DenseSet& d, const Keys& full, const uint64
         prof_begin(c, "dense_emit", words * 4ull + tot * 8ull);
         if (wide)
             dense_emit_wide_k<<<(unsigned)((groups * 32 + BLOCK - 1) / BLOCK), BLOCK, 0, c->stream>>>(d.bitmap->as<unsigned int>(), offs->as<uint64_t>(), groups, d.lo_bits, o.buf->as<uint64_t>(),
-                                                                                                    d.visited, tot, c->d_status);
+                                                                                                    d.visited, tot, c->d_status, d.touched);
         else
             dense_emit_k<<<(unsigned)((groups * 32 + BLOCK - 1) / BLOCK), BLOCK, 0, c->stream>>>(d.bitmap->as<unsigned int>(), words, offs->as<uint64_t>(), groups, d.lo_bits, o.buf->as<uint64_t>(), d.visited, tot, c->d_status);
         check_launch(c, "dense_emit");
@@ -605,6 +624,13 @@ void ops_dense_state_build(xlb_ctx* c, DenseState& s, int hi_bits, int lo_bits, 
         prof_begin(c, "dense_mark", k->n * 8ull);
         dense_mark_k<true><<<grid_for(c, k->n), BLOCK, 0, c->stream>>>(k->ptr(), k->n, lo_bits, s.visited->as<unsigned int>(), s.words, c->d_status);
         check_launch(c, "dense_mark");
+    }
+    s.marks = nullptr;
+    s.touched = nullptr;
+    if (s.words >= DENSE_WIDE_WORDS && s.words % (32 * DW_WPL) == 0) {
+        s.marks = make_buf(c, s.words * 4);
+        CUDA_OK(cudaMemcpyAsync(s.marks->p, s.visited->p, s.words * 4, cudaMemcpyDeviceToDevice, c->stream));
+        s.touched = make_buf(c, s.words / (32 * DW_WPL));
     }
     s.rows = full.n + novel.n;
     s.valid = true;
@@ -717,7 +743,7 @@ void ops_dense_mark_into(xlb_ctx* c, DenseSet& d, const Keys& cand) {
     if (cand.n == 0) return;
     d.bound |= cand.bound;
     prof_begin(c, "dense_mark", cand.n * 8ull);
-    dense_mark_k<true><<<grid_for(c, cand.n), BLOCK, 0, c->stream>>>(cand.ptr(), cand.n, d.lo_bits, d.bitmap->as<unsigned int>(), d.words, c->d_status, d.seeded ? nullptr : d.visited);
+    dense_mark_k<true><<<grid_for(c, cand.n), BLOCK, 0, c->stream>>>(cand.ptr(), cand.n, d.lo_bits, d.bitmap->as<unsigned int>(), d.words, c->d_status, d.seeded ? nullptr : d.visited, d.touched);
     check_launch(c, "dense_mark");
 }
 
@@ -889,7 +915,7 @@ void ops_scan_join_mark(xlb_ctx* c, const Keys& bag, int keysel, int key_bits, c
     prof_begin(c, "scan_join_mark", rel.n * 8ull);
     if ((uintptr_t)rel.ptr() & 15) xlb_fail(XLB_ERR_INVALID, "internal: scan join over a row array that is not 16-byte aligned");
     scan_join_mark_k<<<grid_for(c, rel.n, SJ_TILE), BLOCK, 0, c->stream>>>(rel.ptr(), rel.n, rel_keysel, keyset->as<unsigned int>(), 1ull << key_bits, rel_hi, rel_lo,
-                                                                  d.bitmap->as<unsigned int>(), d.words, d.lo_bits, (unsigned long long*)(d.counts + 1), c->d_status, d.seeded ? nullptr : d.visited);
+                                                                  d.bitmap->as<unsigned int>(), d.words, d.lo_bits, (unsigned long long*)(d.counts + 1), c->d_status, d.seeded ? nullptr : d.visited, nullptr, d.touched);
     check_launch(c, "scan_join_mark");
 }
 
@@ -956,7 +982,7 @@ static Keys join_expand(xlb_ctx* c, const Keys& bag, int keysel, const uint64_t*
         const unsigned grid = (unsigned)c->sm_count * 8;
         prof_begin(c, "expand_mark", bag.n * 24ull);
         expand_k<true><<<grid, BLOCK, 0, c->stream>>>(bag.ptr(), match->as<uint64_t>(), off->as<uint64_t>(), bag.n, 0, ix.S ? ix.S->as<uint64_t>() : nullptr, pay, hi_src, lo_src,
-                                                       nullptr, dense->bitmap->as<unsigned int>(), dense->words, dense->lo_bits, c->d_status, total_dev, dense->seeded ? nullptr : dense->visited);
+                                                       nullptr, dense->bitmap->as<unsigned int>(), dense->words, dense->lo_bits, c->d_status, total_dev, dense->seeded ? nullptr : dense->visited, dense->touched);
         check_launch(c, "expand_mark");
         if (dense->shared) {
             add_word_k<<<1, 1, 0, c->stream>>>((unsigned long long*)(dense->counts + 1), (const unsigned long long*)total_dev);
@@ -975,7 +1001,7 @@ static Keys join_expand(xlb_ctx* c, const Keys& bag, int keysel, const uint64_t*
     uint64_t ntiles = (tot + EX_TILE - 1) / EX_TILE;
     prof_begin(c, "expand", tot * 12ull + bag.n * 24ull);
     expand_k<false><<<(unsigned)ntiles, BLOCK, 0, c->stream>>>(bag.ptr(), match->as<uint64_t>(), off->as<uint64_t>(), bag.n, tot, ix.S ? ix.S->as<uint64_t>() : nullptr, pay, hi_src, lo_src,
-                                                                out.buf->as<uint64_t>(), nullptr, 0, 0, c->d_status, nullptr, nullptr);
+                                                                out.buf->as<uint64_t>(), nullptr, 0, 0, c->d_status, nullptr, nullptr, nullptr);
     check_launch(c, "expand");
     return out;
 }

@@ -82,11 +82,21 @@ struct DenseSet {
     // marking kernel both "known already" and "marked already", and it skips the look-up in
     // `visited`.  ops_dense_finish takes `bitmap & ~visited` either way.
     bool seeded = false;
+    // A set over the persistent marks of a DenseState (ops_dense_begin_state): the count words live
+    // in a buffer of their own, and `touched` has one byte per group of 256 bitmap words that a
+    // marking kernel sets when it sets a bit there, so that counting and emitting skip the rest.
+    Buf counts_buf;
+    unsigned char* touched = nullptr;
 };
 // The tuples of one relation as a bitmap that lives across the iterations of a fixpoint, so that
 // no iteration has to subtract the whole relation from its candidates again.
 struct DenseState {
     Buf visited;
+    // Bitmaps of 2^20 words and more also keep `marks`: the head plus whatever has been marked,
+    // never cleared (what an iteration marks is added to `visited` when it is emitted, so the two
+    // are equal again between iterations and no bitmap is copied or cleared per iteration), and
+    // `touched`, one byte per 256 words, cleared per use.
+    Buf marks, touched;
     uint64_t words = 0;
     int hi_bits = 0, lo_bits = 0;
     uint64_t rows = 0;  // tuples marked (the relation's rows plus what the running iteration found)
@@ -110,6 +120,8 @@ void ops_dense_state_build(xlb_ctx* c, DenseState& s, int hi_bits, int lo_bits, 
 Keys ops_dense_state_rows(xlb_ctx* c, const DenseState& s, uint64_t bound);  // all its tuples, in order
 // A set whose bitmap starts as a copy of `visited` (same domain) instead of empty.
 DenseSet ops_dense_begin_from(xlb_ctx* c, int hi_bits, int lo_bits, unsigned int* visited);
+// The candidate set of one use of a head's bitmap state: its persistent marks when it keeps them, else a copy of the head.
+DenseSet ops_dense_begin_state(xlb_ctx* c, DenseState& s);
 DenseSet ops_dense_begin(xlb_ctx* c, int hi_bits, int lo_bits);
 // Emit, in order, the marked tuples that are new: with d.visited those it lacks (which it then
 // gains; `full` is not read), else those not in `full` (cleared from the bitmap first).
