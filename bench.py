@@ -13,10 +13,10 @@ the edge rows (total work fixed: strong scaling).
 
 The same line carries a `secondary` object: the full transitive closure of the banded R-MAT DAG of
 config 5 at a reduced scale (16 instead of 24: the stated scale derives about 5e12 tuples), which
-is the workload that runs the radix sort, the hash probe, the merge-path set operations and, on
-several ranks, the tuple exchange.  It reports its own time, the per-iteration exchange, the
-roofline of `radix_scatter` and `hash_probe`, and a checksum of the result that is the same at
-every N.  One JSON line is printed by rank 0.
+is the workload that runs the join probes and expansions, the wide-bitmap and hash-set dedup, the
+radix sort and, on several ranks, the tuple exchange.  It reports its own time, the per-iteration
+exchange, the rooflines of `radix_scatter`, `hash_probe` and `expand_mark` (whichever of them the
+evaluation mode at hand launches), and a checksum of the result that is the same at every N.  One JSON line is printed by rank 0.
 """
 from __future__ import annotations
 
@@ -310,7 +310,7 @@ def secondary_block(env, args, peak, peak_kind, flags, label):
     job = Job(env, "c5", args.secondary_scale, flags | A.FLAG_PROFILE)   # phase timers on: they give the exchange time
     for _ in range(args.secondary_warmup):
         job.device_step()
-    ms_t, _, stats, launches, prof = timed_steps(env, job, args.secondary_steps, "radix_scatter,hash_probe")
+    ms_t, _, stats, launches, prof = timed_steps(env, job, args.secondary_steps, "radix_scatter,hash_probe,expand_mark")
     ms = float(ms_t.mean().item())
     digest, shard_rows = job.result_digest()
     parts = env.gather((digest, shard_rows, stats["ms_exchange"], stats["exchange_bytes"],
@@ -339,7 +339,7 @@ def secondary_block(env, args, peak, peak_kind, flags, label):
         "phases_ms_rank0": {"sort": round(parts[0][4], 3), "join": round(parts[0][5], 3), "setops": round(parts[0][6], 3),
                             "exchange": round(parts[0][2], 3)},
         "gpu_launches": int(launches),
-        "roofline": {k: roofline_of(prof, k, peak, peak_kind) for k in ("radix_scatter", "hash_probe")},
+        "roofline": {k: roofline_of(prof, k, peak, peak_kind) for k in ("radix_scatter", "hash_probe", "expand_mark")},
     }
 
 
