@@ -264,12 +264,12 @@ def programs():
         expected=[(3, 1), (4, 2), (5, 1), (6, 1)], source="rows asserted by the reference test")
     # the benchmark programs on tiny inputs (no reference fixture exists for them: the naive evaluator is the pin)
     tree = [(0, 1), (0, 2), (1, 3), (1, 4), (2, 5), (2, 6), (3, 7), (5, 8), (6, 9), (1, 6), (2, 7)]
-    add("same_generation_tiny", "same_generation", "BASELINE configuration 3 program; operator semantics as in "
+    add("same_generation_tiny", "same_generation", "benchmark configuration 3 program; operator semantics as in "
         "crates/xlog-integration/tests/test_same_generation_gpu.rs:168-290", {"edge": tree}, SG, "sg")
-    add("andersen_tiny", "andersen", "BASELINE configuration 4 program",
+    add("andersen_tiny", "andersen", "benchmark configuration 4 program",
         {"addressOf": [(0, 10), (1, 11), (2, 12)], "assign": [(3, 0), (4, 3), (1, 4)], "load": [(5, 3), (6, 1)], "store": [(0, 1), (4, 2)]},
         ANDERSEN, "pt")
-    add("reach_from_0", "reach_from_source", "BASELINE configuration 2 program (bound first argument; "
+    add("reach_from_0", "reach_from_source", "benchmark configuration 2 program (bound first argument; "
         "crates/xlog-logic/tests/test_v085_magic_sets.rs:22-58 for the bound form)", {"edge": IRREGULAR}, REACH0, "r")
     return c
 
